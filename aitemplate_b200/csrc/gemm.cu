@@ -1,0 +1,707 @@
+// gemm_rcr / bmm_rcr family for sm_100a: Y[b] = epilogue(alpha * X[b] . W[b]^T + bias, D0, D1)
+// with X [M,K] and W [N,K] both K-contiguous ("RCR": row-major A, column-major B, row-major C).
+//
+// Replaces the reference's CUTLASS / CuTe-DSL template instantiation for
+//   gemm_rcr            python/aitemplate/backend/cuda/gemm_universal/gemm_rcr.py:148-315
+//   gemm_rcr_bias*      .../gemm_rcr_bias.py:39-61, common_bias_activation.py, common_bias_broadcast.py:86-128
+//   gemm_rcr_bias_permute  .../gemm_rcr_bias_permute.py:55-95, common_permute.py:88-107
+//   bmm_rcr             .../bmm_xxx.py:30-155, bmm_common.py:200-434
+// by one persistent, warp-specialised kernel:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of 128x64 (A) and BNx64 (B) tiles into a
+//               128-byte-swizzled shared-memory ring guarded by full/empty mbarriers
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
+//               accumulators, tcgen05.commit releases smem stages / publishes the accumulator
+//   warps 2-5   epilogue: tcgen05.ld of this warp's 32 TMEM lanes, bias / activation / residual in
+//               fp32, one rounding, 16-byte global stores (row-major with stride, or permuted)
+// The epilogue of tile i overlaps the main loop of tile i+1 (two accumulators).
+// Shapes that TMA cannot address (K or a leading stride not a multiple of 8 elements, unaligned
+// pointers) run on a plain tiled CUDA-core kernel in this file; there is no host fallback.
+#include <cuda.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "common.h"
+#include "epilogue.cuh"
+#include "ptx.cuh"
+
+namespace b200ait {
+
+struct GemmParams {
+  int M, N, K, batch;
+  int tiles_m, tiles_n, num_tiles;
+  int a_batch_mul, b_batch_mul;  // 0 when that operand is broadcast over the batch
+  const void* bias;              // [N] or nullptr
+  const void* d0;                // [M, N] residual operands (row stride ldd) or nullptr
+  const void* d1;
+  void* out;
+  long long lda, ldb;            // only used by the CUDA-core kernel
+  long long a_bs, b_bs;
+  long long ldc, ldd, c_bs, d_bs;
+  float alpha;
+  int epilogue;
+  // store_mode 0: out[b*c_bs + row*ldc + col]
+  // store_mode 1: out[(row / t1)*rs_hi + (row % t1)*rs_lo + (col / (t3*d))*cs2 + ((col / d) % t3)*cs3 + col % d]
+  int store_mode;
+  int t1, t3, d;
+  long long rs_hi, rs_lo, cs2, cs3;
+  int vec_ok;  // 16-byte epilogue accesses are legal
+  int* status;
+};
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGroupM = 8;
+constexpr int kGemmThreads = 192;
+
+template <int BN>
+struct TileCfg {
+  static constexpr int kStageBytes = kBM * kBK * 2 + BN * kBK * 2;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int& b, int& m_blk, int& n_blk) {
+  const int per_batch = p.tiles_m * p.tiles_n;
+  b = tile / per_batch;
+  const int t = tile - b * per_batch;
+  const int group_size = kGroupM * p.tiles_n;
+  const int g = t / group_size;
+  const int first_m = g * kGroupM;
+  const int gm = min(kGroupM, p.tiles_m - first_m);
+  const int r = t - g * group_size;
+  m_blk = first_m + r % gm;
+  n_blk = r / gm;
+}
+
+// offset (in elements) of output element (row, col) relative to the batch base
+__device__ __forceinline__ long long row_offset(const GemmParams& p, int row) {
+  if (p.store_mode == 0) return static_cast<long long>(row) * p.ldc;
+  const int hi = row / p.t1;
+  return hi * p.rs_hi + (row - hi * p.t1) * p.rs_lo;
+}
+__device__ __forceinline__ long long col_offset(const GemmParams& p, int col) {
+  if (p.store_mode == 0) return col;
+  const int c = col / p.d;
+  const int c2 = c / p.t3;
+  return c2 * p.cs2 + (c - c2 * p.t3) * p.cs3 + (col - c * p.d);
+}
+
+// Applies the epilogue to 32 consecutive columns of one row and stores them.
+template <bool BF16>
+__device__ __forceinline__ void epilogue_chunk32(const GemmParams& p, float (&v)[32], int b, int row, int col0,
+                                                 bool row_ok) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  const int u1 = epi_u1(p.epilogue), b1 = epi_b1(p.epilogue), b2 = epi_b2(p.epilogue), u2 = epi_u2(p.epilogue);
+  const bool full = p.vec_ok && (col0 + 32 <= p.N);
+  if (p.alpha != 1.f) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+  }
+  if (p.bias != nullptr) {
+    const T* bias = static_cast<const T*>(p.bias) + col0;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float f[8];
+        unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(bias) + q), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[q * 8 + j] += f[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) v[j] += E::to_float(bias[j]);
+    }
+  }
+  apply_unary_vec(u1, v);
+  if (!row_ok) return;
+  const long long d_base = static_cast<long long>(b) * p.d_bs + static_cast<long long>(row) * p.ldd + col0;
+  if (b1 != kBinaryNone) {
+    const T* d0 = static_cast<const T*>(p.d0) + d_base;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float f[8];
+        unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(d0) + q), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[q * 8 + j] = (b1 == kBinaryAdd) ? v[q * 8 + j] + f[j] : v[q * 8 + j] * f[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) {
+          const float f = E::to_float(d0[j]);
+          v[j] = (b1 == kBinaryAdd) ? v[j] + f : v[j] * f;
+        }
+    }
+  }
+  if (b2 != kBinaryNone) {
+    const T* d1 = static_cast<const T*>(p.d1) + d_base;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float f[8];
+        unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(d1) + q), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[q * 8 + j] = (b2 == kBinaryAdd) ? v[q * 8 + j] + f[j] : v[q * 8 + j] * f[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) {
+          const float f = E::to_float(d1[j]);
+          v[j] = (b2 == kBinaryAdd) ? v[j] + f : v[j] * f;
+        }
+    }
+  }
+  apply_unary_vec(u2, v);
+  T* out = static_cast<T*>(p.out) + static_cast<long long>(b) * p.c_bs + row_offset(p, row);
+  if (full) {
+    if (p.store_mode == 0) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(out + col0 + q * 8) = pack8<BF16>(&v[q * 8]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        *reinterpret_cast<uint4*>(out + col_offset(p, col0 + q * 8)) = pack8<BF16>(&v[q * 8]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) out[col_offset(p, col0 + j)] = E::from_float(v[j]);
+  }
+}
+
+template <int BN, bool BF16>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+               const GemmParams p) {
+  using Cfg = TileCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr uint32_t kABytes = kBM * kBK * 2;
+  constexpr uint32_t kStageBytes = Cfg::kStageBytes;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* acc_full = empty_bar + kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint64_t* drain_bar = acc_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 128);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        int b, m_blk, n_blk;
+        decode_tile(p, tile, b, m_blk, n_blk);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+          tma_load_3d(sa, &tma_a, &full_bar[stage], kb * kBK, m_blk * kBM, b * p.a_batch_mul);
+          tma_load_3d(sa + kABytes, &tma_b, &full_bar[stage], kb * kBK, n_blk * BN, b * p.b_batch_mul);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // give copies that are still in flight a bounded time to land before the CTA exits
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(kBM, BN, BF16, false, false);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, kDevWaitAccEmptyTimeout);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kDevWaitFullTimeout);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * kStageBytes);
+          const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t adesc = umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      if (!ok) {
+        // let MMAs that were already issued finish before TMEM is released
+        umma_commit(drain_bar);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 1000000ull) {
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ----------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      int b, m_blk, n_blk;
+      decode_tile(p, tile, b, m_blk, n_blk);
+      ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, kDevWaitAccFullTimeout);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m_blk * kBM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n_blk * BN + c * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_base + static_cast<uint32_t>(c * 32), r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        epilogue_chunk32<BF16>(p, v, b, row, col0, row_ok);
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// CUDA-core kernel for shapes TMA cannot address. 32x32 output tile per block, K staged in smem.
+template <bool BF16>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const void* a_, const void* b_, const GemmParams p) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  __shared__ float sa[32][33];
+  __shared__ float sb[32][33];
+  const int b = blockIdx.z;
+  const T* a = static_cast<const T*>(a_) + static_cast<long long>(b) * p.a_bs * p.a_batch_mul;
+  const T* w = static_cast<const T*>(b_) + static_cast<long long>(b) * p.b_bs * p.b_batch_mul;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int row0 = blockIdx.y * 32, col0 = blockIdx.x * 32;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < p.K; k0 += 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = ty + i * 8;
+      const int k = k0 + tx;
+      sa[r][tx] = (row0 + r < p.M && k < p.K) ? E::to_float(a[static_cast<long long>(row0 + r) * p.lda + k]) : 0.f;
+      sb[r][tx] = (col0 + r < p.N && k < p.K) ? E::to_float(w[static_cast<long long>(col0 + r) * p.ldb + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 32; ++kk) {
+      const float bv = sb[tx][kk];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] = fmaf(sa[ty + i * 8][kk], bv, acc[i]);
+    }
+    __syncthreads();
+  }
+  const int col = col0 + tx;
+  if (col >= p.N) return;
+  const int u1 = epi_u1(p.epilogue), b1 = epi_b1(p.epilogue), b2 = epi_b2(p.epilogue), u2 = epi_u2(p.epilogue);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = row0 + ty + i * 8;
+    if (row >= p.M) continue;
+    float v = acc[i] * p.alpha;
+    if (p.bias) v += E::to_float(static_cast<const T*>(p.bias)[col]);
+    v = apply_unary(u1, v);
+    const long long di = static_cast<long long>(b) * p.d_bs + static_cast<long long>(row) * p.ldd + col;
+    if (b1 != kBinaryNone) {
+      const float f = E::to_float(static_cast<const T*>(p.d0)[di]);
+      v = (b1 == kBinaryAdd) ? v + f : v * f;
+    }
+    if (b2 != kBinaryNone) {
+      const float f = E::to_float(static_cast<const T*>(p.d1)[di]);
+      v = (b2 == kBinaryAdd) ? v + f : v * f;
+    }
+    v = apply_unary(u2, v);
+    static_cast<T*>(p.out)[static_cast<long long>(b) * p.c_bs + row_offset(p, row) + col_offset(p, col)] =
+        E::from_float(v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  if (!fn) throw Error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+  return fn;
+}
+
+// 3-D map over a [batch, rows, cols] 16-bit tensor, cols contiguous; box = [1, box_rows, 64], 128-byte swizzle
+CUtensorMap make_tile_map(const void* base, bool bf16, long long cols, long long rows, long long batch,
+                          long long row_stride_elems, long long batch_stride_elems, int box_rows) {
+  CUtensorMap m;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_stride_elems) * 2,
+                           static_cast<cuuint64_t>(batch > 1 ? batch_stride_elems : rows * row_stride_elems) * 2};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = get_encode_fn()(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                               const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw Error("cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(r)));
+  return m;
+}
+
+template <int BN, bool BF16>
+void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t stream) {
+  using Cfg = TileCfg<BN>;
+  static std::atomic<uint64_t> configured{0};
+  opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_tc_kernel<BN, BF16>), Cfg::kSmemBytes);
+  p.tiles_m = (p.M + kBM - 1) / kBM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n * p.batch;
+  const int grid = std::min(p.num_tiles, sm_count());
+  gemm_tc_kernel<BN, BF16><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  B200AIT_CUDA_CHECK(cudaGetLastError());
+}
+
+struct GemmArgs {
+  const void *a, *b, *bias, *d0, *d1;
+  void* c;
+  long long batch, m, n, k;
+  long long lda, ldb, ldc, ldd;
+  long long a_bs, b_bs, c_bs, d_bs;
+  int epilogue, dtype;
+  float alpha;
+  int store_mode;
+  long long t1, t2, t3;
+  int tile_n;  // 0 = choose
+  cudaStream_t stream;
+};
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int choose_tile_n(long long m, long long n, long long batch) {
+  const long long sms = sm_count();
+  const long long tm = (m + kBM - 1) / kBM;
+  // the widest tile that still yields at least ~one wave of work
+  for (int bn : {256, 128}) {
+    const long long tiles = tm * ((n + bn - 1) / bn) * batch;
+    if (tiles >= sms) return bn;
+  }
+  return 64;
+}
+
+void gemm_run(const GemmArgs& g) {
+  B200AIT_REQUIRE(g.dtype == kDTypeHalf || g.dtype == kDTypeBFloat16, "gemm: dtype must be float16 or bfloat16");
+  B200AIT_REQUIRE(g.batch >= 0 && g.m >= 0 && g.n >= 0 && g.k >= 0, "gemm: negative dimension");
+  if (g.batch == 0 || g.m == 0 || g.n == 0 || g.k == 0) return;  // reference: zero-size problems launch nothing
+  B200AIT_REQUIRE(g.a && g.b && g.c, "gemm: null operand pointer with non-zero size");
+  B200AIT_REQUIRE(g.m < (1ll << 31) && g.n < (1ll << 31) && g.k < (1ll << 31), "gemm: dimension exceeds int32");
+  const int b1 = epi_b1(g.epilogue), b2 = epi_b2(g.epilogue);
+  B200AIT_REQUIRE(b1 == kBinaryNone || g.d0, "gemm: epilogue needs d0 but d0 is null");
+  B200AIT_REQUIRE(b2 == kBinaryNone || g.d1, "gemm: epilogue needs d1 but d1 is null");
+  const bool bf16 = g.dtype == kDTypeBFloat16;
+
+  GemmParams p{};
+  p.M = static_cast<int>(g.m), p.N = static_cast<int>(g.n), p.K = static_cast<int>(g.k);
+  p.batch = static_cast<int>(g.batch);
+  p.a_batch_mul = (g.batch > 1 && g.a_bs == 0) ? 0 : 1;
+  p.b_batch_mul = (g.batch > 1 && g.b_bs == 0) ? 0 : 1;
+  p.bias = g.bias, p.d0 = g.d0, p.d1 = g.d1, p.out = g.c;
+  p.lda = g.lda, p.ldb = g.ldb, p.a_bs = g.a_bs, p.b_bs = g.b_bs;
+  p.ldc = g.ldc, p.ldd = g.ldd, p.c_bs = g.c_bs, p.d_bs = g.d_bs;
+  p.alpha = g.alpha, p.epilogue = g.epilogue;
+  p.store_mode = 0;
+  p.t1 = 1, p.t3 = 1, p.d = 1;
+  bool vec = (g.n % 8 == 0) && aligned16(g.c) && (g.c_bs % 8 == 0);
+  if (g.bias) vec = vec && aligned16(g.bias);
+  if (b1 != kBinaryNone) vec = vec && aligned16(g.d0) && (g.ldd % 8 == 0) && (g.d_bs % 8 == 0);
+  if (b2 != kBinaryNone) vec = vec && aligned16(g.d1) && (g.ldd % 8 == 0) && (g.d_bs % 8 == 0);
+  if (g.store_mode == 0) {
+    vec = vec && (g.ldc % 8 == 0);
+  } else if (g.store_mode == 1) {
+    // Permute5D "20314": [M/t1, t1, t2, t3, d] -> [t2, M/t1, t3, t1, d], d = N/(t2*t3)
+    // (python/aitemplate/compiler/ops/gemm_universal/gemm_rcr_bias_permute.py:59-69)
+    B200AIT_REQUIRE(g.t1 > 0 && g.t2 > 0 && g.t3 > 0, "gemm permute: shape entries must be positive");
+    B200AIT_REQUIRE(g.m % g.t1 == 0 && g.n % (g.t2 * g.t3) == 0, "gemm permute: M %% t1 or N %% (t2*t3) != 0");
+    B200AIT_REQUIRE(g.batch == 1, "gemm permute 20314 is not batched");
+    const long long d = g.n / (g.t2 * g.t3);
+    p.store_mode = 1;
+    p.t1 = static_cast<int>(g.t1), p.t3 = static_cast<int>(g.t3), p.d = static_cast<int>(d);
+    p.rs_hi = g.t3 * g.t1 * d, p.rs_lo = d;
+    p.cs2 = (g.m / g.t1) * g.t3 * g.t1 * d, p.cs3 = g.t1 * d;
+    vec = vec && (d % 8 == 0);
+  } else if (g.store_mode == 2) {
+    // Permute4D "0213": [M/t1, t1, t2, d] -> [M/t1, t2, t1, d], d = N/t2
+    // (python/aitemplate/compiler/ops/gemm_universal/gemm_rcr_permute.py, bmm_rcr_permute.py layout "0213")
+    B200AIT_REQUIRE(g.t1 > 0 && g.t2 > 0, "gemm permute: shape entries must be positive");
+    B200AIT_REQUIRE(g.m % g.t1 == 0 && g.n % g.t2 == 0, "gemm permute: M %% t1 or N %% t2 != 0");
+    const long long d = g.n / g.t2;
+    p.store_mode = 1;
+    p.t1 = static_cast<int>(g.t1), p.t3 = static_cast<int>(g.t2), p.d = static_cast<int>(d);
+    p.rs_hi = g.t2 * g.t1 * d, p.rs_lo = d;
+    p.cs2 = 0, p.cs3 = g.t1 * d;
+    vec = vec && (d % 8 == 0);
+  } else {
+    throw Error("gemm: unknown store mode");
+  }
+  p.vec_ok = vec ? 1 : 0;
+  p.status = device_status_word();
+
+  const bool tma_ok = (g.k % 8 == 0) && (g.lda % 8 == 0) && (g.ldb % 8 == 0) && aligned16(g.a) && aligned16(g.b) &&
+                      (g.a_bs % 8 == 0) && (g.b_bs % 8 == 0) && g.batch < 65536 * 32;
+  if (!tma_ok) {
+    dim3 grid(static_cast<unsigned>((g.n + 31) / 32), static_cast<unsigned>((g.m + 31) / 32),
+              static_cast<unsigned>(g.batch));
+    B200AIT_REQUIRE(grid.y < 65536 && grid.z < 65536, "gemm: unaligned problem too large for the CUDA-core kernel");
+    if (bf16)
+      gemm_simt_kernel<true><<<grid, 256, 0, g.stream>>>(g.a, g.b, p);
+    else
+      gemm_simt_kernel<false><<<grid, 256, 0, g.stream>>>(g.a, g.b, p);
+    B200AIT_CUDA_CHECK(cudaGetLastError());
+    return;
+  }
+
+  int bn = g.tile_n ? g.tile_n : choose_tile_n(g.m, g.n, g.batch);
+  B200AIT_REQUIRE(bn == 64 || bn == 128 || bn == 256, "gemm: tile_n must be 64, 128 or 256");
+  const long long a_batch = p.a_batch_mul ? g.batch : 1, b_batch = p.b_batch_mul ? g.batch : 1;
+  CUtensorMap ta = make_tile_map(g.a, bf16, g.k, g.m, a_batch, g.lda, g.a_bs, kBM);
+  CUtensorMap tb = make_tile_map(g.b, bf16, g.k, g.n, b_batch, g.ldb, g.b_bs, bn);
+#define B200AIT_LAUNCH(BN_)                                     \
+  if (bf16)                                                     \
+    launch_tc<BN_, true>(ta, tb, p, g.stream);                  \
+  else                                                          \
+    launch_tc<BN_, false>(ta, tb, p, g.stream);
+  if (bn == 256) {
+    B200AIT_LAUNCH(256)
+  } else if (bn == 128) {
+    B200AIT_LAUNCH(128)
+  } else {
+    B200AIT_LAUNCH(64)
+  }
+#undef B200AIT_LAUNCH
+}
+
+}  // namespace b200ait
+
+using namespace b200ait;
+
+// Generic entry point: every gemm_rcr* / bmm_rcr* op of the path maps onto it.
+B200AIT_EXPORT int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void* d0, const void* d1,
+                                    void* c, int64_t batch, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+                                    int64_t ldc, int64_t ldd, int64_t a_batch_stride, int64_t b_batch_stride,
+                                    int64_t c_batch_stride, int64_t d_batch_stride, int epilogue, int dtype,
+                                    float alpha, int store_mode, int64_t t1, int64_t t2, int64_t t3, int tile_n,
+                                    cudaStream_t stream) {
+  return guarded("b200ait_gemm_rcr", [&] {
+    GemmArgs g{a,   b,   bias,           d0,             d1,             c,
+               batch, m,   n,              k,              lda,            ldb,
+               ldc, ldd, a_batch_stride, b_batch_stride, c_batch_stride, d_batch_stride,
+               epilogue, dtype, alpha, store_mode, t1, t2, t3, tile_n, stream};
+    gemm_run(g);
+  });
+}
+
+// Entry points with the argument order of the reference's generated per-op functions
+// (python/aitemplate/backend/cuda/gemm_universal/common_bias.py:77-97: a, b, bias, c, workspace, split_k,
+//  pointers to the dims of a [M,K], b [N,K] and c [M,N], stream). *c_dim0/*c_dim1 are written.
+static int gemm_rcr_bias_named(const char* name, int epilogue, void* a, void* b, void* bias, void* d0, void* d1,
+                               void* c, int64_t* a_dim0, int64_t* a_dim1, int64_t* b_dim0, int64_t* b_dim1,
+                               int64_t* c_dim0, int64_t* c_dim1, bool need_bias, cudaStream_t stream) {
+  return guarded(name, [&] {
+    B200AIT_REQUIRE(a_dim0 && a_dim1 && b_dim0 && b_dim1, "null dimension pointer");
+    const int64_t m = *a_dim0, k = *a_dim1, n = *b_dim0;
+    B200AIT_REQUIRE(*b_dim1 == k, "a and b disagree on K");
+    if (c_dim0) *c_dim0 = m;
+    if (c_dim1) *c_dim1 = n;
+    if (m != 0 && n != 0 && k != 0) B200AIT_REQUIRE(!need_bias || bias, "bias_ptr is null!");
+    GemmArgs g{a, b, bias, d0, d1, c, 1, m, n, k, k, k, n, n, 0, 0, 0, 0, epilogue, kDTypeHalf, 1.f, 0, 1, 1, 1, 0,
+               stream};
+    gemm_run(g);
+  });
+}
+
+#define B200AIT_DEFINE_GEMM_BIAS(NAME, U1)                                                                         \
+  B200AIT_EXPORT int b200ait_##NAME(void* a, void* b, void* bias, void* c, uint8_t* workspace, int split_k,        \
+                                    int64_t* a_dim0, int64_t* a_dim1, int64_t* b_dim0, int64_t* b_dim1,            \
+                                    int64_t* c_dim0, int64_t* c_dim1, cudaStream_t stream) {                       \
+    (void)workspace;                                                                                               \
+    (void)split_k;                                                                                                 \
+    return gemm_rcr_bias_named("b200ait_" #NAME, make_epilogue(U1, kBinaryNone, kBinaryNone, kUnaryIdentity), a, b, \
+                               bias, nullptr, nullptr, c, a_dim0, a_dim1, b_dim0, b_dim1, c_dim0, c_dim1, true,    \
+                               stream);                                                                            \
+  }
+B200AIT_DEFINE_GEMM_BIAS(gemm_rcr_bias, kUnaryIdentity)
+B200AIT_DEFINE_GEMM_BIAS(gemm_rcr_bias_relu, kUnaryRelu)
+B200AIT_DEFINE_GEMM_BIAS(gemm_rcr_bias_gelu, kUnaryGelu)
+B200AIT_DEFINE_GEMM_BIAS(gemm_rcr_bias_fast_gelu, kUnaryFastGelu)
+B200AIT_DEFINE_GEMM_BIAS(gemm_rcr_bias_sigmoid, kUnarySigmoid)
+B200AIT_DEFINE_GEMM_BIAS(gemm_rcr_bias_tanh, kUnaryTanh)
+B200AIT_DEFINE_GEMM_BIAS(gemm_rcr_bias_swish, kUnarySwish)
+B200AIT_DEFINE_GEMM_BIAS(gemm_rcr_bias_hardswish, kUnaryHardswish)
+#undef B200AIT_DEFINE_GEMM_BIAS
+
+// python/aitemplate/backend/cuda/gemm_universal/gemm_rcr.py (common.py:172-198): no bias operand
+B200AIT_EXPORT int b200ait_gemm_rcr_plain(void* a, void* b, void* c, uint8_t* workspace, int split_k, int64_t* a_dim0,
+                                          int64_t* a_dim1, int64_t* b_dim0, int64_t* b_dim1, int64_t* c_dim0,
+                                          int64_t* c_dim1, cudaStream_t stream) {
+  (void)workspace;
+  (void)split_k;
+  return gemm_rcr_bias_named("b200ait_gemm_rcr_plain", 0, a, b, nullptr, nullptr, nullptr, c, a_dim0, a_dim1, b_dim0,
+                             b_dim1, c_dim0, c_dim1, false, stream);
+}
+
+// python/aitemplate/backend/cuda/gemm_universal/common_bias_broadcast.py:276-305: d0 (and d1) precede c
+#define B200AIT_DEFINE_GEMM_BIAS_D0(NAME, U1, B1, U2)                                                                \
+  B200AIT_EXPORT int b200ait_##NAME(void* a, void* b, void* bias, void* d0, void* c, uint8_t* workspace,             \
+                                    int split_k, int64_t* a_dim0, int64_t* a_dim1, int64_t* b_dim0, int64_t* b_dim1, \
+                                    int64_t* c_dim0, int64_t* c_dim1, cudaStream_t stream) {                         \
+    (void)workspace;                                                                                                 \
+    (void)split_k;                                                                                                   \
+    return gemm_rcr_bias_named("b200ait_" #NAME, make_epilogue(U1, B1, kBinaryNone, U2), a, b, bias, d0, nullptr, c, \
+                               a_dim0, a_dim1, b_dim0, b_dim1, c_dim0, c_dim1, true, stream);                        \
+  }
+#define B200AIT_DEFINE_GEMM_BIAS_D0_D1(NAME, U1, B1, B2, U2)                                                         \
+  B200AIT_EXPORT int b200ait_##NAME(void* a, void* b, void* bias, void* d0, void* d1, void* c, uint8_t* workspace,   \
+                                    int split_k, int64_t* a_dim0, int64_t* a_dim1, int64_t* b_dim0, int64_t* b_dim1, \
+                                    int64_t* c_dim0, int64_t* c_dim1, cudaStream_t stream) {                         \
+    (void)workspace;                                                                                                 \
+    (void)split_k;                                                                                                   \
+    return gemm_rcr_bias_named("b200ait_" #NAME, make_epilogue(U1, B1, B2, U2), a, b, bias, d0, d1, c, a_dim0,       \
+                               a_dim1, b_dim0, b_dim1, c_dim0, c_dim1, true, stream);                                \
+  }
+B200AIT_DEFINE_GEMM_BIAS_D0(gemm_rcr_bias_add, kUnaryIdentity, kBinaryAdd, kUnaryIdentity)
+B200AIT_DEFINE_GEMM_BIAS_D0(gemm_rcr_bias_add_relu, kUnaryIdentity, kBinaryAdd, kUnaryRelu)
+B200AIT_DEFINE_GEMM_BIAS_D0(gemm_rcr_bias_mul, kUnaryIdentity, kBinaryMul, kUnaryIdentity)
+B200AIT_DEFINE_GEMM_BIAS_D0(gemm_rcr_bias_mul_tanh, kUnaryIdentity, kBinaryMul, kUnaryTanh)
+B200AIT_DEFINE_GEMM_BIAS_D0(gemm_rcr_bias_sigmoid_mul, kUnarySigmoid, kBinaryMul, kUnaryIdentity)
+B200AIT_DEFINE_GEMM_BIAS_D0(gemm_rcr_bias_sigmoid_mul_tanh, kUnarySigmoid, kBinaryMul, kUnaryTanh)
+B200AIT_DEFINE_GEMM_BIAS_D0_D1(gemm_rcr_bias_add_add, kUnaryIdentity, kBinaryAdd, kBinaryAdd, kUnaryIdentity)
+B200AIT_DEFINE_GEMM_BIAS_D0_D1(gemm_rcr_bias_add_add_relu, kUnaryIdentity, kBinaryAdd, kBinaryAdd, kUnaryRelu)
+B200AIT_DEFINE_GEMM_BIAS_D0_D1(gemm_rcr_bias_mul_add, kUnaryIdentity, kBinaryMul, kBinaryAdd, kUnaryIdentity)
+#undef B200AIT_DEFINE_GEMM_BIAS_D0
+#undef B200AIT_DEFINE_GEMM_BIAS_D0_D1
+
+// python/aitemplate/backend/cuda/gemm_universal/gemm_rcr_bias_permute.py:55-95 (layout "20314", shape (t1,t2,t3))
+B200AIT_EXPORT int b200ait_gemm_rcr_bias_permute(void* a, void* b, void* bias, void* c, uint8_t* workspace,
+                                                 int split_k, int64_t* a_dim0, int64_t* a_dim1, int64_t* b_dim0,
+                                                 int64_t* b_dim1, int64_t* c_dim0, int64_t* c_dim1, int64_t t1,
+                                                 int64_t t2, int64_t t3, cudaStream_t stream) {
+  (void)workspace;
+  (void)split_k;
+  return guarded("b200ait_gemm_rcr_bias_permute", [&] {
+    B200AIT_REQUIRE(a_dim0 && a_dim1 && b_dim0 && b_dim1, "null dimension pointer");
+    const int64_t m = *a_dim0, k = *a_dim1, n = *b_dim0;
+    B200AIT_REQUIRE(*b_dim1 == k, "a and b disagree on K");
+    if (c_dim0) *c_dim0 = m;
+    if (c_dim1) *c_dim1 = n;
+    if (m != 0 && n != 0 && k != 0) B200AIT_REQUIRE(bias, "bias_ptr is null!");
+    GemmArgs g{a, b, bias, nullptr, nullptr, c, 1, m, n, k, k, k, n, n, 0, 0, 0, 0, 0, kDTypeHalf, 1.f, 1, t1, t2, t3,
+               0, stream};
+    gemm_run(g);
+  });
+}
+
+// python/aitemplate/backend/cuda/gemm_universal/bmm_common.py:56-81: a [B,M,K], b [B,N,K], c [B,M,N]
+B200AIT_EXPORT int b200ait_bmm_rcr(void* a, void* b, void* c, uint8_t* workspace, int64_t* a_dim0, int64_t* a_dim1,
+                                   int64_t* a_dim2, int64_t* b_dim0, int64_t* b_dim1, int64_t* b_dim2,
+                                   int64_t* c_dim0, int64_t* c_dim1, int64_t* c_dim2, cudaStream_t stream) {
+  (void)workspace;
+  return guarded("b200ait_bmm_rcr", [&] {
+    B200AIT_REQUIRE(a_dim0 && a_dim1 && a_dim2 && b_dim0 && b_dim1 && b_dim2, "null dimension pointer");
+    const int64_t ba = *a_dim0, m = *a_dim1, k = *a_dim2, bb = *b_dim0, n = *b_dim1;
+    B200AIT_REQUIRE(*b_dim2 == k, "a and b disagree on K");
+    B200AIT_REQUIRE(ba == bb || ba == 1 || bb == 1, "batch sizes are not broadcastable");
+    const int64_t batch = ba > bb ? ba : bb;
+    if (c_dim0) *c_dim0 = batch;
+    if (c_dim1) *c_dim1 = m;
+    if (c_dim2) *c_dim2 = n;
+    GemmArgs g{a, b, nullptr, nullptr, nullptr, c, batch, m, n, k, k, k, n, n,
+               (ba == 1 && batch > 1) ? 0 : m * k, (bb == 1 && batch > 1) ? 0 : n * k, m * n, m * n,
+               0, kDTypeHalf, 1.f, 0, 1, 1, 1, 0, stream};
+    gemm_run(g);
+  });
+}

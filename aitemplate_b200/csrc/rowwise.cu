@@ -1,0 +1,359 @@
+// Row-wise memory-bound kernels: layernorm and softmax.
+//
+// layernorm replaces python/aitemplate/backend/cuda/layernorm_sigmoid_mul/layernorm_sigmoid_mul_kernel.cuh:108-806
+// (two-pass fp32 mean / variance, y = (x - mean) * rsqrt(var + eps) * gamma + beta, one rounding).
+// softmax replaces python/aitemplate/backend/cuda/softmax/softmax.cuh:204-520 (fp32 max, exp, sum, divide).
+//
+// Fast paths keep one row in the registers of one warp: each lane issues all of its 16-byte loads
+// up front (streaming cache hint), reduces with warp shuffles and writes 16-byte vectors, so a row
+// is read once and written once. Other shapes take a block-per-row kernel that re-reads the row
+// from cache. All math is fp32.
+#include "common.h"
+#include "epilogue.cuh"
+
+namespace b200ait {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(uint4* p, const uint4& v) { __stcs(p, v); }
+
+// block-wide reductions (result broadcast to every thread); `red` holds >= 33 floats
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+// ------------------------------------------------------------------------------------- layernorm
+struct LayerNormParams {
+  const void* x;
+  const void* gamma;  // nullptr -> 1
+  const void* beta;   // nullptr -> 0
+  void* y;
+  long long m;
+  int n;
+  long long x_stride, y_stride;  // elements between consecutive rows
+  float eps;
+};
+
+template <int VPL, bool BF16>
+__global__ void __launch_bounds__(256) layernorm_warp_kernel(const LayerNormParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= p.m) return;
+  using T = typename Elem16<BF16>::T;
+  const int nvec = p.n >> 3;
+  const uint4* xin = reinterpret_cast<const uint4*>(static_cast<const T*>(p.x) + row * p.x_stride);
+  uint4 raw[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + 32 * i;
+    raw[i] = (v < nvec) ? ld_stream(xin + v) : make_uint4(0, 0, 0, 0);
+  }
+  float f[VPL][8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    unpack8<BF16>(raw[i], f[i]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += f[i][j];
+  }
+  const float inv_n = 1.f / static_cast<float>(p.n);
+  const float mean = warp_sum(s) * inv_n;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    if (lane + 32 * i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = f[i][j] - mean;
+        q += d * d;
+      }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) * inv_n + p.eps);
+  uint4* yout = reinterpret_cast<uint4*>(static_cast<T*>(p.y) + row * p.y_stride);
+  const uint4* g4 = reinterpret_cast<const uint4*>(p.gamma);
+  const uint4* b4 = reinterpret_cast<const uint4*>(p.beta);
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      float g[8], b[8], o[8];
+      if (g4) {
+        unpack8<BF16>(__ldg(g4 + v), g);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = 1.f;
+      }
+      if (b4) {
+        unpack8<BF16>(__ldg(b4 + v), b);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) b[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (f[i][j] - mean) * rstd * g[j] + b[j];
+      st_stream(yout + v, pack8<BF16>(o));
+    }
+  }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(512) layernorm_block_kernel(const LayerNormParams p) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const T* x = static_cast<const T*>(p.x) + row * p.x_stride;
+  T* y = static_cast<T*>(p.y) + row * p.y_stride;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < p.n; i += blockDim.x) s += E::to_float(x[i]);
+  const float mean = block_sum(s, red) / static_cast<float>(p.n);
+  float q = 0.f;
+  for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
+    const float d = E::to_float(x[i]) - mean;
+    q += d * d;
+  }
+  const float rstd = rsqrtf(block_sum(q, red) / static_cast<float>(p.n) + p.eps);
+  const T* g = static_cast<const T*>(p.gamma);
+  const T* b = static_cast<const T*>(p.beta);
+  for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
+    const float gv = g ? E::to_float(g[i]) : 1.f, bv = b ? E::to_float(b[i]) : 0.f;
+    y[i] = E::from_float((E::to_float(x[i]) - mean) * rstd * gv + bv);
+  }
+}
+
+static bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <bool BF16>
+void layernorm_launch(const LayerNormParams& p, cudaStream_t stream) {
+  const bool vec = (p.n % 8 == 0) && (p.x_stride % 8 == 0) && (p.y_stride % 8 == 0) && al16(p.x) && al16(p.y) &&
+                   (!p.gamma || al16(p.gamma)) && (!p.beta || al16(p.beta)) && p.n <= 4096;
+  if (vec) {
+    const int nvec = p.n / 8;
+    const int vpl = (nvec + 31) / 32;
+    const int wpb = (vpl <= 4) ? 8 : 4;  // warps per block
+    const unsigned grid = static_cast<unsigned>((p.m + wpb - 1) / wpb);
+    const int threads = wpb * 32;
+#define B200AIT_LN(V) layernorm_warp_kernel<V, BF16><<<grid, threads, 0, stream>>>(p)
+    if (vpl <= 1)
+      B200AIT_LN(1);
+    else if (vpl <= 2)
+      B200AIT_LN(2);
+    else if (vpl <= 3)
+      B200AIT_LN(3);
+    else if (vpl <= 4)
+      B200AIT_LN(4);
+    else if (vpl <= 6)
+      B200AIT_LN(6);
+    else if (vpl <= 8)
+      B200AIT_LN(8);
+    else if (vpl <= 12)
+      B200AIT_LN(12);
+    else
+      B200AIT_LN(16);
+#undef B200AIT_LN
+  } else {
+    B200AIT_REQUIRE(p.m < (1ll << 31), "layernorm: too many rows");
+    const int threads = p.n >= 2048 ? 512 : (p.n >= 512 ? 256 : 128);
+    layernorm_block_kernel<BF16><<<static_cast<unsigned>(p.m), threads, 0, stream>>>(p);
+  }
+  B200AIT_CUDA_CHECK(cudaGetLastError());
+}
+
+// --------------------------------------------------------------------------------------- softmax
+struct SoftmaxParams {
+  const void* x;
+  void* y;
+  long long outer;  // product of dims before the reduction dim
+  int k;            // reduction length
+  long long inner;  // product of dims after it
+};
+
+template <int VPL, bool BF16>
+__global__ void __launch_bounds__(256) softmax_warp_kernel(const SoftmaxParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= p.outer) return;
+  using T = typename Elem16<BF16>::T;
+  const int nvec = p.k >> 3;
+  const uint4* xin = reinterpret_cast<const uint4*>(static_cast<const T*>(p.x) + row * p.k);
+  uint4 raw[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + 32 * i;
+    raw[i] = (v < nvec) ? ld_stream(xin + v) : make_uint4(0, 0, 0, 0);
+  }
+  constexpr float kLog2e = 1.4426950408889634f;
+  float f[VPL][8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    unpack8<BF16>(raw[i], f[i]);
+    if (lane + 32 * i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[i][j]);
+    }
+  }
+  mx = warp_max(mx);
+  const float mb = (mx == -INFINITY) ? 0.f : mx * kLog2e;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    if (lane + 32 * i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        f[i][j] = exp2f(f[i][j] * kLog2e - mb);
+        s += f[i][j];
+      }
+    }
+  }
+  const float inv = 1.f / warp_sum(s);
+  uint4* yout = reinterpret_cast<uint4*>(static_cast<T*>(p.y) + row * p.k);
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = f[i][j] * inv;
+      st_stream(yout + v, pack8<BF16>(o));
+    }
+  }
+}
+
+// one block per (outer, inner-chunk); blockDim.x threads walk the reduction dim when inner == 1,
+// otherwise each thread owns one inner index and loops over k (coalesced along inner)
+template <bool BF16>
+__global__ void __launch_bounds__(512) softmax_block_kernel(const SoftmaxParams p) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const T* x = static_cast<const T*>(p.x) + row * p.k;
+  T* y = static_cast<T*>(p.y) + row * p.k;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < p.k; i += blockDim.x) mx = fmaxf(mx, E::to_float(x[i]));
+  mx = block_max(mx, red);
+  if (mx == -INFINITY) mx = 0.f;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < p.k; i += blockDim.x) s += __expf(E::to_float(x[i]) - mx);
+  const float inv = 1.f / block_sum(s, red);
+  for (int i = threadIdx.x; i < p.k; i += blockDim.x) y[i] = E::from_float(__expf(E::to_float(x[i]) - mx) * inv);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) softmax_strided_kernel(const SoftmaxParams p) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= p.outer * p.inner) return;
+  const long long o = idx / p.inner, in = idx - o * p.inner;
+  const T* x = static_cast<const T*>(p.x) + o * p.k * p.inner + in;
+  T* y = static_cast<T*>(p.y) + o * p.k * p.inner + in;
+  float mx = -INFINITY;
+  for (int i = 0; i < p.k; ++i) mx = fmaxf(mx, E::to_float(x[i * p.inner]));
+  if (mx == -INFINITY) mx = 0.f;
+  float s = 0.f;
+  for (int i = 0; i < p.k; ++i) s += __expf(E::to_float(x[i * p.inner]) - mx);
+  const float inv = 1.f / s;
+  for (int i = 0; i < p.k; ++i) y[i * p.inner] = E::from_float(__expf(E::to_float(x[i * p.inner]) - mx) * inv);
+}
+
+template <bool BF16>
+void softmax_launch(const SoftmaxParams& p, cudaStream_t stream) {
+  if (p.inner > 1) {
+    const long long total = p.outer * p.inner;
+    softmax_strided_kernel<BF16><<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(p);
+  } else if (p.k % 8 == 0 && p.k <= 4096 && al16(p.x) && al16(p.y)) {
+    const int vpl = (p.k / 8 + 31) / 32;
+    const int wpb = (vpl <= 4) ? 8 : 4;
+    const unsigned grid = static_cast<unsigned>((p.outer + wpb - 1) / wpb);
+    const int threads = wpb * 32;
+#define B200AIT_SM(V) softmax_warp_kernel<V, BF16><<<grid, threads, 0, stream>>>(p)
+    if (vpl <= 1)
+      B200AIT_SM(1);
+    else if (vpl <= 2)
+      B200AIT_SM(2);
+    else if (vpl <= 4)
+      B200AIT_SM(4);
+    else if (vpl <= 8)
+      B200AIT_SM(8);
+    else
+      B200AIT_SM(16);
+#undef B200AIT_SM
+  } else {
+    B200AIT_REQUIRE(p.outer < (1ll << 31), "softmax: too many rows");
+    const int threads = p.k >= 2048 ? 512 : (p.k >= 256 ? 256 : (p.k >= 64 ? 64 : 32));
+    softmax_block_kernel<BF16><<<static_cast<unsigned>(p.outer), threads, 0, stream>>>(p);
+  }
+  B200AIT_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace b200ait
+
+using namespace b200ait;
+
+// Argument order of the reference's generated function
+// (python/aitemplate/backend/cuda/layernorm_sigmoid_mul/layernorm_sigmoid_mul.py:72-83:
+//  out, in, gamma, beta, m, n, eps, stream), plus row strides for strided accessors and the dtype.
+B200AIT_EXPORT int b200ait_layernorm(void* out, const void* in, const void* gamma, const void* beta, int64_t m,
+                                     int64_t n, float eps, int64_t in_row_stride, int64_t out_row_stride, int dtype,
+                                     cudaStream_t stream) {
+  return guarded("b200ait_layernorm", [&] {
+    B200AIT_REQUIRE(dtype == kDTypeHalf || dtype == kDTypeBFloat16, "layernorm: dtype must be float16 or bfloat16");
+    B200AIT_REQUIRE(m >= 0 && n >= 0, "layernorm: negative dimension");
+    if (m == 0 || n == 0) return;
+    B200AIT_REQUIRE(in && out, "layernorm: null pointer with non-zero size");
+    B200AIT_REQUIRE(n < (1ll << 31), "layernorm: n exceeds int32");
+    LayerNormParams p{in, gamma, beta, out, m, static_cast<int>(n), in_row_stride ? in_row_stride : n,
+                      out_row_stride ? out_row_stride : n, eps};
+    if (dtype == kDTypeBFloat16)
+      layernorm_launch<true>(p, stream);
+    else
+      layernorm_launch<false>(p, stream);
+  });
+}
+
+// Reference: python/aitemplate/backend/cuda/softmax/softmax.py:142-153 (in, out, dims, sm count, stream).
+// The tensor is viewed as [outer, k, inner] with the reduction over k.
+B200AIT_EXPORT int b200ait_softmax(const void* in, void* out, int64_t outer, int64_t k, int64_t inner, int dtype,
+                                   cudaStream_t stream) {
+  return guarded("b200ait_softmax", [&] {
+    B200AIT_REQUIRE(dtype == kDTypeHalf || dtype == kDTypeBFloat16, "softmax: dtype must be float16 or bfloat16");
+    B200AIT_REQUIRE(outer >= 0 && k >= 0 && inner >= 0, "softmax: negative dimension");
+    if (outer == 0 || k == 0 || inner == 0) return;
+    B200AIT_REQUIRE(in && out, "softmax: null pointer with non-zero size");
+    B200AIT_REQUIRE(k < (1ll << 31), "softmax: k exceeds int32");
+    SoftmaxParams p{in, out, outer, static_cast<int>(k), inner};
+    if (dtype == kDTypeBFloat16)
+      softmax_launch<true>(p, stream);
+    else
+      softmax_launch<false>(p, stream);
+  });
+}

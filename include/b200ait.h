@@ -1,0 +1,149 @@
+/* libb200ait: C ABI of the per-op kernels (sm_100a) behind the AITemplate op API.
+ *
+ * Every function returns 0 on success and non-zero on failure; the text of the failure is
+ * available from b200ait_last_error() on the calling thread. Pointers are device pointers unless
+ * stated otherwise; `stream` is a cudaStream_t (NULL = legacy default stream). No function
+ * allocates or synchronises unless its comment says so. Zero-size problems launch nothing.
+ *
+ * The reference generates one C++ function per op instance from Jinja templates; each entry
+ * point below names the template whose signature it follows (paths relative to the reference
+ * repository root).
+ */
+#ifndef B200AIT_H_
+#define B200AIT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* b200ait_stream_t;
+
+/* dtype codes are the values of AITemplateDtype (static/include/model_interface.h:70-78) */
+enum { B200AIT_HALF = 1, B200AIT_FLOAT = 2, B200AIT_BFLOAT16 = 6 };
+
+/* epilogue = u1 | b1 << 4 | b2 << 6 | u2 << 8 :  y = U2(B2(B1(U1(alpha*acc + bias), D0), D1))
+ * (python/aitemplate/backend/cuda/gemm_universal/gemm_rcr_bias_elementwise.py:34-53) */
+enum {
+  B200AIT_UNARY_IDENTITY = 0, B200AIT_UNARY_RELU = 1, B200AIT_UNARY_GELU = 2, B200AIT_UNARY_FAST_GELU = 3,
+  B200AIT_UNARY_SIGMOID = 4, B200AIT_UNARY_TANH = 5, B200AIT_UNARY_SWISH = 6, B200AIT_UNARY_HARDSWISH = 7
+};
+enum { B200AIT_BINARY_NONE = 0, B200AIT_BINARY_ADD = 1, B200AIT_BINARY_MUL = 2 };
+/* store modes of b200ait_gemm_rcr */
+enum { B200AIT_STORE_ROW_MAJOR = 0, B200AIT_STORE_PERMUTE_20314 = 1, B200AIT_STORE_PERMUTE_0213 = 2 };
+
+const char* b200ait_last_error(void);
+int b200ait_version(void);
+/* Synchronises the device, then reads and clears the kernel status word (0 = clean). A non-zero
+ * value means a bounded wait inside a kernel gave up and that kernel's output is invalid. */
+int b200ait_device_status(int* status_out);
+
+/* Generic GEMM: c[b] = epilogue(alpha * a[b] . b[b]^T + bias, d0, d1); a [batch, m, k] (row stride lda),
+ * b [batch, n, k] (row stride ldb), c / d0 / d1 [batch, m, n] (row strides ldc / ldd). A batch stride
+ * of 0 broadcasts that operand. tile_n = 0 lets the library choose (else 64, 128 or 256).
+ * Replaces python/aitemplate/backend/cuda/gemm_universal/common.py:130-617 (CUTLASS instantiation). */
+int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void* d0, const void* d1, void* c,
+                     int64_t batch, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                     int64_t ldd, int64_t a_batch_stride, int64_t b_batch_stride, int64_t c_batch_stride,
+                     int64_t d_batch_stride, int epilogue, int dtype, float alpha, int store_mode, int64_t t1,
+                     int64_t t2, int64_t t3, int tile_n, b200ait_stream_t stream);
+
+/* fp16 entry points with the reference's generated signatures. workspace / split_k are accepted
+ * and ignored. *c_dim0, *c_dim1 are written.
+ * gemm_rcr: python/aitemplate/backend/cuda/gemm_universal/common.py:172-198 */
+int b200ait_gemm_rcr_plain(void* a, void* b, void* c, uint8_t* workspace, int split_k, int64_t* a_dim0,
+                           int64_t* a_dim1, int64_t* b_dim0, int64_t* b_dim1, int64_t* c_dim0, int64_t* c_dim1,
+                           b200ait_stream_t stream);
+/* gemm_rcr_bias + activation: python/aitemplate/backend/cuda/gemm_universal/common_bias.py:77-97 */
+#define B200AIT_DECL_GEMM_BIAS(NAME)                                                                          \
+  int b200ait_##NAME(void* a, void* b, void* bias, void* c, uint8_t* workspace, int split_k, int64_t* a_dim0, \
+                     int64_t* a_dim1, int64_t* b_dim0, int64_t* b_dim1, int64_t* c_dim0, int64_t* c_dim1,     \
+                     b200ait_stream_t stream);
+B200AIT_DECL_GEMM_BIAS(gemm_rcr_bias)
+B200AIT_DECL_GEMM_BIAS(gemm_rcr_bias_relu)
+B200AIT_DECL_GEMM_BIAS(gemm_rcr_bias_gelu)
+B200AIT_DECL_GEMM_BIAS(gemm_rcr_bias_fast_gelu)
+B200AIT_DECL_GEMM_BIAS(gemm_rcr_bias_sigmoid)
+B200AIT_DECL_GEMM_BIAS(gemm_rcr_bias_tanh)
+B200AIT_DECL_GEMM_BIAS(gemm_rcr_bias_swish)
+B200AIT_DECL_GEMM_BIAS(gemm_rcr_bias_hardswish)
+#undef B200AIT_DECL_GEMM_BIAS
+/* gemm_rcr_bias + residual(s): python/aitemplate/backend/cuda/gemm_universal/common_bias_broadcast.py:276-305 */
+#define B200AIT_DECL_GEMM_BIAS_D0(NAME)                                                                        \
+  int b200ait_##NAME(void* a, void* b, void* bias, void* d0, void* c, uint8_t* workspace, int split_k,         \
+                     int64_t* a_dim0, int64_t* a_dim1, int64_t* b_dim0, int64_t* b_dim1, int64_t* c_dim0,      \
+                     int64_t* c_dim1, b200ait_stream_t stream);
+#define B200AIT_DECL_GEMM_BIAS_D0_D1(NAME)                                                                     \
+  int b200ait_##NAME(void* a, void* b, void* bias, void* d0, void* d1, void* c, uint8_t* workspace,            \
+                     int split_k, int64_t* a_dim0, int64_t* a_dim1, int64_t* b_dim0, int64_t* b_dim1,          \
+                     int64_t* c_dim0, int64_t* c_dim1, b200ait_stream_t stream);
+B200AIT_DECL_GEMM_BIAS_D0(gemm_rcr_bias_add)
+B200AIT_DECL_GEMM_BIAS_D0(gemm_rcr_bias_add_relu)
+B200AIT_DECL_GEMM_BIAS_D0(gemm_rcr_bias_mul)
+B200AIT_DECL_GEMM_BIAS_D0(gemm_rcr_bias_mul_tanh)
+B200AIT_DECL_GEMM_BIAS_D0(gemm_rcr_bias_sigmoid_mul)
+B200AIT_DECL_GEMM_BIAS_D0(gemm_rcr_bias_sigmoid_mul_tanh)
+B200AIT_DECL_GEMM_BIAS_D0_D1(gemm_rcr_bias_add_add)
+B200AIT_DECL_GEMM_BIAS_D0_D1(gemm_rcr_bias_add_add_relu)
+B200AIT_DECL_GEMM_BIAS_D0_D1(gemm_rcr_bias_mul_add)
+#undef B200AIT_DECL_GEMM_BIAS_D0
+#undef B200AIT_DECL_GEMM_BIAS_D0_D1
+/* gemm_rcr_bias_permute, layout "20314", shape (t1, t2, t3): result [M, N] is stored as
+ * [t2, M/t1, t3, t1, N/(t2*t3)] (python/aitemplate/backend/cuda/gemm_universal/gemm_rcr_bias_permute.py:55-95) */
+int b200ait_gemm_rcr_bias_permute(void* a, void* b, void* bias, void* c, uint8_t* workspace, int split_k,
+                                  int64_t* a_dim0, int64_t* a_dim1, int64_t* b_dim0, int64_t* b_dim1,
+                                  int64_t* c_dim0, int64_t* c_dim1, int64_t t1, int64_t t2, int64_t t3,
+                                  b200ait_stream_t stream);
+/* bmm_rcr: python/aitemplate/backend/cuda/gemm_universal/bmm_common.py:56-81 */
+int b200ait_bmm_rcr(void* a, void* b, void* c, uint8_t* workspace, int64_t* a_dim0, int64_t* a_dim1,
+                    int64_t* a_dim2, int64_t* b_dim0, int64_t* b_dim1, int64_t* b_dim2, int64_t* c_dim0,
+                    int64_t* c_dim1, int64_t* c_dim2, b200ait_stream_t stream);
+
+/* mem_eff_attention: q [B,H,Sq,D], k [B,H,Skv,D], v [B,H,Skv,Dv] -> output [B,Sq,H,Dv]
+ * (python/aitemplate/backend/cuda/attention/mem_eff_attention.py:632-654). lengths_* must be NULL. */
+int b200ait_mem_eff_attention(void* output, const void* query, const void* key, const void* value,
+                              int64_t batch_size, int64_t seq_len_kv, int64_t seq_len_q, int num_heads,
+                              int head_size, int head_size_v, float softmax_scale, int is_causal,
+                              const int32_t* lengths_kv, const int32_t* lengths_q, int dtype,
+                              b200ait_stream_t stream);
+
+/* layernorm over the last n elements of each of m rows; gamma / beta may be NULL; a row stride of 0
+ * means n (python/aitemplate/backend/cuda/layernorm_sigmoid_mul/layernorm_sigmoid_mul.py:72-83) */
+int b200ait_layernorm(void* out, const void* in, const void* gamma, const void* beta, int64_t m, int64_t n,
+                      float eps, int64_t in_row_stride, int64_t out_row_stride, int dtype,
+                      b200ait_stream_t stream);
+
+/* softmax over the middle axis of a tensor viewed as [outer, k, inner]
+ * (python/aitemplate/backend/cuda/softmax/softmax.py:142-153) */
+int b200ait_softmax(const void* in, void* out, int64_t outer, int64_t k, int64_t inner, int dtype,
+                    b200ait_stream_t stream);
+
+/* concatenate / split (python/aitemplate/backend/common/concatenate_common.py:29-48,
+ * split_common.py:21-40). inputs / input_shapes / masks / shapes are HOST arrays. */
+int b200ait_concatenate(void* output, int64_t* output_shape, const void* const* inputs,
+                        const int64_t* const* input_shapes, const uint8_t* input_masks, int64_t concat_dim,
+                        int64_t rank, int64_t num_inputs, int64_t elem_size, b200ait_stream_t stream);
+int b200ait_split(void* const* outputs, const uint8_t* output_masks, const void* input, const int64_t* input_shape,
+                  int64_t num_splits, const int64_t* split_sizes, int64_t split_dim, int64_t rank,
+                  int64_t elem_size, b200ait_stream_t stream);
+
+/* output = input.permute(dims), made contiguous (python/aitemplate/backend/cuda/tensor/permute.cuh:227-389) */
+int b200ait_permute(const void* input, void* output, const int64_t* input_shape, const int64_t* dims, int64_t rank,
+                    int64_t elem_size, b200ait_stream_t stream);
+
+/* element-wise chain with broadcasting (python/aitemplate/backend/common/elementwise_common.py:201-264):
+ * acc = inputs[0]; acc = ops[s](acc, operand) for each step; operand_index[s] >= 0 selects an input,
+ * -1 the scalar constants[s], -2 nothing (unary op). Op codes: 1 add, 2 sub, 3 mul, 4 div, 5 rsub,
+ * 6 rdiv, 7 max, 8 min, 16 relu, 17 gelu, 18 fast_gelu, 19 sigmoid, 20 tanh, 21 silu, 22 neg, 23 abs,
+ * 24 exp, 25 sqrt, 26 hardswish. */
+int b200ait_elementwise(void* output, const int64_t* out_shape, int64_t rank, const void* const* inputs,
+                        const int64_t* const* input_shapes, int64_t num_inputs, const int* ops,
+                        const int* operand_index, const float* constants, int64_t num_steps, int dtype,
+                        b200ait_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200AIT_H_ */

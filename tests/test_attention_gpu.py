@@ -1,0 +1,90 @@
+"""GPU parity of mem_eff_attention against the CPU oracle, through the C ABI.
+
+Shapes follow tests/unittest/ops/test_attention.py:456-742 ((B16,H4,S8,d=20) and (B16,H16,S1024,d=64)
+scaled to what the host oracle finishes in seconds), :847-1010 (cross attention, Sq != Skv), and the
+BASELINE configurations (BERT S=384 D=64; UNet D=40 with Skv=4096 and Skv=77).
+The reference's tolerance is 1e-3 against an fp16 torch result; against the fp32 oracle the bound
+is atol = rtol = 1e-2 with a tighter 4e-3 absolute check on top.
+"""
+import pytest
+import torch
+
+from oracle import reference_ops as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, seed, scale=1.0, dtype=torch.float16):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def _check(q, k, v, causal=False, atol=1e-2, tight=4e-3):
+    from aitemplate_b200 import kernels
+
+    out = kernels.mem_eff_attention(q.cuda(), k.cuda(), v.cuda(), causal=causal)
+    want = oracle.mem_eff_attention(q, k, v, causal=causal)
+    got = out.float().cpu()
+    assert got.shape == want.shape
+    assert torch.isfinite(got).all()
+    err = (got - want).abs()
+    assert bool((err <= atol + 1e-2 * want.abs()).all()), f"max abs err {float(err.max()):.4g}"
+    assert float(err.max()) < tight, f"max abs err {float(err.max()):.4g}"
+
+
+@pytest.mark.parametrize(
+    "b,h,sq,skv,d",
+    [
+        (16, 4, 8, 8, 20),      # CUDA-core kernel (head dim not a multiple of 8)
+        (2, 12, 384, 384, 64),  # BERT-base
+        (2, 4, 1024, 1024, 64),
+        (1, 2, 4096, 4096, 40),  # UNet self-attention
+        (2, 8, 4096, 77, 40),    # UNet cross-attention
+        (3, 2, 200, 129, 64),    # ragged query and key tails
+        (2, 2, 128, 128, 128),   # two 64-wide head-dim chunks
+        (1, 3, 130, 260, 96),
+        (2, 2, 64, 50, 8),
+    ],
+)
+def test_non_causal(b, h, sq, skv, d):
+    q = _rand((b, h, sq, d), 1)
+    k = _rand((b, h, skv, d), 2)
+    v = _rand((b, h, skv, d), 3)
+    _check(q, k, v)
+
+
+@pytest.mark.parametrize("b,h,s,d", [(2, 4, 384, 64), (1, 2, 300, 40), (4, 2, 8, 20)])
+def test_causal(b, h, s, d):
+    q = _rand((b, h, s, d), 4)
+    k = _rand((b, h, s, d), 5)
+    v = _rand((b, h, s, d), 6)
+    _check(q, k, v, causal=True)
+
+
+def test_large_scores_stay_finite():
+    # rows whose maximum moves between key blocks exercise the running-max rescale
+    q = _rand((1, 2, 256, 64), 7, scale=4.0)
+    k = _rand((1, 2, 512, 64), 8, scale=4.0)
+    v = _rand((1, 2, 512, 64), 9)
+    _check(q, k, v, tight=8e-3)
+
+
+def test_different_value_head_size():
+    q = _rand((2, 2, 256, 64), 10)
+    k = _rand((2, 2, 192, 64), 11)
+    v = _rand((2, 2, 192, 32), 12)
+    _check(q, k, v)
+
+
+def test_bf16():
+    q = _rand((2, 2, 256, 64), 13, dtype=torch.bfloat16)
+    k = _rand((2, 2, 256, 64), 14, dtype=torch.bfloat16)
+    v = _rand((2, 2, 256, 64), 15, dtype=torch.bfloat16)
+    _check(q, k, v, atol=3e-2, tight=3e-2)
+
+
+def test_zero_batch():
+    from aitemplate_b200 import kernels
+
+    z = torch.zeros((0, 4, 16, 64), dtype=torch.float16, device="cuda")
+    assert tuple(kernels.mem_eff_attention(z, z, z).shape) == (0, 16, 4, 64)

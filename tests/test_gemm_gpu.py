@@ -1,0 +1,241 @@
+"""GPU parity of the gemm_rcr / bmm_rcr family against the CPU oracle, through the C ABI.
+
+Shapes follow the reference's tests: tests/unittest/ops/test_gemm_bias.py:43-99 (M 4096/1000, (N,K) in
+{(4,4),(81,1024),(3,256),(64,1024)}, zero sizes), test_gemm_rcr_bias_fast_gelu.py:44-128 (M in
+{1,7,64,127,128}, K=1024, N=64), test_gemm_bias_broadcast.py (8x8x8, 256x128, 1024x512),
+test_bmm.py:32-70, plus the BASELINE configurations.
+Tolerance: atol = rtol = 1e-2 against the fp32 oracle (fp16 storage, fp32 accumulation).
+"""
+import pytest
+import torch
+
+from oracle import reference_ops as oracle
+
+pytestmark = pytest.mark.gpu
+
+ATOL = RTOL = 1e-2
+
+
+def _kernels():
+    from aitemplate_b200 import kernels
+
+    return kernels
+
+
+def _rand(shape, seed, dist="normal", scale=1.0, dtype=torch.float16):
+    g = torch.Generator().manual_seed(seed)
+    if dist == "uniform":
+        t = torch.rand(shape, generator=g) * 2 - 1
+    else:
+        t = torch.randn(shape, generator=g)
+    return (t * scale).to(dtype)
+
+
+def _close(got, want, atol=ATOL, rtol=RTOL):
+    got = got.float().cpu()
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert torch.isfinite(got).all()
+    err = (got - want).abs()
+    bound = atol + rtol * want.abs()
+    bad = err > bound
+    assert not bad.any(), (
+        f"{int(bad.sum())}/{bad.numel()} mismatches, max abs err {float(err.max()):.4g}, "
+        f"first bad index {bad.nonzero()[0].tolist()}"
+    )
+
+
+def test_config1_gemm_rcr_bias_fast_gelu():
+    k = _kernels()
+    x = _rand((256, 768), 1234, "uniform")
+    w = _rand((3072, 768), 1235, scale=0.02)
+    b = _rand((3072,), 1236, scale=0.02)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), epilogue="fast_gelu")
+    _close(y, oracle.gemm_rcr(x, w, b, epilogue="fast_gelu"))
+
+
+@pytest.mark.parametrize("epilogue", sorted(oracle.EPILOGUES.keys()))
+def test_every_epilogue(epilogue):
+    k = _kernels()
+    m, n, kk = 384, 520, 256
+    x = _rand((m, kk), 1, "uniform")
+    w = _rand((n, kk), 2, scale=0.05)
+    b = _rand((n,), 3, scale=0.5)
+    d0 = _rand((m, n), 4)
+    d1 = _rand((m, n), 5)
+    _, b1, b2, _ = oracle.EPILOGUES[epilogue]
+    kw = dict(epilogue=epilogue)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), d0.cuda() if b1 else None, d1.cuda() if b2 else None, **kw)
+    _close(y, oracle.gemm_rcr(x, w, b, d0 if b1 else None, d1 if b2 else None, **kw))
+
+
+@pytest.mark.parametrize("m", [1, 7, 64, 127, 128, 129, 1000])
+@pytest.mark.parametrize("n,kk", [(64, 1024), (72, 72), (264, 8), (512, 200)])
+def test_ragged_shapes(m, n, kk):
+    k = _kernels()
+    x = _rand((m, kk), 10 + m, "uniform")
+    w = _rand((n, kk), 11 + n, scale=0.05)
+    b = _rand((n,), 12, scale=0.1)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), epilogue="relu")
+    _close(y, oracle.gemm_rcr(x, w, b, epilogue="relu"))
+
+
+@pytest.mark.parametrize("n,kk", [(4, 4), (81, 1024), (3, 256), (64, 1021), (7, 5)])
+def test_unaligned_shapes_use_cuda_core_kernel(n, kk):
+    k = _kernels()
+    m = 1000
+    x = _rand((m, kk), 20, "uniform")
+    w = _rand((n, kk), 21, scale=0.05)
+    b = _rand((n,), 22, scale=0.1)
+    d0 = _rand((m, n), 23)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), d0.cuda(), epilogue="add_relu")
+    _close(y, oracle.gemm_rcr(x, w, b, d0, epilogue="add_relu"))
+
+
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+def test_forced_tile_width_many_tiles(tile_n):
+    # more tiles than SMs: exercises the persistent loop, both accumulators and every stage phase
+    k = _kernels()
+    m, n, kk = 4096, 2304, 768
+    x = _rand((m, kk), 30)
+    w = _rand((n, kk), 31, scale=0.02)
+    b = _rand((n,), 32, scale=0.02)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), epilogue="", tile_n=tile_n)
+    _close(y, oracle.gemm_rcr(x, w, b))
+
+
+def test_no_bias_and_alpha():
+    k = _kernels()
+    x = _rand((300, 320), 40)
+    w = _rand((320, 320), 41, scale=0.05)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), None, alpha=0.5)
+    _close(y, oracle.gemm_rcr(x, w, None, alpha=0.5))
+
+
+def test_leading_dims_fold_into_m():
+    k = _kernels()
+    x = _rand((2, 21, 5, 64), 42)
+    w = _rand((128, 64), 43, scale=0.1)
+    b = _rand((128,), 44)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda())
+    assert tuple(y.shape) == (2, 21, 5, 128)
+    _close(y, oracle.gemm_rcr(x, w, b))
+
+
+@pytest.mark.parametrize("m,n,kk", [(0, 64, 64), (64, 0, 64), (64, 64, 0)])
+def test_zero_size_launches_nothing(m, n, kk):
+    k = _kernels()
+    x = torch.zeros((m, kk), dtype=torch.float16, device="cuda")
+    w = torch.zeros((n, kk), dtype=torch.float16, device="cuda")
+    b = torch.zeros((n,), dtype=torch.float16, device="cuda")
+    y = k.gemm_rcr(x, w, b)
+    assert tuple(y.shape) == (m, n)
+
+
+def test_null_residual_is_an_error():
+    k = _kernels()
+    x = _rand((64, 64), 1).cuda()
+    w = _rand((64, 64), 2).cuda()
+    b = _rand((64,), 3).cuda()
+    with pytest.raises(RuntimeError, match="d0"):
+        k.gemm_rcr(x, w, b, None, epilogue="add")
+
+
+def test_bf16():
+    k = _kernels()
+    x = _rand((512, 256), 50, dtype=torch.bfloat16)
+    w = _rand((384, 256), 51, scale=0.05, dtype=torch.bfloat16)
+    b = _rand((384,), 52, scale=0.1, dtype=torch.bfloat16)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), epilogue="gelu")
+    _close(y, oracle.gemm_rcr(x, w, b, epilogue="gelu"), atol=5e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("bsz,s,h,d", [(2, 8, 4, 20), (4, 384, 12, 64), (2, 100, 3, 40)])
+def test_permute_20314_epilogue(bsz, s, h, d):
+    # the QKV projection of nn.MultiheadAttention: shape=(seq, 3, heads)
+    # (python/aitemplate/frontend/nn/attention.py:162-168, tests/unittest/ops/test_attention.py:352-424)
+    k = _kernels()
+    hid = h * d
+    x = _rand((bsz * s, hid), 60)
+    w = _rand((3 * hid, hid), 61, scale=0.05)
+    b = _rand((3 * hid,), 62, scale=0.1)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), permute_shape=(s, 3, h))
+    assert tuple(y.shape) == (3, bsz, h, s, d)
+    _close(y, oracle.gemm_rcr_bias_permute(x, w, b, (s, 3, h)))
+
+
+def test_permute_0213_epilogue():
+    k = _kernels()
+    x = _rand((2 * 96, 320), 63)
+    w = _rand((320, 320), 64, scale=0.05)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), None, permute_shape=(96, 8), permute_layout="0213")
+    assert tuple(y.shape) == (2, 8, 96, 40)
+    _close(y, oracle.gemm_rcr_bias_permute(x, w, None, (96, 8), layout="0213"))
+
+
+@pytest.mark.parametrize("bsz,m,n,kk", [(1, 128, 512, 256), (5, 100, 512, 256), (64, 512, 512, 64), (3, 32, 40, 24)])
+def test_bmm_rcr(bsz, m, n, kk):
+    k = _kernels()
+    a = _rand((bsz, m, kk), 70, "uniform")
+    b = _rand((bsz, n, kk), 71, "uniform")
+    y = k.bmm_rcr(a.cuda(), b.cuda())
+    _close(y, oracle.bmm_rcr(a, b))
+
+
+def test_bmm_rcr_broadcast_and_zero_batch():
+    k = _kernels()
+    a = _rand((6, 64, 128), 72, "uniform")
+    b = _rand((1, 96, 128), 73, "uniform")
+    _close(k.bmm_rcr(a.cuda(), b.cuda()), oracle.bmm_rcr(a, b))
+    _close(k.bmm_rcr(b.cuda(), a.cuda()), oracle.bmm_rcr(b, a))
+    z = k.bmm_rcr(torch.zeros((0, 8, 8), dtype=torch.float16, device="cuda"),
+                  torch.zeros((0, 8, 8), dtype=torch.float16, device="cuda"))
+    assert tuple(z.shape) == (0, 8, 8)
+
+
+def test_reference_signature_entry_points():
+    """The per-op entry points that take the reference's generated argument list."""
+    import ctypes
+
+    from aitemplate_b200 import _lib
+
+    lib = _lib.load()
+    m, n, kk = 200, 136, 64
+    x = _rand((m, kk), 80)
+    w = _rand((n, kk), 81, scale=0.1)
+    b = _rand((n,), 82)
+    d0 = _rand((m, n), 83)
+    xg, wg, bg, dg = x.cuda(), w.cuda(), b.cuda(), d0.cuda()
+    out = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    dims = [ctypes.c_int64(v) for v in (m, kk, n, kk, 0, 0)]
+    refs = [ctypes.byref(v) for v in dims]
+    stream = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.b200ait_gemm_rcr_bias_fast_gelu(xg.data_ptr(), wg.data_ptr(), bg.data_ptr(), out.data_ptr(), None, 1,
+                                                  *refs, stream), "fast_gelu")
+    assert (dims[4].value, dims[5].value) == (m, n)
+    _close(out, oracle.gemm_rcr(x, w, b, epilogue="fast_gelu"))
+    _lib.check(lib.b200ait_gemm_rcr_bias_add(xg.data_ptr(), wg.data_ptr(), bg.data_ptr(), dg.data_ptr(), out.data_ptr(),
+                                            None, 1, *refs, stream), "add")
+    _close(out, oracle.gemm_rcr(x, w, b, d0, epilogue="add"))
+    # a null bias with a non-empty problem is rejected like the reference ("bias_ptr is null!")
+    assert lib.b200ait_gemm_rcr_bias(xg.data_ptr(), wg.data_ptr(), None, out.data_ptr(), None, 1, *refs, stream) != 0
+    assert "bias_ptr is null" in _lib.last_error()
+
+
+def test_large_gemm_rows_sampled_against_oracle():
+    # BASELINE config 5 at M = 8192, N = K = 8192: the oracle checks 48 sampled rows (4 GFLOP on the host)
+    k = _kernels()
+    m, n, kk = 8192, 8192, 8192
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = (torch.rand((m, kk), generator=g, device="cuda") * 2 - 1).half()
+    w = (torch.randn((n, kk), generator=g, device="cuda") * 0.01).half()
+    b = (torch.randn((n,), generator=g, device="cuda") * 0.01).half()
+    y = k.gemm_rcr(x, w, b, epilogue="relu")
+    rows = torch.randint(0, m, (48,), generator=torch.Generator().manual_seed(6))
+    rows[0], rows[1] = 0, m - 1
+    want = oracle.gemm_rcr(x[rows.cuda()], w, b, epilogue="relu")
+    _close(y[rows.cuda()], want)
+    # linearity in the residual: (x W^T + b + d) - (x W^T + b) == d up to two roundings
+    d = (torch.randn((m, n), generator=g, device="cuda")).half()
+    y0 = k.gemm_rcr(x, w, b, epilogue="")
+    y1 = k.gemm_rcr(x, w, b, d, epilogue="add")
+    assert float(((y1.float() - y0.float()) - d.float()).abs().max()) < 1e-2
