@@ -1,0 +1,293 @@
+"""GPU tests of the drop-in boundary: ops graph -> compile_model() -> Model.run_with_tensors().
+
+Written the way the reference's tests are (tests/unittest/ops/test_gemm_rcr_bias_fast_gelu.py:72-100,
+tests/unittest/backend/test_model_api.py): build a tiny graph, compile, run, compare with the oracle
+expression; plus the runtime's error behaviour (wrong dtype / shape / count, dynamic-dim bounds,
+closed model, unset constants).
+"""
+import os
+import tempfile
+
+import pytest
+import torch
+
+from oracle import reference_ops as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _imports():
+    from aitemplate_b200.compiler import Model, compile_model, ops
+    from aitemplate_b200.frontend import IntVar, Tensor, nn
+    from aitemplate_b200.testing import detect_target
+
+    return Model, compile_model, ops, IntVar, Tensor, nn, detect_target
+
+
+def _rand(shape, seed, scale=1.0):
+    return (torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * scale).half()
+
+
+def _close(got, want, tol=1e-2):
+    got = got.float().cpu()
+    assert got.shape == want.shape, (got.shape, want.shape)
+    err = (got - want).abs()
+    assert bool((err <= tol + tol * want.abs()).all()), f"max abs err {float(err.max()):.4g}"
+
+
+@pytest.fixture()
+def workdir():
+    with tempfile.TemporaryDirectory() as d:
+        yield d
+
+
+@pytest.mark.parametrize("ms", [[128], [1, 7, 64, 127]])
+def test_gemm_rcr_bias_fast_gelu_static_and_dynamic_m(workdir, ms):
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    from aitemplate_b200.utils import shape_utils
+
+    k, n = 1024, 64
+    m_dim = shape_utils.gen_int_var_min_max(ms, name="m")
+    X = Tensor(shape=[m_dim, k], dtype="float16", name="input_0", is_input=True)
+    W = Tensor(shape=[n, k], dtype="float16", name="input_1", is_input=True)
+    B = Tensor(shape=[n], dtype="float16", name="input_2", is_input=True)
+    Y = ops.gemm_rcr_bias_fast_gelu()(X, W, B)
+    Y._attrs["name"] = "output_0"
+    Y._attrs["is_output"] = True
+    module = compile_model(Y, detect_target(), workdir, f"gemm_rcr_bias_fast_gelu_{len(ms)}")
+    for m in ms:
+        x, w, b = _rand((m, k), 1), _rand((n, k), 2, 0.05), _rand((n,), 3)
+        y = torch.empty((max(ms), n), dtype=torch.float16, device="cuda")
+        res = module.run_with_tensors({"input_0": x.cuda(), "input_1": w.cuda(), "input_2": b.cuda()}, [y])
+        assert tuple(res["output_0"].shape) == (m, n)
+        _close(res["output_0"], oracle.gemm_rcr(x, w, b, epilogue="fast_gelu"))
+
+
+def test_dynamic_dim_out_of_range_is_an_error(workdir):
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    X = Tensor(shape=[IntVar([2, 16], name="m"), 64], name="x", is_input=True)
+    W = Tensor(shape=[32, 64], name="w", is_input=True)
+    Y = ops.gemm_rcr()(X, W)
+    Y._attrs["name"] = "y"
+    Y._attrs["is_output"] = True
+    module = compile_model(Y, detect_target(), workdir, "dyn_bounds")
+    w = _rand((32, 64), 1).cuda()
+    y = torch.empty((16, 32), dtype=torch.float16, device="cuda")
+    for bad_m in (1, 17):
+        with pytest.raises(RuntimeError, match="AITemplateModelContainerRun"):
+            module.run_with_tensors([_rand((bad_m, 64), 2).cuda(), w], [y])
+    ok = module.run_with_tensors([_rand((5, 64), 2).cuda(), w], [y])
+    assert tuple(ok["y"].shape) == (5, 32)
+
+
+def test_runtime_argument_errors(workdir):
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    X = Tensor(shape=[8, 64], name="x", is_input=True)
+    W = Tensor(shape=[32, 64], name="w", is_input=True)
+    Y = ops.gemm_rcr()(X, W)
+    Y._attrs["name"] = "y"
+    Y._attrs["is_output"] = True
+    module = compile_model(Y, detect_target(), workdir, "arg_errors")
+    x, w = _rand((8, 64), 1).cuda(), _rand((32, 64), 2).cuda()
+    y = torch.empty((8, 32), dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):  # CPU tensor
+        module.run_with_tensors([x.cpu(), w], [y])
+    with pytest.raises(ValueError):  # non-contiguous
+        module.run_with_tensors([x.t().contiguous().t(), w], [y])
+    with pytest.raises(ValueError):  # unknown input name
+        module.run_with_tensors({"x": x, "nope": w}, [y])
+    with pytest.raises(ValueError):  # wrong count in a dict
+        module.run_with_tensors({"x": x}, [y])
+    with pytest.raises(RuntimeError):  # wrong count in a list
+        module.run_with_tensors([x], [y])
+    with pytest.raises(RuntimeError):  # wrong dtype
+        module.run_with_tensors([x.float(), w], [y])
+    with pytest.raises(RuntimeError):  # wrong static shape
+        module.run_with_tensors([_rand((8, 32), 1).cuda(), w], [y])
+    assert module.get_input_name_to_index_map() == {"x": 0, "w": 1}
+    assert module.get_output_name_to_index_map() == {"y": 0}
+    assert module.get_output_maximum_shape(0) == [8, 32]
+    assert module.get_output_dtype(0) == 1
+    assert module.get_num_runtimes() == 1
+    module.close()
+    with pytest.raises(RuntimeError, match="closed"):
+        module.run_with_tensors([x, w], [y])
+
+
+def test_constants_bound_unbound_and_double_buffer(workdir):
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    X = Tensor(shape=[16, 64], name="x", is_input=True)
+    W = Tensor(shape=[32, 64], name="w")
+    B = Tensor(shape=[32], name="b")
+    Y = ops.gemm_rcr_bias()(X, W, B)
+    Y._attrs["name"] = "y"
+    Y._attrs["is_output"] = True
+    w, b, x = _rand((32, 64), 1, 0.1), _rand((32,), 2), _rand((16, 64), 3)
+    module = compile_model(Y, detect_target(), workdir, "constants", constants={"w": w})
+    y = torch.empty((16, 32), dtype=torch.float16, device="cuda")
+    assert sorted(module.get_constant_names(unbound_constants_only=False)) == ["b", "w"]
+    assert module.get_constant_names() == ["b"]
+    with pytest.raises(RuntimeError, match="Run"):  # b was never set
+        module.run_with_tensors([x.cuda()], [y])
+    module.set_constant_with_tensor("b", b.cuda())
+    _close(module.run_with_tensors([x.cuda()], [y])["y"], oracle.gemm_rcr(x, w, b))
+    with pytest.raises(RuntimeError):  # wrong size
+        module.set_constant_with_tensor("b", _rand((31,), 4).cuda())
+    with pytest.raises(RuntimeError):  # unknown name
+        module.set_constant_with_tensor("nope", b.cuda())
+    # double buffering: the new value is only used after swap_constants()
+    w2 = _rand((32, 64), 5, 0.1)
+    module.set_double_buffer_constant_with_tensor("w", w2.cuda())
+    _close(module.run_with_tensors([x.cuda()], [y])["y"], oracle.gemm_rcr(x, w, b))
+    module.swap_constants()
+    _close(module.run_with_tensors([x.cuda()], [y])["y"], oracle.gemm_rcr(x, w2, b))
+    # AIT_RECOMPILE=0 reloads the stored plan (bound constants included)
+    os.environ["AIT_RECOMPILE"] = "0"
+    try:
+        again = compile_model(Y, detect_target(), workdir, "constants")
+    finally:
+        del os.environ["AIT_RECOMPILE"]
+    again.set_constant_with_tensor("b", b.cuda())
+    _close(again.run_with_tensors([x.cuda()], [y])["y"], oracle.gemm_rcr(x, w, b))
+
+
+def test_fuse_mm_elementwise_and_views(workdir):
+    """gemm_rcr + ADD(bias) + FASTGELU written with plain ops is fused into one launch, and an
+    output that is a view of an intermediate is written in place."""
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    from aitemplate_b200.compiler.ops import FuncEnum
+
+    batch = IntVar([1, 8], name="batch")
+    X = Tensor(shape=[batch, 48, 64], name="x", is_input=True)
+    W = Tensor(shape=[96, 64], name="w", is_input=True)
+    B = Tensor(shape=[96], name="b", is_input=True)
+    h = ops.gemm_rcr()(ops.reshape()(X, [-1, 64]), W)
+    h = ops.elementwise(FuncEnum.FASTGELU)(ops.elementwise(FuncEnum.ADD)(h, B))
+    Y = ops.reshape()(h, [batch, 48, 96])
+    Y._attrs["name"] = "y"
+    Y._attrs["is_output"] = True
+    module = compile_model(Y, detect_target(), workdir, "fuse")
+    kernels = [op._attrs["op"] for t in module.debug_sorted_graph for op in t._attrs["src_ops"]]
+    assert "gemm_rcr_bias_fast_gelu" in kernels and "elementwise" not in kernels
+    for bsz in (1, 3, 8):
+        x, w, b = _rand((bsz, 48, 64), 1), _rand((96, 64), 2, 0.1), _rand((96,), 3)
+        y = torch.empty((8, 48, 96), dtype=torch.float16, device="cuda")
+        res = module.run_with_tensors({"x": x.cuda(), "w": w.cuda(), "b": b.cuda()}, {"y": y})
+        assert tuple(res["y"].shape) == (bsz, 48, 96)
+        _close(res["y"], oracle.gemm_rcr(x, w, b, epilogue="fast_gelu"))
+
+
+def test_layout_ops_in_a_graph_are_bit_exact(workdir):
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    xs = [Tensor(shape=[64, 32 * (i + 1)], name=f"x{i}", is_input=True) for i in range(3)]
+    cat = ops.concatenate()(xs, dim=1)
+    a, b = ops.split()(cat, [64, 128], dim=1)
+    p = ops.permute()(ops.reshape()(b, [64, 4, 32]), [1, 0, 2])
+    outs = []
+    for name, t in (("cat", cat), ("a", a), ("p", p)):
+        t._attrs["name"] = name
+        t._attrs["is_output"] = True
+        outs.append(t)
+    module = compile_model(outs, detect_target(), workdir, "layout")
+    data = [_rand((64, 32 * (i + 1)), i) for i in range(3)]
+    bufs = {"cat": torch.empty((64, 192), dtype=torch.float16, device="cuda"),
+            "a": torch.empty((64, 64), dtype=torch.float16, device="cuda"),
+            "p": torch.empty((4, 64, 32), dtype=torch.float16, device="cuda")}
+    res = module.run_with_tensors({f"x{i}": d.cuda() for i, d in enumerate(data)}, bufs)
+    want = torch.cat(data, 1)
+    assert torch.equal(res["cat"].cpu(), want)
+    assert torch.equal(res["a"].cpu(), want[:, :64])
+    assert torch.equal(res["p"].cpu(), want[:, 64:].reshape(64, 4, 32).permute(1, 0, 2).contiguous())
+
+
+def test_softmax_layernorm_bmm_attention_graph(workdir):
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    q = Tensor(shape=[2, 4, 96, 64], name="q", is_input=True)
+    k = Tensor(shape=[2, 4, 80, 64], name="k", is_input=True)
+    v = Tensor(shape=[2, 4, 80, 64], name="v", is_input=True)
+    att = ops.mem_eff_attention(causal=False)(q, k, v)
+    att._attrs["name"] = "att"
+    att._attrs["is_output"] = True
+    s = ops.bmm_rcr()(ops.reshape()(q, [8, 96, 64]), ops.reshape()(k, [8, 80, 64]))
+    sm = ops.softmax()(s, -1)
+    sm._attrs["name"] = "sm"
+    sm._attrs["is_output"] = True
+    ln = ops.layernorm()(ops.reshape()(att, [2 * 96, 256]), None, None, [256], 1e-5)
+    ln._attrs["name"] = "ln"
+    ln._attrs["is_output"] = True
+    module = compile_model([att, sm, ln], detect_target(), workdir, "mixed")
+    qd, kd, vd = _rand((2, 4, 96, 64), 1), _rand((2, 4, 80, 64), 2), _rand((2, 4, 80, 64), 3)
+    bufs = {"att": torch.empty((2, 96, 4, 64), dtype=torch.float16, device="cuda"),
+            "sm": torch.empty((8, 96, 80), dtype=torch.float16, device="cuda"),
+            "ln": torch.empty((192, 256), dtype=torch.float16, device="cuda")}
+    res = module.run_with_tensors({"q": qd.cuda(), "k": kd.cuda(), "v": vd.cuda()}, bufs)
+    want_att = oracle.mem_eff_attention(qd, kd, vd)
+    _close(res["att"], want_att, 4e-3)
+    want_s = oracle.bmm_rcr(qd.reshape(8, 96, 64), kd.reshape(8, 80, 64))
+    _close(res["sm"], oracle.softmax(want_s.half(), -1), 1e-2)
+    _close(res["ln"], oracle.layernorm(res["att"].reshape(192, 256).cpu(), None, None), 4e-3)
+
+
+@pytest.mark.parametrize("graph_mode", [False, True])
+def test_bert_layer_matches_oracle(workdir, graph_mode):
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    from aitemplate_b200.testing import workloads
+
+    batch, seq = 4, 384
+    x, params = workloads.bert_layer_inputs(batch, seq)
+    _, y = workloads.build_bert_layer(batch, seq)
+    module = compile_model(y, detect_target(), workdir, "bert_layer", num_runtimes=2)
+    module.set_many_constants_with_tensors({n: params[k].cuda() for n, k in workloads.BERT_PARAM_NAMES.items()})
+    out = torch.empty((batch, seq, 768), dtype=torch.float16, device="cuda")
+    want = oracle.bert_layer(x, params)
+    for _ in range(3):  # eager warm-up, capture, replay
+        out.zero_()
+        res = module.run_with_tensors({"hidden_states": x.cuda()}, {"output_0": out}, graph_mode=graph_mode)
+        _close(res["output_0"], want, 2e-2)
+    mean, std, _ = module.benchmark_with_tensors({"hidden_states": x.cuda()}, {"output_0": out}, count=5, repeat=2,
+                                                 graph_mode=graph_mode)
+    assert mean > 0
+    prof = os.path.join(workdir, "prof.json")
+    module.profile_with_tensors({"hidden_states": x.cuda()}, {"output_0": out}, 2, prof)
+    import json
+
+    with open(prof) as f:
+        names = list(json.load(f).keys())
+    assert sum(n.startswith("gemm_rcr") for n in names) == 4 and any(n.startswith("mem_eff_attention") for n in names)
+
+
+def test_concurrent_runs_share_the_pool(workdir):
+    import threading
+
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    X = Tensor(shape=[256, 128], name="x", is_input=True)
+    W = Tensor(shape=[128, 128], name="w", is_input=True)
+    Y = ops.gemm_rcr()(ops.gemm_rcr()(X, W), W)
+    Y._attrs["name"] = "y"
+    Y._attrs["is_output"] = True
+    module = compile_model(Y, detect_target(), workdir, "pool", num_runtimes=2)
+    x, w = _rand((256, 128), 1), _rand((128, 128), 2, 0.1)
+    want = oracle.gemm_rcr(oracle.gemm_rcr(x, w).half(), w)
+    xg, wg = x.cuda(), w.cuda()
+    results, errors = [None] * 4, []
+
+    def worker(i):
+        try:
+            torch.cuda.set_device(0)
+            s = torch.cuda.Stream()
+            y = torch.empty((256, 128), dtype=torch.float16, device="cuda")
+            with torch.cuda.stream(s):
+                for _ in range(10):
+                    module.run_with_tensors([xg, wg], [y], stream_ptr=s.cuda_stream, sync=True)
+            results[i] = y
+        except Exception as e:  # pragma: no cover
+            errors.append(e)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for y in results:
+        _close(y, want, 2e-2)
