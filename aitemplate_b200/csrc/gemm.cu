@@ -30,6 +30,8 @@ namespace b200ait {
 struct GemmParams {
   int M, N, K, batch;
   int tiles_m, tiles_n, num_tiles;
+  int splits, kb_per_split, num_units;  // split-K: unit = tile * splits + split
+  float* partial;                       // [splits, batch, M, N] fp32 partial sums when splits > 1
   int a_batch_mul, b_batch_mul;  // 0 when that operand is broadcast over the batch
   const void* bias;              // [N] or nullptr
   const void* d0;                // [M, N] residual operands (row stride ldd) or nullptr
@@ -229,10 +231,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      for (int unit = blockIdx.x; ok && unit < p.num_units; unit += gridDim.x) {
         int b, m_blk, n_blk;
+        const int tile = unit / p.splits, split = unit - tile * p.splits;
         decode_tile(p, tile, b, m_blk, n_blk);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
           if (!ok) break;
           uint8_t* sa = smem + stage * kStageBytes;
@@ -262,12 +266,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      for (int unit = blockIdx.x; ok && unit < p.num_units; unit += gridDim.x) {
         ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, kDevWaitAccEmptyTimeout);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int split = unit % p.splits;
+        const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kDevWaitFullTimeout);
           if (!ok) break;
           tc_fence_after();
@@ -277,7 +283,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           for (int k = 0; k < kBK / 16; ++k) {
             const uint64_t adesc = umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == kStages) {
@@ -305,8 +311,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+    for (int unit = blockIdx.x; ok && unit < p.num_units; unit += gridDim.x) {
       int b, m_blk, n_blk;
+      const int tile = unit / p.splits, split = unit - tile * p.splits;
       decode_tile(p, tile, b, m_blk, n_blk);
       ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, kDevWaitAccFullTimeout);
       if (!ok) break;
@@ -321,6 +328,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_base + static_cast<uint32_t>(c * 32), r);
         tmem_ld_wait();
+        if (p.splits > 1) {
+          // split-K: raw fp32 partial sums; the reduce kernel applies the epilogue
+          if (row_ok) {
+            float* dst = p.partial + ((static_cast<long long>(split) * p.batch + b) * p.M + row) * p.N + col0;
+            if (p.vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<uint4*>(dst + q * 4) = make_uint4(r[q * 4], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst[j] = __uint_as_float(r[j]);
+            }
+          }
+          continue;
+        }
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -339,6 +362,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+}
+
+// ------------------------------------------------------------------------------------------------
+// split-K second pass: sums the fp32 partials of every split and applies the fused epilogue.
+// One thread per (batch, row, 32-column chunk); a warp reads 4 KB of contiguous partials per split.
+template <bool BF16>
+__global__ void __launch_bounds__(256) gemm_splitk_reduce_kernel(const GemmParams p) {
+  const int chunks = (p.N + 31) / 32;
+  const long long total = static_cast<long long>(p.batch) * p.M * chunks;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int chunk = static_cast<int>(idx % chunks);
+  const long long br = idx / chunks;
+  const int row = static_cast<int>(br % p.M), b = static_cast<int>(br / p.M);
+  const int col0 = chunk * 32;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = 0.f;
+  const bool full = p.vec_ok && col0 + 32 <= p.N;
+  for (int s = 0; s < p.splits; ++s) {
+    const float* src = p.partial + ((static_cast<long long>(s) * p.batch + b) * p.M + row) * p.N + col0;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float4 f = *reinterpret_cast<const float4*>(src + q * 4);
+        v[q * 4] += f.x, v[q * 4 + 1] += f.y, v[q * 4 + 2] += f.z, v[q * 4 + 3] += f.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) v[j] += src[j];
+    }
+  }
+  epilogue_chunk32<BF16>(p, v, b, row, col0, true);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -442,9 +499,15 @@ void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cuda
   p.tiles_m = (p.M + kBM - 1) / kBM;
   p.tiles_n = (p.N + BN - 1) / BN;
   p.num_tiles = p.tiles_m * p.tiles_n * p.batch;
-  const int grid = std::min(p.num_tiles, sm_count());
+  p.num_units = p.num_tiles * p.splits;
+  const int grid = std::min(p.num_units, sm_count());
   gemm_tc_kernel<BN, BF16><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
   B200AIT_CUDA_CHECK(cudaGetLastError());
+  if (p.splits > 1) {
+    const long long total = static_cast<long long>(p.batch) * p.M * ((p.N + 31) / 32);
+    gemm_splitk_reduce_kernel<BF16><<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(p);
+    B200AIT_CUDA_CHECK(cudaGetLastError());
+  }
 }
 
 struct GemmArgs {
@@ -459,6 +522,9 @@ struct GemmArgs {
   long long t1, t2, t3;
   int tile_n;  // 0 = choose
   cudaStream_t stream;
+  void* workspace = nullptr;  // fp32 scratch for split-K partial sums (may be null: no split-K)
+  long long workspace_bytes = 0;
+  int split_k = 0;  // 0 = choose, 1 = off, n = at most n splits
 };
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -472,6 +538,32 @@ int choose_tile_n(long long m, long long n, long long batch) {
     if (tiles >= sms) return bn;
   }
   return 64;
+}
+
+// Split-K plan: how many K-splits a problem gets and the fp32 workspace they need.
+// Splitting pays when the output tiles cannot fill the SMs but K is deep enough to share out.
+struct SplitPlan {
+  int tile_n, splits, kb_per_split;
+  long long bytes;
+};
+SplitPlan plan_split_k(long long batch, long long m, long long n, long long k, int tile_n, int max_splits,
+                       long long workspace_bytes) {
+  SplitPlan sp{tile_n ? tile_n : choose_tile_n(m, n, batch), 1, 0, 0};
+  const long long num_kb = (k + kBK - 1) / kBK;
+  sp.kb_per_split = static_cast<int>(num_kb);
+  const long long tiles = ((m + kBM - 1) / kBM) * ((n + sp.tile_n - 1) / sp.tile_n) * batch;
+  const long long sms = sm_count();
+  if (max_splits == 1 || tiles * 2 > sms || num_kb < 4) return sp;
+  long long s = std::min<long long>(std::min<long long>(sms / tiles, num_kb / 2), 16);
+  if (max_splits > 1) s = std::min<long long>(s, max_splits);
+  while (s > 1 && s * batch * m * n * 4 > workspace_bytes) --s;
+  if (s <= 1) return sp;
+  const long long per = (num_kb + s - 1) / s;
+  sp.splits = static_cast<int>((num_kb + per - 1) / per);  // no empty split
+  sp.kb_per_split = static_cast<int>(per);
+  sp.bytes = static_cast<long long>(sp.splits) * batch * m * n * 4;
+  if (sp.splits <= 1) sp = SplitPlan{sp.tile_n, 1, static_cast<int>(num_kb), 0};
+  return sp;
 }
 
 void gemm_run(const GemmArgs& g) {
@@ -530,6 +622,9 @@ void gemm_run(const GemmArgs& g) {
   }
   p.vec_ok = vec ? 1 : 0;
   p.status = device_status_word();
+  p.splits = 1;
+  p.kb_per_split = static_cast<int>((g.k + kBK - 1) / kBK);
+  p.partial = nullptr;
 
   const bool tma_ok = (g.k % 8 == 0) && (g.lda % 8 == 0) && (g.ldb % 8 == 0) && aligned16(g.a) && aligned16(g.b) &&
                       (g.a_bs % 8 == 0) && (g.b_bs % 8 == 0) && g.batch < 65536 * 32;
@@ -545,8 +640,14 @@ void gemm_run(const GemmArgs& g) {
     return;
   }
 
-  int bn = g.tile_n ? g.tile_n : choose_tile_n(g.m, g.n, g.batch);
-  B200AIT_REQUIRE(bn == 64 || bn == 128 || bn == 256, "gemm: tile_n must be 64, 128 or 256");
+  B200AIT_REQUIRE(g.tile_n == 0 || g.tile_n == 64 || g.tile_n == 128 || g.tile_n == 256,
+                  "gemm: tile_n must be 64, 128 or 256");
+  const bool ws_ok = g.workspace != nullptr && aligned16(g.workspace);
+  const SplitPlan sp = plan_split_k(g.batch, g.m, g.n, g.k, g.tile_n, g.split_k, ws_ok ? g.workspace_bytes : 0);
+  const int bn = sp.tile_n;
+  p.splits = sp.splits;
+  p.kb_per_split = sp.kb_per_split;
+  p.partial = static_cast<float*>(g.workspace);
   const long long a_batch = p.a_batch_mul ? g.batch : 1, b_batch = p.b_batch_mul ? g.batch : 1;
   CUtensorMap ta = make_tile_map(g.a, bf16, g.k, g.m, a_batch, g.lda, g.a_bs, kBM);
   CUtensorMap tb = make_tile_map(g.b, bf16, g.k, g.n, b_batch, g.ldb, g.b_bs, bn);
@@ -570,18 +671,34 @@ void gemm_run(const GemmArgs& g) {
 using namespace b200ait;
 
 // Generic entry point: every gemm_rcr* / bmm_rcr* op of the path maps onto it.
+// `workspace` (may be null) is fp32 scratch for split-K partial sums; split_k: 0 = library chooses,
+// 1 = never split, n > 1 = at most n splits. Without a workspace the GEMM never splits.
 B200AIT_EXPORT int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void* d0, const void* d1,
                                     void* c, int64_t batch, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
                                     int64_t ldc, int64_t ldd, int64_t a_batch_stride, int64_t b_batch_stride,
                                     int64_t c_batch_stride, int64_t d_batch_stride, int epilogue, int dtype,
                                     float alpha, int store_mode, int64_t t1, int64_t t2, int64_t t3, int tile_n,
-                                    cudaStream_t stream) {
+                                    void* workspace, int64_t workspace_bytes, int split_k, cudaStream_t stream) {
   return guarded("b200ait_gemm_rcr", [&] {
     GemmArgs g{a,   b,   bias,           d0,             d1,             c,
                batch, m,   n,              k,              lda,            ldb,
                ldc, ldd, a_batch_stride, b_batch_stride, c_batch_stride, d_batch_stride,
                epilogue, dtype, alpha, store_mode, t1, t2, t3, tile_n, stream};
+    g.workspace = workspace;
+    g.workspace_bytes = workspace_bytes;
+    g.split_k = split_k;
     gemm_run(g);
+  });
+}
+
+// Bytes of split-K workspace b200ait_gemm_rcr would use for this problem if given enough.
+B200AIT_EXPORT int b200ait_gemm_rcr_workspace_bytes(int64_t batch, int64_t m, int64_t n, int64_t k, int tile_n,
+                                                    int split_k, int64_t* bytes_out) {
+  return guarded("b200ait_gemm_rcr_workspace_bytes", [&] {
+    B200AIT_REQUIRE(bytes_out, "bytes_out is null");
+    *bytes_out = 0;
+    if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) return;
+    *bytes_out = plan_split_k(batch, m, n, k, tile_n, split_k, (1ll << 62)).bytes;
   });
 }
 

@@ -39,7 +39,8 @@
 extern "C" {
 int b200ait_gemm_rcr(const void*, const void*, const void*, const void*, const void*, void*, int64_t, int64_t, int64_t,
                      int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int, int, float,
-                     int, int64_t, int64_t, int64_t, int, cudaStream_t);
+                     int, int64_t, int64_t, int64_t, int, void*, int64_t, int, cudaStream_t);
+int b200ait_gemm_rcr_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int, int, int64_t*);
 int b200ait_mem_eff_attention(void*, const void*, const void*, const void*, int64_t, int64_t, int64_t, int, int, int,
                               float, int, const int32_t*, const int32_t*, int, cudaStream_t);
 int b200ait_layernorm(void*, const void*, const void*, const void*, int64_t, int64_t, float, int64_t, int64_t, int,
@@ -261,6 +262,25 @@ class Executor {
  public:
   Executor(const Plan& plan, AITemplateAllocator& alloc) : plan_(plan), alloc_(alloc) {
     blob_ = alloc_.Allocate(static_cast<size_t>(plan.blob_bytes));
+    // one split-K scratch area shared by every GEMM of the plan, sized for the hungriest of them at the
+    // lower and upper bound of its dynamic dims (reference: global workspace = max over ops,
+    // python/aitemplate/compiler/transform/memory_planning.py:141-195)
+    for (const OpInfo& op : plan.ops) {
+      if (op.kernel != "gemm_rcr") continue;
+      const TensorInfo& a = plan.tensors[op.operands[0]];
+      const TensorInfo& b = plan.tensors[op.operands[1]];
+      if (a.dims.empty() || b.dims.size() != 2 || !b.dims[0].is_static || !a.dims.back().is_static) continue;
+      for (int bound = 0; bound < 2; ++bound) {
+        int64_t m = 1;
+        for (size_t i = 0; i + 1 < a.dims.size(); ++i)
+          m *= a.dims[i].is_static ? a.dims[i].v : (bound ? plan.dims[a.dims[i].v].hi : plan.dims[a.dims[i].v].lo);
+        int64_t bytes = 0;
+        if (b200ait_gemm_rcr_workspace_bytes(1, m, b.dims[0].v, a.dims.back().v, 0, 0, &bytes) == 0)
+          workspace_bytes_ = std::max(workspace_bytes_, bytes);
+      }
+    }
+    workspace_bytes_ = std::min<int64_t>(workspace_bytes_, 256ll << 20);
+    if (workspace_bytes_ > 0) workspace_ = alloc_.Allocate(static_cast<size_t>(workspace_bytes_));
     B200AIT_CUDA_CHECK(cudaEventCreateWithFlags(&run_finished_, cudaEventDisableTiming));
     B200AIT_CUDA_CHECK(cudaStreamCreateWithFlags(&graph_stream_, cudaStreamNonBlocking));
     st_.dims.assign(plan.dims.size(), 0);
@@ -273,6 +293,7 @@ class Executor {
     if (graph_stream_) cudaStreamDestroy(graph_stream_);
     if (run_finished_) cudaEventDestroy(run_finished_);
     if (blob_) alloc_.Free(blob_);
+    if (workspace_) alloc_.Free(workspace_);
   }
 
   RunState& state() { return st_; }
@@ -348,6 +369,8 @@ class Executor {
   const Plan& plan_;
   AITemplateAllocator& alloc_;
   void* blob_ = nullptr;
+  void* workspace_ = nullptr;
+  int64_t workspace_bytes_ = 0;
   RunState st_;
   std::vector<void*> ptrs_;
   cudaEvent_t run_finished_ = nullptr;
@@ -413,7 +436,7 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     check(b200ait_gemm_rcr(ptr_of(a), ptr_of(b), ptr_of(bias), ptr_of(d0), ptr_of(d1), c, 1, m, n, k, k, k,
                            out_stride, n, 0, 0, 0, 0, static_cast<int>(op.ints[0]), T[a].dtype,
                            static_cast<float>(op.floats[0]), static_cast<int>(op.ints[1]), op.ints[2], op.ints[3],
-                           op.ints[4], 0, stream),
+                           op.ints[4], 0, workspace_, workspace_bytes_, 0, stream),
           op);
     return;
   }
@@ -430,7 +453,7 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     if (!launch) return;
     check(b200ait_gemm_rcr(ptr_of(a), ptr_of(b), nullptr, nullptr, nullptr, ptr_of(out0), batch, m, n, k, k, k, n, n,
                            (ba == 1 && batch > 1) ? 0 : m * k, (bb == 1 && batch > 1) ? 0 : n * k, m * n, m * n, 0,
-                           T[a].dtype, static_cast<float>(op.floats[0]), 0, 1, 1, 1, 0, stream),
+                           T[a].dtype, static_cast<float>(op.floats[0]), 0, 1, 1, 1, 0, nullptr, 0, 1, stream),
           op);
     return;
   }

@@ -102,8 +102,10 @@ def gemm_rcr(
     alpha: float = 1.0,
     tile_n: int = 0,
     out: Optional[torch.Tensor] = None,
+    split_k: int = 0,
 ) -> torch.Tensor:
-    """y = epilogue(x @ w.T + bias, d0, d1); x [..., K] (leading dims fold into M), w [N, K]."""
+    """y = epilogue(x @ w.T + bias, d0, d1); x [..., K] (leading dims fold into M), w [N, K].
+    split_k: 0 lets the library decide, 1 disables split-K, n allows at most n splits."""
     _check_cuda(x, w, bias, d0, d1, out)
     k = x.shape[-1]
     m = x.numel() // k if k else math.prod(x.shape[:-1])
@@ -126,13 +128,27 @@ def gemm_rcr(
         out_shape = list(x.shape[:-1]) + [n]
     if out is None:
         out = torch.empty(out_shape, dtype=x.dtype, device=x.device)
+    ws = None
+    if split_k != 1 and m and n and k:
+        ws_bytes = gemm_workspace_bytes(1, m, n, k, tile_n, split_k)
+        if ws_bytes:
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     code = _lib.load().b200ait_gemm_rcr(
         _ptr(x), _ptr(w), _ptr(bias), _ptr(d0), _ptr(d1), _ptr(out),
         1, m, n, k, k, k, n, n, 0, 0, 0, 0,
-        epilogue_code(epilogue), _dtype_code(x), c_float(alpha), store_mode, t1, t2, t3, tile_n, _stream(),
+        epilogue_code(epilogue), _dtype_code(x), c_float(alpha), store_mode, t1, t2, t3, tile_n,
+        _ptr(ws), ws.numel() if ws is not None else 0, split_k, _stream(),
     )
     _lib.check(code, "b200ait_gemm_rcr")
     return out
+
+
+def gemm_workspace_bytes(batch: int, m: int, n: int, k: int, tile_n: int = 0, split_k: int = 0) -> int:
+    """Bytes of fp32 split-K scratch the library would use for this problem (0 = it would not split)."""
+    out = c_int64(0)
+    _lib.check(_lib.load().b200ait_gemm_rcr_workspace_bytes(batch, m, n, k, tile_n, split_k, ctypes.byref(out)),
+               "b200ait_gemm_rcr_workspace_bytes")
+    return out.value
 
 
 def bmm_rcr(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, tile_n: int = 0) -> torch.Tensor:
@@ -150,7 +166,7 @@ def bmm_rcr(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, tile_n: int = 
         _ptr(a3), _ptr(b3), None, None, None, _ptr(out),
         batch, m, n, k, k, k, n, n,
         0 if (ba == 1 and batch > 1) else m * k, 0 if (bb == 1 and batch > 1) else n * k, m * n, m * n,
-        0, _dtype_code(a), c_float(alpha), 0, 1, 1, 1, tile_n, _stream(),
+        0, _dtype_code(a), c_float(alpha), 0, 1, 1, 1, tile_n, None, 0, 1, _stream(),
     )
     _lib.check(code, "b200ait_gemm_rcr")
     return out

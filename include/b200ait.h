@@ -43,12 +43,21 @@ int b200ait_device_status(int* status_out);
 /* Generic GEMM: c[b] = epilogue(alpha * a[b] . b[b]^T + bias, d0, d1); a [batch, m, k] (row stride lda),
  * b [batch, n, k] (row stride ldb), c / d0 / d1 [batch, m, n] (row strides ldc / ldd). A batch stride
  * of 0 broadcasts that operand. tile_n = 0 lets the library choose (else 64, 128 or 256).
+ * workspace / workspace_bytes / split_k: see b200ait_gemm_rcr_workspace_bytes below.
  * Replaces python/aitemplate/backend/cuda/gemm_universal/common.py:130-617 (CUTLASS instantiation). */
 int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void* d0, const void* d1, void* c,
                      int64_t batch, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
                      int64_t ldd, int64_t a_batch_stride, int64_t b_batch_stride, int64_t c_batch_stride,
                      int64_t d_batch_stride, int epilogue, int dtype, float alpha, int store_mode, int64_t t1,
-                     int64_t t2, int64_t t3, int tile_n, b200ait_stream_t stream);
+                     int64_t t2, int64_t t3, int tile_n, void* workspace, int64_t workspace_bytes, int split_k,
+                     b200ait_stream_t stream);
+/* Split-K (reference: split_k search, python/aitemplate/compiler/ops/gemm_universal/gemm_common.py:579-594):
+ * when the output tiles cannot fill the GPU and K is deep, K is divided among CTAs that write fp32 partial
+ * sums into `workspace` ([splits, batch, m, n] floats) and a second kernel reduces them and applies the
+ * epilogue. split_k: 0 = library chooses, 1 = off, n = at most n. A null workspace disables splitting.
+ * b200ait_gemm_rcr_workspace_bytes reports what the library would use for a problem. */
+int b200ait_gemm_rcr_workspace_bytes(int64_t batch, int64_t m, int64_t n, int64_t k, int tile_n, int split_k,
+                                     int64_t* bytes_out);
 
 /* fp16 entry points with the reference's generated signatures. workspace / split_k are accepted
  * and ignored. *c_dim0, *c_dim1 are written.

@@ -239,3 +239,39 @@ def test_large_gemm_rows_sampled_against_oracle():
     y0 = k.gemm_rcr(x, w, b, epilogue="")
     y1 = k.gemm_rcr(x, w, b, d, epilogue="add")
     assert float(((y1.float() - y0.float()) - d.float()).abs().max()) < 1e-2
+
+
+@pytest.mark.parametrize(
+    "m,n,kk,epilogue,split_k",
+    [
+        (128, 768, 3072, "add", 0),       # few tiles, deep K: the library splits on its own
+        (384, 768, 768, "fast_gelu", 0),  # BERT-base at batch 1
+        (100, 520, 1000, "add_relu", 5),  # ragged M / N / K with a capped split count
+        (64, 64, 4096, "", 0),
+        (7, 264, 2048, "mul", 3),
+        (128, 256, 512, "relu", 1),       # split-K switched off
+    ],
+)
+def test_split_k_matches_oracle(m, n, kk, epilogue, split_k):
+    k = _kernels()
+    x = _rand((m, kk), 90, "uniform")
+    w = _rand((n, kk), 91, scale=0.05)
+    b = _rand((n,), 92, scale=0.1)
+    d0 = _rand((m, n), 93)
+    _, b1, _, _ = oracle.EPILOGUES[epilogue]
+    if split_k != 1:
+        assert k.gemm_workspace_bytes(1, m, n, kk, 0, split_k) > 0, "this shape is expected to split"
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), d0.cuda() if b1 else None, epilogue=epilogue, split_k=split_k)
+    _close(y, oracle.gemm_rcr(x, w, b, d0 if b1 else None, epilogue=epilogue))
+
+
+def test_split_k_with_permuted_store():
+    k = _kernels()
+    s, h, d, bsz = 16, 2, 64, 4
+    hid = h * d
+    x = _rand((bsz * s, 2048), 94, scale=0.5)
+    w = _rand((3 * hid, 2048), 95, scale=0.05)
+    b = _rand((3 * hid,), 96, scale=0.1)
+    assert k.gemm_workspace_bytes(1, bsz * s, 3 * hid, 2048) > 0
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), permute_shape=(s, 3, h))
+    _close(y, oracle.gemm_rcr_bias_permute(x, w, b, (s, 3, h)))
