@@ -160,7 +160,21 @@ class permute(_permute_base):
 
     def __call__(self, x: Tensor, dims: Sequence[int]) -> Tensor:
         dims = [wrap_dim(d, x._rank()) for d in dims]
-        assert sorted(dims) == list(range(x._rank())), f"expected a permutation of {list(range(x._rank()))}, got {dims}"
+        sorted_dims = list(range(x._rank()))
+        assert sorted(dims) == sorted_dims, f"expected a permutation of {sorted_dims}, but got {dims}"
+        self._attrs["dims"] = dims
+        # same dispatch to the fixed-pattern ops as the reference (permute.py:64-92); all of them run
+        # on the one permute kernel here, the op name is kept for graph-level compatibility
+        if dims == [0, 2, 1]:
+            return permute021()(x)
+        if dims == [1, 0, 2]:
+            return permute102()(x)
+        if dims == [2, 1, 0]:
+            return permute210()(x)
+        if dims == [0, 2, 1, 3] and x.shape()[1].lower_bound() >= 24:
+            return permute0213()(x)
+        if len(dims) > 3 and dims[:-2] + [dims[-1], dims[-2]] == sorted_dims and x.shape()[-1].lower_bound() >= 8:
+            return permute021()(x)
         return self._build(x, dims)
 
 

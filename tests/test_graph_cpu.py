@@ -1,0 +1,213 @@
+"""Host-side logic without a GPU: IR arithmetic, naming, the gemm+elementwise fusion pass, split ->
+views, memory planning and the plan text handed to the native runtime."""
+import pytest
+
+from aitemplate_b200.compiler import compiler as C
+from aitemplate_b200.compiler import ops
+from aitemplate_b200.compiler.base import IntImm, IntVar, Tensor
+from aitemplate_b200.compiler.ops import FuncEnum
+from aitemplate_b200.compiler.transform import (
+    fuse_mm_elementwise,
+    mark_param_tensor,
+    memory_planning,
+    name_graph,
+    remove_no_ops,
+    reset_name_counters,
+    split_to_views,
+    toposort,
+)
+from aitemplate_b200.compiler.transform.toposort import sorted_ops
+from aitemplate_b200.testing import workloads
+
+
+def _lower(outs, fuse=True):
+    reset_name_counters()
+    g = toposort(outs)
+    C._validate_tensor_args(g, outs)
+    g = remove_no_ops(g)
+    mark_param_tensor(g)
+    if fuse:
+        g = fuse_mm_elementwise(g, outs)
+        mark_param_tensor(g)
+        split_to_views(g)
+    name_graph(g)
+    copies = C._assign_storage(g, outs)
+    blob, consts = memory_planning(g)
+    return g, C._lower_to_plan(g, outs, "t", blob, consts, copies, None, {}), blob, consts
+
+
+def _out(t, name):
+    t._attrs["name"] = name
+    t._attrs["is_output"] = True
+    return t
+
+
+def test_intvar_arithmetic_is_conservative():
+    b = IntVar([2, 8], name="b")
+    assert (b * 3)._attrs["values"] == [6, 24]
+    assert (b + 1)._attrs["values"] == [3, 9]
+    assert (b - 1)._attrs["values"] == [1, 7]
+    assert (b / 2)._attrs["values"] == [1, 4]
+    assert isinstance(IntVar([4, 4]), IntVar) and IntVar([4, 4])._attrs["values"] == [4, 4]
+    assert IntImm(5) == 5 and IntImm(5) == IntImm(5) and IntImm(5) != IntImm(6)
+    with pytest.raises(RuntimeError):
+        IntVar([3])
+    with pytest.raises(RuntimeError):
+        IntVar([-1, 3])
+    with pytest.raises(RuntimeError):
+        IntImm(2.5)
+
+
+def test_shape_errors_match_the_reference_rules():
+    x = Tensor([16, 64], name="x", is_input=True)
+    with pytest.raises(RuntimeError, match="shape mismatch"):
+        ops.gemm_rcr()(x, Tensor([32, 48], name="w"))
+    with pytest.raises(RuntimeError, match="K must be static"):
+        ops.gemm_rcr()(Tensor([16, IntVar([8, 64], "k")], name="xd"), Tensor([32, IntVar([8, 64], "k")], name="wd"))
+    with pytest.raises(RuntimeError, match="1D"):
+        ops.gemm_rcr_bias()(x, Tensor([32, 64], name="w"), Tensor([1, 32], name="b"))
+    with pytest.raises(RuntimeError, match="same as the output"):
+        ops.gemm_rcr_bias_add()(x, Tensor([32, 64], name="w"), Tensor([32], name="b"), Tensor([16, 31], name="d"))
+    with pytest.raises(NotImplementedError):
+        ops.softmax()(Tensor([4, IntVar([1, 9], "n")], name="s"), -1)
+    with pytest.raises(RuntimeError, match="sum of split_sizes"):
+        ops.split()(x, [10, 10], dim=0)
+    with pytest.raises(AssertionError):
+        ops.permute()(x, [0, 0])
+    with pytest.raises(NotImplementedError):
+        ops.gemm_rcr_bias_permute(shape=(2, 2, 2), layout="m2n3")
+    with pytest.raises(RuntimeError, match="not compatible"):
+        ops.layernorm()(x, None, None, [32])
+
+
+def test_fusion_patterns():
+    def chain(*funcs, residuals=0):
+        x = Tensor([IntVar([1, 32], "m"), 64], name="x", is_input=True)
+        w, b = Tensor([48, 64], name="w"), Tensor([48], name="b")
+        h = ops.elementwise(FuncEnum.ADD)(ops.gemm_rcr()(x, w), b)
+        for i, f in enumerate(funcs):
+            if f in (FuncEnum.ADD, FuncEnum.MUL):
+                h = ops.elementwise(f)(h, Tensor([x.shape()[0], 48], name=f"d{i}", is_input=True))
+            else:
+                h = ops.elementwise(f)(h)
+        outs = [_out(h, "y")]
+        g, plan, _, _ = _lower(outs)
+        return [op._attrs["op"] for op in sorted_ops(g)]
+
+    assert chain() == ["gemm_rcr_bias"]
+    assert chain(FuncEnum.RELU) == ["gemm_rcr_bias_relu"]
+    assert chain(FuncEnum.FASTGELU) == ["gemm_rcr_bias_fast_gelu"]
+    assert chain(FuncEnum.GELU) == ["gemm_rcr_bias_gelu"]
+    assert chain(FuncEnum.SILU) == ["gemm_rcr_bias_swish"]
+    assert chain(FuncEnum.ADD) == ["gemm_rcr_bias_add"]
+    assert chain(FuncEnum.ADD, FuncEnum.RELU) == ["gemm_rcr_bias_add_relu"]
+    assert chain(FuncEnum.ADD, FuncEnum.ADD, FuncEnum.RELU) == ["gemm_rcr_bias_add_add_relu"]
+    assert chain(FuncEnum.MUL, FuncEnum.ADD) == ["gemm_rcr_bias_mul_add"]
+    assert chain(FuncEnum.SIGMOID, FuncEnum.MUL, FuncEnum.TANH) == ["gemm_rcr_bias_sigmoid_mul_tanh"]
+    # not absorbable: a second activation stays an elementwise op
+    assert chain(FuncEnum.RELU, FuncEnum.TANH) == ["gemm_rcr_bias_relu", "elementwise"]
+
+
+def test_fusion_keeps_multi_consumer_and_output_tensors():
+    x = Tensor([8, 64], name="x", is_input=True)
+    w = Tensor([48, 64], name="w")
+    h = ops.gemm_rcr()(x, w)
+    a = ops.elementwise(FuncEnum.RELU)(h)
+    b = ops.elementwise(FuncEnum.TANH)(h)  # h has two consumers: no fusion
+    g, _, _, _ = _lower([_out(a, "a"), _out(b, "b")])
+    assert [op._attrs["op"] for op in sorted_ops(g)].count("gemm_rcr") == 1
+
+
+def test_validate_outputs():
+    x = Tensor([8, 64], name="x", is_input=True)
+    y = ops.elementwise(FuncEnum.RELU)(x)
+    with pytest.raises(ValueError, match="non-output"):
+        C._validate_tensor_args(toposort([y]), [y])
+    y._attrs["is_output"] = True
+    y._attrs["name"] = "y"
+    z = _out(ops.elementwise(FuncEnum.TANH)(y), "z")
+    with pytest.raises(ValueError, match="was not passed"):
+        C._validate_tensor_args(toposort([z]), [z])
+    with pytest.raises(ValueError, match="duplicate"):
+        C._validate_tensor_args(toposort([z]), [z, z])
+
+
+def test_bert_layer_plan_and_memory_plan():
+    _, y = workloads.build_bert_layer(2, 384)
+    g, plan, blob, consts = _lower([y])
+    kernels = [line.split()[1] for line in plan.splitlines() if line.startswith("op ")]
+    assert [k for k in kernels if k != "view"] == [
+        "gemm_rcr", "split", "mem_eff_attention", "gemm_rcr", "layernorm", "gemm_rcr", "gemm_rcr", "layernorm"]
+    # the dim-0 split became three views at byte offsets; nothing is copied
+    split_line = next(line for line in plan.splitlines() if line.startswith("op split"))
+    assert split_line.split()[-5:-1] == ["0", "0", "0", "0"] or split_line.endswith("0 0 0 0")
+    views = [line.split() for line in plan.splitlines() if line.startswith("tensor split_")]
+    assert [int(v[5]) for v in views] == [0, 2 * 12 * 384 * 64 * 2, 2 * 2 * 12 * 384 * 64 * 2]
+    assert consts >= 2 * (2304 * 768 + 768 * 768 + 2 * 3072 * 768)
+    # lifetimes: tensors that are alive at the same time never overlap in the blob
+    ops_sorted = sorted_ops(g)
+    idx = {id(op): i for i, op in enumerate(ops_sorted)}
+    from aitemplate_b200.compiler.transform.memory_planning import storage_root
+
+    life = {}
+    for t in g:
+        r = storage_root(t)
+        if r._attrs["is_input"] or r._attrs["is_param"] or r._attrs.get("output_slot") is not None:
+            continue
+        uses = [idx[id(o)] for o in list(t._attrs["src_ops"]) + list(t._attrs["dst_ops"]) if id(o) in idx]
+        lo, hi = life.get(id(r), (10 ** 9, -1, r))[:2]
+        life[id(r)] = (min([lo] + uses), max([hi] + uses), r)
+    items = list(life.values())
+    for i, (f1, l1, a) in enumerate(items):
+        for f2, l2, b in items[i + 1:]:
+            if l1 < f2 or l2 < f1:
+                continue
+            a0, a1 = a._attrs["offset"], a._attrs["offset"] + a.size_bytes()
+            b0, b1 = b._attrs["offset"], b._attrs["offset"] + b.size_bytes()
+            assert a1 <= b0 or b1 <= a0, (a._attrs["name"], b._attrs["name"])
+    assert blob >= max(t._attrs["offset"] + t.size_bytes() for _, _, t in items)
+    assert all(t._attrs["offset"] % 256 == 0 for _, _, t in items)
+
+
+def test_output_aliasing_input_gets_a_copy():
+    x = Tensor([4, 6], name="x", is_input=True)
+    y = _out(ops.reshape()(x, [6, 4]), "y")
+    _, plan, _, _ = _lower([y])
+    assert any(line.startswith("op copy") for line in plan.splitlines())
+    assert "output 0" in plan
+
+
+def test_dynamic_reshape_names_and_tokens():
+    b = IntVar([1, 64], name="batch")
+    x = Tensor([b, 384, 768], name="x", is_input=True)
+    w = Tensor([768, 768], name="w")
+    h = ops.gemm_rcr()(ops.reshape()(x, [-1, 768]), w)
+    y = _out(ops.reshape()(h, [b, 384, 768]), "y")
+    g, plan, _, _ = _lower([y])
+    lines = plan.splitlines()
+    assert "dim batch 1 64" in lines
+    assert any(line.startswith("dim ") and line.endswith("384 24576") for line in lines)
+    out_line = next(line for line in lines if line.startswith("tensor y "))
+    assert out_line.split()[-3:] == ["d0", "s384", "s768"]
+
+
+def test_nn_modules_name_parameters():
+    from aitemplate_b200.frontend import nn
+
+    layer = workloads.BertEncoderLayer(2, 384)
+    layer.name_parameter_tensor()
+    names = sorted(p.tensor()._attrs["name"] for p in layer.parameters())
+    assert names == sorted(workloads.BERT_PARAM_NAMES.keys())
+    lin = nn.Linear(8, 16, specialization="relu")
+    assert lin._op_name == "gemm_rcr_bias_relu"
+    with pytest.raises(NotImplementedError):
+        nn.Linear(8, 16, specialization="nope")
+
+
+def test_target_rejects_fp16_accumulation():
+    from aitemplate_b200.testing import detect_target
+
+    t = detect_target(no_tf32=True)
+    assert t.name() == "cuda" and t._kwargs["no_tf32"] is True
+    with pytest.raises(NotImplementedError):
+        detect_target(use_fp16_acc=True)
