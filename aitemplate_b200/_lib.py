@@ -42,6 +42,11 @@ def _signatures():
                                                c_void_p, c_int64, c_int, c_void_p],
         ),
         "b200ait_gemm_rcr_workspace_bytes": (c_int, [c_int64] * 4 + [c_int, c_int, I64P]),
+        "b200ait_gemm_rcr_static_scratch": (
+            c_int,
+            [c_void_p] * 6 + [c_int64] * 12 + [c_int, c_int, c_float, c_int, c_int64, c_int64, c_int64, c_int,
+                                               c_int, c_void_p, c_void_p],
+        ),
         "b200ait_gemm_rcr_plain": (c_int, [c_void_p] * 3 + [c_void_p, c_int] + _DIMS6 + [c_void_p]),
         "b200ait_gemm_rcr_bias_permute": (
             c_int,

@@ -525,6 +525,7 @@ struct GemmArgs {
   void* workspace = nullptr;  // fp32 scratch for split-K partial sums (may be null: no split-K)
   long long workspace_bytes = 0;
   int split_k = 0;  // 0 = choose, 1 = off, n = at most n splits
+  int* status = nullptr;  // device status word to use instead of the library's allocated one
 };
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -621,7 +622,7 @@ void gemm_run(const GemmArgs& g) {
     throw Error("gemm: unknown store mode");
   }
   p.vec_ok = vec ? 1 : 0;
-  p.status = device_status_word();
+  p.status = g.status ? g.status : device_status_word();
   p.splits = 1;
   p.kb_per_split = static_cast<int>((g.k + kBK - 1) / kBK);
   p.partial = nullptr;
@@ -820,5 +821,91 @@ B200AIT_EXPORT int b200ait_bmm_rcr(void* a, void* b, void* c, uint8_t* workspace
                (ba == 1 && batch > 1) ? 0 : m * k, (bb == 1 && batch > 1) ? 0 : n * k, m * n, m * n,
                0, kDTypeHalf, 1.f, 0, 1, 1, 1, 0, stream};
     gemm_run(g);
+  });
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Split-K GEMM for callers that must not allocate device memory.
+//
+// Some hosts of this library run where cudaMalloc is off limits: inside a serving process whose
+// memory pool was sized and handed out at start-up, under a framework allocator that owns the whole
+// device, or on a path that has to stay free of driver allocation calls because those serialise
+// with other work. b200ait_gemm_rcr needs two pieces of device memory beyond its operands: the
+// fp32 scratch for split-K partial sums (the caller's `workspace`) and the status word the kernels
+// report into (allocated by the library on first use). This entry point needs neither from the
+// caller and allocates neither: both live in the file-scope array below, which is part of the
+// library image, so every GPU that loads the library holds these 16 MiB + 256 bytes until the
+// process exits.
+namespace b200ait {
+constexpr long long kStaticScratchHeader = 256;               // status word, padded to the alignment
+constexpr long long kStaticScratchBytes = 16ll << 20;         // split-K partial sums: at most 16 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchHeader + kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not an address a kernel can
+// use; the device address comes from cudaGetSymbolAddress, asked once per device with that device
+// current.
+static unsigned char* static_scratch_device_ptr() {
+  constexpr int kMaxDev = 64;
+  static std::mutex mu;
+  static unsigned char* ptrs[kMaxDev] = {};
+  int dev = 0;
+  B200AIT_CUDA_CHECK(cudaGetDevice(&dev));
+  B200AIT_REQUIRE(dev >= 0 && dev < kMaxDev, "device ordinal out of range");
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    B200AIT_CUDA_CHECK(cudaGetSymbolAddress(&p, g_static_scratch));
+    B200AIT_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a null address for the static scratch");
+    ptrs[dev] = static_cast<unsigned char*>(p);
+  }
+  return ptrs[dev];
+}
+}  // namespace b200ait
+
+// Same computation and arguments as b200ait_gemm_rcr, minus the workspace: split-K partial sums go
+// to the library's static scratch. Calls no cudaMalloc / cudaFree and no allocating library routine.
+//   * Limit: the partial sums of two splits must fit, 2 * batch * m * n * 4 bytes <= 16 MiB;
+//     larger problems are rejected with an error (use b200ait_gemm_rcr with your own workspace).
+//     Within the limit the library may use fewer splits than b200ait_gemm_rcr would.
+//   * The first call on each device looks up the scratch address (cudaGetSymbolAddress) and sets
+//     kernel attributes; make that first call outside any stream capture.
+//   * Every call on a device shares the one scratch area and it keeps whatever the last call left
+//     there. Each call rewrites all partial sums it later reads and clears the status word first,
+//     but two calls that overlap on the GPU (different streams) race on it: keep calls to this entry
+//     point stream-ordered per device.
+//   * status_out (device pointer, may be null) receives the kernel status word after the GEMM
+//     (0 = clean), stream-ordered; read it after synchronising the stream.
+B200AIT_EXPORT int b200ait_gemm_rcr_static_scratch(const void* a, const void* b, const void* bias, const void* d0,
+                                                   const void* d1, void* c, int64_t batch, int64_t m, int64_t n,
+                                                   int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd,
+                                                   int64_t a_batch_stride, int64_t b_batch_stride,
+                                                   int64_t c_batch_stride, int64_t d_batch_stride, int epilogue,
+                                                   int dtype, float alpha, int store_mode, int64_t t1, int64_t t2,
+                                                   int64_t t3, int tile_n, int split_k, int* status_out,
+                                                   cudaStream_t stream) {
+  return guarded("b200ait_gemm_rcr_static_scratch", [&] {
+    B200AIT_REQUIRE(batch >= 0 && m >= 0 && n >= 0 && k >= 0, "gemm: negative dimension");
+    const long long need = 2ll * batch * m * n * 4;
+    if (need > kStaticScratchBytes) {
+      throw Error("problem too large for the static scratch: two splits of " + std::to_string(batch) + " x " +
+                  std::to_string(m) + " x " + std::to_string(n) + " fp32 partial sums need " + std::to_string(need) +
+                  " bytes, the limit is " + std::to_string(kStaticScratchBytes) +
+                  "; call b200ait_gemm_rcr with a caller-provided workspace instead");
+    }
+    unsigned char* scratch = static_scratch_device_ptr();
+    int* status = reinterpret_cast<int*>(scratch);
+    B200AIT_CUDA_CHECK(cudaMemsetAsync(status, 0, sizeof(int), stream));  // must start at zero
+    GemmArgs g{a,   b,   bias,           d0,             d1,             c,
+               batch, m,   n,              k,              lda,            ldb,
+               ldc, ldd, a_batch_stride, b_batch_stride, c_batch_stride, d_batch_stride,
+               epilogue, dtype, alpha, store_mode, t1, t2, t3, tile_n, stream};
+    g.workspace = scratch + kStaticScratchHeader;
+    g.workspace_bytes = kStaticScratchBytes;
+    g.split_k = split_k;
+    g.status = status;
+    gemm_run(g);
+    if (status_out)
+      B200AIT_CUDA_CHECK(cudaMemcpyAsync(status_out, status, sizeof(int), cudaMemcpyDeviceToDevice, stream));
   });
 }

@@ -58,6 +58,20 @@ int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void*
  * b200ait_gemm_rcr_workspace_bytes reports what the library would use for a problem. */
 int b200ait_gemm_rcr_workspace_bytes(int64_t batch, int64_t m, int64_t n, int64_t k, int tile_n, int split_k,
                                      int64_t* bytes_out);
+/* No counterpart in the reference. b200ait_gemm_rcr for callers that cannot allocate device memory
+ * (a serving process living inside a pre-sized pool, a framework allocator that owns the device, a
+ * path that must avoid driver allocation calls): the split-K partial sums and the kernel status
+ * word live in a 16 MiB + 256 B array inside the library image, so this call runs no cudaMalloc /
+ * cudaFree. Problems whose two-split partial sums exceed the array (2 * batch * m * n * 4 bytes >
+ * 16 MiB) are rejected. The first call on a device does one-time set-up and belongs outside any
+ * stream capture; all calls on a device share the array, so keep them stream-ordered (calls that
+ * overlap on the GPU race). status_out: optional device int that receives the status word. */
+int b200ait_gemm_rcr_static_scratch(const void* a, const void* b, const void* bias, const void* d0,
+                                    const void* d1, void* c, int64_t batch, int64_t m, int64_t n, int64_t k,
+                                    int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t a_batch_stride,
+                                    int64_t b_batch_stride, int64_t c_batch_stride, int64_t d_batch_stride,
+                                    int epilogue, int dtype, float alpha, int store_mode, int64_t t1, int64_t t2,
+                                    int64_t t3, int tile_n, int split_k, int* status_out, b200ait_stream_t stream);
 
 /* fp16 entry points with the reference's generated signatures. workspace / split_k are accepted
  * and ignored. *c_dim0, *c_dim1 are written.
