@@ -210,6 +210,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
       const int key0 = j * BLOCK_N;
       int limit = kv_len - key0;  // keys [0, limit) of this block are valid
       if (p.causal) limit = min(limit, q_idx - key0 + 1);
+      // A key block is "plain" when every key of it is visible to every row of this warp: then the two
+      // passes run without per-element masks (the common case; only the last block of a ragged or
+      // causal sequence needs them).
+      const int limit_min = __reduce_min_sync(0xffffffffu, limit);
+      const bool plain = limit_min >= BLOCK_N;
       // pass 1: row maximum
       float m_blk = -INFINITY;
 #pragma unroll 1
@@ -217,9 +222,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 32, v);
         tmem_ld_wait();
+        if (plain) {
+          float m0 = __uint_as_float(v[0]), m1 = __uint_as_float(v[1]), m2 = __uint_as_float(v[2]),
+                m3 = __uint_as_float(v[3]);
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < limit) m_blk = fmaxf(m_blk, __uint_as_float(v[i]));
+          for (int i = 4; i < 32; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(v[i]));
+            m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
+            m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+          }
+          m_blk = fmaxf(m_blk, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < limit) m_blk = fmaxf(m_blk, __uint_as_float(v[i]));
+        }
       }
       const float m_new = fmaxf(m_run, m_blk * p.scale_log2);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -232,12 +250,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
         tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 32, v);
         tmem_ld_wait();
         uint32_t packed[16];
+        if (plain) {
+          float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = (c * 32 + i < limit) ? exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_use) : 0.f;
-          float p1 = (c * 32 + i + 1 < limit) ? exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - m_use) : 0.f;
-          l_blk += p0 + p1;
-          packed[i >> 1] = E::from_float2(p0, p1);
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
+            const float p1 = exp2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
+            l0 += p0;
+            l1 += p1;
+            packed[i >> 1] = E::from_float2(p0, p1);
+          }
+          l_blk += l0 + l1;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 =
+                (c * 32 + i < limit) ? exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use)) : 0.f;
+            const float p1 =
+                (c * 32 + i + 1 < limit) ? exp2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use)) : 0.f;
+            l_blk += p0 + p1;
+            packed[i >> 1] = E::from_float2(p0, p1);
+          }
         }
         // keys c*32 .. c*32+31 live in 64-key chunk (c >> 1), 16-byte units (c & 1)*4 .. +3 of row r
         uint8_t* row_base = sP + (c >> 1) * kBlockM * 128 + r * 128;

@@ -1,0 +1,526 @@
+// Device code of the tcgen05 GEMM (see gemm.cu for the design notes and the host side).
+// Included by gemm.cu (parameters, scalar epilogue) and by the per-tile-width instantiation units
+// gemm_bn64.cu / gemm_bn128.cu / gemm_bn256.cu.
+#pragma once
+#include <cuda.h>
+
+#include <atomic>
+
+#include "common.h"
+#include "epilogue.cuh"
+#include "ptx.cuh"
+
+namespace b200ait {
+
+struct GemmParams {
+  int M, N, K, batch;
+  int tiles_m, tiles_n, num_tiles;
+  int splits, kb_per_split, num_units;  // split-K: unit = tile * splits + split
+  float* partial;                       // [splits, batch, M, N] fp32 partial sums when splits > 1
+  int a_batch_mul, b_batch_mul;  // 0 when that operand is broadcast over the batch
+  const void* bias;              // [N] or nullptr
+  const void* d0;                // [M, N] residual operands (row stride ldd) or nullptr
+  const void* d1;
+  void* out;
+  long long lda, ldb;            // only used by the CUDA-core kernel
+  long long a_bs, b_bs;
+  long long ldc, ldd, c_bs, d_bs;
+  float alpha;
+  int epilogue;
+  // store_mode 0: out[b*c_bs + row*ldc + col]
+  // store_mode 1: out[(row / t1)*rs_hi + (row % t1)*rs_lo + (col / (t3*d))*cs2 + ((col / d) % t3)*cs3 + col % d]
+  int store_mode;
+  int t1, t3, d;
+  long long rs_hi, rs_lo, cs2, cs3;
+  int vec_ok;  // 16-byte epilogue accesses are legal
+  int* status;
+};
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGroupM = 8;
+constexpr int kEpiWarps = 8;                      // two per TMEM lane quarter, each takes half of the columns
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;  // producer warp + MMA warp + epilogue warps
+
+template <int BN>
+struct TileCfg {
+  static constexpr int kStageBytes = kBM * kBK * 2 + BN * kBK * 2;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
+                                    2 * BN * 4 /*bias tile, fp32, one per accumulator*/;
+};
+
+__device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int& b, int& m_blk, int& n_blk) {
+  const int per_batch = p.tiles_m * p.tiles_n;
+  b = tile / per_batch;
+  const int t = tile - b * per_batch;
+  const int group_size = kGroupM * p.tiles_n;
+  const int g = t / group_size;
+  const int first_m = g * kGroupM;
+  const int gm = min(kGroupM, p.tiles_m - first_m);
+  const int r = t - g * group_size;
+  m_blk = first_m + r % gm;
+  n_blk = r / gm;
+}
+
+// offset (in elements) of output element (row, col) relative to the batch base
+__device__ __forceinline__ long long row_offset(const GemmParams& p, int row) {
+  if (p.store_mode == 0) return static_cast<long long>(row) * p.ldc;
+  const int hi = row / p.t1;
+  return hi * p.rs_hi + (row - hi * p.t1) * p.rs_lo;
+}
+__device__ __forceinline__ long long col_offset(const GemmParams& p, int col) {
+  if (p.store_mode == 0) return col;
+  const int c = col / p.d;
+  const int c2 = c / p.t3;
+  return c2 * p.cs2 + (c - c2 * p.t3) * p.cs3 + (col - c * p.d);
+}
+
+// Applies the epilogue to 32 consecutive columns of one row and stores them.
+template <bool BF16>
+__device__ __forceinline__ void epilogue_chunk32(const GemmParams& p, float (&v)[32], int b, int row, int col0,
+                                                 bool row_ok) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  const int u1 = epi_u1(p.epilogue), b1 = epi_b1(p.epilogue), b2 = epi_b2(p.epilogue), u2 = epi_u2(p.epilogue);
+  const bool full = p.vec_ok && (col0 + 32 <= p.N);
+  if (p.alpha != 1.f) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+  }
+  if (p.bias != nullptr) {
+    const T* bias = static_cast<const T*>(p.bias) + col0;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float f[8];
+        unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(bias) + q), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[q * 8 + j] += f[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) v[j] += E::to_float(bias[j]);
+    }
+  }
+  apply_unary_vec(u1, v);
+  if (!row_ok) return;
+  const long long d_base = static_cast<long long>(b) * p.d_bs + static_cast<long long>(row) * p.ldd + col0;
+  if (b1 != kBinaryNone) {
+    const T* d0 = static_cast<const T*>(p.d0) + d_base;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float f[8];
+        unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(d0) + q), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[q * 8 + j] = (b1 == kBinaryAdd) ? v[q * 8 + j] + f[j] : v[q * 8 + j] * f[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) {
+          const float f = E::to_float(d0[j]);
+          v[j] = (b1 == kBinaryAdd) ? v[j] + f : v[j] * f;
+        }
+    }
+  }
+  if (b2 != kBinaryNone) {
+    const T* d1 = static_cast<const T*>(p.d1) + d_base;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float f[8];
+        unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(d1) + q), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[q * 8 + j] = (b2 == kBinaryAdd) ? v[q * 8 + j] + f[j] : v[q * 8 + j] * f[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) {
+          const float f = E::to_float(d1[j]);
+          v[j] = (b2 == kBinaryAdd) ? v[j] + f : v[j] * f;
+        }
+    }
+  }
+  apply_unary_vec(u2, v);
+  T* out = static_cast<T*>(p.out) + static_cast<long long>(b) * p.c_bs + row_offset(p, row);
+  if (full) {
+    if (p.store_mode == 0) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(out + col0 + q * 8) = pack8<BF16>(&v[q * 8]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        *reinterpret_cast<uint4*>(out + col_offset(p, col0 + q * 8)) = pack8<BF16>(&v[q * 8]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) out[col_offset(p, col0 + j)] = E::from_float(v[j]);
+  }
+}
+
+
+// EPI >= 0 fixes the epilogue code at compile time (straight-line code for the common epilogues);
+// EPI == -1 reads it from the parameters.
+template <int EPI>
+__device__ __forceinline__ int epilogue_code_of(const GemmParams& p) {
+  return EPI >= 0 ? EPI : p.epilogue;
+}
+
+// Fused epilogue of the tensor-core kernel for 32 consecutive columns of one row. `v` already holds
+// alpha * acc + bias. d0 is prefetched by the caller (d0v valid when the chunk is `full`).
+template <bool BF16, int EPI>
+__device__ __forceinline__ void epilogue_store32(const GemmParams& p, float (&v)[32], const uint4 (&d0v)[4], int b,
+                                                 int row, int col0, bool full, bool chunk_contig) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  const int code = epilogue_code_of<EPI>(p);
+  const int u1 = epi_u1(code), b1 = epi_b1(code), b2 = epi_b2(code), u2 = epi_u2(code);
+  apply_unary_vec(u1, v);
+  const long long d_base = static_cast<long long>(b) * p.d_bs + static_cast<long long>(row) * p.ldd + col0;
+  if (b1 != kBinaryNone) {
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float f[8];
+        unpack8<BF16>(d0v[q], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[q * 8 + j] = (b1 == kBinaryAdd) ? v[q * 8 + j] + f[j] : v[q * 8 + j] * f[j];
+      }
+    } else {
+      const T* d0 = static_cast<const T*>(p.d0) + d_base;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) {
+          const float f = E::to_float(d0[j]);
+          v[j] = (b1 == kBinaryAdd) ? v[j] + f : v[j] * f;
+        }
+    }
+  }
+  if (b2 != kBinaryNone) {
+    const T* d1 = static_cast<const T*>(p.d1) + d_base;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float f[8];
+        unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(d1) + q), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[q * 8 + j] = (b2 == kBinaryAdd) ? v[q * 8 + j] + f[j] : v[q * 8 + j] * f[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) {
+          const float f = E::to_float(d1[j]);
+          v[j] = (b2 == kBinaryAdd) ? v[j] + f : v[j] * f;
+        }
+    }
+  }
+  apply_unary_vec(u2, v);
+  T* out = static_cast<T*>(p.out) + static_cast<long long>(b) * p.c_bs + row_offset(p, row);
+  if (full) {
+    if (chunk_contig) {
+      T* dst = out + col_offset(p, col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + q * 8) = pack8<BF16>(&v[q * 8]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        *reinterpret_cast<uint4*>(out + col_offset(p, col0 + q * 8)) = pack8<BF16>(&v[q * 8]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) out[col_offset(p, col0 + j)] = E::from_float(v[j]);
+  }
+}
+
+template <int BN, bool BF16, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+               const GemmParams p) {
+  using Cfg = TileCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr uint32_t kABytes = kBM * kBK * 2;
+  constexpr uint32_t kStageBytes = Cfg::kStageBytes;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* acc_full = empty_bar + kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint64_t* drain_bar = acc_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* sbias = reinterpret_cast<float*>(smem + kStages * kStageBytes + 256);  // [2][BN]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 32 * kEpiWarps);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; ok && unit < p.num_units; unit += gridDim.x) {
+        int b, m_blk, n_blk;
+        const int tile = unit / p.splits, split = unit - tile * p.splits;
+        decode_tile(p, tile, b, m_blk, n_blk);
+        const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+          tma_load_3d(sa, &tma_a, &full_bar[stage], kb * kBK, m_blk * kBM, b * p.a_batch_mul);
+          tma_load_3d(sa + kABytes, &tma_b, &full_bar[stage], kb * kBK, n_blk * BN, b * p.b_batch_mul);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // give copies that are still in flight a bounded time to land before the CTA exits
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(kBM, BN, BF16, false, false);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; ok && unit < p.num_units; unit += gridDim.x) {
+        ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, kDevWaitAccEmptyTimeout);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        const int split = unit % p.splits;
+        const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kDevWaitFullTimeout);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * kStageBytes);
+          const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t adesc = umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      if (!ok) {
+        // let MMAs that were already issued finish before TMEM is released
+        umma_commit(drain_bar);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 1000000ull) {
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ----------------------------------------------------------------- epilogue
+    // Warp w of the eight reads TMEM lanes [32*(warp%4), +32) (a hardware rule) and the column half
+    // w / 4 of the tile. Per tile: stage the bias slice in shared memory while the MMAs still run,
+    // then walk the chunks with the next chunk's TMEM load and residual load already in flight.
+    using E = Elem16<BF16>;
+    using T = typename E::T;
+    constexpr int kChunksPerWarp = BN / 64;  // 32-column chunks per warp
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int half = ew >> 2;
+    const int et = threadIdx.x - 64;  // 0..255
+    const int code = epilogue_code_of<EPI>(p);
+    const bool has_d0 = epi_b1(code) != kBinaryNone;
+    const bool chunk_contig = p.store_mode == 0 || (p.d % 32 == 0);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int unit = blockIdx.x; ok && unit < p.num_units; unit += gridDim.x) {
+      int b, m_blk, n_blk;
+      const int tile = unit / p.splits, split = unit - tile * p.splits;
+      decode_tile(p, tile, b, m_blk, n_blk);
+      float* bias_s = sbias + acc * BN;
+      if (et < BN) {
+        const int col = n_blk * BN + et;
+        bias_s[et] = (p.bias != nullptr && p.splits == 1 && col < p.N) ? E::to_float(static_cast<const T*>(p.bias)[col]) : 0.f;
+      }
+      named_bar_sync(1, 32 * kEpiWarps);
+      const int row = m_blk * kBM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const int colh = n_blk * BN + half * (BN / 2);  // first column of this warp's half
+      const T* d0_row = static_cast<const T*>(p.d0) + static_cast<long long>(b) * p.d_bs + static_cast<long long>(row) * p.ldd;
+      uint4 d0v[4];
+      auto prefetch_d0 = [&](int col0) {
+        if (has_d0 && row_ok && p.vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) d0v[q] = __ldg(reinterpret_cast<const uint4*>(d0_row + col0) + q);
+        }
+      };
+      if (p.splits == 1) prefetch_d0(colh);
+      ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, kDevWaitAccFullTimeout);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                              static_cast<uint32_t>(acc * BN + half * (BN / 2));
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_base, r);
+#pragma unroll 1
+      for (int c = 0; c < kChunksPerWarp; ++c) {
+        const int col0 = colh + c * 32;
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        uint4 d0c[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) d0c[q] = d0v[q];
+        if (c + 1 < kChunksPerWarp && col0 + 32 < p.N) {  // next chunk's loads go out before this chunk's math
+          tmem_ld_32x32b_x32(t_base + static_cast<uint32_t>((c + 1) * 32), r);
+          if (p.splits == 1) prefetch_d0(col0 + 32);
+        }
+        if (col0 >= p.N) continue;  // warp-uniform
+        const bool full = p.vec_ok && (col0 + 32 <= p.N);
+        if (p.splits > 1) {
+          // split-K: raw fp32 partial sums; the reduce kernel applies the epilogue
+          if (row_ok) {
+            float* dst = p.partial + ((static_cast<long long>(split) * p.batch + b) * p.M + row) * p.N + col0;
+            if (full) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst[j] = v[j];
+            }
+          }
+          continue;
+        }
+        const float* bs = bias_s + half * (BN / 2) + c * 32;
+        if (p.alpha != 1.f) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 f = *reinterpret_cast<const float4*>(bs + q * 4);
+          v[q * 4] += f.x, v[q * 4 + 1] += f.y, v[q * 4 + 2] += f.z, v[q * 4 + 3] += f.w;
+        }
+        if (row_ok) epilogue_store32<BF16, EPI>(p, v, d0c, b, row, col0, full, chunk_contig);
+      }
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int BN, bool BF16, int EPI>
+void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  using Cfg = TileCfg<BN>;
+  static std::atomic<uint64_t> configured{0};
+  opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_tc_kernel<BN, BF16, EPI>), Cfg::kSmemBytes);
+  gemm_tc_kernel<BN, BF16, EPI><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  B200AIT_CUDA_CHECK(cudaGetLastError());
+}
+
+// Epilogues that get their own straight-line instantiation (fp16): bias, relu, gelu, fast_gelu, add,
+// add_relu, mul. Everything else, and bf16, runs the generic instantiation.
+#define B200AIT_FOR_EACH_FAST_EPILOGUE(X)                                                  \
+  X(make_epilogue(kUnaryIdentity, kBinaryNone, kBinaryNone, kUnaryIdentity))              \
+  X(make_epilogue(kUnaryRelu, kBinaryNone, kBinaryNone, kUnaryIdentity))                  \
+  X(make_epilogue(kUnaryGelu, kBinaryNone, kBinaryNone, kUnaryIdentity))                  \
+  X(make_epilogue(kUnaryFastGelu, kBinaryNone, kBinaryNone, kUnaryIdentity))              \
+  X(make_epilogue(kUnaryIdentity, kBinaryAdd, kBinaryNone, kUnaryIdentity))               \
+  X(make_epilogue(kUnaryIdentity, kBinaryAdd, kBinaryNone, kUnaryRelu))                   \
+  X(make_epilogue(kUnaryIdentity, kBinaryMul, kBinaryNone, kUnaryIdentity))
+
+// Defined once per tile width in gemm_bn<BN>.cu.
+template <int BN>
+void launch_tc_width(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                     cudaStream_t stream);
+
+template <>
+void launch_tc_width<64>(bool, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
+template <>
+void launch_tc_width<128>(bool, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
+template <>
+void launch_tc_width<256>(bool, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
+
+#define B200AIT_DEFINE_LAUNCH_TC_WIDTH(BN_)                                                                    \
+  template <>                                                                                                  \
+  void launch_tc_width<BN_>(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,      \
+                            int grid, cudaStream_t stream) {                                                   \
+    if (bf16) {                                                                                                \
+      launch_tc<BN_, true, -1>(ta, tb, p, grid, stream);                                                       \
+      return;                                                                                                  \
+    }                                                                                                          \
+    switch (p.epilogue) {                                                                                      \
+      B200AIT_FOR_EACH_FAST_EPILOGUE(B200AIT_CASE_##BN_)                                                       \
+      default:                                                                                                 \
+        launch_tc<BN_, false, -1>(ta, tb, p, grid, stream);                                                    \
+    }                                                                                                          \
+  }
+
+}  // namespace b200ait
