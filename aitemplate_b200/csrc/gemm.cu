@@ -152,6 +152,22 @@ CUtensorMap make_tile_map(const void* base, bool bf16, long long cols, long long
   return m;
 }
 
+// 5-D map over the GEMM output for the shared-memory-staged store; box = 64 columns x 32 rows,
+// 128-byte swizzle. dims / strides are innermost first; strides in elements.
+CUtensorMap make_out_map(void* base, bool bf16, const long long (&dims)[5], const long long (&strides)[4]) {
+  CUtensorMap m;
+  cuuint64_t gd[5], gs[4];
+  for (int i = 0; i < 5; ++i) gd[i] = static_cast<cuuint64_t>(dims[i]);
+  for (int i = 0; i < 4; ++i) gs[i] = static_cast<cuuint64_t>(strides[i]) * 2;
+  cuuint32_t box[5] = {64, 32, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = get_encode_fn()(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, base,
+                               gd, gs, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw Error("cuTensorMapEncodeTiled (output) failed with CUresult " + std::to_string(static_cast<int>(r)));
+  return m;
+}
+
 struct GemmArgs {
   const void *a, *b, *bias, *d0, *d1;
   void* c;
@@ -294,17 +310,37 @@ void gemm_run(const GemmArgs& g) {
   const long long a_batch = p.a_batch_mul ? g.batch : 1, b_batch = p.b_batch_mul ? g.batch : 1;
   CUtensorMap ta = make_tile_map(g.a, bf16, g.k, g.m, a_batch, g.lda, g.a_bs, kBM);
   CUtensorMap tb = make_tile_map(g.b, bf16, g.k, g.n, b_batch, g.ldb, g.b_bs, bn);
+  // Staged TMA store: row-major output with 16-byte aligned rows, or a permuted output whose 64-column
+  // groups and 32-row groups each stay inside one contiguous run of the destination.
+  CUtensorMap tout = ta;
+  p.tma_store = 0;
+  if (bn >= 128 && p.splits == 1 && p.vec_ok) {
+    if (p.store_mode == 0) {
+      const long long bs = g.batch > 1 ? g.c_bs : g.m * g.ldc;
+      const long long dims[5] = {g.n, g.m, g.batch, 1, 1};
+      const long long strides[4] = {g.ldc, bs, bs, bs};
+      tout = make_out_map(g.c, bf16, dims, strides);
+      p.tma_store = 1;
+    } else if (p.d % 64 == 0 && p.t1 % 32 == 0 && g.batch == 1) {
+      // destination [c2][row / t1][c3][row % t1][d]: dims innermost first (d, t1, t3, M / t1, c2 extent)
+      const long long c2_extent = g.n / (static_cast<long long>(p.d) * p.t3);
+      const long long dims[5] = {p.d, p.t1, p.t3, g.m / p.t1, c2_extent};
+      const long long strides[4] = {p.rs_lo, p.cs3, p.rs_hi, p.cs2 > 0 ? p.cs2 : p.rs_hi * (g.m / p.t1)};
+      tout = make_out_map(g.c, bf16, dims, strides);
+      p.tma_store = 1;
+    }
+  }
   p.tiles_m = (p.M + kBM - 1) / kBM;
   p.tiles_n = (p.N + bn - 1) / bn;
   p.num_tiles = p.tiles_m * p.tiles_n * p.batch;
   p.num_units = p.num_tiles * p.splits;
   const int grid = std::min(p.num_units, sm_count());
   if (bn == 256)
-    launch_tc_width<256>(bf16, ta, tb, p, grid, g.stream);
+    launch_tc_width<256>(bf16, ta, tb, tout, p, grid, g.stream);
   else if (bn == 128)
-    launch_tc_width<128>(bf16, ta, tb, p, grid, g.stream);
+    launch_tc_width<128>(bf16, ta, tb, tout, p, grid, g.stream);
   else
-    launch_tc_width<64>(bf16, ta, tb, p, grid, g.stream);
+    launch_tc_width<64>(bf16, ta, tb, tout, p, grid, g.stream);
   if (p.splits > 1) {
     const long long total = static_cast<long long>(p.batch) * p.M * ((p.N + 31) / 32);
     const unsigned blocks = static_cast<unsigned>((total + 255) / 256);

@@ -4,7 +4,7 @@
 namespace b200ait {
 #define B200AIT_CASE_256(CODE)                                 \
   case (CODE):                                                  \
-    launch_tc<256, false, (CODE)>(ta, tb, p, grid, stream);     \
+    launch_tc<256, false, (CODE)>(ta, tb, tout, p, grid, stream);     \
     break;
 B200AIT_DEFINE_LAUNCH_TC_WIDTH(256)
 #undef B200AIT_CASE_256

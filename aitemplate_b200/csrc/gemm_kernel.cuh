@@ -33,6 +33,7 @@ struct GemmParams {
   int t1, t3, d;
   long long rs_hi, rs_lo, cs2, cs3;
   int vec_ok;  // 16-byte epilogue accesses are legal
+  int tma_store;  // output goes through shared memory + TMA store (tensor map `tma_out`)
   int* status;
 };
 
@@ -47,7 +48,8 @@ struct TileCfg {
   static constexpr int kStageBytes = kBM * kBK * 2 + BN * kBK * 2;
   static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
+  static constexpr int kStagingBytes = (BN >= 128) ? kEpiWarps * 4096 : 0;  // per-warp 32x64 output boxes
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 256 /*barriers*/ +
                                     2 * BN * 4 /*bias tile, fp32, one per accumulator*/;
 };
 
@@ -172,18 +174,18 @@ __device__ __forceinline__ int epilogue_code_of(const GemmParams& p) {
   return EPI >= 0 ? EPI : p.epilogue;
 }
 
-// Fused epilogue of the tensor-core kernel for 32 consecutive columns of one row. `v` already holds
-// alpha * acc + bias. d0 is prefetched by the caller (d0v valid when the chunk is `full`).
+// Fused epilogue math of the tensor-core kernel for 32 consecutive columns of one row. `v` already
+// holds alpha * acc + bias. d0 is prefetched by the caller (d0v valid when the chunk is `full`).
 template <bool BF16, int EPI>
-__device__ __forceinline__ void epilogue_store32(const GemmParams& p, float (&v)[32], const uint4 (&d0v)[4], int b,
-                                                 int row, int col0, bool full, bool chunk_contig) {
+__device__ __forceinline__ void epilogue_math32(const GemmParams& p, float (&v)[32], const uint4 (&d0v)[4], int b,
+                                                int row, int col0, bool full, bool row_ok) {
   using E = Elem16<BF16>;
   using T = typename E::T;
   const int code = epilogue_code_of<EPI>(p);
   const int u1 = epi_u1(code), b1 = epi_b1(code), b2 = epi_b2(code), u2 = epi_u2(code);
   apply_unary_vec(u1, v);
   const long long d_base = static_cast<long long>(b) * p.d_bs + static_cast<long long>(row) * p.ldd + col0;
-  if (b1 != kBinaryNone) {
+  if (b1 != kBinaryNone && row_ok) {
     if (full) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -202,7 +204,7 @@ __device__ __forceinline__ void epilogue_store32(const GemmParams& p, float (&v)
         }
     }
   }
-  if (b2 != kBinaryNone) {
+  if (b2 != kBinaryNone && row_ok) {
     const T* d1 = static_cast<const T*>(p.d1) + d_base;
     if (full) {
 #pragma unroll
@@ -222,6 +224,14 @@ __device__ __forceinline__ void epilogue_store32(const GemmParams& p, float (&v)
     }
   }
   apply_unary_vec(u2, v);
+}
+
+// Direct register -> global store of 32 consecutive columns of one row.
+template <bool BF16>
+__device__ __forceinline__ void epilogue_direct_store32(const GemmParams& p, const float (&v)[32], int b, int row,
+                                                        int col0, bool full, bool chunk_contig) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
   T* out = static_cast<T*>(p.out) + static_cast<long long>(b) * p.c_bs + row_offset(p, row);
   if (full) {
     if (chunk_contig) {
@@ -243,22 +253,26 @@ __device__ __forceinline__ void epilogue_store32(const GemmParams& p, float (&v)
 template <int BN, bool BF16, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap tma_out, const GemmParams p) {
   using Cfg = TileCfg<BN>;
   constexpr int kStages = Cfg::kStages;
   constexpr uint32_t kABytes = kBM * kBK * 2;
   constexpr uint32_t kStageBytes = Cfg::kStageBytes;
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0u) {  // swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevBadSmemAlignment);
+    return;
+  }
+  uint8_t* staging = smem + kStages * kStageBytes;  // [kEpiWarps][32 rows][128 B], 128-byte swizzled
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + Cfg::kStagingBytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* acc_full = empty_bar + kStages;
   uint64_t* acc_empty = acc_full + 2;
   uint64_t* drain_bar = acc_empty + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* sbias = reinterpret_cast<float*>(smem + kStages * kStageBytes + 256);  // [2][BN]
+  float* sbias = reinterpret_cast<float*>(staging + Cfg::kStagingBytes + 256);  // [2][BN]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -278,6 +292,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (p.tma_store) tma_prefetch_desc(&tma_out);
   }
   __syncthreads();
   if (warp == 1) {
@@ -384,6 +399,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const int code = epilogue_code_of<EPI>(p);
     const bool has_d0 = epi_b1(code) != kBinaryNone;
     const bool chunk_contig = p.store_mode == 0 || (p.d % 32 == 0);
+    const bool use_tma = (BN >= 128) && p.tma_store != 0;
+    uint8_t* my_staging = staging + ew * 4096;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -458,7 +475,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           const float4 f = *reinterpret_cast<const float4*>(bs + q * 4);
           v[q * 4] += f.x, v[q * 4 + 1] += f.y, v[q * 4 + 2] += f.z, v[q * 4 + 3] += f.w;
         }
-        if (row_ok) epilogue_store32<BF16, EPI>(p, v, d0c, b, row, col0, full, chunk_contig);
+        if (use_tma) {
+          // Stage this warp's 32 rows x 64 columns (two chunks) in 128-byte-swizzled shared memory and
+          // let TMA write the box: full 128-byte lines reach L2, rows / columns past M / N are clipped.
+          epilogue_math32<BF16, EPI>(p, v, d0c, b, row, col0, full, row_ok);
+          if ((c & 1) == 0) {  // the box buffer is about to be rewritten: its last store must have read it
+            if (lane == 0) bulk_wait_group_read0();
+            __syncwarp();
+          }
+          uint8_t* row_base = my_staging + lane * 128;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int unit = ((c & 1) * 4 + u) ^ (lane & 7);
+            *reinterpret_cast<uint4*>(row_base + unit * 16) = pack8<BF16>(&v[u * 8]);
+          }
+          if ((c & 1) != 0 || col0 + 32 >= p.N) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const int gcol = colh + (c & ~1) * 32;
+              const int row0 = m_blk * kBM + quarter * 32;
+              if (p.store_mode == 0) {
+                tma_store_5d(&tma_out, my_staging, gcol, row0, b, 0, 0);
+              } else {
+                const int cc = gcol / p.d, r_b = row0 / p.t1;
+                tma_store_5d(&tma_out, my_staging, gcol - cc * p.d, row0 - r_b * p.t1, cc % p.t3, r_b, cc / p.t3);
+              }
+              bulk_commit_group();
+            }
+          }
+        } else if (row_ok) {
+          epilogue_math32<BF16, EPI>(p, v, d0c, b, row, col0, full, true);
+          epilogue_direct_store32<BF16>(p, v, b, row, col0, full, chunk_contig);
+        }
       }
       tmem_ld_wait();
       tc_fence_before();
@@ -466,6 +515,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (use_tma && lane == 0) bulk_wait_group0();  // shared memory must outlive the stores that read it
   }
 
   tc_fence_before();
@@ -477,11 +527,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 }
 
 template <int BN, bool BF16, int EPI>
-void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout, const GemmParams& p, int grid,
+               cudaStream_t stream) {
   using Cfg = TileCfg<BN>;
   static std::atomic<uint64_t> configured{0};
   opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_tc_kernel<BN, BF16, EPI>), Cfg::kSmemBytes);
-  gemm_tc_kernel<BN, BF16, EPI><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  gemm_tc_kernel<BN, BF16, EPI><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout, p);
   B200AIT_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -498,28 +549,31 @@ void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
 
 // Defined once per tile width in gemm_bn<BN>.cu.
 template <int BN>
-void launch_tc_width(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
-                     cudaStream_t stream);
+void launch_tc_width(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
+                     const GemmParams& p, int grid, cudaStream_t stream);
 
 template <>
-void launch_tc_width<64>(bool, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
+void launch_tc_width<64>(bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int,
+                          cudaStream_t);
 template <>
-void launch_tc_width<128>(bool, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
+void launch_tc_width<128>(bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int,
+                          cudaStream_t);
 template <>
-void launch_tc_width<256>(bool, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
+void launch_tc_width<256>(bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int,
+                          cudaStream_t);
 
 #define B200AIT_DEFINE_LAUNCH_TC_WIDTH(BN_)                                                                    \
   template <>                                                                                                  \
-  void launch_tc_width<BN_>(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,      \
-                            int grid, cudaStream_t stream) {                                                   \
+  void launch_tc_width<BN_>(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,  \
+                            const GemmParams& p, int grid, cudaStream_t stream) {                              \
     if (bf16) {                                                                                                \
-      launch_tc<BN_, true, -1>(ta, tb, p, grid, stream);                                                       \
+      launch_tc<BN_, true, -1>(ta, tb, tout, p, grid, stream);                                                 \
       return;                                                                                                  \
     }                                                                                                          \
     switch (p.epilogue) {                                                                                      \
       B200AIT_FOR_EACH_FAST_EPILOGUE(B200AIT_CASE_##BN_)                                                       \
       default:                                                                                                 \
-        launch_tc<BN_, false, -1>(ta, tb, p, grid, stream);                                                    \
+        launch_tc<BN_, false, -1>(ta, tb, tout, p, grid, stream);                                              \
     }                                                                                                          \
   }
 
