@@ -20,6 +20,7 @@
 
 #include <atomic>
 #include <cmath>
+#include <type_traits>
 
 #include "common.h"
 #include "epilogue.cuh"
@@ -44,26 +45,32 @@ struct AttnParams {
 
 constexpr int kAttnThreads = 192;
 constexpr int kBlockM = 128;
+constexpr int kBlockN = 64;     // keys per block
+constexpr int kKvStages = 3;    // K/V ring: blocks j, j+1, j+2 are in flight
 
-template <int BLOCK_N, int DCH>
+template <int DCH>
 struct AttnCfg {
   static constexpr int kQBytes = DCH * kBlockM * 128;
-  static constexpr int kKBytes = DCH * BLOCK_N * 128;  // one K (or V) stage
-  static constexpr int kPBytes = (BLOCK_N / 64) * kBlockM * 128;
-  static constexpr int kStages = 2;
-  static constexpr int kDataBytes = kQBytes + kStages * 2 * kKBytes + kPBytes;
+  static constexpr int kKBytes = DCH * kBlockN * 128;  // one K (or V) block
+  static constexpr int kPBytes = kBlockM * 128;        // one P block: 128 rows x 64 keys
+  static constexpr int kDataBytes = kQBytes + kKvStages * 2 * kKBytes + 2 * kPBytes;
   // the dynamic shared-memory window is declared 1024-byte aligned, so no slack is reserved:
-  // two CTAs of the 64-wide configuration must fit one SM
+  // two CTAs of the 64-wide configuration (96 KB each) must fit one SM
   static constexpr int kSmemBytes = kDataBytes + 128;
-  static constexpr int kTmemCols = (BLOCK_N + DCH * 64 <= 128) ? 128 : 256;  // S then T
+  static constexpr int kTWidth = DCH * 64;                       // columns of one T = P V accumulator
+  static constexpr int kTmemCols = (DCH == 1) ? 256 : 512;       // S x2 (64 each) then T x2
 };
 
-template <int BLOCK_N, int DCH, bool BF16>
+// Pipeline (per CTA, key blocks j = 0 .. n-1, everything double-buffered on j & 1):
+//   MMA warp:      S(0), S(1); then for each j: wait P(j) -> T(j) = P(j) V(j) -> S(j+2)
+//   softmax warps: wait S(j) -> max / exp2 / row sum -> P(j) -> signal; then fold T(j-1) into O
+// so the tensor core computes S(j+1), S(j+2) and T(j-1) while the softmax threads work on block j,
+// and the softmax threads never wait for an MMA that was not issued a whole block earlier.
+template <int DCH, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, (DCH == 1) ? 2 : 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                     const __grid_constant__ CUtensorMap tma_v, const AttnParams p) {
-  using Cfg = AttnCfg<BLOCK_N, DCH>;
-  constexpr int kStages = Cfg::kStages;
+  using Cfg = AttnCfg<DCH>;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0u) {  // swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevBadSmemAlignment);
@@ -71,14 +78,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
   }
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + Cfg::kQBytes;  // stage s: K at sKV + s*2*kKBytes, V right after K
-  uint8_t* sP = sKV + kStages * 2 * Cfg::kKBytes;
-  uint64_t* q_full = reinterpret_cast<uint64_t*>(sP + Cfg::kPBytes);
+  uint8_t* sP = sKV + kKvStages * 2 * Cfg::kKBytes;  // two P blocks
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(sP + 2 * Cfg::kPBytes);
   uint64_t* kv_full = q_full + 1;
-  uint64_t* kv_empty = kv_full + kStages;
-  uint64_t* s_full = kv_empty + kStages;
-  uint64_t* p_full = s_full + 1;
-  uint64_t* t_full = p_full + 1;
-  uint64_t* drain_bar = t_full + 1;
+  uint64_t* kv_empty = kv_full + kKvStages;
+  uint64_t* s_full = kv_empty + kKvStages;  // [2]
+  uint64_t* p_full = s_full + 2;            // [2]
+  uint64_t* t_full = p_full + 2;            // [2]
+  uint64_t* drain_bar = t_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -88,18 +95,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
   const int q0 = q_blk * kBlockM;
   int kv_len = p.Skv;
   if (p.causal) kv_len = min(kv_len, q0 + kBlockM);
-  const int n_blocks = (kv_len + BLOCK_N - 1) / BLOCK_N;
+  const int n_blocks = (kv_len + kBlockN - 1) / kBlockN;
   const int dsteps = (p.D + 15) / 16;  // k-steps of Q K^T
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kKvStages; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
-    mbar_init(t_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&t_full[i], 1);
+    }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -116,8 +125,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;            // BLOCK_N columns
-  const uint32_t tmem_t = tmem_base + BLOCK_N;  // DCH*64 columns
+  const uint32_t tmem_s = tmem_base;        // S(j) at + (j & 1) * 64
+  const uint32_t tmem_t = tmem_base + 128;  // T(j) at + (j & 1) * kTWidth
 
   if (warp == 0) {
     if (lane == 0) {
@@ -126,8 +135,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
       for (int c = 0; c < DCH; ++c) tma_load_3d(sQ + c * kBlockM * 128, &tma_q, q_full, c * 64, q0, bh);
       bool ok = true;
       for (int j = 0; ok && j < n_blocks; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (j / kStages) & 1;
+        const int st = j % kKvStages;
+        const uint32_t ph = (j / kKvStages) & 1;
         ok = mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
         if (!ok) break;
         uint8_t* sK = sKV + st * 2 * Cfg::kKBytes;
@@ -135,8 +144,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
         mbar_arrive_expect_tx(&kv_full[st], 2 * Cfg::kKBytes);
 #pragma unroll
         for (int c = 0; c < DCH; ++c) {
-          tma_load_3d(sK + c * BLOCK_N * 128, &tma_k, &kv_full[st], c * 64, j * BLOCK_N, bh);
-          tma_load_3d(sV + c * BLOCK_N * 128, &tma_v, &kv_full[st], c * 64, j * BLOCK_N, bh);
+          tma_load_3d(sK + c * kBlockN * 128, &tma_k, &kv_full[st], c * 64, j * kBlockN, bh);
+          tma_load_3d(sV + c * kBlockN * 128, &tma_v, &kv_full[st], c * 64, j * kBlockN, bh);
         }
       }
       if (!ok) {
@@ -148,40 +157,45 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_f16(kBlockM, BLOCK_N, BF16, false, false);
-      constexpr uint32_t idesc_t = umma_idesc_f16(kBlockM, DCH * 64, BF16, false, true);  // V is MN-major
+      constexpr uint32_t idesc_s = umma_idesc_f16(kBlockM, kBlockN, BF16, false, false);
+      constexpr uint32_t idesc_t = umma_idesc_f16(kBlockM, Cfg::kTWidth, BF16, false, true);  // V is MN-major
+      const uint32_t q_addr = smem_u32(sQ);
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kDevWaitFullTimeout);
-      for (int j = 0; ok && j < n_blocks; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (j / kStages) & 1;
-        ok = mbar_wait(&kv_full[st], ph, abort_flag, p.status, kDevWaitFullTimeout);
-        if (!ok) break;
+      // S(j) = Q K(j)^T into S buffer j & 1
+      auto issue_s = [&](int j) -> bool {
+        const int st = j % kKvStages;
+        if (!mbar_wait(&kv_full[st], (j / kKvStages) & 1, abort_flag, p.status, kDevWaitFullTimeout)) return false;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ);
         const uint32_t k_addr = smem_u32(sKV + st * 2 * Cfg::kKBytes);
-        const uint32_t v_addr = k_addr + Cfg::kKBytes;
         for (int k = 0; k < dsteps; ++k) {
           const int c = k >> 2, kk = k & 3;
           const uint64_t adesc = umma_smem_desc_sw128(q_addr + c * kBlockM * 128 + kk * 32, 16, 1024);
-          const uint64_t bdesc = umma_smem_desc_sw128(k_addr + c * BLOCK_N * 128 + kk * 32, 16, 1024);
-          umma_f16_ss(tmem_s, adesc, bdesc, idesc_s, k != 0 ? 1u : 0u);
+          const uint64_t bdesc = umma_smem_desc_sw128(k_addr + c * kBlockN * 128 + kk * 32, 16, 1024);
+          umma_f16_ss(tmem_s + static_cast<uint32_t>((j & 1) * kBlockN), adesc, bdesc, idesc_s, k != 0 ? 1u : 0u);
         }
-        umma_commit(s_full);
-        ok = mbar_wait(p_full, j & 1, abort_flag, p.status, kDevWaitOtherTimeout);
+        umma_commit(&s_full[j & 1]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      if (ok && n_blocks > 1) ok = issue_s(1);
+      for (int j = 0; ok && j < n_blocks; ++j) {
+        ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, abort_flag, p.status, kDevWaitOtherTimeout);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t p_addr = smem_u32(sP);
+        const int st = j % kKvStages;
+        const uint32_t p_addr = smem_u32(sP + (j & 1) * Cfg::kPBytes);
+        const uint32_t v_addr = smem_u32(sKV + st * 2 * Cfg::kKBytes + Cfg::kKBytes);
 #pragma unroll
-        for (int k = 0; k < BLOCK_N / 16; ++k) {
-          const int c = k >> 2, kk = k & 3;
-          const uint64_t adesc = umma_smem_desc_sw128(p_addr + c * kBlockM * 128 + kk * 32, 16, 1024);
-          // V tile rows are keys (128 B each): 16 keys per step = 2048 B; 64-wide d chunks are
-          // BLOCK_N*128 B apart (leading byte offset), 8-key groups 1024 B apart (stride byte offset)
-          const uint64_t bdesc = umma_smem_desc_sw128(v_addr + k * 2048, BLOCK_N * 128, 1024);
-          umma_f16_ss(tmem_t, adesc, bdesc, idesc_t, k != 0 ? 1u : 0u);
+        for (int k = 0; k < kBlockN / 16; ++k) {
+          const uint64_t adesc = umma_smem_desc_sw128(p_addr + k * 32, 16, 1024);
+          // V block rows are keys (128 B each): 16 keys per step = 2048 B; 64-wide d chunks are
+          // kBlockN*128 B apart (leading byte offset), 8-key groups 1024 B apart (stride byte offset)
+          const uint64_t bdesc = umma_smem_desc_sw128(v_addr + k * 2048, kBlockN * 128, 1024);
+          umma_f16_ss(tmem_t + static_cast<uint32_t>((j & 1) * Cfg::kTWidth), adesc, bdesc, idesc_t, k != 0 ? 1u : 0u);
         }
-        umma_commit(t_full);
+        umma_commit(&t_full[j & 1]);
         umma_commit(&kv_empty[st]);
+        if (j + 2 < n_blocks) ok = issue_s(j + 2);
       }
       if (!ok) {
         umma_commit(drain_bar);
@@ -201,107 +215,101 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
     float o[DCH * 64];
 #pragma unroll
     for (int i = 0; i < DCH * 64; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
     bool ok = true;
-    for (int j = 0; ok && j < n_blocks; ++j) {
-      ok = mbar_wait(s_full, j & 1, abort_flag, p.status, kDevWaitAccFullTimeout);
-      if (!ok) break;
+    // O = O * alpha + T(j)
+    auto fold_t = [&](int j, float alpha) -> bool {
+      if (!mbar_wait(&t_full[j & 1], (j >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout)) return false;
       tc_fence_after();
-      const int key0 = j * BLOCK_N;
-      int limit = kv_len - key0;  // keys [0, limit) of this block are valid
-      if (p.causal) limit = min(limit, q_idx - key0 + 1);
-      // A key block is "plain" when every key of it is visible to every row of this warp: then the two
-      // passes run without per-element masks (the common case; only the last block of a ragged or
-      // causal sequence needs them).
-      const int limit_min = __reduce_min_sync(0xffffffffu, limit);
-      const bool plain = limit_min >= BLOCK_N;
-      // pass 1: row maximum
-      float m_blk = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 32, v);
-        tmem_ld_wait();
-        if (plain) {
-          float m0 = __uint_as_float(v[0]), m1 = __uint_as_float(v[1]), m2 = __uint_as_float(v[2]),
-                m3 = __uint_as_float(v[3]);
-#pragma unroll
-          for (int i = 4; i < 32; i += 4) {
-            m0 = fmaxf(m0, __uint_as_float(v[i]));
-            m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
-            m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
-            m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
-          }
-          m_blk = fmaxf(m_blk, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < limit) m_blk = fmaxf(m_blk, __uint_as_float(v[i]));
-        }
-      }
-      const float m_new = fmaxf(m_run, m_blk * p.scale_log2);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);
-      // pass 2: p = exp2(s*scale - m), row sum, P -> swizzled smem
-      float l_blk = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 32, v);
-        tmem_ld_wait();
-        uint32_t packed[16];
-        if (plain) {
-          float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
-            const float p1 = exp2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
-            l0 += p0;
-            l1 += p1;
-            packed[i >> 1] = E::from_float2(p0, p1);
-          }
-          l_blk += l0 + l1;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 =
-                (c * 32 + i < limit) ? exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use)) : 0.f;
-            const float p1 =
-                (c * 32 + i + 1 < limit) ? exp2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use)) : 0.f;
-            l_blk += p0 + p1;
-            packed[i >> 1] = E::from_float2(p0, p1);
-          }
-        }
-        // keys c*32 .. c*32+31 live in 64-key chunk (c >> 1), 16-byte units (c & 1)*4 .. +3 of row r
-        uint8_t* row_base = sP + (c >> 1) * kBlockM * 128 + r * 128;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int unit = ((c & 1) * 4 + u) ^ (r & 7);
-          *reinterpret_cast<uint4*>(row_base + unit * 16) =
-              make_uint4(packed[u * 4], packed[u * 4 + 1], packed[u * 4 + 2], packed[u * 4 + 3]);
-        }
-      }
-      l_run = l_run * alpha + l_blk;
-      m_run = m_new;
-      tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(p_full);
-      // O = O * alpha + P V
-      ok = mbar_wait(t_full, j & 1, abort_flag, p.status, kDevWaitAccFullTimeout);
-      if (!ok) break;
-      tc_fence_after();
+      const uint32_t t_addr = tmem_t + lane_addr + static_cast<uint32_t>((j & 1) * Cfg::kTWidth);
 #pragma unroll
       for (int c = 0; c < DCH * 2; ++c) {
         if (c * 32 < p.Dv) {  // warp-uniform
           uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_t + lane_addr + c * 32, v);
+          tmem_ld_32x32b_x32(t_addr + c * 32, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(v[i]);
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(v[i]));
         }
       }
       tc_fence_before();
+      return true;
+    };
+    for (int j = 0; ok && j < n_blocks; ++j) {
+      ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t s_addr = tmem_s + lane_addr + static_cast<uint32_t>((j & 1) * kBlockN);
+      const int key0 = j * kBlockN;
+      int limit = kv_len - key0;  // keys [0, limit) of this block are visible to this row
+      if (p.causal) limit = min(limit, q_idx - key0 + 1);
+      // A key block is "plain" when every key of it is visible to every row of this warp: then both
+      // passes run without per-element masks (only the last block of a ragged or causal sequence
+      // needs them).
+      const bool plain = __reduce_min_sync(0xffffffffu, limit) >= kBlockN;
+      uint32_t s0[32], s1[32];
+      tmem_ld_32x32b_x32(s_addr, s0);
+      tmem_ld_32x32b_x32(s_addr + 32, s1);
+      tmem_ld_wait();
+      uint8_t* row_base = sP + (j & 1) * Cfg::kPBytes + r * 128;
+      float alpha, m_new, l0 = 0.f, l1 = 0.f;
+      // One body, compiled twice: kPlain drops every per-element mask.
+      auto softmax_block = [&](auto plain_tag) {
+        constexpr bool kPlain = decltype(plain_tag)::value;
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float a0 = __uint_as_float(s0[i]), a1 = __uint_as_float(s0[i + 1]);
+          const float b0 = __uint_as_float(s1[i]), b1 = __uint_as_float(s1[i + 1]);
+          m0 = fmaxf(m0, (kPlain || i < limit) ? a0 : -INFINITY);
+          m1 = fmaxf(m1, (kPlain || i + 1 < limit) ? a1 : -INFINITY);
+          m2 = fmaxf(m2, (kPlain || 32 + i < limit) ? b0 : -INFINITY);
+          m3 = fmaxf(m3, (kPlain || 33 + i < limit) ? b1 : -INFINITY);
+        }
+        const float m_blk = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        m_new = fmaxf(m_run, m_blk * p.scale_log2);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha = exp2f(m_run - m_use);
+        // p = exp2(s * scale - m), row sum, P -> swizzled shared memory (16-byte unit u of row r sits
+        // at unit u ^ (r & 7))
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t(&sv)[32] = h == 0 ? s0 : s1;
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = exp2f(fmaf(__uint_as_float(sv[i]), p.scale_log2, -m_use));
+            float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -m_use));
+            if (!kPlain) {
+              p0 = (h * 32 + i < limit) ? p0 : 0.f;
+              p1 = (h * 32 + i + 1 < limit) ? p1 : 0.f;
+            }
+            l0 += p0;
+            l1 += p1;
+            packed[i >> 1] = E::from_float2(p0, p1);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int unit = (h * 4 + u) ^ (r & 7);
+            *reinterpret_cast<uint4*>(row_base + unit * 16) =
+                make_uint4(packed[u * 4], packed[u * 4 + 1], packed[u * 4 + 2], packed[u * 4 + 3]);
+          }
+        }
+      };
+      if (plain)
+        softmax_block(std::true_type{});
+      else
+        softmax_block(std::false_type{});
+      l_run = l_run * alpha + (l0 + l1);
+      m_run = m_new;
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(&p_full[j & 1]);
+      // fold the previous block's P V into O while the tensor core works on this block's
+      if (j > 0) ok = fold_t(j - 1, alpha_prev);
+      alpha_prev = alpha;
     }
+    if (ok && n_blocks > 0) ok = fold_t(n_blocks - 1, alpha_prev);
     if (ok && q_idx < p.Sq) {
       const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
       const int b = bh / p.H, h = bh - b * p.H;
@@ -412,18 +420,18 @@ static CUtensorMap make_attn_map(const void* base, bool bf16, int d, int s, long
   return m;
 }
 
-template <int BLOCK_N, int DCH, bool BF16>
+template <int DCH, bool BF16>
 void launch_attn(const void* q, const void* k, const void* v, const AttnParams& p, cudaStream_t stream) {
-  using Cfg = AttnCfg<BLOCK_N, DCH>;
+  using Cfg = AttnCfg<DCH>;
   static std::atomic<uint64_t> configured{0};
-  opt_in_smem_once(configured, reinterpret_cast<const void*>(&attention_tc_kernel<BLOCK_N, DCH, BF16>), Cfg::kSmemBytes);
+  opt_in_smem_once(configured, reinterpret_cast<const void*>(&attention_tc_kernel<DCH, BF16>), Cfg::kSmemBytes);
   const long long bh = static_cast<long long>(p.B) * p.H;
   CUtensorMap tq = make_attn_map(q, BF16, p.D, p.Sq, bh, kBlockM);
-  CUtensorMap tk = make_attn_map(k, BF16, p.D, p.Skv, bh, BLOCK_N);
-  CUtensorMap tv = make_attn_map(v, BF16, p.Dv, p.Skv, bh, BLOCK_N);
+  CUtensorMap tk = make_attn_map(k, BF16, p.D, p.Skv, bh, kBlockN);
+  CUtensorMap tv = make_attn_map(v, BF16, p.Dv, p.Skv, bh, kBlockN);
   const long long grid = bh * p.q_blocks;
   B200AIT_REQUIRE(grid < (1ll << 31), "attention: grid too large");
-  attention_tc_kernel<BLOCK_N, DCH, BF16><<<static_cast<unsigned>(grid), kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, p);
+  attention_tc_kernel<DCH, BF16><<<static_cast<unsigned>(grid), kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, p);
   B200AIT_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -467,14 +475,14 @@ B200AIT_EXPORT int b200ait_mem_eff_attention(void* output, const void* query, co
       const bool two = head_size > 64 || head_size_v > 64;
       if (two) {
         if (bf16)
-          launch_attn<128, 2, true>(query, key, value, p, stream);
+          launch_attn<2, true>(query, key, value, p, stream);
         else
-          launch_attn<128, 2, false>(query, key, value, p, stream);
+          launch_attn<2, false>(query, key, value, p, stream);
       } else {
         if (bf16)
-          launch_attn<128, 1, true>(query, key, value, p, stream);
+          launch_attn<1, true>(query, key, value, p, stream);
         else
-          launch_attn<128, 1, false>(query, key, value, p, stream);
+          launch_attn<1, false>(query, key, value, p, stream);
       }
     } else {
       B200AIT_REQUIRE(head_size_v <= 256, "attention: head_size_v > 256 is not supported");
