@@ -18,6 +18,7 @@
 // Head dims that are not a multiple of 8, or larger than 128, run on a CUDA-core kernel.
 #include <cuda.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <type_traits>
@@ -37,6 +38,7 @@ EncodeTiledFn get_encode_fn();
 struct AttnParams {
   int B, H, Sq, Skv, D, Dv;
   int q_blocks;
+  int num_items;  // B * H * q_blocks work items of 128 query rows
   float scale_log2;  // softmax scale * log2(e)
   int causal;
   void* out;  // [B, Sq, H, Dv]
@@ -61,7 +63,10 @@ struct AttnCfg {
   static constexpr int kTmemCols = (DCH == 1) ? 256 : 512;       // S x2 (64 each) then T x2
 };
 
-// Pipeline (per CTA, key blocks j = 0 .. n-1, everything double-buffered on j & 1):
+// Persistent CTAs: each walks work items (one item = 128 query rows of one (batch, head)) with stride
+// gridDim.x, so barrier set-up, TMEM allocation and the load latency of the first tiles are paid once
+// and the next item's Q / K / V stream in while the current item drains.
+// Pipeline (key blocks numbered globally g = 0, 1, .. across items; everything double-buffered on g & 1):
 //   MMA warp:      S(0), S(1); then for each j: wait P(j) -> T(j) = P(j) V(j) -> S(j+2)
 //   softmax warps: wait S(j) -> max / exp2 / row sum -> P(j) -> signal; then fold T(j-1) into O
 // so the tensor core computes S(j+1), S(j+2) and T(j-1) while the softmax threads work on block j,
@@ -86,16 +91,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
   uint64_t* p_full = s_full + 2;            // [2]
   uint64_t* t_full = p_full + 2;            // [2]
   uint64_t* drain_bar = t_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  uint64_t* q_empty = drain_bar + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_blk = blockIdx.x % p.q_blocks;
-  const int bh = blockIdx.x / p.q_blocks;
-  const int q0 = q_blk * kBlockM;
-  int kv_len = p.Skv;
-  if (p.causal) kv_len = min(kv_len, q0 + kBlockM);
-  const int n_blocks = (kv_len + kBlockN - 1) / kBlockN;
+  // work item -> (batch*head index, first query row, visible key count, key blocks)
+  auto decode_item = [&](int item, int& bh, int& q0, int& kv_len, int& n_blocks) {
+    const int q_blk = item % p.q_blocks;
+    bh = item / p.q_blocks;
+    q0 = q_blk * kBlockM;
+    kv_len = p.Skv;
+    if (p.causal) kv_len = min(kv_len, q0 + kBlockM);
+    n_blocks = (kv_len + kBlockN - 1) / kBlockN;
+  };
   const int dsteps = (p.D + 15) / 16;  // k-steps of Q K^T
 
   if (threadIdx.x == 0) {
@@ -110,6 +119,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
       mbar_init(&t_full[i], 1);
     }
     mbar_init(drain_bar, 1);
+    mbar_init(q_empty, 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tma_q);
@@ -130,22 +140,31 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, Cfg::kQBytes);
-#pragma unroll
-      for (int c = 0; c < DCH; ++c) tma_load_3d(sQ + c * kBlockM * 128, &tma_q, q_full, c * 64, q0, bh);
       bool ok = true;
-      for (int j = 0; ok && j < n_blocks; ++j) {
-        const int st = j % kKvStages;
-        const uint32_t ph = (j / kKvStages) & 1;
-        ok = mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
+      int g = 0;  // global key-block counter (K/V ring position)
+      int it = 0;
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++it) {
+        int bh, q0, kv_len, n_blocks;
+        decode_item(item, bh, q0, kv_len, n_blocks);
+        // the Q tile is free once the previous item's last S = Q K^T has completed
+        ok = mbar_wait(q_empty, (it & 1) ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
         if (!ok) break;
-        uint8_t* sK = sKV + st * 2 * Cfg::kKBytes;
-        uint8_t* sV = sK + Cfg::kKBytes;
-        mbar_arrive_expect_tx(&kv_full[st], 2 * Cfg::kKBytes);
+        mbar_arrive_expect_tx(q_full, Cfg::kQBytes);
 #pragma unroll
-        for (int c = 0; c < DCH; ++c) {
-          tma_load_3d(sK + c * kBlockN * 128, &tma_k, &kv_full[st], c * 64, j * kBlockN, bh);
-          tma_load_3d(sV + c * kBlockN * 128, &tma_v, &kv_full[st], c * 64, j * kBlockN, bh);
+        for (int c = 0; c < DCH; ++c) tma_load_3d(sQ + c * kBlockM * 128, &tma_q, q_full, c * 64, q0, bh);
+        for (int j = 0; j < n_blocks; ++j, ++g) {
+          const int st = g % kKvStages;
+          const uint32_t ph = (g / kKvStages) & 1;
+          ok = mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
+          if (!ok) break;
+          uint8_t* sK = sKV + st * 2 * Cfg::kKBytes;
+          uint8_t* sV = sK + Cfg::kKBytes;
+          mbar_arrive_expect_tx(&kv_full[st], 2 * Cfg::kKBytes);
+#pragma unroll
+          for (int c = 0; c < DCH; ++c) {
+            tma_load_3d(sK + c * kBlockN * 128, &tma_k, &kv_full[st], c * 64, j * kBlockN, bh);
+            tma_load_3d(sV + c * kBlockN * 128, &tma_v, &kv_full[st], c * 64, j * kBlockN, bh);
+          }
         }
       }
       if (!ok) {
@@ -160,42 +179,55 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
       constexpr uint32_t idesc_s = umma_idesc_f16(kBlockM, kBlockN, BF16, false, false);
       constexpr uint32_t idesc_t = umma_idesc_f16(kBlockM, Cfg::kTWidth, BF16, false, true);  // V is MN-major
       const uint32_t q_addr = smem_u32(sQ);
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kDevWaitFullTimeout);
-      // S(j) = Q K(j)^T into S buffer j & 1
-      auto issue_s = [&](int j) -> bool {
-        const int st = j % kKvStages;
-        if (!mbar_wait(&kv_full[st], (j / kKvStages) & 1, abort_flag, p.status, kDevWaitFullTimeout)) return false;
+      bool ok = true;
+      // S(g) = Q K(g)^T into S buffer g & 1 (g = global key-block index)
+      auto issue_s = [&](int g) -> bool {
+        const int st = g % kKvStages;
+        if (!mbar_wait(&kv_full[st], (g / kKvStages) & 1, abort_flag, p.status, kDevWaitFullTimeout)) return false;
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sKV + st * 2 * Cfg::kKBytes);
         for (int k = 0; k < dsteps; ++k) {
           const int c = k >> 2, kk = k & 3;
           const uint64_t adesc = umma_smem_desc_sw128(q_addr + c * kBlockM * 128 + kk * 32, 16, 1024);
           const uint64_t bdesc = umma_smem_desc_sw128(k_addr + c * kBlockN * 128 + kk * 32, 16, 1024);
-          umma_f16_ss(tmem_s + static_cast<uint32_t>((j & 1) * kBlockN), adesc, bdesc, idesc_s, k != 0 ? 1u : 0u);
+          umma_f16_ss(tmem_s + static_cast<uint32_t>((g & 1) * kBlockN), adesc, bdesc, idesc_s, k != 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[j & 1]);
+        umma_commit(&s_full[g & 1]);
         return true;
       };
-      if (ok) ok = issue_s(0);
-      if (ok && n_blocks > 1) ok = issue_s(1);
-      for (int j = 0; ok && j < n_blocks; ++j) {
-        ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, abort_flag, p.status, kDevWaitOtherTimeout);
-        if (!ok) break;
-        tc_fence_after();
-        const int st = j % kKvStages;
-        const uint32_t p_addr = smem_u32(sP + (j & 1) * Cfg::kPBytes);
-        const uint32_t v_addr = smem_u32(sKV + st * 2 * Cfg::kKBytes + Cfg::kKBytes);
+      int gb = 0;  // global index of the item's first key block
+      int it = 0;
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++it) {
+        int bh, q0, kv_len, n_blocks;
+        decode_item(item, bh, q0, kv_len, n_blocks);
+        ok = mbar_wait(q_full, it & 1, abort_flag, p.status, kDevWaitFullTimeout);
+        if (ok) ok = issue_s(gb);
+        if (ok && n_blocks > 1) ok = issue_s(gb + 1);
+        if (ok && n_blocks <= 2) umma_commit(q_empty);  // every S of this item has been issued
+        for (int j = 0; ok && j < n_blocks; ++j) {
+          const int g = gb + j;
+          ok = mbar_wait(&p_full[g & 1], (g >> 1) & 1, abort_flag, p.status, kDevWaitOtherTimeout);
+          if (!ok) break;
+          tc_fence_after();
+          const int st = g % kKvStages;
+          const uint32_t p_addr = smem_u32(sP + (g & 1) * Cfg::kPBytes);
+          const uint32_t v_addr = smem_u32(sKV + st * 2 * Cfg::kKBytes + Cfg::kKBytes);
 #pragma unroll
-        for (int k = 0; k < kBlockN / 16; ++k) {
-          const uint64_t adesc = umma_smem_desc_sw128(p_addr + k * 32, 16, 1024);
-          // V block rows are keys (128 B each): 16 keys per step = 2048 B; 64-wide d chunks are
-          // kBlockN*128 B apart (leading byte offset), 8-key groups 1024 B apart (stride byte offset)
-          const uint64_t bdesc = umma_smem_desc_sw128(v_addr + k * 2048, kBlockN * 128, 1024);
-          umma_f16_ss(tmem_t + static_cast<uint32_t>((j & 1) * Cfg::kTWidth), adesc, bdesc, idesc_t, k != 0 ? 1u : 0u);
+          for (int k = 0; k < kBlockN / 16; ++k) {
+            const uint64_t adesc = umma_smem_desc_sw128(p_addr + k * 32, 16, 1024);
+            // V block rows are keys (128 B each): 16 keys per step = 2048 B; 64-wide d chunks are
+            // kBlockN*128 B apart (leading byte offset), 8-key groups 1024 B apart (stride byte offset)
+            const uint64_t bdesc = umma_smem_desc_sw128(v_addr + k * 2048, kBlockN * 128, 1024);
+            umma_f16_ss(tmem_t + static_cast<uint32_t>((g & 1) * Cfg::kTWidth), adesc, bdesc, idesc_t, k != 0 ? 1u : 0u);
+          }
+          umma_commit(&t_full[g & 1]);
+          umma_commit(&kv_empty[st]);
+          if (j + 2 < n_blocks) {
+            ok = issue_s(g + 2);
+            if (ok && j + 3 == n_blocks) umma_commit(q_empty);
+          }
         }
-        umma_commit(&t_full[j & 1]);
-        umma_commit(&kv_empty[st]);
-        if (j + 2 < n_blocks) ok = issue_s(j + 2);
+        gb += n_blocks;
       }
       if (!ok) {
         umma_commit(drain_bar);
@@ -210,18 +242,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
     using T = typename E::T;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;  // row inside the tile == TMEM lane
-    const int q_idx = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float o[DCH * 64];
-#pragma unroll
-    for (int i = 0; i < DCH * 64; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
     bool ok = true;
-    // O = O * alpha + T(j)
-    auto fold_t = [&](int j, float alpha) -> bool {
-      if (!mbar_wait(&t_full[j & 1], (j >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout)) return false;
+    // O = O * alpha + T(g)
+    auto fold_t = [&](int g, float alpha) -> bool {
+      if (!mbar_wait(&t_full[g & 1], (g >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout)) return false;
       tc_fence_after();
-      const uint32_t t_addr = tmem_t + lane_addr + static_cast<uint32_t>((j & 1) * Cfg::kTWidth);
+      const uint32_t t_addr = tmem_t + lane_addr + static_cast<uint32_t>((g & 1) * Cfg::kTWidth);
 #pragma unroll
       for (int c = 0; c < DCH * 2; ++c) {
         if (c * 32 < p.Dv) {  // warp-uniform
@@ -235,11 +263,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
       tc_fence_before();
       return true;
     };
-    for (int j = 0; ok && j < n_blocks; ++j) {
-      ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t s_addr = tmem_s + lane_addr + static_cast<uint32_t>((j & 1) * kBlockN);
+    int gb = 0;  // global index of the item's first key block
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      int bh, q0, kv_len, n_blocks;
+      decode_item(item, bh, q0, kv_len, n_blocks);
+      const int q_idx = q0 + r;
+#pragma unroll
+      for (int i = 0; i < DCH * 64; ++i) o[i] = 0.f;
+      float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+      for (int j = 0; ok && j < n_blocks; ++j) {
+        const int g = gb + j;
+        ok = mbar_wait(&s_full[g & 1], (g >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t s_addr = tmem_s + lane_addr + static_cast<uint32_t>((g & 1) * kBlockN);
       const int key0 = j * kBlockN;
       int limit = kv_len - key0;  // keys [0, limit) of this block are visible to this row
       if (p.causal) limit = min(limit, q_idx - key0 + 1);
@@ -251,7 +288,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
       tmem_ld_32x32b_x32(s_addr, s0);
       tmem_ld_32x32b_x32(s_addr + 32, s1);
       tmem_ld_wait();
-      uint8_t* row_base = sP + (j & 1) * Cfg::kPBytes + r * 128;
+      uint8_t* row_base = sP + (g & 1) * Cfg::kPBytes + r * 128;
       float alpha, m_new, l0 = 0.f, l1 = 0.f;
       // One body, compiled twice: kPlain drops every per-element mask.
       auto softmax_block = [&](auto plain_tag) {
@@ -304,23 +341,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
       m_run = m_new;
       tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(&p_full[j & 1]);
+      mbar_arrive(&p_full[g & 1]);
       // fold the previous block's P V into O while the tensor core works on this block's
-      if (j > 0) ok = fold_t(j - 1, alpha_prev);
-      alpha_prev = alpha;
-    }
-    if (ok && n_blocks > 0) ok = fold_t(n_blocks - 1, alpha_prev);
-    if (ok && q_idx < p.Sq) {
-      const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
-      const int b = bh / p.H, h = bh - b * p.H;
-      T* out = static_cast<T*>(p.out) + ((static_cast<long long>(b) * p.Sq + q_idx) * p.H + h) * p.Dv;
+        if (j > 0) ok = fold_t(g - 1, alpha_prev);
+        alpha_prev = alpha;
+      }
+      if (ok) ok = fold_t(gb + n_blocks - 1, alpha_prev);
+      gb += n_blocks;
+      if (ok && q_idx < p.Sq) {
+        const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
+        const int b = bh / p.H, h = bh - b * p.H;
+        T* out = static_cast<T*>(p.out) + ((static_cast<long long>(b) * p.Sq + q_idx) * p.H + h) * p.Dv;
 #pragma unroll
-      for (int c = 0; c < DCH * 8; ++c) {
-        if (c * 8 < p.Dv) {
-          float f[8];
+        for (int c = 0; c < DCH * 8; ++c) {
+          if (c * 8 < p.Dv) {
+            float f[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = o[c * 8 + i] * inv;
-          *reinterpret_cast<uint4*>(out + c * 8) = pack8<BF16>(f);
+            for (int i = 0; i < 8; ++i) f[i] = o[c * 8 + i] * inv;
+            *reinterpret_cast<uint4*>(out + c * 8) = pack8<BF16>(f);
+          }
         }
       }
     }
@@ -429,9 +468,12 @@ void launch_attn(const void* q, const void* k, const void* v, const AttnParams& 
   CUtensorMap tq = make_attn_map(q, BF16, p.D, p.Sq, bh, kBlockM);
   CUtensorMap tk = make_attn_map(k, BF16, p.D, p.Skv, bh, kBlockN);
   CUtensorMap tv = make_attn_map(v, BF16, p.Dv, p.Skv, bh, kBlockN);
-  const long long grid = bh * p.q_blocks;
-  B200AIT_REQUIRE(grid < (1ll << 31), "attention: grid too large");
-  attention_tc_kernel<DCH, BF16><<<static_cast<unsigned>(grid), kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, p);
+  const long long items = bh * p.q_blocks;
+  B200AIT_REQUIRE(items < (1ll << 31), "attention: too many work items");
+  AttnParams pp = p;
+  pp.num_items = static_cast<int>(items);
+  const long long grid = std::min<long long>(items, static_cast<long long>(sm_count()) * (DCH == 1 ? 2 : 1));
+  attention_tc_kernel<DCH, BF16><<<static_cast<unsigned>(grid), kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, pp);
   B200AIT_CUDA_CHECK(cudaGetLastError());
 }
 
