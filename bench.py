@@ -157,7 +157,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     x_cpu, params = workloads.bert_layer_inputs(BATCH, SEQ, HIDDEN, FFN, seed=1334 + rank)
     _, y = workloads.build_bert_layer(BATCH, SEQ, HIDDEN, HEADS, FFN)
     workdir = tempfile.mkdtemp(prefix=f"b200ait_bench_r{rank}_")
-    model = compile_model(y, detect_target(), workdir, "bert_layer")
+    model = compile_model(y, detect_target(), workdir, "bert_layer", num_runtimes=2)
     dev_params = {name: params[key].cuda() for name, key in workloads.BERT_PARAM_NAMES.items()}
     model.set_many_constants_with_tensors(dev_params)
     # device-resident inputs: rotate through several buffers so a step never finds its input in L2
@@ -200,23 +200,52 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         total_ms = float(t.item())
     value = world * BATCH * args.steps / (total_ms / 1000.0)
 
-    # ---- end to end through the public API: pinned host input -> device, run, output -> pinned host
-    x_pin = x_cpu.pin_memory()
-    y_pin = torch.empty((BATCH, SEQ, HIDDEN), dtype=torch.float16).pin_memory()
-    x_dev = torch.empty_like(xs[0])
+    # ---- end to end through the public API: every step copies its input from pinned host memory to the
+    # device, runs Model.run_with_tensors and copies the output back to pinned host memory. The three
+    # stages run on three streams over a ring of NB device buffers, so step i+1's upload and step i-1's
+    # download overlap step i's kernels; all of it is inside the timed region.
+    NB = 3
+    x_pins = [x_cpu.pin_memory() for _ in range(2)]
+    y_pins = [torch.empty((BATCH, SEQ, HIDDEN), dtype=torch.float16).pin_memory() for _ in range(NB)]
+    x_devs = [torch.empty_like(xs[0]) for _ in range(NB)]
+    y_devs = [torch.empty_like(out) for _ in range(NB)]
+    s_h2d, s_run, s_d2h = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_h2d = [torch.cuda.Event() for _ in range(NB)]
+    ev_run = [torch.cuda.Event() for _ in range(NB)]
+    ev_d2h = [torch.cuda.Event() for _ in range(NB)]
 
-    def e2e_step():
-        x_dev.copy_(x_pin, non_blocking=True)
-        model.run_with_tensors({"hidden_states": x_dev}, {"output_0": out}, sync=False, graph_mode=True)
-        y_pin.copy_(out, non_blocking=True)
+    def e2e_step(i: int):
+        k = i % NB
+        with torch.cuda.stream(s_h2d):
+            s_h2d.wait_event(ev_run[k])  # the run that last read this input buffer
+            x_devs[k].copy_(x_pins[i % 2], non_blocking=True)
+            ev_h2d[k].record(s_h2d)
+        with torch.cuda.stream(s_run):
+            s_run.wait_event(ev_h2d[k])
+            s_run.wait_event(ev_d2h[k])  # the download that last read this output buffer
+            model.run_with_tensors({"hidden_states": x_devs[k]}, {"output_0": y_devs[k]},
+                                   stream_ptr=s_run.cuda_stream, sync=False, graph_mode=True)
+            ev_run[k].record(s_run)
+        with torch.cuda.stream(s_d2h):
+            s_d2h.wait_event(ev_run[k])
+            y_pins[k].copy_(y_devs[k], non_blocking=True)
+            ev_d2h[k].record(s_d2h)
 
-    for _ in range(3):
-        e2e_step()
+    def e2e_join():
+        for st in (s_h2d, s_run, s_d2h):
+            stream.wait_stream(st)
+
+    for i in range(2 * NB):
+        e2e_step(i)
+    e2e_join()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for _ in range(args.steps):
-        e2e_step()
+    for st in (s_h2d, s_run, s_d2h):
+        st.wait_event(e0)
+    for i in range(args.steps):
+        e2e_step(i)
+    e2e_join()
     e1.record(stream)
     barrier()
     e2e_ms = e0.elapsed_time(e1)
@@ -224,6 +253,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
+    y_pin = y_pins[(args.steps - 1) % NB]
+    x_pin = x_pins[0]
     e2e_value = world * BATCH * args.steps / (e2e_ms / 1000.0)
     checksum = float(y_pin.float().abs().mean())
 
@@ -263,6 +294,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                              "sample": f"8 of {BATCH} sequences x {runs} runs, fp32 torch oracle, all host threads"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_pin.numel() * 2,
                     "d2h_bytes_per_step": y_pin.numel() * 2, "ms_per_step": e2e_ms / args.steps,
+                    "pipeline": "3 streams (upload / run / download), ring of 3 device buffers",
                     "output_abs_mean": checksum},
             "gpu_launches": 7 * args.steps,
             "clocks": clocks,
