@@ -307,16 +307,104 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         print(json.dumps(line), flush=True)
 
 
+def run_ops_suite(args) -> None:
+    """Per-op sweep over the BASELINE configurations: one JSON line per op (not the driver's contract line)."""
+    import torch
+
+    from aitemplate_b200.testing import benchmark_ops
+
+    torch.cuda.set_device(0)
+    peaks = _peaks()
+    for row in benchmark_ops.run_suite(peaks):
+        print(json.dumps(row), flush=True)
+
+
+def run_nsplit_suite(args, rank: int, world: int, local_rank: int) -> None:
+    """BASELINE config 5 at M = 65536, N = K = 8192 on `world` GPUs, two partitionings:
+    M-sharded (rows split, no collective) and N-split (weight rows split, X replicated, one NCCL
+    all-gather of the output column shards + re-layout). Rank 0 prints one JSON line."""
+    import torch
+    import torch.distributed as dist
+
+    from aitemplate_b200 import kernels as K
+    from aitemplate_b200 import sharding
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    m, n, k = 65536, 8192, 8192
+    g = torch.Generator(device="cuda").manual_seed(500 + rank)
+    w = (torch.randn((n, k), generator=g, device="cuda") * 0.01).half()
+    b = (torch.randn((n,), generator=g, device="cuda") * 0.01).half()
+    start, stop = sharding.shard_range(m, world, rank)
+    x_rows = (torch.rand((stop - start, k), generator=g, device="cuda") * 2 - 1).half()
+    y_rows = torch.empty((stop - start, n), dtype=torch.float16, device="cuda")
+    w_r, b_r = sharding.split_weight_columns(w, b, world, rank)
+    x_full = (torch.rand((m, k), generator=g, device="cuda") * 2 - 1).half()
+    y_cols = torch.empty((m, n // world), dtype=torch.float16, device="cuda")
+    gathered = torch.empty((world * m, n // world), dtype=torch.float16, device="cuda")
+
+    def timed(fn, iters):
+        for _ in range(2):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        if world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    iters = max(args.steps // 5, 3)
+    ms_m = timed(lambda: K.gemm_rcr(x_rows, w, b, epilogue="relu", out=y_rows), iters)
+    ms_gemm = timed(lambda: K.gemm_rcr(x_full, w_r, b_r, epilogue="relu", out=y_cols), iters)
+    if world > 1:
+        ms_gather = timed(lambda: sharding.gather_columns(y_cols, world, gathered=gathered), iters)
+        ms_total = timed(lambda: sharding.gather_columns(
+            K.gemm_rcr(x_full, w_r, b_r, epilogue="relu", out=y_cols), world, gathered=gathered), iters)
+    else:
+        ms_gather, ms_total = 0.0, ms_gemm
+    flops = 2.0 * m * n * k
+    if rank == 0:
+        print(json.dumps({
+            "suite": "nsplit", "workload": "gemm_rcr_bias_relu M=65536 N=K=8192 fp16", "n_gpus": world,
+            "m_sharded": {"ms": ms_m, "tflops_total": flops / (ms_m / 1e3) / 1e12, "collective": None},
+            "n_split": {"gemm_ms": ms_gemm, "all_gather_relayout_ms": ms_gather, "total_ms": ms_total,
+                        "tflops_total": flops / (ms_total / 1e3) / 1e12,
+                        "gathered_bytes_per_rank": (world - 1) * m * (n // world) * 2, "collective": "ncclAllGather"},
+        }), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--suite", choices=["layer", "ops", "nsplit"], default="layer",
+                    help="layer: the contract benchmark (default); ops: per-op sweep; nsplit: config 5 on N GPUs")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.suite == "ops":
+        if rank == 0:
+            run_ops_suite(args)
+        return
+    if args.suite == "nsplit":
+        run_nsplit_suite(args, rank, world, local_rank)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
     else:
