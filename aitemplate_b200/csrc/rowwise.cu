@@ -61,7 +61,7 @@ struct LayerNormParams {
 };
 
 template <int VPL, bool BF16>
-__global__ void __launch_bounds__(256) layernorm_warp_kernel(const LayerNormParams p) {
+__global__ void __launch_bounds__(256, (VPL >= 12) ? 2 : 1) layernorm_warp_kernel(const LayerNormParams p) {
   const int lane = threadIdx.x & 31;
   const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= p.m) return;
@@ -74,13 +74,15 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const LayerNormPara
     const int v = lane + 32 * i;
     raw[i] = (v < nvec) ? ld_stream(xin + v) : make_uint4(0, 0, 0, 0);
   }
-  float f[VPL][8];
+  // Only the packed row stays in registers (VPL x 16 bytes per lane); each pass unpacks on the fly,
+  // which keeps wide rows (N = 4096: 16 vectors per lane) at full occupancy.
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    unpack8<BF16>(raw[i], f[i]);
+    float f[8];
+    unpack8<BF16>(raw[i], f);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) s += f[i][j];
+    for (int j = 0; j < 8; ++j) s += f[j];
   }
   const float inv_n = 1.f / static_cast<float>(p.n);
   const float mean = warp_sum(s) * inv_n;
@@ -88,9 +90,11 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const LayerNormPara
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     if (lane + 32 * i < nvec) {
+      float f[8];
+      unpack8<BF16>(raw[i], f);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float d = f[i][j] - mean;
+        const float d = f[j] - mean;
         q += d * d;
       }
     }
@@ -103,7 +107,8 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const LayerNormPara
   for (int i = 0; i < VPL; ++i) {
     const int v = lane + 32 * i;
     if (v < nvec) {
-      float g[8], b[8], o[8];
+      float f[8], g[8], b[8], o[8];
+      unpack8<BF16>(raw[i], f);
       if (g4) {
         unpack8<BF16>(__ldg(g4 + v), g);
       } else {
@@ -117,7 +122,7 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const LayerNormPara
         for (int j = 0; j < 8; ++j) b[j] = 0.f;
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = (f[i][j] - mean) * rstd * g[j] + b[j];
+      for (int j = 0; j < 8; ++j) o[j] = (f[j] - mean) * rstd * g[j] + b[j];
       st_stream(yout + v, pack8<BF16>(o));
     }
   }
@@ -210,14 +215,15 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SoftmaxParams p
     raw[i] = (v < nvec) ? ld_stream(xin + v) : make_uint4(0, 0, 0, 0);
   }
   constexpr float kLog2e = 1.4426950408889634f;
-  float f[VPL][8];
+  // Only the packed row stays in registers; exp2 is evaluated once for the sum and once for the output.
   float mx = -INFINITY;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    unpack8<BF16>(raw[i], f[i]);
     if (lane + 32 * i < nvec) {
+      float f[8];
+      unpack8<BF16>(raw[i], f);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[i][j]);
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);
     }
   }
   mx = warp_max(mx);
@@ -226,11 +232,10 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SoftmaxParams p
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     if (lane + 32 * i < nvec) {
+      float f[8];
+      unpack8<BF16>(raw[i], f);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        f[i][j] = exp2f(f[i][j] * kLog2e - mb);
-        s += f[i][j];
-      }
+      for (int j = 0; j < 8; ++j) s += exp2f(f[j] * kLog2e - mb);
     }
   }
   const float inv = 1.f / warp_sum(s);
@@ -239,9 +244,10 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SoftmaxParams p
   for (int i = 0; i < VPL; ++i) {
     const int v = lane + 32 * i;
     if (v < nvec) {
-      float o[8];
+      float f[8], o[8];
+      unpack8<BF16>(raw[i], f);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = f[i][j] * inv;
+      for (int j = 0; j < 8; ++j) o[j] = exp2f(f[j] * kLog2e - mb) * inv;
       st_stream(yout + v, pack8<BF16>(o));
     }
   }
