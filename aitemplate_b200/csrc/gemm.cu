@@ -186,6 +186,8 @@ struct GemmArgs {
   int* status = nullptr;  // device status word to use instead of the library's allocated one
 };
 
+constexpr int kTilePair = 512;  // tile_n value that asks for 256 x 256 tiles on CTA pairs
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int choose_tile_n(long long m, long long n, long long batch) {
@@ -299,17 +301,24 @@ void gemm_run(const GemmArgs& g) {
     return;
   }
 
-  B200AIT_REQUIRE(g.tile_n == 0 || g.tile_n == 64 || g.tile_n == 128 || g.tile_n == 256,
-                  "gemm: tile_n must be 64, 128 or 256");
+  B200AIT_REQUIRE(g.tile_n == 0 || g.tile_n == 64 || g.tile_n == 128 || g.tile_n == 256 || g.tile_n == kTilePair,
+                  "gemm: tile_n must be 64, 128, 256 or 512 (256 x 256 tiles on CTA pairs)");
   const bool ws_ok = g.workspace != nullptr && aligned16(g.workspace);
-  const SplitPlan sp = plan_split_k(g.batch, g.m, g.n, g.k, g.tile_n, g.split_k, ws_ok ? g.workspace_bytes : 0);
+  const bool force_pair = g.tile_n == kTilePair;
+  const SplitPlan sp = force_pair ? SplitPlan{256, 1, static_cast<int>((g.k + kBK - 1) / kBK), 0}
+                                  : plan_split_k(g.batch, g.m, g.n, g.k, g.tile_n, g.split_k,
+                                                 ws_ok ? g.workspace_bytes : 0);
   const int bn = sp.tile_n;
+  // CTA pairs (256 x 256 tiles, cta_group::2): a third less operand traffic per flop into each SM. Chosen
+  // when the 256-wide tile was picked automatically and the 256-row tiles still fill every pair once.
+  const long long pair_tiles = ((g.m + 2 * kBM - 1) / (2 * kBM)) * ((g.n + 255) / 256) * g.batch;
+  const bool pair = force_pair || (g.tile_n == 0 && bn == 256 && sp.splits == 1 && pair_tiles >= sm_count() / 2);
   p.splits = sp.splits;
   p.kb_per_split = sp.kb_per_split;
   p.partial = static_cast<float*>(g.workspace);
   const long long a_batch = p.a_batch_mul ? g.batch : 1, b_batch = p.b_batch_mul ? g.batch : 1;
   CUtensorMap ta = make_tile_map(g.a, bf16, g.k, g.m, a_batch, g.lda, g.a_bs, kBM);
-  CUtensorMap tb = make_tile_map(g.b, bf16, g.k, g.n, b_batch, g.ldb, g.b_bs, bn);
+  CUtensorMap tb = make_tile_map(g.b, bf16, g.k, g.n, b_batch, g.ldb, g.b_bs, pair ? bn / 2 : bn);
   // Staged TMA store: row-major output with 16-byte aligned rows, or a permuted output whose 64-column
   // groups and 32-row groups each stay inside one contiguous run of the destination.
   CUtensorMap tout = ta;
@@ -330,12 +339,21 @@ void gemm_run(const GemmArgs& g) {
       p.tma_store = 1;
     }
   }
-  p.tiles_m = (p.M + kBM - 1) / kBM;
+  p.tiles_m = pair ? (p.M + 2 * kBM - 1) / (2 * kBM) : (p.M + kBM - 1) / kBM;
   p.tiles_n = (p.N + bn - 1) / bn;
   p.num_tiles = p.tiles_m * p.tiles_n * p.batch;
   p.num_units = p.num_tiles * p.splits;
-  const int grid = std::min(p.num_units, sm_count());
-  if (bn == 256)
+  const int grid = pair ? 2 * std::min(p.num_units, sm_count() / 2) : std::min(p.num_units, sm_count());
+  CUtensorMap td0 = ta;
+  p.tma_d0 = 0;
+  if (pair && p.tma_store && b1 != kBinaryNone && b2 == kBinaryNone) {
+    // residual boxes of 32 rows x 64 columns, fetched by the epilogue warps into their staging buffers
+    td0 = make_tile_map(g.d0, bf16, g.n, g.m, g.batch, g.ldd, g.d_bs, 32);
+    p.tma_d0 = 1;
+  }
+  if (pair)
+    launch_tc_pair256(bf16, ta, tb, tout, td0, p, grid, g.stream);
+  else if (bn == 256)
     launch_tc_width<256>(bf16, ta, tb, tout, p, grid, g.stream);
   else if (bn == 128)
     launch_tc_width<128>(bf16, ta, tb, tout, p, grid, g.stream);
@@ -384,7 +402,7 @@ B200AIT_EXPORT int b200ait_gemm_rcr_workspace_bytes(int64_t batch, int64_t m, in
     B200AIT_REQUIRE(bytes_out, "bytes_out is null");
     *bytes_out = 0;
     if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) return;
-    *bytes_out = plan_split_k(batch, m, n, k, tile_n, split_k, (1ll << 62)).bytes;
+    *bytes_out = tile_n == kTilePair ? 0 : plan_split_k(batch, m, n, k, tile_n, split_k, (1ll << 62)).bytes;
   });
 }
 

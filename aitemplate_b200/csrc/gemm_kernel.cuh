@@ -34,6 +34,7 @@ struct GemmParams {
   long long rs_hi, rs_lo, cs2, cs3;
   int vec_ok;  // 16-byte epilogue accesses are legal
   int tma_store;  // output goes through shared memory + TMA store (tensor map `tma_out`)
+  int tma_d0;     // the residual d0 arrives by TMA in the output staging boxes (tensor map `tma_d0`)
   int* status;
 };
 
@@ -43,15 +44,30 @@ constexpr int kGroupM = 8;
 constexpr int kEpiWarps = 8;                      // two per TMEM lane quarter, each takes half of the columns
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;  // producer warp + MMA warp + epilogue warps
 
-template <int BN>
+// PAIR: two CTAs of a cluster compute one 256 x BN tile with cta_group::2 MMAs. Each CTA loads its own 128
+// rows of A and its own half (BN / 2 rows) of B, so a CTA moves 2/3 of the bytes per flop of the
+// single-CTA 128 x 256 tile, and keeps its own 128 x BN half of the accumulator.
+// D0BOX: the residual operand d0 is fetched by TMA into the output staging boxes (two boxes per epilogue
+// warp, one ring stage fewer) and combined in place, instead of per-thread global loads.
+template <int BN, bool PAIR = false, bool D0BOX = false>
 struct TileCfg {
-  static constexpr int kStageBytes = kBM * kBK * 2 + BN * kBK * 2;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+  static_assert(!D0BOX || PAIR, "staged residual boxes are only built for the CTA-pair tile");
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;  // B rows this CTA loads per stage
+  static constexpr int kStageBytes = kBM * kBK * 2 + kBRows * kBK * 2;
+  static constexpr int kStages = PAIR ? (D0BOX ? 5 : 6) : (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators
-  static constexpr int kStagingBytes = (BN >= 128) ? kEpiWarps * 4096 : 0;  // per-warp 32x64 output boxes
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 256 /*barriers*/ +
+  static constexpr int kBoxesPerWarp = D0BOX ? 2 : 1;  // 32 rows x 64 columns x 16 bit = 4 KB each
+  static constexpr int kStagingBytes = (BN >= 128) ? kEpiWarps * kBoxesPerWarp * 4096 : 0;
+  static constexpr int kBarrierBytes = 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes +
                                     2 * BN * 4 /*bias tile, fp32, one per accumulator*/;
 };
+
+// whether the compile-time epilogue code EPI takes its residual through staged boxes
+template <int EPI, bool PAIR>
+__host__ __device__ constexpr bool d0_box_of() {
+  return PAIR && EPI >= 0 && epi_b1(EPI) != kBinaryNone && epi_b2(EPI) == kBinaryNone;
+}
 
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int& b, int& m_blk, int& n_blk) {
   const int per_batch = p.tiles_m * p.tiles_n;
@@ -250,29 +266,38 @@ __device__ __forceinline__ void epilogue_direct_store32(const GemmParams& p, con
   }
 }
 
-template <int BN, bool BF16, int EPI>
+template <int BN, bool BF16, int EPI, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const __grid_constant__ CUtensorMap tma_out, const GemmParams p) {
-  using Cfg = TileCfg<BN>;
+               const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_d0,
+               const GemmParams p) {
+  constexpr bool D0BOX = d0_box_of<EPI, PAIR>();
+  using Cfg = TileCfg<BN, PAIR, D0BOX>;
   constexpr int kStages = Cfg::kStages;
   constexpr uint32_t kABytes = kBM * kBK * 2;
   constexpr uint32_t kStageBytes = Cfg::kStageBytes;
 
   extern __shared__ __align__(1024) uint8_t smem[];
-  if ((smem_u32(smem) & 1023u) != 0u) {  // swizzled tiles need 1024-byte alignment
-    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevBadSmemAlignment);
-    return;
-  }
+  // Swizzled tiles need 1024-byte alignment. A misaligned CTA does no work but still walks through every
+  // CTA-wide and cluster-wide barrier below.
+  const bool misaligned = (smem_u32(smem) & 1023u) != 0u;
+  if (misaligned && threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevBadSmemAlignment);
+  const int num_units = misaligned ? 0 : p.num_units;
+  // Work distribution: a single CTA, or a pair of CTAs (cluster ranks 0 and 1), walks the units.
+  const int pair_rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
+  const int walker = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+  const int num_walkers = PAIR ? (gridDim.x >> 1) : gridDim.x;
   uint8_t* staging = smem + kStages * kStageBytes;  // [kEpiWarps][32 rows][128 B], 128-byte swizzled
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + Cfg::kStagingBytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* acc_full = empty_bar + kStages;
   uint64_t* acc_empty = acc_full + 2;
   uint64_t* drain_bar = acc_empty + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  uint64_t* d0_bar = drain_bar + 1;  // [kEpiWarps][2]: a residual box has landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d0_bar + 2 * kEpiWarps);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* sbias = reinterpret_cast<float*>(staging + Cfg::kStagingBytes + 256);  // [2][BN]
+  static_assert((2 * kStages + 5 + 2 * kEpiWarps) * 8 + 8 <= Cfg::kBarrierBytes, "barrier area too small");
+  float* sbias = reinterpret_cast<float*>(staging + Cfg::kStagingBytes + Cfg::kBarrierBytes);  // [2][BN]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -285,22 +310,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 32 * kEpiWarps);
+      mbar_init(&acc_empty[i], (PAIR ? 2 : 1) * 32 * kEpiWarps);  // the leader hears from both CTAs' epilogues
     }
     mbar_init(drain_bar, 1);
+    for (int i = 0; i < 2 * kEpiWarps; ++i) mbar_init(&d0_bar[i], 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
     if (p.tma_store) tma_prefetch_desc(&tma_out);
+    if (D0BOX && p.tma_d0) tma_prefetch_desc(&tma_d0);
   }
   __syncthreads();
   if (warp == 1) {
-    tmem_alloc(tmem_slot, Cfg::kTmemCols);
-    tmem_relinquish();
+    if (PAIR) {  // the same warp of both CTAs, same result slot
+      tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, Cfg::kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -310,18 +343,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; ok && unit < p.num_units; unit += gridDim.x) {
+      for (int unit = walker; ok && unit < num_units; unit += num_walkers) {
         int b, m_blk, n_blk;
         const int tile = unit / p.splits, split = unit - tile * p.splits;
         decode_tile(p, tile, b, m_blk, n_blk);
+        if (PAIR) m_blk = 2 * m_blk + pair_rank;
         const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
           if (!ok) break;
           uint8_t* sa = smem + stage * kStageBytes;
-          mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
-          tma_load_3d(sa, &tma_a, &full_bar[stage], kb * kBK, m_blk * kBM, b * p.a_batch_mul);
-          tma_load_3d(sa + kABytes, &tma_b, &full_bar[stage], kb * kBK, n_blk * BN, b * p.b_batch_mul);
+          if (PAIR) {
+            // Both CTAs' copies are credited to the leader's barrier, which expects the bytes of both.
+            const uint32_t leader_bar = mapa_shared(smem_u32(&full_bar[stage]), 0);
+            if (pair_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
+            tma_load_3d_pair(sa, &tma_a, leader_bar, kb * kBK, m_blk * kBM, b * p.a_batch_mul);
+            tma_load_3d_pair(sa + kABytes, &tma_b, leader_bar, kb * kBK, n_blk * BN + pair_rank * (BN / 2),
+                             b * p.b_batch_mul);
+          } else {
+            mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+            tma_load_3d(sa, &tma_a, &full_bar[stage], kb * kBK, m_blk * kBM, b * p.a_batch_mul);
+            tma_load_3d(sa + kABytes, &tma_b, &full_bar[stage], kb * kBK, n_blk * BN, b * p.b_batch_mul);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (PAIR) {
+        // The leader's MMA commits release stages in BOTH CTAs: wait until every release addressed to this
+        // CTA has landed, so that none arrives after the CTA has gone.
+        for (int s = 0; ok && s < kStages; ++s) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -338,14 +392,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     __syncwarp();
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(kBM, BN, BF16, false, false);
+    if (lane == 0 && pair_rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(PAIR ? 2 * kBM : kBM, BN, BF16, false, false);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; ok && unit < p.num_units; unit += gridDim.x) {
+      for (int unit = walker; ok && unit < num_units; unit += num_walkers) {
         ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, kDevWaitAccEmptyTimeout);
         if (!ok) break;
         tc_fence_after();
@@ -362,22 +416,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           for (int k = 0; k < kBK / 16; ++k) {
             const uint64_t adesc = umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
+            if (PAIR) {
+              umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
+            } else {
+              umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
+            }
           }
-          umma_commit(&empty_bar[stage]);
+          if (PAIR) {
+            umma_commit_pair(&empty_bar[stage], 3);  // frees this stage in both CTAs
+          } else {
+            umma_commit(&empty_bar[stage]);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit(&acc_full[acc]);
+        if (PAIR) {
+          umma_commit_pair(&acc_full[acc], 3);  // both CTAs' epilogues read their half
+        } else {
+          umma_commit(&acc_full[acc]);
+        }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
       if (!ok) {
         // let MMAs that were already issued finish before TMEM is released
-        umma_commit(drain_bar);
+        if (PAIR) {
+          umma_commit_pair(drain_bar, 1);
+        } else {
+          umma_commit(drain_bar);
+        }
         const uint64_t t0 = globaltimer_ns();
         while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 1000000ull) {
         }
@@ -400,14 +470,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const bool has_d0 = epi_b1(code) != kBinaryNone;
     const bool chunk_contig = p.store_mode == 0 || (p.d % 32 == 0);
     const bool use_tma = (BN >= 128) && p.tma_store != 0;
-    uint8_t* my_staging = staging + ew * 4096;
+    // residual through staging boxes: needs the TMA store path and a tensor map over d0
+    const bool box_d0 = D0BOX && use_tma && p.tma_d0 != 0;
+    uint8_t* my_staging = staging + ew * (Cfg::kBoxesPerWarp * 4096);
+    uint64_t* my_d0_bar = d0_bar + 2 * ew;
+    uint32_t d0_phase_bits = 0;  // bit i: parity to wait for on my_d0_bar[i]
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int unit = blockIdx.x; ok && unit < p.num_units; unit += gridDim.x) {
+    const uint32_t acc_empty_leader[2] = {PAIR ? mapa_shared(smem_u32(&acc_empty[0]), 0) : 0u,
+                                          PAIR ? mapa_shared(smem_u32(&acc_empty[1]), 0) : 0u};
+    for (int unit = walker; ok && unit < num_units; unit += num_walkers) {
       int b, m_blk, n_blk;
       const int tile = unit / p.splits, split = unit - tile * p.splits;
       decode_tile(p, tile, b, m_blk, n_blk);
+      if (PAIR) m_blk = 2 * m_blk + pair_rank;
+      const int colh = n_blk * BN + half * (BN / 2);  // first column of this warp's half
+      const int row0 = m_blk * kBM + quarter * 32;    // first row of this warp
+      if (box_d0) {
+        // Fetch this warp's two 32 x 64 residual boxes into its staging buffers while the tile's MMAs run.
+        // The previous tile's stores must have finished reading the buffers first.
+        if (lane == 0) {
+          bulk_wait_group_read0();
+#pragma unroll
+          for (int bx = 0; bx < 2; ++bx) {
+            const int gcol = colh + bx * 64;
+            if (row0 < p.M && gcol < p.N) {
+              mbar_arrive_expect_tx(&my_d0_bar[bx], 4096);
+              tma_load_3d(my_staging + bx * 4096, &tma_d0, &my_d0_bar[bx], gcol, row0, b);
+            }
+          }
+        }
+        __syncwarp();
+      }
       float* bias_s = sbias + acc * BN;
       if (et < BN) {
         const int col = n_blk * BN + et;
@@ -416,7 +511,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       named_bar_sync(1, 32 * kEpiWarps);
       const int row = m_blk * kBM + quarter * 32 + lane;
       const bool row_ok = row < p.M;
-      const int colh = n_blk * BN + half * (BN / 2);  // first column of this warp's half
       const T* d0_row = static_cast<const T*>(p.d0) + static_cast<long long>(b) * p.d_bs + static_cast<long long>(row) * p.ldd;
       uint4 d0v[4];
       auto prefetch_d0 = [&](int col0) {
@@ -425,7 +519,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           for (int q = 0; q < 4; ++q) d0v[q] = __ldg(reinterpret_cast<const uint4*>(d0_row + col0) + q);
         }
       };
-      if (p.splits == 1) prefetch_d0(colh);
+      if (p.splits == 1 && !box_d0) prefetch_d0(colh);
       ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, kDevWaitAccFullTimeout);
       if (!ok) break;
       tc_fence_after();
@@ -445,7 +539,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         for (int q = 0; q < 4; ++q) d0c[q] = d0v[q];
         if (c + 1 < kChunksPerWarp && col0 + 32 < p.N) {  // next chunk's loads go out before this chunk's math
           tmem_ld_32x32b_x32(t_base + static_cast<uint32_t>((c + 1) * 32), r);
-          if (p.splits == 1) prefetch_d0(col0 + 32);
+          if (p.splits == 1 && !box_d0) prefetch_d0(col0 + 32);
         }
         if (col0 >= p.N) continue;  // warp-uniform
         const bool full = p.vec_ok && (col0 + 32 <= p.N);
@@ -478,12 +572,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         if (use_tma) {
           // Stage this warp's 32 rows x 64 columns (two chunks) in 128-byte-swizzled shared memory and
           // let TMA write the box: full 128-byte lines reach L2, rows / columns past M / N are clipped.
-          epilogue_math32<BF16, EPI>(p, v, d0c, b, row, col0, full, row_ok);
-          if ((c & 1) == 0) {  // the box buffer is about to be rewritten: its last store must have read it
+          uint8_t* box = my_staging + (box_d0 ? (c >> 1) * 4096 : 0);
+          uint8_t* row_base = box + lane * 128;
+          if (box_d0) {
+            // the residual box sits where the output box will be written: combine in place
+            if ((c & 1) == 0 && row0 < p.M) {
+              const int bx = c >> 1;
+              ok = mbar_wait(&my_d0_bar[bx], (d0_phase_bits >> bx) & 1u, abort_flag, p.status, kDevWaitOtherTimeout);
+              d0_phase_bits ^= 1u << bx;
+              if (!ok) break;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              d0c[u] = *reinterpret_cast<const uint4*>(row_base + ((((c & 1) * 4 + u) ^ (lane & 7)) * 16));
+          }
+          epilogue_math32<BF16, EPI>(p, v, d0c, b, row, col0, full || box_d0, row_ok);
+          if (!box_d0 && (c & 1) == 0) {  // the box buffer is about to be rewritten: its last store must have read it
             if (lane == 0) bulk_wait_group_read0();
             __syncwarp();
           }
-          uint8_t* row_base = my_staging + lane * 128;
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int unit = ((c & 1) * 4 + u) ^ (lane & 7);
@@ -492,14 +599,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           if ((c & 1) != 0 || col0 + 32 >= p.N) {
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
+            if (lane == 0 && row0 < p.M) {  // a box that starts past the last row has nothing to write
               const int gcol = colh + (c & ~1) * 32;
-              const int row0 = m_blk * kBM + quarter * 32;
               if (p.store_mode == 0) {
-                tma_store_5d(&tma_out, my_staging, gcol, row0, b, 0, 0);
+                tma_store_5d(&tma_out, box, gcol, row0, b, 0, 0);
               } else {
                 const int cc = gcol / p.d, r_b = row0 / p.t1;
-                tma_store_5d(&tma_out, my_staging, gcol - cc * p.d, row0 - r_b * p.t1, cc % p.t3, r_b, cc / p.t3);
+                tma_store_5d(&tma_out, box, gcol - cc * p.d, row0 - r_b * p.t1, cc % p.t3, r_b, cc / p.t3);
               }
               bulk_commit_group();
             }
@@ -509,9 +615,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           epilogue_direct_store32<BF16>(p, v, b, row, col0, full, chunk_contig);
         }
       }
+      if (!ok) break;
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&acc_empty[acc]);
+      if (PAIR) {
+        mbar_arrive_cluster(acc_empty_leader[acc]);
+      } else {
+        mbar_arrive(&acc_empty[acc]);
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -520,9 +631,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // neither CTA leaves, or frees TMEM, while its peer can still signal or read it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if (PAIR) {
+      tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    } else {
+      tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
   }
 }
 
@@ -531,9 +647,32 @@ void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
                cudaStream_t stream) {
   using Cfg = TileCfg<BN>;
   static std::atomic<uint64_t> configured{0};
-  opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_tc_kernel<BN, BF16, EPI>), Cfg::kSmemBytes);
-  gemm_tc_kernel<BN, BF16, EPI><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout, p);
+  opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_tc_kernel<BN, BF16, EPI, false>), Cfg::kSmemBytes);
+  gemm_tc_kernel<BN, BF16, EPI, false><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout, tout, p);
   B200AIT_CUDA_CHECK(cudaGetLastError());
+}
+
+// CTA-pair variant: `grid` counts CTAs (twice the number of pairs); launched as clusters of two.
+template <int BN, bool BF16, int EPI>
+void launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout, const CUtensorMap& td0,
+                    const GemmParams& p, int grid, cudaStream_t stream) {
+  using Cfg = TileCfg<BN, true, d0_box_of<EPI, true>()>;
+  static std::atomic<uint64_t> configured{0};
+  auto* kernel = &gemm_tc_kernel<BN, BF16, EPI, true>;
+  opt_in_smem_once(configured, reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B200AIT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tout, td0, p));
 }
 
 // Epilogues that get their own straight-line instantiation (fp16): bias, relu, gelu, fast_gelu, add,
@@ -561,6 +700,10 @@ void launch_tc_width<128>(bool, const CUtensorMap&, const CUtensorMap&, const CU
 template <>
 void launch_tc_width<256>(bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int,
                           cudaStream_t);
+
+// CTA-pair kernel, 256 x 256 tiles; defined in gemm_pair256.cu.
+void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
+                       const CUtensorMap& td0, const GemmParams& p, int grid, cudaStream_t stream);
 
 #define B200AIT_DEFINE_LAUNCH_TC_WIDTH(BN_)                                                                    \
   template <>                                                                                                  \

@@ -1,0 +1,24 @@
+// Instantiations of the tcgen05 GEMM kernel for 256 x 256 output tiles computed by CTA pairs
+// (cta_group::2, see gemm_kernel.cuh).
+#include "gemm_kernel.cuh"
+
+namespace b200ait {
+#define B200AIT_CASE_PAIR(CODE)                                          \
+  case (CODE):                                                           \
+    launch_tc_pair<256, false, (CODE)>(ta, tb, tout, td0, p, grid, stream);   \
+    break;
+
+void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
+                       const CUtensorMap& td0, const GemmParams& p, int grid, cudaStream_t stream) {
+  if (bf16) {
+    launch_tc_pair<256, true, -1>(ta, tb, tout, td0, p, grid, stream);
+    return;
+  }
+  switch (p.epilogue) {
+    B200AIT_FOR_EACH_FAST_EPILOGUE(B200AIT_CASE_PAIR)
+    default:
+      launch_tc_pair<256, false, -1>(ta, tb, tout, td0, p, grid, stream);
+  }
+}
+#undef B200AIT_CASE_PAIR
+}  // namespace b200ait
