@@ -310,9 +310,11 @@ void gemm_run(const GemmArgs& g) {
                                                  ws_ok ? g.workspace_bytes : 0);
   const int bn = sp.tile_n;
   // CTA pairs (256 x 256 tiles, cta_group::2): a third less operand traffic per flop into each SM. Chosen
-  // when the 256-wide tile was picked automatically and the 256-row tiles still fill every pair once.
+  // when the 256-wide tile was picked automatically, the 256-row tiles still fill every pair once, and K is
+  // deep enough for the main loop (not the per-tile epilogue and pair hand-shake) to set the pace.
   const long long pair_tiles = ((g.m + 2 * kBM - 1) / (2 * kBM)) * ((g.n + 255) / 256) * g.batch;
-  const bool pair = force_pair || (g.tile_n == 0 && bn == 256 && sp.splits == 1 && pair_tiles >= sm_count() / 2);
+  const bool pair = force_pair || (g.tile_n == 0 && bn == 256 && sp.splits == 1 && g.k >= 512 &&
+                                   pair_tiles >= sm_count() / 2);
   p.splits = sp.splits;
   p.kb_per_split = sp.kb_per_split;
   p.partial = static_cast<float*>(g.workspace);

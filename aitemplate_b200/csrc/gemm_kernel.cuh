@@ -468,6 +468,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const int et = threadIdx.x - 64;  // 0..255
     const int code = epilogue_code_of<EPI>(p);
     const bool has_d0 = epi_b1(code) != kBinaryNone;
+    const bool has_bias = p.bias != nullptr && p.splits == 1;
     const bool chunk_contig = p.store_mode == 0 || (p.d % 32 == 0);
     const bool use_tma = (BN >= 128) && p.tma_store != 0;
     // residual through staging boxes: needs the TMA store path and a tensor map over d0
@@ -504,11 +505,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         __syncwarp();
       }
       float* bias_s = sbias + acc * BN;
-      if (et < BN) {
-        const int col = n_blk * BN + et;
-        bias_s[et] = (p.bias != nullptr && p.splits == 1 && col < p.N) ? E::to_float(static_cast<const T*>(p.bias)[col]) : 0.f;
+      if (has_bias) {  // CTA-uniform
+        if (et < BN) {
+          const int col = n_blk * BN + et;
+          bias_s[et] = col < p.N ? E::to_float(static_cast<const T*>(p.bias)[col]) : 0.f;
+        }
+        named_bar_sync(1, 32 * kEpiWarps);
       }
-      named_bar_sync(1, 32 * kEpiWarps);
       const int row = m_blk * kBM + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       const T* d0_row = static_cast<const T*>(p.d0) + static_cast<long long>(b) * p.d_bs + static_cast<long long>(row) * p.ldd;
@@ -525,23 +528,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       tc_fence_after();
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                               static_cast<uint32_t>(acc * BN + half * (BN / 2));
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(t_base, r);
-#pragma unroll 1
-      for (int c = 0; c < kChunksPerWarp; ++c) {
+      // Two register buffers alternate between "being read" and "being loaded", so that a chunk is used where
+      // tcgen05.ld put it. The accumulator goes back to the MMA warp as soon as its last chunk is in registers.
+      uint32_t ra[32], rb[32];
+      bool released = false;
+      tmem_ld_32x32b_x32(t_base, ra);
+      auto chunk_step = [&](const int c, uint32_t (&cur)[32], uint32_t (&nxt)[32]) {
+        if (!ok) return;
         const int col0 = colh + c * 32;
         tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         uint4 d0c[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) d0c[q] = d0v[q];
         if (c + 1 < kChunksPerWarp && col0 + 32 < p.N) {  // next chunk's loads go out before this chunk's math
-          tmem_ld_32x32b_x32(t_base + static_cast<uint32_t>((c + 1) * 32), r);
+          tmem_ld_32x32b_x32(t_base + static_cast<uint32_t>((c + 1) * 32), nxt);
           if (p.splits == 1 && !box_d0) prefetch_d0(col0 + 32);
+        } else if (!released) {
+          released = true;
+          tc_fence_before();
+          if (PAIR) {
+            mbar_arrive_cluster(acc_empty_leader[acc]);
+          } else {
+            mbar_arrive(&acc_empty[acc]);
+          }
         }
-        if (col0 >= p.N) continue;  // warp-uniform
+        if (col0 >= p.N) return;  // warp-uniform
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(cur[j]);
         const bool full = p.vec_ok && (col0 + 32 <= p.N);
         if (p.splits > 1) {
           // split-K: raw fp32 partial sums; the reduce kernel applies the epilogue
@@ -557,17 +571,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                 if (col0 + j < p.N) dst[j] = v[j];
             }
           }
-          continue;
+          return;
         }
-        const float* bs = bias_s + half * (BN / 2) + c * 32;
         if (p.alpha != 1.f) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
         }
+        if (has_bias) {
+          const float* bs = bias_s + half * (BN / 2) + c * 32;
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const float4 f = *reinterpret_cast<const float4*>(bs + q * 4);
-          v[q * 4] += f.x, v[q * 4 + 1] += f.y, v[q * 4 + 2] += f.z, v[q * 4 + 3] += f.w;
+          for (int q = 0; q < 8; ++q) {
+            const float4 f = *reinterpret_cast<const float4*>(bs + q * 4);
+            v[q * 4] += f.x, v[q * 4 + 1] += f.y, v[q * 4 + 2] += f.z, v[q * 4 + 3] += f.w;
+          }
         }
         if (use_tma) {
           // Stage this warp's 32 rows x 64 columns (two chunks) in 128-byte-swizzled shared memory and
@@ -580,7 +596,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               const int bx = c >> 1;
               ok = mbar_wait(&my_d0_bar[bx], (d0_phase_bits >> bx) & 1u, abort_flag, p.status, kDevWaitOtherTimeout);
               d0_phase_bits ^= 1u << bx;
-              if (!ok) break;
+              if (!ok) return;
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u)
@@ -614,15 +630,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           epilogue_math32<BF16, EPI>(p, v, d0c, b, row, col0, full, true);
           epilogue_direct_store32<BF16>(p, v, b, row, col0, full, chunk_contig);
         }
+      };
+#pragma unroll
+      for (int c = 0; c < kChunksPerWarp; c += 2) {
+        chunk_step(c, ra, rb);
+        if (c + 1 < kChunksPerWarp) chunk_step(c + 1, rb, ra);
       }
       if (!ok) break;
-      tmem_ld_wait();
-      tc_fence_before();
-      if (PAIR) {
-        mbar_arrive_cluster(acc_empty_leader[acc]);
-      } else {
-        mbar_arrive(&acc_empty[acc]);
-      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }

@@ -42,7 +42,8 @@ int b200ait_device_status(int* status_out);
 
 /* Generic GEMM: c[b] = epilogue(alpha * a[b] . b[b]^T + bias, d0, d1); a [batch, m, k] (row stride lda),
  * b [batch, n, k] (row stride ldb), c / d0 / d1 [batch, m, n] (row strides ldc / ldd). A batch stride
- * of 0 broadcasts that operand. tile_n = 0 lets the library choose (else 64, 128 or 256).
+ * of 0 broadcasts that operand. tile_n = 0 lets the library choose; else 64, 128 or 256 (128 x tile_n tiles,
+ * one CTA each) or 512 (256 x 256 tiles, each computed by a pair of CTAs with cta_group::2 MMAs).
  * workspace / workspace_bytes / split_k: see b200ait_gemm_rcr_workspace_bytes below.
  * Replaces python/aitemplate/backend/cuda/gemm_universal/common.py:130-617 (CUTLASS instantiation). */
 int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void* d0, const void* d1, void* c,

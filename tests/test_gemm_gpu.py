@@ -91,7 +91,7 @@ def test_unaligned_shapes_use_cuda_core_kernel(n, kk):
     _close(y, oracle.gemm_rcr(x, w, b, d0, epilogue="add_relu"))
 
 
-@pytest.mark.parametrize("tile_n", [64, 128, 256])
+@pytest.mark.parametrize("tile_n", [64, 128, 256, 512])
 def test_forced_tile_width_many_tiles(tile_n):
     # more tiles than SMs: exercises the persistent loop, both accumulators and every stage phase
     k = _kernels()
@@ -101,6 +101,49 @@ def test_forced_tile_width_many_tiles(tile_n):
     b = _rand((n,), 32, scale=0.02)
     y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), epilogue="", tile_n=tile_n)
     _close(y, oracle.gemm_rcr(x, w, b))
+
+
+# tile_n = 512 asks for 256 x 256 tiles computed by CTA pairs (cta_group::2); the library picks it by itself
+# for large problems, these cases force it on shapes that exercise its edges.
+@pytest.mark.parametrize(
+    "m,n,kk,epilogue",
+    [
+        (256, 256, 64, ""),          # one tile, one k-block
+        (512, 512, 256, "relu"),
+        (200, 296, 128, ""),         # the second CTA of the pair owns rows 128..199 only; ragged N
+        (100, 256, 128, "gelu"),     # the second CTA's rows are all out of range
+        (200, 296, 128, "add"),      # residual boxes clipped in both directions
+        (100, 256, 128, "add_relu"),
+        (1000, 776, 256, "mul"),
+        (2048, 1024, 512, "add"),
+        (2048, 1024, 512, "add_add"),  # second residual: register path next to the staged first one
+        (4096, 768, 3072, "add"),    # many tiles per pair: every ring stage and both accumulators wrap
+    ],
+)
+def test_cta_pair_tiles(m, n, kk, epilogue):
+    k = _kernels()
+    x = _rand((m, kk), 300, dist="uniform")
+    w = _rand((n, kk), 301, scale=0.05)
+    b = _rand((n,), 302, scale=0.1)
+    nres = {"add": 1, "add_relu": 1, "mul": 1, "add_add": 2}.get(epilogue, 0)
+    d = [_rand((m, n), 303 + i) for i in range(nres)]
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), *[t.cuda() for t in d], epilogue=epilogue, tile_n=512)
+    assert k.device_status() == 0
+    _close(y, oracle.gemm_rcr(x, w, b, *d, epilogue=epilogue))
+
+
+def test_cta_pair_tiles_bf16_and_permuted_store():
+    k = _kernels()
+    s_, h, dd, bsz = 384, 12, 64, 4
+    x = _rand((bsz * s_, h * dd), 310)
+    w = _rand((3 * h * dd, h * dd), 311, scale=0.05)
+    b = _rand((3 * h * dd,), 312, scale=0.1)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), permute_shape=(s_, 3, h), tile_n=512)
+    _close(y, oracle.gemm_rcr_bias_permute(x, w, b, (s_, 3, h)))
+    xb, wb, bb = x.to(torch.bfloat16), w.to(torch.bfloat16), b.to(torch.bfloat16)
+    db = _rand((bsz * s_, 3 * h * dd), 313, dtype=torch.bfloat16)
+    yb = k.gemm_rcr(xb.cuda(), wb.cuda(), bb.cuda(), db.cuda(), epilogue="add", tile_n=512)
+    _close(yb, oracle.gemm_rcr(xb, wb, bb, db, epilogue="add"), atol=5e-2, rtol=5e-2)
 
 
 def test_no_bias_and_alpha():
