@@ -212,11 +212,33 @@ SplitPlan plan_split_k(long long batch, long long m, long long n, long long k, i
   SplitPlan sp{tile_n ? tile_n : choose_tile_n(m, n, batch), 1, 0, 0};
   const long long num_kb = (k + kBK - 1) / kBK;
   sp.kb_per_split = static_cast<int>(num_kb);
-  const long long tiles = ((m + kBM - 1) / kBM) * ((n + sp.tile_n - 1) / sp.tile_n) * batch;
   const long long sms = sm_count();
-  if (max_splits == 1 || tiles * 2 > sms || num_kb < 4) return sp;
-  long long s = std::min<long long>(std::min<long long>(sms / tiles, num_kb / 2), 16);
-  if (max_splits > 1) s = std::min<long long>(s, max_splits);
+  if (max_splits == 1 || num_kb < 4) return sp;
+  // One tile row (M <= 128): the run time is the time to stream the weights once. A tcgen05 MMA takes as long
+  // as its M x K says, whatever N is, so a CTA consumes weight rows fastest through wide tiles: 128- and
+  // 64-wide tiles cap a CTA at half and a quarter of the 256-wide rate, below its share of HBM bandwidth.
+  // Take 256-wide tiles and split K to occupy the SMs, unless the fp32 partial sums that costs would add more
+  // than ~5 % to the weight traffic (then 128-wide tiles, half the splits).
+  if (tile_n == 0 && max_splits == 0 && batch == 1 && m <= kBM && num_kb >= 32) {
+    for (int bn : {256, 128}) {
+      const long long tiles_n = (n + bn - 1) / bn;
+      const long long s = std::min<long long>(std::min<long long>(sms / tiles_n, num_kb / 8), 16);
+      if (s < 2 || tiles_n * s * 2 < sms) continue;  // would leave most SMs idle anyway
+      if (bn == 256 && s * m * 4 * 20 > k * 2) continue;  // partial sums: s * m * n * 4 bytes against n * k * 2
+      if (s * m * n * 4 > workspace_bytes) continue;
+      const long long per = (num_kb + s - 1) / s;
+      return SplitPlan{bn, static_cast<int>((num_kb + per - 1) / per), static_cast<int>(per),
+                       ((num_kb + per - 1) / per) * m * n * 4};
+    }
+  }
+  const long long tiles = ((m + kBM - 1) / kBM) * ((n + sp.tile_n - 1) / sp.tile_n) * batch;
+  long long s;
+  if (max_splits > 1) {
+    s = std::min<long long>(max_splits, num_kb / 2);  // the caller's choice
+  } else {
+    if (tiles * 2 > sms) return sp;
+    s = std::min<long long>(std::min<long long>(sms / tiles, num_kb / 2), 16);
+  }
   while (s > 1 && s * batch * m * n * 4 > workspace_bytes) --s;
   if (s <= 1) return sp;
   const long long per = (num_kb + s - 1) / s;
