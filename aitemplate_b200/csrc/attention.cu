@@ -8,13 +8,15 @@
 // row sum (attention_scaling_coefs_updater.h:85-165), P rounded to 16 bits before P.V, O kept in fp32
 // and divided by the row sum at the end. S is never written to global memory.
 //
-// One CTA owns 128 query rows of one (batch, head):
-//   warp 0      TMA producer: Q tile once, then K/V tiles of kBlockN keys into a 2-stage ring
+// Persistent CTAs walk work items of 128 query rows of one (batch, head):
+//   warp 0      TMA producer: the item's Q tile, then K/V blocks of kBlockN keys into a 3-stage ring;
+//               the next item's Q streams in while the current item drains
 //   warp 1      MMA issuer:   S = Q K^T  (tcgen05.mma, fp32 accumulator in TMEM)
 //                             T = P V    (P from shared memory, V as an MN-major B operand)
-//   warps 2-5   one thread per query row: TMEM -> registers, mask, running max / sum, exp2,
-//               P -> swizzled shared memory, O (registers) = O * alpha + T
-// Two CTAs share an SM (head dim <= 64) so one CTA's softmax overlaps the other's MMAs.
+//               S, P and T are double-buffered: the MMAs of key block j+1 overlap the softmax of block j
+//   warps 2-5   one thread per query row: TMEM -> registers, mask (skipped for full, unmasked blocks),
+//               running max / sum, exp2, P -> swizzled shared memory, O (registers) = O * alpha + T
+// Two CTAs share an SM (head dim <= 64) so one CTA's softmax also overlaps the other's MMAs.
 // Head dims that are not a multiple of 8, or larger than 128, run on a CUDA-core kernel.
 #include <cuda.h>
 

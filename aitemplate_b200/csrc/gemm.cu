@@ -190,15 +190,25 @@ constexpr int kTilePair = 512;  // tile_n value that asks for 256 x 256 tiles on
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int choose_tile_n(long long m, long long n, long long batch) {
+// Tile width by a cost model of the persistent kernel. A tcgen05 MMA of 128 rows takes ~128 cycles per 16
+// of K whatever its N (the array is as wide as N = 256; narrower tiles leave columns idle), so a tile's main
+// loop costs the same at every width and only the epilogue shrinks with it. Per CTA the run is
+//   waves x max(main loop, epilogue) + one last epilogue,   waves = ceil(tiles / SMs),
+// so narrow tiles pay only when they save a whole wave (or the problem is all epilogue).
+int choose_tile_n(long long m, long long n, long long k, long long batch) {
   const long long sms = sm_count();
   const long long tm = (m + kBM - 1) / kBM;
-  // the widest tile that still yields at least ~one wave of work
-  for (int bn : {256, 128}) {
+  const long long mainloop = ((k + kBK - 1) / kBK) * 512;  // cycles
+  int best = 256;
+  long long best_cost = -1;
+  for (int bn : {256, 128, 64}) {
     const long long tiles = tm * ((n + bn - 1) / bn) * batch;
-    if (tiles >= sms) return bn;
+    const long long waves = (tiles + sms - 1) / sms;
+    const long long epilogue = 1500 + 8 * bn;  // measured: ~3.5 k cycles for a 128 x 256 tile, ~1.5 k of it fixed
+    const long long cost = waves * std::max(mainloop, epilogue) + epilogue;
+    if (best_cost < 0 || cost < best_cost) best = bn, best_cost = cost;
   }
-  return 64;
+  return best;
 }
 
 // Split-K plan: how many K-splits a problem gets and the fp32 workspace they need.
@@ -209,7 +219,7 @@ struct SplitPlan {
 };
 SplitPlan plan_split_k(long long batch, long long m, long long n, long long k, int tile_n, int max_splits,
                        long long workspace_bytes) {
-  SplitPlan sp{tile_n ? tile_n : choose_tile_n(m, n, batch), 1, 0, 0};
+  SplitPlan sp{tile_n ? tile_n : choose_tile_n(m, n, k, batch), 1, 0, 0};
   const long long num_kb = (k + kBK - 1) / kBK;
   sp.kb_per_split = static_cast<int>(num_kb);
   const long long sms = sm_count();
