@@ -28,6 +28,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 BATCH, SEQ, HIDDEN, HEADS, FFN = 64, 384, 768, 12, 3072
+GEMM_DRAM_TRAFFIC_PER_STEP = 547.8e6  # ncu: dram__bytes_read.sum + dram__bytes_write.sum over the 4 launches
 METRIC = "bert_base_layer_seqs_per_sec"
 UNIT = "seq/s"
 WORKLOAD = "BERT-base encoder layer, fp16, batch 64, seq 384, hidden 768, 12 heads x 64, FFN 3072 (BASELINE config 2)"
@@ -288,7 +289,11 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "roofline": {"kernel": "gemm_tc_kernel (4 launches per step)", "bound": "tensor", "achieved": achieved,
                          "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops_burst"] if achieved else None,
-                         "peak_source": peaks["source"] + " burst (each kernel timed alone)", "traffic": None,
+                         "peak_source": peaks["source"] + " burst (each kernel timed alone)",
+                         # DRAM read + write bytes of the four GEMM launches of one step, from the committed
+                         # ncu capture of this workload (profiles/gemm_tc_kernel_bert_layer.md); the algorithmic
+                         # bytes of the same four launches are 693.6e6.
+                         "traffic": GEMM_DRAM_TRAFFIC_PER_STEP, "traffic_unit": "bytes per step (4 launches)",
                          "per_op_us": per_op},
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"8 of {BATCH} sequences x {runs} runs, fp32 torch oracle, all host threads"},
