@@ -210,3 +210,35 @@ def bert_layer(hidden, p: dict, num_heads: int = 12, eps: float = 1e-12) -> torc
     f = F.gelu(F.linear(h1, w["fc1_weight"], w["fc1_bias"]), approximate="tanh")
     out = F.layer_norm(F.linear(f, w["fc2_weight"], w["fc2_bias"]) + h1, (hid,), w["ln2_gamma"], w["ln2_beta"], eps)
     return out.reshape(b, s, hid)
+
+
+def sd_transformer_block(x, context, p: dict, heads: int = 8, eps: float = 1e-5) -> torch.Tensor:
+    """Stable-Diffusion UNet BasicTransformerBlock as examples/05_stable_diffusion/src/modeling/clip.py:137-175
+    builds it: x += attn1(norm1(x)); x += attn2(norm2(x), context); x += ff(norm3(x)), with bias-free q/k/v
+    projections (clip.py:59-61) and a GEGLU feed-forward, proj(x) * gelu_tanh(gate(x)) (clip.py:100-107)."""
+    x, context = _f32(x), _f32(context)
+    w = {k: _f32(v) for k, v in p.items()}
+    b, n, dim = x.shape
+    d = dim // heads
+
+    def attention(name, h, ctx):
+        def split_heads(t):
+            return t.reshape(b, -1, heads, d).permute(0, 2, 1, 3)
+
+        q = split_heads(F.linear(h, w[f"{name}_to_q_weight"]))
+        k = split_heads(F.linear(ctx, w[f"{name}_to_k_weight"]))
+        v = split_heads(F.linear(ctx, w[f"{name}_to_v_weight"]))
+        a = torch.softmax(torch.matmul(q, k.transpose(-1, -2)) / math.sqrt(d), dim=-1) @ v
+        a = a.permute(0, 2, 1, 3).reshape(b, n, dim)
+        return F.linear(a, w[f"{name}_to_out_weight"], w[f"{name}_to_out_bias"])
+
+    def norm(name, t):
+        return F.layer_norm(t, (dim,), w[f"{name}_weight"], w[f"{name}_bias"], eps)
+
+    h = norm("norm1", x)
+    x = attention("attn1", h, h) + x
+    x = attention("attn2", norm("norm2", x), context) + x
+    h = norm("norm3", x)
+    gate = F.gelu(F.linear(h, w["ff_gate_weight"], w["ff_gate_bias"]), approximate="tanh")
+    ff = F.linear(F.linear(h, w["ff_proj_weight"], w["ff_proj_bias"]) * gate, w["ff_out_weight"], w["ff_out_bias"])
+    return ff + x

@@ -169,6 +169,18 @@ def test_bert_layer_plan_and_memory_plan():
     assert all(t._attrs["offset"] % 256 == 0 for _, _, t in items)
 
 
+def test_sd_transformer_block_plan():
+    # BASELINE configuration 3 lowers to GEMMs, permutes, two attentions and three layernorms; every residual
+    # add is fused into the GEMM before it (no stand-alone elementwise kernel is left).
+    y = workloads.build_sd_block(2)
+    g, plan, blob, consts = _lower([y])
+    kernels = [line.split()[1] for line in plan.splitlines() if line.startswith("op ") and line.split()[1] != "view"]
+    attn = ["gemm_rcr", "permute"] * 3 + ["mem_eff_attention", "gemm_rcr"]
+    assert kernels == ["layernorm"] + attn + ["layernorm"] + attn + ["layernorm", "gemm_rcr", "gemm_rcr", "gemm_rcr"]
+    assert consts >= 2 * (4 * 320 * 320 + 2 * 320 * 768 + 2 * 320 * 320 + 3 * 1280 * 320)
+    assert blob >= 2 * 4096 * 1280 * 2
+
+
 def test_output_aliasing_input_gets_a_copy():
     x = Tensor([4, 6], name="x", is_input=True)
     y = _out(ops.reshape()(x, [6, 4]), "y")

@@ -256,6 +256,28 @@ def test_bert_layer_matches_oracle(workdir, graph_mode):
     assert sum(n.startswith("gemm_rcr") for n in names) == 4 and any(n.startswith("mem_eff_attention") for n in names)
 
 
+@pytest.mark.parametrize("tokens", [1024, 4096])
+def test_sd_transformer_block_matches_oracle(workdir, tokens):
+    # BASELINE configuration 3: Stable-Diffusion UNet transformer block, batch 2, dim 320, 8 heads x 40
+    # (head dim 40 = 5 x 8: the tensor-core attention path with a zero-padded head), self-attention over the
+    # latent tokens, cross-attention against 77 context tokens of dim 768, GEGLU feed-forward.
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    from aitemplate_b200.testing import workloads
+
+    batch = 2
+    x, context, params = workloads.sd_block_inputs(batch, tokens)
+    y = workloads.build_sd_block(batch, tokens=tokens)
+    module = compile_model(y, detect_target(), workdir, "sd_block")
+    module.set_many_constants_with_tensors({k: v.cuda() for k, v in params.items()})
+    out = torch.empty((batch, tokens, 320), dtype=torch.float16, device="cuda")
+    want = oracle.sd_transformer_block(x, context, params)
+    for graph_mode in (False, True, True):
+        out.zero_()
+        res = module.run_with_tensors({"latent": x.cuda(), "context": context.cuda()}, {"output_0": out},
+                                      graph_mode=graph_mode)
+        _close(res["output_0"], want, 2e-2)
+
+
 def test_concurrent_runs_share_the_pool(workdir):
     import threading
 
