@@ -1,6 +1,7 @@
 // Library-wide host state: last-error text, per-device status word, device properties.
 #include "common.h"
 
+#include <cstring>
 #include <mutex>
 
 namespace b200ait {
@@ -76,3 +77,38 @@ B200AIT_EXPORT int b200ait_device_status(int* status_out) {
 }
 
 B200AIT_EXPORT int b200ait_version() { return 1; }
+
+// ------------------------------------------------------------------------------------------------
+// Peer buffers for multi-GPU runs (one process per GPU on one node): a buffer allocated here can be opened by
+// the other ranks through a CUDA IPC handle, which gives them a pointer they can pass as an extra output of
+// b200ait_gemm_rcr_multi_out. The handle is 64 opaque bytes that the caller ships to its peers.
+B200AIT_EXPORT int b200ait_peer_alloc(int64_t bytes, void** ptr_out, void* handle64_out) {
+  return b200ait::guarded("b200ait_peer_alloc", [&] {
+    B200AIT_REQUIRE(ptr_out && handle64_out && bytes > 0, "b200ait_peer_alloc: bad argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void* p = nullptr;
+    B200AIT_CUDA_CHECK(cudaMalloc(&p, static_cast<size_t>(bytes)));
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+      cudaFree(p);
+      B200AIT_CUDA_CHECK(e);
+    }
+    memcpy(handle64_out, &h, 64);
+    *ptr_out = p;
+  });
+}
+B200AIT_EXPORT int b200ait_peer_open(const void* handle64, void** ptr_out) {
+  return b200ait::guarded("b200ait_peer_open", [&] {
+    B200AIT_REQUIRE(handle64 && ptr_out, "b200ait_peer_open: bad argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    B200AIT_CUDA_CHECK(cudaIpcOpenMemHandle(ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+  });
+}
+B200AIT_EXPORT int b200ait_peer_close(void* opened_ptr) {
+  return b200ait::guarded("b200ait_peer_close", [&] { B200AIT_CUDA_CHECK(cudaIpcCloseMemHandle(opened_ptr)); });
+}
+B200AIT_EXPORT int b200ait_peer_free(void* allocated_ptr) {
+  return b200ait::guarded("b200ait_peer_free", [&] { B200AIT_CUDA_CHECK(cudaFree(allocated_ptr)); });
+}

@@ -180,6 +180,8 @@ struct GemmArgs {
   long long t1, t2, t3;
   int tile_n;  // 0 = choose
   cudaStream_t stream;
+  int num_out = 1;                                // destinations: c, then extra_out[0 .. num_out - 2]
+  void* extra_out[kMaxOut - 1] = {};              // same shape and strides as c (e.g. peers' copies of the result)
   void* workspace = nullptr;  // fp32 scratch for split-K partial sums (may be null: no split-K)
   long long workspace_bytes = 0;
   int split_k = 0;  // 0 = choose, 1 = off, n = at most n splits
@@ -283,6 +285,11 @@ void gemm_run(const GemmArgs& g) {
   p.t1 = 1, p.t3 = 1, p.d = 1;
   bool vec = (g.n % 8 == 0) && aligned16(g.c) && (g.c_bs % 8 == 0);
   if (g.bias) vec = vec && aligned16(g.bias);
+  B200AIT_REQUIRE(g.num_out >= 1 && g.num_out <= kMaxOut, "gemm: between 1 and 8 output buffers");
+  for (int i = 1; i < g.num_out; ++i) {
+    B200AIT_REQUIRE(g.extra_out[i - 1] != nullptr, "gemm: null extra output buffer");
+    vec = vec && aligned16(g.extra_out[i - 1]);
+  }
   if (b1 != kBinaryNone) vec = vec && aligned16(g.d0) && (g.ldd % 8 == 0) && (g.d_bs % 8 == 0);
   if (b2 != kBinaryNone) vec = vec && aligned16(g.d1) && (g.ldd % 8 == 0) && (g.d_bs % 8 == 0);
   if (g.store_mode == 0) {
@@ -321,6 +328,7 @@ void gemm_run(const GemmArgs& g) {
 
   const bool tma_ok = (g.k % 8 == 0) && (g.lda % 8 == 0) && (g.ldb % 8 == 0) && aligned16(g.a) && aligned16(g.b) &&
                       (g.a_bs % 8 == 0) && (g.b_bs % 8 == 0) && g.batch < 65536 * 32;
+  B200AIT_REQUIRE(tma_ok || g.num_out == 1, "gemm: several output buffers need TMA-addressable operands");
   if (!tma_ok) {
     dim3 grid(static_cast<unsigned>((g.n + 31) / 32), static_cast<unsigned>((g.m + 31) / 32),
               static_cast<unsigned>(g.batch));
@@ -337,9 +345,10 @@ void gemm_run(const GemmArgs& g) {
                   "gemm: tile_n must be 64, 128, 256 or 512 (256 x 256 tiles on CTA pairs)");
   const bool ws_ok = g.workspace != nullptr && aligned16(g.workspace);
   const bool force_pair = g.tile_n == kTilePair;
-  const SplitPlan sp = force_pair ? SplitPlan{256, 1, static_cast<int>((g.k + kBK - 1) / kBK), 0}
-                                  : plan_split_k(g.batch, g.m, g.n, g.k, g.tile_n, g.split_k,
-                                                 ws_ok ? g.workspace_bytes : 0);
+  SplitPlan sp = force_pair ? SplitPlan{256, 1, static_cast<int>((g.k + kBK - 1) / kBK), 0}
+                            : plan_split_k(g.batch, g.m, g.n, g.k, g.tile_n, g.num_out > 1 ? 1 : g.split_k,
+                                           ws_ok ? g.workspace_bytes : 0);
+  if (g.num_out > 1 && sp.tile_n == 64 && g.tile_n == 0) sp.tile_n = 128;  // several destinations need the staged store
   const int bn = sp.tile_n;
   // CTA pairs (256 x 256 tiles, cta_group::2): a third less operand traffic per flop into each SM. Chosen
   // when the 256-wide tile was picked automatically, the 256-row tiles still fill every pair once, and K is
@@ -355,24 +364,32 @@ void gemm_run(const GemmArgs& g) {
   CUtensorMap tb = make_tile_map(g.b, bf16, g.k, g.n, b_batch, g.ldb, g.b_bs, pair ? bn / 2 : bn);
   // Staged TMA store: row-major output with 16-byte aligned rows, or a permuted output whose 64-column
   // groups and 32-row groups each stay inside one contiguous run of the destination.
-  CUtensorMap tout = ta;
+  OutMaps tout;
+  for (int i = 0; i < kMaxOut; ++i) tout.m[i] = ta;  // placeholders: only the first num_out are ever read
   p.tma_store = 0;
+  p.num_out = g.num_out;
   if (bn >= 128 && p.splits == 1 && p.vec_ok) {
-    if (p.store_mode == 0) {
-      const long long bs = g.batch > 1 ? g.c_bs : g.m * g.ldc;
-      const long long dims[5] = {g.n, g.m, g.batch, 1, 1};
-      const long long strides[4] = {g.ldc, bs, bs, bs};
-      tout = make_out_map(g.c, bf16, dims, strides);
-      p.tma_store = 1;
-    } else if (p.d % 64 == 0 && p.t1 % 32 == 0 && g.batch == 1) {
-      // destination [c2][row / t1][c3][row % t1][d]: dims innermost first (d, t1, t3, M / t1, c2 extent)
-      const long long c2_extent = g.n / (static_cast<long long>(p.d) * p.t3);
-      const long long dims[5] = {p.d, p.t1, p.t3, g.m / p.t1, c2_extent};
-      const long long strides[4] = {p.rs_lo, p.cs3, p.rs_hi, p.cs2 > 0 ? p.cs2 : p.rs_hi * (g.m / p.t1)};
-      tout = make_out_map(g.c, bf16, dims, strides);
-      p.tma_store = 1;
+    for (int i = 0; i < g.num_out; ++i) {
+      void* dst = i == 0 ? g.c : g.extra_out[i - 1];
+      if (p.store_mode == 0) {
+        const long long bs = g.batch > 1 ? g.c_bs : g.m * g.ldc;
+        const long long dims[5] = {g.n, g.m, g.batch, 1, 1};
+        const long long strides[4] = {g.ldc, bs, bs, bs};
+        tout.m[i] = make_out_map(dst, bf16, dims, strides);
+        p.tma_store = 1;
+      } else if (p.d % 64 == 0 && p.t1 % 32 == 0 && g.batch == 1) {
+        // destination [c2][row / t1][c3][row % t1][d]: dims innermost first (d, t1, t3, M / t1, c2 extent)
+        const long long c2_extent = g.n / (static_cast<long long>(p.d) * p.t3);
+        const long long dims[5] = {p.d, p.t1, p.t3, g.m / p.t1, c2_extent};
+        const long long strides[4] = {p.rs_lo, p.cs3, p.rs_hi, p.cs2 > 0 ? p.cs2 : p.rs_hi * (g.m / p.t1)};
+        tout.m[i] = make_out_map(dst, bf16, dims, strides);
+        p.tma_store = 1;
+      }
     }
   }
+  B200AIT_REQUIRE(g.num_out == 1 || p.tma_store,
+                  "gemm: several output buffers need the staged TMA store (tile_n >= 128, no split-K, N and the "
+                  "output strides multiples of 8, 16-byte aligned pointers)");
   p.tiles_m = pair ? (p.M + 2 * kBM - 1) / (2 * kBM) : (p.M + kBM - 1) / kBM;
   p.tiles_n = (p.N + bn - 1) / bn;
   p.num_tiles = p.tiles_m * p.tiles_n * p.batch;
@@ -425,6 +442,26 @@ B200AIT_EXPORT int b200ait_gemm_rcr(const void* a, const void* b, const void* bi
     g.workspace = workspace;
     g.workspace_bytes = workspace_bytes;
     g.split_k = split_k;
+    gemm_run(g);
+  });
+}
+
+// The same GEMM with its result written to num_out buffers of identical shape and strides (1 <= num_out <= 8)
+// by the epilogue's TMA stores: outs[0] is usually this GPU's buffer and the others are peer-mapped pointers
+// to other GPUs' buffers, so that a rank that computes one column block of Y = X W^T places it in every
+// rank's full Y while the next tile is being computed (no separate gather pass). Never splits K; needs the
+// staged store (N and ldc multiples of 8, 16-byte aligned pointers).
+B200AIT_EXPORT int b200ait_gemm_rcr_multi_out(const void* a, const void* b, const void* bias, const void* d0,
+                                              void* const* outs, int num_out, int64_t m, int64_t n, int64_t k,
+                                              int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int epilogue,
+                                              int dtype, float alpha, int tile_n, cudaStream_t stream) {
+  return guarded("b200ait_gemm_rcr_multi_out", [&] {
+    B200AIT_REQUIRE(outs != nullptr && num_out >= 1 && num_out <= kMaxOut, "outs: 1 to 8 output pointers");
+    GemmArgs g{a, b, bias, d0, nullptr, outs[0], 1, m, n, k, lda, ldb, ldc, ldd, 0, 0, 0, 0,
+               epilogue, dtype, alpha, 0, 1, 1, 1, tile_n, stream};
+    g.num_out = num_out;
+    for (int i = 1; i < num_out; ++i) g.extra_out[i - 1] = outs[i];
+    g.split_k = 1;
     gemm_run(g);
   });
 }

@@ -33,9 +33,17 @@ struct GemmParams {
   int t1, t3, d;
   long long rs_hi, rs_lo, cs2, cs3;
   int vec_ok;  // 16-byte epilogue accesses are legal
-  int tma_store;  // output goes through shared memory + TMA store (tensor map `tma_out`)
+  int tma_store;  // output goes through shared memory + TMA store (tensor maps `outs`)
+  int num_out;    // destinations of the staged store (1 unless the caller passed several output buffers)
   int tma_d0;     // the residual d0 arrives by TMA in the output staging boxes (tensor map `tma_d0`)
   int* status;
+};
+
+// Tensor maps of the output: one per destination buffer. More than one destination is how a rank that owns a
+// column block of the result writes it straight into every rank's copy of the full matrix (peer pointers).
+constexpr int kMaxOut = 8;
+struct OutMaps {
+  CUtensorMap m[kMaxOut];
 };
 
 constexpr int kBM = 128;
@@ -269,7 +277,7 @@ __device__ __forceinline__ void epilogue_direct_store32(const GemmParams& p, con
 template <int BN, bool BF16, int EPI, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_d0,
+               const __grid_constant__ OutMaps outs, const __grid_constant__ CUtensorMap tma_d0,
                const GemmParams p) {
   constexpr bool D0BOX = d0_box_of<EPI, PAIR>();
   using Cfg = TileCfg<BN, PAIR, D0BOX>;
@@ -318,7 +326,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
-    if (p.tma_store) tma_prefetch_desc(&tma_out);
+    if (p.tma_store)
+      for (int i = 0; i < p.num_out; ++i) tma_prefetch_desc(&outs.m[i]);
     if (D0BOX && p.tma_d0) tma_prefetch_desc(&tma_d0);
   }
   __syncthreads();
@@ -618,10 +627,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             if (lane == 0 && row0 < p.M) {  // a box that starts past the last row has nothing to write
               const int gcol = colh + (c & ~1) * 32;
               if (p.store_mode == 0) {
-                tma_store_5d(&tma_out, box, gcol, row0, b, 0, 0);
+                tma_store_5d(&outs.m[0], box, gcol, row0, b, 0, 0);
+                for (int i = 1; i < p.num_out; ++i) tma_store_5d(&outs.m[i], box, gcol, row0, b, 0, 0);
               } else {
                 const int cc = gcol / p.d, r_b = row0 / p.t1;
-                tma_store_5d(&tma_out, box, gcol - cc * p.d, row0 - r_b * p.t1, cc % p.t3, r_b, cc / p.t3);
+                for (int i = 0; i < p.num_out; ++i)
+                  tma_store_5d(&outs.m[i], box, gcol - cc * p.d, row0 - r_b * p.t1, cc % p.t3, r_b, cc / p.t3);
               }
               bulk_commit_group();
             }
@@ -657,18 +668,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 }
 
 template <int BN, bool BF16, int EPI>
-void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout, const GemmParams& p, int grid,
+void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout, const GemmParams& p, int grid,
                cudaStream_t stream) {
   using Cfg = TileCfg<BN>;
   static std::atomic<uint64_t> configured{0};
   opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_tc_kernel<BN, BF16, EPI, false>), Cfg::kSmemBytes);
-  gemm_tc_kernel<BN, BF16, EPI, false><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout, tout, p);
+  gemm_tc_kernel<BN, BF16, EPI, false><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout, ta, p);
   B200AIT_CUDA_CHECK(cudaGetLastError());
 }
 
 // CTA-pair variant: `grid` counts CTAs (twice the number of pairs); launched as clusters of two.
 template <int BN, bool BF16, int EPI>
-void launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout, const CUtensorMap& td0,
+void launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout, const CUtensorMap& td0,
                     const GemmParams& p, int grid, cudaStream_t stream) {
   using Cfg = TileCfg<BN, true, d0_box_of<EPI, true>()>;
   static std::atomic<uint64_t> configured{0};
@@ -702,26 +713,26 @@ void launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensor
 
 // Defined once per tile width in gemm_bn<BN>.cu.
 template <int BN>
-void launch_tc_width(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
+void launch_tc_width(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout,
                      const GemmParams& p, int grid, cudaStream_t stream);
 
 template <>
-void launch_tc_width<64>(bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int,
+void launch_tc_width<64>(bool, const CUtensorMap&, const CUtensorMap&, const OutMaps&, const GemmParams&, int,
                           cudaStream_t);
 template <>
-void launch_tc_width<128>(bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int,
+void launch_tc_width<128>(bool, const CUtensorMap&, const CUtensorMap&, const OutMaps&, const GemmParams&, int,
                           cudaStream_t);
 template <>
-void launch_tc_width<256>(bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int,
+void launch_tc_width<256>(bool, const CUtensorMap&, const CUtensorMap&, const OutMaps&, const GemmParams&, int,
                           cudaStream_t);
 
 // CTA-pair kernel, 256 x 256 tiles; defined in gemm_pair256.cu.
-void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
+void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout,
                        const CUtensorMap& td0, const GemmParams& p, int grid, cudaStream_t stream);
 
 #define B200AIT_DEFINE_LAUNCH_TC_WIDTH(BN_)                                                                    \
   template <>                                                                                                  \
-  void launch_tc_width<BN_>(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,  \
+  void launch_tc_width<BN_>(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout,  \
                             const GemmParams& p, int grid, cudaStream_t stream) {                              \
     if (bf16) {                                                                                                \
       launch_tc<BN_, true, -1>(ta, tb, tout, p, grid, stream);                                                 \

@@ -8,7 +8,7 @@ namespace b200ait {
     launch_tc_pair<256, false, (CODE)>(ta, tb, tout, td0, p, grid, stream);   \
     break;
 
-void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
+void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout,
                        const CUtensorMap& td0, const GemmParams& p, int grid, cudaStream_t stream) {
   if (bf16) {
     launch_tc_pair<256, true, -1>(ta, tb, tout, td0, p, grid, stream);

@@ -143,6 +143,35 @@ def gemm_rcr(
     return out
 
 
+def gemm_rcr_multi_out(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    out_ptrs: Sequence[int],
+    ldc: int,
+    d0: Optional[torch.Tensor] = None,
+    epilogue: str = "",
+    alpha: float = 1.0,
+    tile_n: int = 0,
+) -> None:
+    """epilogue(x @ w.T + bias [, d0]) written to every device address in `out_ptrs` (row stride `ldc`
+    elements): this GPU's buffer and peer-mapped pointers to other GPUs' buffers (see sharding.PeerBuffer)."""
+    _check_cuda(x, w, bias, d0)
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError(f"gemm_rcr_multi_out: K mismatch {tuple(x.shape)} vs {tuple(w.shape)}")
+    if not 1 <= len(out_ptrs) <= 8:
+        raise ValueError("gemm_rcr_multi_out: 1 to 8 output pointers")
+    outs = (c_void_p * len(out_ptrs))(*[c_void_p(int(q)) for q in out_ptrs])
+    code = _lib.load().b200ait_gemm_rcr_multi_out(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(d0), outs, len(out_ptrs), m, n, k, k, k, ldc,
+        d0.stride(0) if d0 is not None else n, epilogue_code(epilogue), _dtype_code(x), c_float(alpha), tile_n,
+        _stream(),
+    )
+    _lib.check(code, "b200ait_gemm_rcr_multi_out")
+
+
 def gemm_workspace_bytes(batch: int, m: int, n: int, k: int, tile_n: int = 0, split_k: int = 0) -> int:
     """Bytes of fp32 split-K scratch the library would use for this problem (0 = it would not split)."""
     out = c_int64(0)

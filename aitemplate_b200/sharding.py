@@ -63,3 +63,87 @@ def gather_columns(y_local: torch.Tensor, world: int, group=None,
     dist.all_gather_into_tensor(gathered.view(world * m, n_local), y_local.contiguous(), group=group)
     fn = relayout or _default_relayout
     return fn(gathered.view(world, m, n_local)).reshape(m, world * n_local)
+
+
+class PeerBuffer:
+    """A [rows, cols] device matrix on every rank of a one-node group, each rank holding pointers to all of
+    them (CUDA IPC through the library's b200ait_peer_* entry points; the 64-byte handles travel over the
+    process group). `ptrs[r]` is the address of rank r's matrix as seen from this process, `local` this rank's
+    matrix as a torch tensor (a view of the same memory, not a copy)."""
+
+    def __init__(self, rows: int, cols: int, dtype: torch.dtype, rank: int, world: int, group=None) -> None:
+        import ctypes
+
+        import torch.distributed as dist
+
+        from . import _lib
+
+        self._lib = _lib.load()
+        self.rank, self.world, self.shape, self.dtype = rank, world, (rows, cols), dtype
+        nbytes = rows * cols * torch.empty((), dtype=dtype).element_size()
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        _lib.check(self._lib.b200ait_peer_alloc(nbytes, ctypes.byref(ptr), handle), "b200ait_peer_alloc")
+        self._own = ptr.value
+        handles = [None] * world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.ptrs, self._opened = [], []
+        for r, h in enumerate(handles):
+            if r == rank:
+                self.ptrs.append(self._own)
+                continue
+            q = ctypes.c_void_p()
+            _lib.check(self._lib.b200ait_peer_open(ctypes.create_string_buffer(h, 64), ctypes.byref(q)),
+                       "b200ait_peer_open")
+            self.ptrs.append(q.value)
+            self._opened.append(q.value)
+        self.local = _tensor_from_ptr(self._own, (rows, cols), dtype)
+
+    def column_ptrs(self, col0: int) -> list:
+        """Addresses of column `col0` of row 0 in every rank's matrix, this rank's first."""
+        esz = torch.empty((), dtype=self.dtype).element_size()
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        return [self.ptrs[r] + col0 * esz for r in order]
+
+    def close(self) -> None:
+        import ctypes
+
+        for q in self._opened:
+            self._lib.b200ait_peer_close(ctypes.c_void_p(q))
+        self._opened = []
+        if self._own is not None:
+            self.local = None
+            self._lib.b200ait_peer_free(ctypes.c_void_p(self._own))
+            self._own = None
+
+
+def _tensor_from_ptr(ptr: int, shape, dtype: torch.dtype) -> torch.Tensor:
+    """A torch view of device memory this process did not allocate through torch."""
+
+    class _Holder:
+        pass
+
+    esz = torch.empty((), dtype=dtype).element_size()
+    numel = 1
+    for d in shape:
+        numel *= d
+    typestr = {torch.float16: "<f2", torch.bfloat16: "<V2", torch.float32: "<f4"}[dtype]
+    h = _Holder()
+    h.__cuda_array_interface__ = {"shape": (numel,), "typestr": "<f2" if esz == 2 else typestr, "data": (ptr, False),
+                                  "version": 3}
+    t = torch.as_tensor(h, device="cuda")
+    if dtype == torch.bfloat16:
+        t = t.view(torch.bfloat16)
+    return t.view(*shape)
+
+
+def gemm_rcr_nsplit_fused(x: torch.Tensor, w_shard: torch.Tensor, bias_shard: Optional[torch.Tensor], y: PeerBuffer,
+                          epilogue: str = "") -> None:
+    """N-split GEMM whose epilogue is the exchange step: this rank computes the column block
+    [rank N/g, (rank + 1) N/g) of Y = epilogue(X W^T + b) and its TMA stores place every tile in ALL ranks'
+    Y (own memory and peers' over NVLink) while the next tile is computed. The caller synchronises the ranks
+    before reading Y (every rank's kernel must have finished)."""
+    from . import kernels
+
+    n_local = w_shard.shape[0]
+    kernels.gemm_rcr_multi_out(x, w_shard, bias_shard, y.column_ptrs(y.rank * n_local), y.shape[1], epilogue=epilogue)

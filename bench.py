@@ -324,6 +324,10 @@ def run_ops_suite(args) -> None:
         print(json.dumps(row), flush=True)
 
 
+def flops_of(m: int, n: int, k: int) -> float:
+    return 2.0 * m * n * k
+
+
 def run_nsplit_suite(args, rank: int, world: int, local_rank: int) -> None:
     """BASELINE config 5 at M = 65536, N = K = 8192 on `world` GPUs, two partitionings:
     M-sharded (rows split, no collective) and N-split (weight rows split, X replicated, one NCCL
@@ -346,6 +350,10 @@ def run_nsplit_suite(args, rank: int, world: int, local_rank: int) -> None:
     y_rows = torch.empty((stop - start, n), dtype=torch.float16, device="cuda")
     w_r, b_r = sharding.split_weight_columns(w, b, world, rank)
     x_full = (torch.rand((m, k), generator=g, device="cuda") * 2 - 1).half()
+    if world > 1:  # the N-split forms need the same X, W and bias on every rank
+        for t in (x_full, w, b):
+            dist.broadcast(t, 0)
+        w_r, b_r = sharding.split_weight_columns(w, b, world, rank)
     y_cols = torch.empty((m, n // world), dtype=torch.float16, device="cuda")
     gathered = torch.empty((world * m, n // world), dtype=torch.float16, device="cuda")
 
@@ -377,6 +385,24 @@ def run_nsplit_suite(args, rank: int, world: int, local_rank: int) -> None:
             K.gemm_rcr(x_full, w_r, b_r, epilogue="relu", out=y_cols), world, gathered=gathered), iters)
     else:
         ms_gather, ms_total = 0.0, ms_gemm
+    # fused form: the GEMM epilogue's TMA stores write every tile into all ranks' row-major Y (peer pointers),
+    # so there is no gather pass; a rank's timed kernel ends when its own remote stores have completed
+    fused = None
+    if world > 1:
+        ybuf = sharding.PeerBuffer(m, n, torch.float16, rank, world)
+        ms_fused = timed(lambda: sharding.gemm_rcr_nsplit_fused(x_full, w_r, b_r, ybuf, "relu"), iters)
+        dist.barrier()
+        torch.cuda.synchronize()
+        want = sharding.gather_columns(K.gemm_rcr(x_full, w_r, b_r, epilogue="relu", out=y_cols), world,
+                                       gathered=gathered)
+        same = torch.tensor([1 if torch.equal(ybuf.local, want) else 0], device="cuda")
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        fused = {"total_ms": ms_fused, "tflops_total": flops_of(m, n, k) / (ms_fused / 1e3) / 1e12,
+                 "remote_store_bytes_per_rank": (world - 1) * m * (n // world) * 2,
+                 "collective": "none: epilogue TMA stores into peer memory over NVLink",
+                 "matches_all_gather_bitwise": bool(same.item())}
+        dist.barrier()
+        ybuf.close()
     flops = 2.0 * m * n * k
     if rank == 0:
         print(json.dumps({
@@ -385,6 +411,7 @@ def run_nsplit_suite(args, rank: int, world: int, local_rank: int) -> None:
             "n_split": {"gemm_ms": ms_gemm, "all_gather_relayout_ms": ms_gather, "total_ms": ms_total,
                         "tflops_total": flops / (ms_total / 1e3) / 1e12,
                         "gathered_bytes_per_rank": (world - 1) * m * (n // world) * 2, "collective": "ncclAllGather"},
+            "n_split_fused": fused,
         }), flush=True)
     if world > 1:
         dist.barrier()

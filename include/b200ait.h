@@ -59,6 +59,23 @@ int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void*
  * b200ait_gemm_rcr_workspace_bytes reports what the library would use for a problem. */
 int b200ait_gemm_rcr_workspace_bytes(int64_t batch, int64_t m, int64_t n, int64_t k, int tile_n, int split_k,
                                      int64_t* bytes_out);
+/* No counterpart in the reference (it is single-GPU: no communication backend anywhere under python/aitemplate
+ * or static/). The same GEMM with its result written to num_out buffers of identical shape and strides
+ * (1 <= num_out <= 8) by the epilogue's TMA stores. outs[0] is normally this GPU's buffer and the others
+ * peer-mapped pointers into other GPUs' buffers (b200ait_peer_open), so a rank that computes one column
+ * block of Y = X W^T places it in every rank's full Y while it computes the next tile, instead of an all-gather
+ * pass afterwards. Never splits K; needs N and ldc multiples of 8 and 16-byte aligned pointers. */
+int b200ait_gemm_rcr_multi_out(const void* a, const void* b, const void* bias, const void* d0, void* const* outs,
+                               int num_out, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                               int64_t ldd, int epilogue, int dtype, float alpha, int tile_n,
+                               b200ait_stream_t stream);
+/* Device buffers that other processes of the node can open (CUDA IPC; one process per GPU).
+ * b200ait_peer_alloc returns the pointer and a 64-byte handle to ship to the peers; b200ait_peer_open turns a
+ * received handle into a pointer valid in this process; close what was opened, free what was allocated. */
+int b200ait_peer_alloc(int64_t bytes, void** ptr_out, void* handle64_out);
+int b200ait_peer_open(const void* handle64, void** ptr_out);
+int b200ait_peer_close(void* opened_ptr);
+int b200ait_peer_free(void* allocated_ptr);
 /* No counterpart in the reference. b200ait_gemm_rcr for callers that cannot allocate device memory
  * (a serving process living inside a pre-sized pool, a framework allocator that owns the device, a
  * path that must avoid driver allocation calls): the split-K partial sums and the kernel status

@@ -146,6 +146,29 @@ def test_cta_pair_tiles_bf16_and_permuted_store():
     _close(yb, oracle.gemm_rcr(xb, wb, bb, db, epilogue="add"), atol=5e-2, rtol=5e-2)
 
 
+@pytest.mark.parametrize("m,n,kk,epilogue,num_out", [(1024, 768, 512, "relu", 2), (300, 264, 128, "add", 3),
+                                                      (4096, 1024, 1024, "", 8)])
+def test_multi_destination_store(m, n, kk, epilogue, num_out):
+    # the N-split exchange form: every tile is TMA-stored into several buffers of a wider row-major matrix
+    # (here all on this GPU; on several GPUs the extra pointers are peer mappings)
+    k = _kernels()
+    x = _rand((m, kk), 320, dist="uniform")
+    w = _rand((n, kk), 321, scale=0.05)
+    b = _rand((n,), 322, scale=0.1)
+    d0 = _rand((m, n), 323) if epilogue == "add" else None
+    ldc, col0 = 2 * n + 64, 64
+    bufs = [torch.full((m, ldc), 7.0, dtype=torch.float16, device="cuda") for _ in range(num_out)]
+    ptrs = [t.data_ptr() + col0 * 2 for t in bufs]
+    k.gemm_rcr_multi_out(x.cuda(), w.cuda(), b.cuda(), ptrs, ldc, d0=None if d0 is None else d0.cuda(),
+                         epilogue=epilogue)
+    assert k.device_status() == 0
+    want = oracle.gemm_rcr(x, w, b, *([d0] if d0 is not None else []), epilogue=epilogue)
+    for t in bufs:
+        _close(t[:, col0:col0 + n], want)
+        assert torch.equal(t[:, col0:col0 + n], bufs[0][:, col0:col0 + n])
+        assert bool((t[:, :col0] == 7.0).all()) and bool((t[:, col0 + n:] == 7.0).all())  # nothing outside the block
+
+
 def test_no_bias_and_alpha():
     k = _kernels()
     x = _rand((300, 320), 40)
