@@ -4,7 +4,8 @@ Same signature and validation as the reference (python/aitemplate/compiler/compi
 where the reference renders C++ per op, runs nvcc and links `test.so`, this build lowers the graph to
 a *plan* for the prebuilt runtime in libb200ait.so:
 
-  toposort -> remove_no_ops -> mark_param_tensor -> fuse_mm_elementwise -> name_graph
+  toposort -> remove_no_ops -> mark_param_tensor -> fuse_mm_elementwise -> split_to_views -> fuse_strided_cat
+  -> name_graph
   -> memory_planning -> write <workdir>/<test_name>/<dll_name>.plan (+ constants.bin) -> Model(plan)
 
 There is no profiling step (tile choice happens inside the library at launch) and no code
@@ -22,6 +23,7 @@ from .dtype import dtype_str_to_enum
 from .model import Model
 from .transform import (
     fuse_mm_elementwise,
+    fuse_strided_cat,
     mark_param_tensor,
     memory_planning,
     name_graph,
@@ -105,11 +107,13 @@ def _lower_to_plan(sorted_graph: List[Tensor], outputs: List[Tensor], test_name:
         if t._attrs["is_input"] and t._attrs["is_view_of"] is None:
             index[id(t)] = emit(t, KIND_INPUT, len(input_slots), 0, -1)
             input_slots.append(index[id(t)])
-    for t in sorted_graph:
+    def place(t: Tensor) -> None:
         if id(t) in index or t.is_a_const_num():
-            continue
+            return
         view_of = t._attrs["is_view_of"]
         if view_of is not None:
+            place(view_of)  # the runtime wants a base before its views (a producer fused into a concat
+            # aliases the concat output, which comes later in graph order)
             alias = t._attrs["name"] + "__alias" if t._attrs.get("own_output_slot") is not None else None
             index[id(t)] = emit(t, KIND_VIEW, -1, t._attrs.get("view_offset_bytes", 0), index[id(view_of)], name=alias)
         elif t._attrs["is_param"]:
@@ -118,6 +122,9 @@ def _lower_to_plan(sorted_graph: List[Tensor], outputs: List[Tensor], test_name:
             index[id(t)] = emit(t, KIND_OUTPUT, t._attrs["output_slot"], 0, -1)
         else:
             index[id(t)] = emit(t, KIND_BLOB, -1, t._attrs["offset"], -1)
+
+    for t in sorted_graph:
+        place(t)
     op_lines: List[str] = []
 
     def op_line(kernel: str, name: str, operands, outs, ints, floats) -> None:
@@ -222,6 +229,7 @@ def compile_model(
         graph = fuse_mm_elementwise(graph, outputs)
         mark_param_tensor(graph)
         split_to_views(graph)
+        fuse_strided_cat(graph)
     name_graph(graph)
     copies = _assign_storage(graph, outputs)
     blob_bytes, constants_bytes = memory_planning(graph)

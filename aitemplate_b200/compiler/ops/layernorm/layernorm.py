@@ -85,4 +85,7 @@ class layernorm(Operator):
         n = 1
         for d in self._attrs["normalized_shape"]:
             n *= d.value()
-        return {"kernel": "layernorm", "operands": [x, gamma, beta], "ints": [n], "floats": [float(self._attrs["eps"])]}
+        acc = self._attrs["output_accessors"][0]
+        out_stride = acc.row_stride() if acc.stride_dim is not None else 0  # 0: contiguous rows of n
+        return {"kernel": "layernorm", "operands": [x, gamma, beta], "ints": [n, acc.offset, out_stride],
+                "floats": [float(self._attrs["eps"])]}

@@ -1,0 +1,69 @@
+"""Strided-output ("memory") fusion into concatenate.
+
+A GEMM or layernorm whose only consumer is a concatenate along the last dim can write its rows straight into
+the concatenated buffer: the producer's output TensorAccessor is re-based onto the concat output (element
+offset of its column block + the wider row stride), the producer's own tensor becomes an alias of that
+buffer, and the concat's input mask for it is cleared so the copy kernel skips it. A concat whose inputs are
+all fused launches nothing. This is the "cat pattern" of the reference's pass
+(python/aitemplate/compiler/transform/transform_strided_ops.py:94-333, with the accessor arithmetic of
+python/aitemplate/compiler/tensor_accessor.py:349-404), restricted to the producers of this path whose kernels
+take an output offset and row stride: the gemm_rcr family without a permuted store, and layernorm.
+"""
+from __future__ import annotations
+
+from typing import List
+
+from ..base import IntImm, Tensor
+from .toposort import sorted_ops
+
+
+def _fusible_producer(op) -> bool:
+    from ..ops.gemm_universal.gemm_rcr import gemm
+    from ..ops.layernorm import layernorm
+
+    if isinstance(op, gemm):
+        return op._attrs.get("layout") is None
+    return isinstance(op, layernorm)
+
+
+def fuse_strided_cat(sorted_graph: List[Tensor]) -> int:
+    """Applies the fusion wherever it is legal; returns the number of concat inputs that were fused."""
+    from ..ops.tensor import concatenate
+
+    fused = 0
+    for op in sorted_ops(sorted_graph):
+        if not isinstance(op, concatenate):
+            continue
+        out = op._attrs["outputs"][0]
+        shape = out._attrs["shape"]
+        dim = op._attrs["concat_dim"]
+        if dim != len(shape) - 1 or not isinstance(shape[dim], IntImm):
+            continue  # rows of the producers must map to rows of the buffer
+        inputs = op._attrs["original_inputs"]
+        offset = 0
+        for i, x in enumerate(inputs):
+            xs = x._attrs["shape"]
+            if len(xs) != len(shape) or not isinstance(xs[dim], IntImm):
+                break  # an empty placeholder or a dynamic width: offsets after it are unknown
+            width = xs[dim].value()
+            src = list(x._attrs["src_ops"])
+            ok = (
+                op._attrs["input_masks"][i]
+                and len(src) == 1
+                and _fusible_producer(src[0])
+                and len(src[0]._attrs["outputs"]) == 1
+                and set(x._attrs["dst_ops"]) == {op}
+                and sum(1 for y in inputs if y is x) == 1
+                and not x._attrs["is_output"]
+                and x._attrs["is_view_of"] is None
+                and src[0]._attrs["output_accessors"][0].stride_dim is None
+                and width > 0
+            )
+            if ok:
+                src[0]._attrs["output_accessors"][0].update_base_tensor(out, dim, offset)
+                x._attrs["is_view_of"] = out       # same storage; the accessor carries offset and stride
+                x._attrs["view_offset_bytes"] = 0
+                op._attrs["input_masks"][i] = False
+                fused += 1
+            offset += width
+    return fused

@@ -478,8 +478,12 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     int64_t numel = 1;
     for (auto d : xs) numel *= d;
     const int64_t m = n ? numel / n : 0;
-    check(b200ait_layernorm(ptr_of(out0), ptr_of(x), ptr_of(in(1)), ptr_of(in(2)), m, n,
-                            static_cast<float>(op.floats[0]), 0, 0, T[x].dtype, stream),
+    // ints[1], ints[2]: element offset and row stride of the output when it is a column block of a wider
+    // buffer (a layernorm fused into a concatenate); 0 stride = contiguous rows
+    const int64_t out_off = op.ints.size() > 2 ? op.ints[1] : 0, out_stride = op.ints.size() > 2 ? op.ints[2] : 0;
+    uint8_t* y = static_cast<uint8_t*>(ptr_of(out0)) + out_off * dtype_size(T[out0].dtype);
+    check(b200ait_layernorm(y, ptr_of(x), ptr_of(in(1)), ptr_of(in(2)), m, n, static_cast<float>(op.floats[0]), 0,
+                            out_stride, T[x].dtype, stream),
           op);
     return;
   }

@@ -8,6 +8,7 @@ from aitemplate_b200.compiler.base import IntImm, IntVar, Tensor
 from aitemplate_b200.compiler.ops import FuncEnum
 from aitemplate_b200.compiler.transform import (
     fuse_mm_elementwise,
+    fuse_strided_cat,
     mark_param_tensor,
     memory_planning,
     name_graph,
@@ -30,10 +31,23 @@ def _lower(outs, fuse=True):
         g = fuse_mm_elementwise(g, outs)
         mark_param_tensor(g)
         split_to_views(g)
+        fuse_strided_cat(g)
     name_graph(g)
     copies = C._assign_storage(g, outs)
     blob, consts = memory_planning(g)
     return g, C._lower_to_plan(g, outs, "t", blob, consts, copies, None, {}), blob, consts
+
+
+def _parse_op(line):
+    """op <kernel> <name> <n> operands.. <n> outputs.. <n> ints.. <n> floats.."""
+    tok = line.split()
+    pos = 3
+    fields = {}
+    for key, conv in (("operands", int), ("outputs", int), ("ints", int), ("floats", float)):
+        n = int(tok[pos])
+        fields[key] = [conv(v) for v in tok[pos + 1:pos + 1 + n]]
+        pos += 1 + n
+    return fields
 
 
 def _out(t, name):
@@ -179,6 +193,50 @@ def test_sd_transformer_block_plan():
     assert kernels == ["layernorm"] + attn + ["layernorm"] + attn + ["layernorm", "gemm_rcr", "gemm_rcr", "gemm_rcr"]
     assert consts >= 2 * (4 * 320 * 320 + 2 * 320 * 768 + 2 * 320 * 320 + 3 * 1280 * 320)
     assert blob >= 2 * 4096 * 1280 * 2
+
+
+def test_strided_cat_fusion_plan():
+    # the reference's "cat pattern" (tests/unittest/compiler/test_strided_op_cat_pattern.py): GEMMs and a layernorm
+    # feeding a last-dim concatenate write straight into its buffer; an input from outside keeps its copy
+    x = Tensor([IntVar([1, 64], name="m"), 128], name="x", is_input=True)
+    z = Tensor([IntVar([1, 64], name="m"), 24], name="z", is_input=True)
+    w1, b1 = Tensor([96, 128], name="w1"), Tensor([96], name="b1")
+    w2 = Tensor([40, 128], name="w2")
+    g1 = ops.gemm_rcr_bias_relu()(x, w1, b1)
+    g2 = ops.gemm_rcr()(x, w2)
+    ln = ops.layernorm()(x, None, None, [IntImm(128)], 1e-5)
+    y = _out(ops.concatenate()([g1, z, g2, ln], dim=1), "y")
+    g, plan, blob, consts = _lower([y])
+    lines = plan.splitlines()
+    cat = _parse_op(next(l for l in lines if l.startswith("op concatenate")))
+    assert cat["ints"] == [1, 4, 0, 1, 0, 0]                                # dim, count, masks: only z is copied
+    gemms = [_parse_op(l) for l in lines if l.startswith("op gemm_rcr")]
+    assert [g_["ints"][-2:] for g_ in gemms] == [[0, 288], [96 + 24, 288]]   # (offset, row stride) in elements
+    lnl = _parse_op(next(l for l in lines if l.startswith("op layernorm")))
+    assert lnl["ints"] == [128, 96 + 24 + 40, 288]
+    # the producers' tensors alias the concat output, which is emitted before them
+    tl = [l.split() for l in lines if l.startswith("tensor ")]
+    idx_y = next(i for i, t in enumerate(tl) if t[1] == "y")
+    views = [t for t in tl if t[3] == "4" and int(t[6]) == idx_y]
+    assert len(views) == 3 and all(tl.index(v) > idx_y for v in views)
+
+
+def test_strided_cat_fusion_is_skipped_when_illegal():
+    x = Tensor([8, 64], name="x", is_input=True)
+    w = Tensor([32, 64], name="w")
+    g1 = ops.gemm_rcr()(x, w)
+    g2 = ops.gemm_rcr()(x, w)
+    both = ops.concatenate()([g1, g2], dim=0)            # not the last dim
+    y0 = _out(both, "y0")
+    _, plan, _, _ = _lower([y0])
+    assert _parse_op(next(l for l in plan.splitlines() if l.startswith("op concatenate")))["ints"] == [0, 2, 1, 1]
+    g3 = ops.gemm_rcr()(x, w)
+    y1 = _out(ops.concatenate()([g3, g3], dim=1), "y1")   # the same tensor twice
+    g4 = _out(ops.gemm_rcr()(x, w), "g4")                 # a graph output of its own
+    y2 = _out(ops.concatenate()([g4, x], dim=1), "y2")
+    _, plan, _, _ = _lower([y1, y2, g4])
+    cats = [l for l in plan.splitlines() if l.startswith("op concatenate")]
+    assert all(_parse_op(c)["ints"] == [1, 2, 1, 1] for c in cats)
 
 
 def test_output_aliasing_input_gets_a_copy():

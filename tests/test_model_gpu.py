@@ -278,6 +278,38 @@ def test_sd_transformer_block_matches_oracle(workdir, tokens):
         _close(res["output_0"], want, 2e-2)
 
 
+@pytest.mark.parametrize("m", [64, 1000])
+def test_strided_output_fusion_into_concat(workdir, m):
+    # GEMMs and a layernorm write their column blocks straight into the concatenated buffer
+    # (tests/unittest/compiler/test_strided_op_cat_pattern.py, test_strided_layernorm.py); widths chosen so that
+    # one block starts 16-byte aligned (vector / TMA store) and one does not (scalar store path)
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    from aitemplate_b200.frontend import IntImm
+
+    kdim = 128
+    x = Tensor([m, kdim], name="x", is_input=True)
+    z = Tensor([m, 20], name="z", is_input=True)
+    w1, b1 = Tensor([96, kdim], name="w1"), Tensor([96], name="b1")
+    w2 = Tensor([264, kdim], name="w2")
+    g1 = ops.gemm_rcr_bias_relu()(x, w1, b1)
+    g2 = ops.gemm_rcr()(x, w2)
+    ln = ops.layernorm()(x, None, None, [IntImm(kdim)], 1e-5)
+    y = ops.concatenate()([g1, z, g2, ln], dim=1)
+    y._attrs["name"], y._attrs["is_output"] = "y", True
+    module = compile_model(y, detect_target(), workdir, "strided_cat")
+    plan = open(os.path.join(workdir, "strided_cat", "test.so.plan")).read()
+    assert [l for l in plan.splitlines() if l.startswith("op concatenate")][0].split()[-7:-1] == ["1", "4", "0", "1", "0", "0"]
+    xd, zd = _rand((m, kdim), 1), _rand((m, 20), 2)
+    w1d, b1d, w2d = _rand((96, kdim), 3, 0.05), _rand((96,), 4, 0.1), _rand((264, kdim), 5, 0.05)
+    module.set_many_constants_with_tensors({"w1": w1d.cuda(), "b1": b1d.cuda(), "w2": w2d.cuda()})
+    out = torch.full((m, 96 + 20 + 264 + kdim), 9.0, dtype=torch.float16, device="cuda")
+    res = module.run_with_tensors({"x": xd.cuda(), "z": zd.cuda()}, {"y": out})["y"]
+    want = torch.cat([oracle.gemm_rcr(xd, w1d, b1d, epilogue="relu"), zd.float(), oracle.gemm_rcr(xd, w2d),
+                      oracle.layernorm(xd, None, None)], dim=1)
+    _close(res, want, 1e-2)
+    assert torch.equal(res[:, 96:116].cpu(), zd)  # the copied block is bit-exact
+
+
 def test_concurrent_runs_share_the_pool(workdir):
     import threading
 
