@@ -146,6 +146,36 @@ def bench_concat_split(config: str, peaks: Dict) -> List[Dict]:
             _row(config, "split", "[8192x4096] -> 4 parts", ms_s, 0.0, nbytes, "hbm", peaks)]
 
 
+def bench_sd_block(config: str, peaks: Dict) -> Dict:
+    """The whole Stable-Diffusion UNet transformer block of BASELINE configuration 3 through compile_model() and
+    Model.benchmark_with_tensors() in graph mode (22 kernels per run)."""
+    import tempfile
+
+    from ..compiler import compile_model
+    from . import detect_target, workloads
+
+    batch = 2
+    x, context, params = workloads.sd_block_inputs(batch)
+    y = workloads.build_sd_block(batch)
+    module = compile_model(y, detect_target(), tempfile.mkdtemp(prefix="b200ait_sd_"), "sd_block")
+    module.set_many_constants_with_tensors({k: v.cuda() for k, v in params.items()})
+    out = torch.empty((batch, 4096, 320), dtype=torch.float16, device="cuda")
+    ins = {"latent": x.cuda(), "context": context.cuda()}
+    module.run_with_tensors(ins, {"output_0": out}, graph_mode=True)
+    time.sleep(0.2)
+    mean_ms, _, _ = module.benchmark_with_tensors(ins, {"output_0": out}, count=20, repeat=3, graph_mode=True)
+    tokens, dim, ctx, cdim = 4096, 320, 77, 768
+    gemm = 2.0 * batch * (tokens * dim * dim * 4 + tokens * dim * dim * 2 + 2 * ctx * cdim * dim
+                          + 2 * tokens * dim * 4 * dim + tokens * 4 * dim * dim)
+    attn = 4.0 * batch * 8 * tokens * (tokens + ctx) * 40
+    row = {"config": config, "op": "sd_transformer_block (22 kernels, graph mode)", "shape": "B2 4096x320, ctx 77x768",
+           "us": round(mean_ms * 1e3, 2), "bound": "tensor"}
+    tf = (gemm + attn) / (mean_ms * 1e-3) / 1e12
+    row.update(tflops=round(tf, 1), frac_measured=round(tf / peaks["tflops_burst"], 3),
+               frac_nominal=round(tf / NOMINAL_TFLOPS, 3))
+    return row
+
+
 def run_suite(peaks: Dict) -> List[Dict]:
     rows: List[Dict] = []
     rows.append(bench_gemm("1", 256, 3072, 768, "fast_gelu", peaks))
@@ -167,6 +197,7 @@ def run_suite(peaks: Dict) -> List[Dict]:
     rows.append(bench_gemm("4", 8192, 1280, 320, "mul", peaks, residual=True))
     rows.append(bench_gemm("4", 8192, 320, 1280, "add", peaks, residual=True))
     rows.append(bench_layernorm("4", 8192, 320, 1e-5, peaks))
+    rows.append(bench_sd_block("4", peaks))
     rows.append(bench_bmm("5", 1024, 512, 512, 64, peaks))
     for m in (1, 16, 128, 1024, 8192, 65536):  # the seconds-long cases last: they leave the GPU power-capped
         rows.append(bench_gemm("5", m, 8192, 8192, "relu", peaks, w_scale=0.01))
