@@ -438,8 +438,8 @@ class IntVarTensor(Tensor):
 
 
 class DynamicProfileStrategy(Enum):
-    """Accepted for API compatibility (python/aitemplate/compiler/base.py:1081-1093); kernels here are
-    prebuilt and tile selection happens at launch, so the strategy has no effect."""
+    """Which size of a dynamic M the compile-time GEMM profiler times (python/aitemplate/compiler/base.py:1081-1093):
+    MAX the upper bound (default), MIN the lower bound; HINTS is treated as MAX."""
 
     MIN = 1
     MAX = 2

@@ -8,9 +8,11 @@ a *plan* for the prebuilt runtime in libb200ait.so:
   -> name_graph
   -> memory_planning -> write <workdir>/<test_name>/<dll_name>.plan (+ constants.bin) -> Model(plan)
 
-There is no profiling step (tile choice happens inside the library at launch) and no code
-generation; `profile_devs`, `dynamic_profiling_strategy`, `profile_dir`, `profile_timeout` and
-`debug_settings` are accepted for compatibility and ignored.
+There is no code generation. Profiling is optional: by default the library's planner picks tile width and
+split-K at launch; with `profile_devs` given (or AIT_B200_PROFILE=1) every gemm_rcr-family op is timed over
+the launch configurations on the current GPU, per `dynamic_profiling_strategy` for dynamic M, and the winners
+are written into the plan and kept in a cache file (`profile_dir`, default ~/.aitemplate_b200).
+`profile_timeout` and `debug_settings` are accepted for compatibility and ignored.
 """
 from __future__ import annotations
 
@@ -181,6 +183,25 @@ def _lower_to_plan(sorted_graph: List[Tensor], outputs: List[Tensor], test_name:
     return "\n".join(lines) + "\n"
 
 
+def _profile(graph: List[Tensor], profile_dir: Optional[str], strategy) -> None:
+    """Compile-time GEMM profiling (python/aitemplate/compiler/compiler.py:286-306 in the reference)."""
+    from ..backend.profiler_cache import GemmProfileCache
+    from .transform.profile import cuda_gemm_timer, profile_gemms
+
+    cache = GemmProfileCache(os.path.join(profile_dir, "gemm_profile_cache.json") if profile_dir else None)
+    timer, device = None, ""
+    try:
+        import torch
+
+        if torch.cuda.is_available():
+            timer, device = cuda_gemm_timer, torch.cuda.get_device_name()
+    except ImportError:
+        pass
+    if timer is None:
+        _LOGGER.warning("no CUDA device: only cached GEMM profiles are applied")
+    profile_gemms(graph, cache, timer, use_max=strategy != DynamicProfileStrategy.MIN, device_name=device)
+
+
 def compile_model(
     tensor: Union[Tensor, List[Tensor]],
     target,
@@ -231,6 +252,8 @@ def compile_model(
         split_to_views(graph)
         fuse_strided_cat(graph)
     name_graph(graph)
+    if profile_devs is not None or os.getenv("AIT_B200_PROFILE", "0") == "1":
+        _profile(graph, profile_dir, dynamic_profiling_strategy)
     copies = _assign_storage(graph, outputs)
     blob_bytes, constants_bytes = memory_planning(graph)
     bound: Dict[str, tuple] = {}

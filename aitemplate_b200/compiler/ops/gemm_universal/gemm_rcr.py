@@ -93,7 +93,9 @@ class gemm(Operator):
         return {
             "kernel": "gemm_rcr",
             "operands": [a, b, bias, d0, d1],
-            "ints": [epilogue_code(*self._epi), store_mode, t[0], t[1], t[2], acc.offset, out_stride],
+            # the last two: tile width and split-K picked by the compile-time profiler (0 = the library decides)
+            "ints": [epilogue_code(*self._epi), store_mode, t[0], t[1], t[2], acc.offset, out_stride,
+                     int(self._attrs.get("tile_n", 0)), int(self._attrs.get("split_k", 0))],
             "floats": [float(self._attrs["alpha"])],
         }
 

@@ -275,7 +275,10 @@ class Executor {
         for (size_t i = 0; i + 1 < a.dims.size(); ++i)
           m *= a.dims[i].is_static ? a.dims[i].v : (bound ? plan.dims[a.dims[i].v].hi : plan.dims[a.dims[i].v].lo);
         int64_t bytes = 0;
-        if (b200ait_gemm_rcr_workspace_bytes(1, m, b.dims[0].v, a.dims.back().v, 0, 0, &bytes) == 0)
+        // ints[7], ints[8]: tile width and split-K chosen by the compile-time profiler (0 = library decides)
+        const int tile_hint = op.ints.size() > 8 ? static_cast<int>(op.ints[7]) : 0;
+        const int split_hint = op.ints.size() > 8 ? static_cast<int>(op.ints[8]) : 0;
+        if (b200ait_gemm_rcr_workspace_bytes(1, m, b.dims[0].v, a.dims.back().v, tile_hint, split_hint, &bytes) == 0)
           workspace_bytes_ = std::max(workspace_bytes_, bytes);
       }
     }
@@ -432,11 +435,13 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     bind_shape(out0, os, "gemm output");
     if (!launch) return;
     const int64_t out_off = op.ints[5], out_stride = op.ints[6];
+    const int tile_hint = op.ints.size() > 8 ? static_cast<int>(op.ints[7]) : 0;
+    const int split_hint = op.ints.size() > 8 ? static_cast<int>(op.ints[8]) : 0;
     uint8_t* c = static_cast<uint8_t*>(ptr_of(out0)) + out_off * dtype_size(T[out0].dtype);
     check(b200ait_gemm_rcr(ptr_of(a), ptr_of(b), ptr_of(bias), ptr_of(d0), ptr_of(d1), c, 1, m, n, k, k, k,
                            out_stride, n, 0, 0, 0, 0, static_cast<int>(op.ints[0]), T[a].dtype,
                            static_cast<float>(op.floats[0]), static_cast<int>(op.ints[1]), op.ints[2], op.ints[3],
-                           op.ints[4], 0, workspace_, workspace_bytes_, 0, stream),
+                           op.ints[4], tile_hint, workspace_, workspace_bytes_, split_hint, stream),
           op);
     return;
   }

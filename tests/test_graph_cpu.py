@@ -211,7 +211,7 @@ def test_strided_cat_fusion_plan():
     cat = _parse_op(next(l for l in lines if l.startswith("op concatenate")))
     assert cat["ints"] == [1, 4, 0, 1, 0, 0]                                # dim, count, masks: only z is copied
     gemms = [_parse_op(l) for l in lines if l.startswith("op gemm_rcr")]
-    assert [g_["ints"][-2:] for g_ in gemms] == [[0, 288], [96 + 24, 288]]   # (offset, row stride) in elements
+    assert [g_["ints"][5:7] for g_ in gemms] == [[0, 288], [96 + 24, 288]]   # (offset, row stride) in elements
     lnl = _parse_op(next(l for l in lines if l.startswith("op layernorm")))
     assert lnl["ints"] == [128, 96 + 24 + 40, 288]
     # the producers' tensors alias the concat output, which is emitted before them
@@ -237,6 +237,55 @@ def test_strided_cat_fusion_is_skipped_when_illegal():
     _, plan, _, _ = _lower([y1, y2, g4])
     cats = [l for l in plan.splitlines() if l.startswith("op concatenate")]
     assert all(_parse_op(c)["ints"] == [1, 2, 1, 1] for c in cats)
+
+
+def test_gemm_profile_cache_and_plan_hints(tmp_path):
+    # compile-time profiling with a stand-in timer: the winner lands in the cache file and in the plan's gemm ints;
+    # a second graph with the same problem is served from the cache without timing anything
+    from aitemplate_b200.backend.profiler_cache import GemmProfileCache, gemm_key
+    from aitemplate_b200.compiler.transform.profile import CANDIDATES, profile_gemms
+
+    def graph():
+        x = Tensor([IntVar([1, 512], name="m"), 256], name="x", is_input=True)
+        w, b = Tensor([384, 256], name="w"), Tensor([384], name="b")
+        return _out(ops.gemm_rcr_bias_relu()(x, w, b), "y")
+
+    calls = []
+
+    def timer(op, m, n, k, tile_n, split_k):
+        calls.append((m, n, k, tile_n, split_k))
+        if tile_n == 512:
+            return None                      # "not legal for this problem"
+        return 100.0 - (50.0 if (tile_n, split_k) == (128, 2) else 0.0) + tile_n * 1e-3
+
+    path = str(tmp_path / "cache.json")
+    y = graph()
+    reset_name_counters()
+    g = toposort([y])
+    mark_param_tensor(g)
+    name_graph(g)
+    chosen = profile_gemms(g, GemmProfileCache(path), timer, use_max=True, device_name="fake")
+    assert list(chosen.values()) == [(128, 2)] and len(calls) == len(CANDIDATES)
+    assert all(c[:3] == (512, 384, 256) for c in calls)      # the upper bound of the dynamic M was timed
+    assert GemmProfileCache(path).lookup(gemm_key("gemm_rcr_bias_relu", "float16", 512, 384, 256, "", "fake")) == (128, 2)
+    copies = C._assign_storage(g, [y])
+    blob, consts = memory_planning(g)
+    plan = C._lower_to_plan(g, [y], "t", blob, consts, copies, None, {})
+    assert _parse_op(next(l for l in plan.splitlines() if l.startswith("op gemm_rcr")))["ints"][7:9] == [128, 2]
+    calls.clear()
+    y2 = graph()
+    g2 = toposort([y2])
+    mark_param_tensor(g2)
+    name_graph(g2)
+    assert list(profile_gemms(g2, GemmProfileCache(path), timer, device_name="fake").values()) == [(128, 2)]
+    assert calls == []
+    # lower bound strategy times M = 1 instead
+    y3 = graph()
+    g3 = toposort([y3])
+    mark_param_tensor(g3)
+    name_graph(g3)
+    profile_gemms(g3, GemmProfileCache(path), timer, use_max=False, device_name="fake")
+    assert calls and all(c[0] == 1 for c in calls)
 
 
 def test_output_aliasing_input_gets_a_copy():

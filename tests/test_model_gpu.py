@@ -310,6 +310,32 @@ def test_strided_output_fusion_into_concat(workdir, m):
     assert torch.equal(res[:, 96:116].cpu(), zd)  # the copied block is bit-exact
 
 
+def test_compile_time_gemm_profiling(workdir):
+    # profile_devs given: every GEMM of the graph is timed over the launch configurations, the winners go into the
+    # plan and a cache file, and the model still matches the oracle
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    from aitemplate_b200.backend.profiler_cache import GemmProfileCache
+
+    m, k, n = 512, 1024, 768
+    x = Tensor([m, k], name="x", is_input=True)
+    w, b = Tensor([n, k], name="w"), Tensor([n], name="b")
+    y = ops.gemm_rcr_bias_fast_gelu()(x, w, b)
+    y._attrs["name"], y._attrs["is_output"] = "y", True
+    module = compile_model(y, detect_target(), workdir, "profiled", profile_devs=[0], profile_dir=workdir)
+    cache = GemmProfileCache(os.path.join(workdir, "gemm_profile_cache.json"))
+    assert len(cache.entries) == 1
+    (entry,) = cache.entries.values()
+    assert entry["tile_n"] in (64, 128, 256, 512) and entry["us"] > 0
+    plan = open(os.path.join(workdir, "profiled", "test.so.plan")).read()
+    gemm_line = next(l for l in plan.splitlines() if l.startswith("op gemm_rcr")).split()
+    assert str(entry["tile_n"]) in gemm_line and plan.count("op gemm_rcr") == 1
+    xd, wd, bd = _rand((m, k), 1), _rand((n, k), 2, 0.02), _rand((n,), 3, 0.02)
+    module.set_many_constants_with_tensors({"w": wd.cuda(), "b": bd.cuda()})
+    out = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    res = module.run_with_tensors({"x": xd.cuda()}, {"y": out})["y"]
+    _close(res, oracle.gemm_rcr(xd, wd, bd, epilogue="fast_gelu"), 1e-2)
+
+
 def test_concurrent_runs_share_the_pool(workdir):
     import threading
 
