@@ -42,6 +42,10 @@ def _signatures():
                                                c_void_p, c_int64, c_int, c_void_p],
         ),
         "b200ait_gemm_rcr_workspace_bytes": (c_int, [c_int64] * 4 + [c_int, c_int, I64P]),
+        "b200ait_gemm_rrr": (
+            c_int,
+            [c_void_p] * 6 + [c_int64] * 12 + [c_int, c_int, c_float, c_int, c_void_p, c_int64, c_int, c_void_p],
+        ),
         "b200ait_gemm_rcr_multi_out": (
             c_int,
             [c_void_p] * 4 + [POINTER(c_void_p), c_int] + [c_int64] * 7 + [c_int, c_int, c_float, c_int, c_void_p],

@@ -1,4 +1,4 @@
-"""bmm_rcr graph node: C[b] = alpha * A[b] @ B[b]^T, A [B, M, K], B [B, N, K]
+"""bmm_rcr / bmm_rrr graph nodes: C[b] = alpha * A[b] @ B[b]^T, A [B, M, K], B [B, N, K]
 (python/aitemplate/compiler/ops/gemm_universal/bmm.py:69-119, bmm_xxx.py:261-278).
 A 2-D operand, or a batch of 1, broadcasts over the other operand's batch."""
 from __future__ import annotations
@@ -58,3 +58,26 @@ class bmm_rcr(bmm):
     def _lower(self) -> Dict[str, Any]:
         a, b = self._attrs["inputs"]
         return {"kernel": "bmm_rcr", "operands": [a, b], "ints": [], "floats": [float(self._attrs["alpha"])]}
+
+
+class bmm_rrr(bmm):
+    """C[b] = alpha * A[b] @ B[b], A [B, M, K], B [B, K, N]
+    (python/aitemplate/compiler/ops/gemm_universal/bmm_xxx.py:223-260)."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self._attrs["op"] = "bmm_rrr"
+
+    def _infer_shapes(self, a: Tensor, b: Tensor) -> List[IntVar]:
+        a_shape, b_shape = a._attrs["shape"], b._attrs["shape"]
+        if a_shape[-1] != b_shape[-2]:
+            raise RuntimeError(f"bmm_rrr operand A and B should have the same K dim! A: {a_shape}, B: {b_shape}")
+        return [self._batch_dim(a, b), a_shape[-2], b_shape[-1]]
+
+    def __call__(self, a: Tensor, b: Tensor) -> Tensor:
+        self._sanity_check(a, b)
+        return self._finish([a, b], self._infer_shapes(a, b))
+
+    def _lower(self) -> Dict[str, Any]:
+        a, b = self._attrs["inputs"]
+        return {"kernel": "bmm_rrr", "operands": [a, b], "ints": [], "floats": [float(self._attrs["alpha"])]}

@@ -291,3 +291,58 @@ class gemm_rcr_permute(gemm_rcr):
         if m.value() % t1 or n.value() % t2:
             raise RuntimeError(f"permute shape {self._attrs['shape']} does not divide M={m.value()}, N={n.value()}")
         return reshape()(out, [m.value() // t1, t2, t1, n.value() // t2])
+
+
+# ---- row-major B ("rrr"): Y = X @ W + bias with W stored [K, N]
+# (python/aitemplate/compiler/ops/gemm_universal/gemm_rrr.py:26-80, gemm_rrr_bias.py). Same kernel; the runtime
+# hands the tensor core W as an MN-major operand.
+
+
+class gemm_rrr(gemm):
+    """y = a @ b: a [..., K] row-major, b [K, N] row-major."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self._attrs["op"] = "gemm_rrr"
+
+    def _infer_shapes(self, a: Tensor, b: Tensor) -> List[IntVar]:
+        return list(a._attrs["shape"][:-1]) + [b._attrs["shape"][1]]
+
+    def _check_ab(self, a: Tensor, b: Tensor) -> None:
+        a_shape, b_shape = a._attrs["shape"], b._attrs["shape"]
+        self._sanity_check(a, b)
+        if a_shape[-1] != b_shape[0]:
+            raise RuntimeError(f"A/B shape mismatch! A: {a_shape}, B: {b_shape}")
+        if not isinstance(b_shape[0], IntImm) or not isinstance(b_shape[1], IntImm):
+            raise RuntimeError(f"K and N must be static! B: {b_shape}")
+
+    def __call__(self, a: Tensor, b: Tensor) -> Tensor:
+        self._check_ab(a, b)
+        return self._finish([a, b], self._infer_shapes(a, b))
+
+    def _lower(self) -> Dict[str, Any]:
+        low = super()._lower()
+        b = self._attrs["inputs"][1]
+        acc = self._attrs["output_accessors"][0]
+        n = b._attrs["shape"][1].value()
+        low["kernel"] = "gemm_rrr"
+        low["ints"][6] = acc.row_stride() if acc.stride_dim is not None else n
+        return low
+
+
+class gemm_rrr_bias(gemm_rrr):
+    """y = a @ b + bias; bias is a static 1-D tensor of length N."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self._attrs["op"] = "gemm_rrr_bias"
+        self._has_bias = True
+
+    def __call__(self, a: Tensor, b: Tensor, bias: Tensor) -> Tensor:
+        self._check_ab(a, b)
+        bias_shape = bias._attrs["shape"]
+        if len(bias_shape) != 1:
+            raise RuntimeError(f"Bias should be 1D vector! Current bias shape: {bias_shape}")
+        if bias_shape[0] != b._attrs["shape"][1]:
+            raise RuntimeError(f"bias length {bias_shape[0]} does not match N {b._attrs['shape'][1]}")
+        return self._finish([a, b, bias], self._infer_shapes(a, b))

@@ -70,6 +70,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const void* a_, const vo
   const int b = blockIdx.z;
   const T* a = static_cast<const T*>(a_) + static_cast<long long>(b) * p.a_bs * p.a_batch_mul;
   const T* w = static_cast<const T*>(b_) + static_cast<long long>(b) * p.b_bs * p.b_batch_mul;
+  const long long w_n = p.b_mn ? 1 : p.ldb, w_k = p.b_mn ? p.ldb : 1;  // element strides of B along n and k
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
   const int row0 = blockIdx.y * 32, col0 = blockIdx.x * 32;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const void* a_, const vo
       const int r = ty + i * 8;
       const int k = k0 + tx;
       sa[r][tx] = (row0 + r < p.M && k < p.K) ? E::to_float(a[static_cast<long long>(row0 + r) * p.lda + k]) : 0.f;
-      sb[r][tx] = (col0 + r < p.N && k < p.K) ? E::to_float(w[static_cast<long long>(col0 + r) * p.ldb + k]) : 0.f;
+      sb[r][tx] = (col0 + r < p.N && k < p.K) ? E::to_float(w[static_cast<long long>(col0 + r) * w_n + k * w_k]) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -180,6 +181,7 @@ struct GemmArgs {
   long long t1, t2, t3;
   int tile_n;  // 0 = choose
   cudaStream_t stream;
+  int b_mn = 0;  // B is [K, N] with N contiguous (the reference's "rrr" layouts) instead of [N, K]
   int num_out = 1;                                // destinations: c, then extra_out[0 .. num_out - 2]
   void* extra_out[kMaxOut - 1] = {};              // same shape and strides as c (e.g. peers' copies of the result)
   void* workspace = nullptr;  // fp32 scratch for split-K partial sums (may be null: no split-K)
@@ -277,6 +279,7 @@ void gemm_run(const GemmArgs& g) {
   p.batch = static_cast<int>(g.batch);
   p.a_batch_mul = (g.batch > 1 && g.a_bs == 0) ? 0 : 1;
   p.b_batch_mul = (g.batch > 1 && g.b_bs == 0) ? 0 : 1;
+  p.b_mn = g.b_mn;
   p.bias = g.bias, p.d0 = g.d0, p.d1 = g.d1, p.out = g.c;
   p.lda = g.lda, p.ldb = g.ldb, p.a_bs = g.a_bs, p.b_bs = g.b_bs;
   p.ldc = g.ldc, p.ldd = g.ldd, p.c_bs = g.c_bs, p.d_bs = g.d_bs;
@@ -361,7 +364,8 @@ void gemm_run(const GemmArgs& g) {
   p.partial = static_cast<float*>(g.workspace);
   const long long a_batch = p.a_batch_mul ? g.batch : 1, b_batch = p.b_batch_mul ? g.batch : 1;
   CUtensorMap ta = make_tile_map(g.a, bf16, g.k, g.m, a_batch, g.lda, g.a_bs, kBM);
-  CUtensorMap tb = make_tile_map(g.b, bf16, g.k, g.n, b_batch, g.ldb, g.b_bs, pair ? bn / 2 : bn);
+  CUtensorMap tb = g.b_mn ? make_tile_map(g.b, bf16, g.n, g.k, b_batch, g.ldb, g.b_bs, kBK)  // 64 x 64 boxes
+                          : make_tile_map(g.b, bf16, g.k, g.n, b_batch, g.ldb, g.b_bs, pair ? bn / 2 : bn);
   // Staged TMA store: row-major output with 16-byte aligned rows, or a permuted output whose 64-column
   // groups and 32-row groups each stay inside one contiguous run of the destination.
   OutMaps tout;
@@ -439,6 +443,28 @@ B200AIT_EXPORT int b200ait_gemm_rcr(const void* a, const void* b, const void* bi
                batch, m,   n,              k,              lda,            ldb,
                ldc, ldd, a_batch_stride, b_batch_stride, c_batch_stride, d_batch_stride,
                epilogue, dtype, alpha, store_mode, t1, t2, t3, tile_n, stream};
+    g.workspace = workspace;
+    g.workspace_bytes = workspace_bytes;
+    g.split_k = split_k;
+    gemm_run(g);
+  });
+}
+
+// b200ait_gemm_rcr with B stored [batch, k, n] (n contiguous, row stride ldb): the reference's gemm_rrr / bmm_rrr
+// layouts (python/aitemplate/compiler/ops/gemm_universal/gemm_rrr.py, bmm_xxx.py "rrr"). Same kernel, the B tile
+// reaches the tensor core as an MN-major operand.
+B200AIT_EXPORT int b200ait_gemm_rrr(const void* a, const void* b, const void* bias, const void* d0, const void* d1,
+                                    void* c, int64_t batch, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+                                    int64_t ldc, int64_t ldd, int64_t a_batch_stride, int64_t b_batch_stride,
+                                    int64_t c_batch_stride, int64_t d_batch_stride, int epilogue, int dtype,
+                                    float alpha, int tile_n, void* workspace, int64_t workspace_bytes, int split_k,
+                                    cudaStream_t stream) {
+  return guarded("b200ait_gemm_rrr", [&] {
+    GemmArgs g{a,   b,   bias,           d0,             d1,             c,
+               batch, m,   n,              k,              lda,            ldb,
+               ldc, ldd, a_batch_stride, b_batch_stride, c_batch_stride, d_batch_stride,
+               epilogue, dtype, alpha, 0, 1, 1, 1, tile_n, stream};
+    g.b_mn = 1;
     g.workspace = workspace;
     g.workspace_bytes = workspace_bytes;
     g.split_k = split_k;

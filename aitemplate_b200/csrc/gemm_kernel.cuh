@@ -18,6 +18,7 @@ struct GemmParams {
   int splits, kb_per_split, num_units;  // split-K: unit = tile * splits + split
   float* partial;                       // [splits, batch, M, N] fp32 partial sums when splits > 1
   int a_batch_mul, b_batch_mul;  // 0 when that operand is broadcast over the batch
+  int b_mn;                      // B is stored [K, N] (N contiguous, "row-major B") instead of [N, K]
   const void* bias;              // [N] or nullptr
   const void* d0;                // [M, N] residual operands (row stride ldd) or nullptr
   const void* d1;
@@ -367,12 +368,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             const uint32_t leader_bar = mapa_shared(smem_u32(&full_bar[stage]), 0);
             if (pair_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
             tma_load_3d_pair(sa, &tma_a, leader_bar, kb * kBK, m_blk * kBM, b * p.a_batch_mul);
-            tma_load_3d_pair(sa + kABytes, &tma_b, leader_bar, kb * kBK, n_blk * BN + pair_rank * (BN / 2),
-                             b * p.b_batch_mul);
+            const int n0 = n_blk * BN + pair_rank * (BN / 2);
+            if (p.b_mn) {  // [K, N] storage: one box of 64 k-rows x 64 columns per 64-column chunk
+#pragma unroll
+              for (int ch = 0; ch < Cfg::kBRows / 64; ++ch)
+                tma_load_3d_pair(sa + kABytes + ch * 8192, &tma_b, leader_bar, n0 + ch * 64, kb * kBK,
+                                 b * p.b_batch_mul);
+            } else {
+              tma_load_3d_pair(sa + kABytes, &tma_b, leader_bar, kb * kBK, n0, b * p.b_batch_mul);
+            }
           } else {
             mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
             tma_load_3d(sa, &tma_a, &full_bar[stage], kb * kBK, m_blk * kBM, b * p.a_batch_mul);
-            tma_load_3d(sa + kABytes, &tma_b, &full_bar[stage], kb * kBK, n_blk * BN, b * p.b_batch_mul);
+            if (p.b_mn) {
+#pragma unroll
+              for (int ch = 0; ch < Cfg::kBRows / 64; ++ch)
+                tma_load_3d(sa + kABytes + ch * 8192, &tma_b, &full_bar[stage], n_blk * BN + ch * 64, kb * kBK,
+                            b * p.b_batch_mul);
+            } else {
+              tma_load_3d(sa + kABytes, &tma_b, &full_bar[stage], kb * kBK, n_blk * BN, b * p.b_batch_mul);
+            }
           }
           if (++stage == kStages) {
             stage = 0;
@@ -402,7 +417,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0 && pair_rank == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(PAIR ? 2 * kBM : kBM, BN, BF16, false, false);
+      const uint32_t idesc = umma_idesc_f16(PAIR ? 2 * kBM : kBM, BN, BF16, false, p.b_mn != 0);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -424,7 +439,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             const uint64_t adesc = umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
-            const uint64_t bdesc = umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
+            // [N, K] storage: K-major tile, 32 bytes per k-step. [K, N] storage: MN-major tile, rows are k (128 B
+            // each): 16 k-rows = 2048 B per k-step, 64-column chunks 8192 B apart, 8-row groups 1024 B apart.
+            const uint64_t bdesc = p.b_mn ? umma_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
+                                          : umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
             if (PAIR) {
               umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
             } else {

@@ -41,6 +41,9 @@ int b200ait_gemm_rcr(const void*, const void*, const void*, const void*, const v
                      int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int, int, float,
                      int, int64_t, int64_t, int64_t, int, void*, int64_t, int, cudaStream_t);
 int b200ait_gemm_rcr_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int, int, int64_t*);
+int b200ait_gemm_rrr(const void*, const void*, const void*, const void*, const void*, void*, int64_t, int64_t, int64_t,
+                     int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int, int, float, int,
+                     void*, int64_t, int, cudaStream_t);
 int b200ait_mem_eff_attention(void*, const void*, const void*, const void*, int64_t, int64_t, int64_t, int, int, int,
                               float, int, const int32_t*, const int32_t*, int, cudaStream_t);
 int b200ait_layernorm(void*, const void*, const void*, const void*, int64_t, int64_t, float, int64_t, int64_t, int,
@@ -442,6 +445,44 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
                            out_stride, n, 0, 0, 0, 0, static_cast<int>(op.ints[0]), T[a].dtype,
                            static_cast<float>(op.floats[0]), static_cast<int>(op.ints[1]), op.ints[2], op.ints[3],
                            op.ints[4], tile_hint, workspace_, workspace_bytes_, split_hint, stream),
+          op);
+    return;
+  }
+  if (op.kernel == "gemm_rrr") {  // B stored [K, N]
+    const int a = in(0), b = in(1), bias = in(2), d0 = in(3), d1 = in(4);
+    const auto as = shape_of(a);
+    const auto bs = shape_of(b);
+    const int64_t k = as.back(), n = bs[1];
+    int64_t m = 1;
+    for (size_t i = 0; i + 1 < as.size(); ++i) m *= as[i];
+    if (bs[0] != k) throw Error("gemm '" + op.name + "': K mismatch");
+    std::vector<int64_t> os(as.begin(), as.end() - 1);
+    os.push_back(n);
+    bind_shape(out0, os, "gemm output");
+    if (!launch) return;
+    const int64_t out_off = op.ints[5], out_stride = op.ints[6];
+    uint8_t* c = static_cast<uint8_t*>(ptr_of(out0)) + out_off * dtype_size(T[out0].dtype);
+    check(b200ait_gemm_rrr(ptr_of(a), ptr_of(b), ptr_of(bias), ptr_of(d0), ptr_of(d1), c, 1, m, n, k, k, n, out_stride,
+                           n, 0, 0, 0, 0, static_cast<int>(op.ints[0]), T[a].dtype, static_cast<float>(op.floats[0]),
+                           static_cast<int>(op.ints[7]), workspace_, workspace_bytes_, static_cast<int>(op.ints[8]),
+                           stream),
+          op);
+    return;
+  }
+  if (op.kernel == "bmm_rrr") {
+    const int a = in(0), b = in(1);
+    auto as = shape_of(a), bs = shape_of(b);
+    if (as.size() == 2) as.insert(as.begin(), 1);
+    if (bs.size() == 2) bs.insert(bs.begin(), 1);
+    const int64_t ba = as[0], bb = bs[0], m = as[1], k = as[2], n = bs[2];
+    if (bs[1] != k) throw Error("bmm '" + op.name + "': K mismatch");
+    if (!(ba == bb || ba == 1 || bb == 1)) throw Error("bmm '" + op.name + "': batch sizes are not broadcastable");
+    const int64_t batch = std::max(ba, bb);
+    bind_shape(out0, {batch, m, n}, "bmm output");
+    if (!launch) return;
+    check(b200ait_gemm_rrr(ptr_of(a), ptr_of(b), nullptr, nullptr, nullptr, ptr_of(out0), batch, m, n, k, k, n, n, n,
+                           (ba == 1 && batch > 1) ? 0 : m * k, (bb == 1 && batch > 1) ? 0 : n * k, m * n, m * n, 0,
+                           T[a].dtype, static_cast<float>(op.floats[0]), 0, nullptr, 0, 1, stream),
           op);
     return;
   }

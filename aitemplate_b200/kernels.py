@@ -172,6 +172,42 @@ def gemm_rcr_multi_out(
     _lib.check(code, "b200ait_gemm_rcr_multi_out")
 
 
+def gemm_rrr(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, epilogue: str = "",
+             alpha: float = 1.0, tile_n: int = 0) -> torch.Tensor:
+    """y = epilogue(x @ w + bias) with w stored [K, N] (row-major B); x [..., K]."""
+    _check_cuda(x, w, bias)
+    k = x.shape[-1]
+    m = x.numel() // k if k else math.prod(x.shape[:-1])
+    if w.dim() != 2 or w.shape[0] != k:
+        raise ValueError(f"gemm_rrr: K mismatch {tuple(x.shape)} vs {tuple(w.shape)}")
+    n = w.shape[1]
+    out = torch.empty(list(x.shape[:-1]) + [n], dtype=x.dtype, device=x.device)
+    code = _lib.load().b200ait_gemm_rrr(
+        _ptr(x), _ptr(w), _ptr(bias), None, None, _ptr(out), 1, m, n, k, k, n, n, n, 0, 0, 0, 0,
+        epilogue_code(epilogue), _dtype_code(x), c_float(alpha), tile_n, None, 0, 1, _stream())
+    _lib.check(code, "b200ait_gemm_rrr")
+    return out
+
+
+def bmm_rrr(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, tile_n: int = 0) -> torch.Tensor:
+    """c[i] = a[i] @ b[i] with a [B, M, K] (or [M, K]) and b [B, K, N] (or [K, N]); batch 1 broadcasts."""
+    _check_cuda(a, b)
+    a3 = a if a.dim() == 3 else a.unsqueeze(0)
+    b3 = b if b.dim() == 3 else b.unsqueeze(0)
+    ba, m, k = a3.shape
+    bb, k2, n = b3.shape
+    if k != k2 or not (ba == bb or ba == 1 or bb == 1):
+        raise ValueError(f"bmm_rrr: incompatible shapes {tuple(a.shape)} and {tuple(b.shape)}")
+    batch = max(ba, bb)
+    out = torch.empty((batch, m, n), dtype=a.dtype, device=a.device)
+    code = _lib.load().b200ait_gemm_rrr(
+        _ptr(a3), _ptr(b3), None, None, None, _ptr(out), batch, m, n, k, k, n, n, n,
+        0 if (ba == 1 and batch > 1) else m * k, 0 if (bb == 1 and batch > 1) else n * k, m * n, m * n,
+        0, _dtype_code(a), c_float(alpha), tile_n, None, 0, 1, _stream())
+    _lib.check(code, "b200ait_gemm_rrr")
+    return out
+
+
 def gemm_workspace_bytes(batch: int, m: int, n: int, k: int, tile_n: int = 0, split_k: int = 0) -> int:
     """Bytes of fp32 split-K scratch the library would use for this problem (0 = it would not split)."""
     out = c_int64(0)

@@ -59,6 +59,13 @@ int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void*
  * b200ait_gemm_rcr_workspace_bytes reports what the library would use for a problem. */
 int b200ait_gemm_rcr_workspace_bytes(int64_t batch, int64_t m, int64_t n, int64_t k, int tile_n, int split_k,
                                      int64_t* bytes_out);
+/* b200ait_gemm_rcr with B stored [batch, k, n] (n contiguous, row stride ldb): gemm_rrr / gemm_rrr_bias / bmm_rrr
+ * (python/aitemplate/compiler/ops/gemm_universal/gemm_rrr.py:26-80, bmm_xxx.py:223-260). No permuted store. */
+int b200ait_gemm_rrr(const void* a, const void* b, const void* bias, const void* d0, const void* d1, void* c,
+                     int64_t batch, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                     int64_t ldd, int64_t a_batch_stride, int64_t b_batch_stride, int64_t c_batch_stride,
+                     int64_t d_batch_stride, int epilogue, int dtype, float alpha, int tile_n, void* workspace,
+                     int64_t workspace_bytes, int split_k, b200ait_stream_t stream);
 /* No counterpart in the reference (it is single-GPU: no communication backend anywhere under python/aitemplate
  * or static/). The same GEMM with its result written to num_out buffers of identical shape and strides
  * (1 <= num_out <= 8) by the epilogue's TMA stores. outs[0] is normally this GPU's buffer and the others

@@ -92,6 +92,23 @@ def gemm_rcr(x, w, bias=None, d0=None, d1=None, epilogue: str = "", alpha: float
     return _unary(u2, y)
 
 
+def gemm_rrr(x, w, bias=None) -> torch.Tensor:
+    """tests/unittest/ops/test_gemm.py (rrr case) / test_gemm_bias.py: torch.matmul(X, W) [+ bias], W stored [K, N]."""
+    x, w, bias = map(_f32, (x, w, bias))
+    y = torch.matmul(x, w)
+    return y if bias is None else y + bias
+
+
+def bmm_rrr(a, b, alpha: float = 1.0) -> torch.Tensor:
+    """tests/unittest/ops/test_bmm.py: torch.bmm(A, B), B stored [batch, K, N]."""
+    a, b = _f32(a), _f32(b)
+    if a.dim() == 2:
+        a = a.unsqueeze(0)
+    if b.dim() == 2:
+        b = b.unsqueeze(0)
+    return torch.matmul(a, b) * alpha
+
+
 def gemm_rcr_bias_permute(x, w, bias, shape: Sequence[int], layout: str = "20314") -> torch.Tensor:
     """tests/unittest/ops/test_gemm_bias_permute.py:74-75 and test_attention.py:146-149:
     linear -> reshape [M/t1, t1, t2, t3, N/t2/t3] -> permute (2, 0, 3, 1, 4)."""

@@ -40,6 +40,12 @@ CASES = [
     ("bmm_rcr_dynamic_batch", "bmm_rcr", {}, [[[1, 977], 100, 256], [[1, 977], 512, 256]], {}),
     ("bmm_rcr_broadcast_b", "bmm_rcr", {}, [[5, 32, 256], [1, 512, 256]], {}),
     ("bmm_rcr_2d_b", "bmm_rcr", {}, [[5, 32, 256], [512, 256]], {}),
+    ("gemm_rrr", "gemm_rrr", {}, [[[1, 1024], 256], [256, 384]], {}),
+    ("gemm_rrr_3d_a", "gemm_rrr", {}, [[4, 17, 64], [64, 72]], {}),
+    ("gemm_rrr_bias", "gemm_rrr_bias", {}, [[1000, 128], [128, 264], [264]], {}),
+    ("bmm_rrr", "bmm_rrr", {}, [[16, 384, 384], [16, 384, 64]], {}),
+    ("bmm_rrr_dynamic_batch", "bmm_rrr", {}, [[[1, 64], 48, 40], [[1, 64], 40, 24]], {}),
+    ("bmm_rrr_broadcast_b", "bmm_rrr", {}, [[5, 32, 256], [1, 256, 72]], {}),
     ("mem_eff_attention", "mem_eff_attention", {"causal": False}, [[64, 12, 384, 64]] * 3, {}),
     ("mem_eff_attention_cross", "mem_eff_attention", {"causal": False},
      [[2, 8, 4096, 40], [2, 8, 77, 40], [2, 8, 77, 40]], {}),

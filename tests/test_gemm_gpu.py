@@ -169,6 +169,36 @@ def test_multi_destination_store(m, n, kk, epilogue, num_out):
         assert bool((t[:, :col0] == 7.0).all()) and bool((t[:, col0 + n:] == 7.0).all())  # nothing outside the block
 
 
+# row-major B ("rrr" layouts of the reference: tests/unittest/ops/test_gemm.py, test_bmm.py): W stored [K, N]
+@pytest.mark.parametrize("m,n,kk,tile_n", [(256, 512, 128, 0), (1000, 264, 200, 0), (128, 64, 64, 64), (300, 640, 1024, 128),
+                                            (2048, 1024, 512, 256), (4096, 768, 768, 512), (7, 72, 72, 0)])
+def test_gemm_rrr(m, n, kk, tile_n):
+    k = _kernels()
+    x = _rand((m, kk), 400, dist="uniform")
+    w = _rand((kk, n), 401, scale=0.05)
+    b = _rand((n,), 402, scale=0.1)
+    y = k.gemm_rrr(x.cuda(), w.cuda(), b.cuda(), tile_n=tile_n)
+    assert k.device_status() == 0
+    _close(y, oracle.gemm_rrr(x, w, b))
+    y0 = k.gemm_rrr(x.cuda(), w.cuda(), None, epilogue="", tile_n=tile_n)
+    _close(y0, oracle.gemm_rrr(x, w))
+
+
+def test_gemm_rrr_unaligned_uses_cuda_core_kernel():
+    k = _kernels()
+    x, w = _rand((33, 21), 410), _rand((21, 19), 411, scale=0.2)   # N and K not multiples of 8
+    _close(k.gemm_rrr(x.cuda(), w.cuda()), oracle.gemm_rrr(x, w))
+
+
+@pytest.mark.parametrize("bsz,m,n,kk", [(4, 128, 256, 64), (3, 100, 72, 40), (16, 384, 64, 384), (1, 64, 64, 64)])
+def test_bmm_rrr(bsz, m, n, kk):
+    k = _kernels()
+    a, b = _rand((bsz, m, kk), 420, dist="uniform"), _rand((bsz, kk, n), 421, dist="uniform")
+    _close(k.bmm_rrr(a.cuda(), b.cuda()), oracle.bmm_rrr(a, b))
+    b1 = _rand((1, kk, n), 422, dist="uniform")                      # broadcast B over the batch
+    _close(k.bmm_rrr(a.cuda(), b1.cuda()), oracle.bmm_rrr(a, b1))
+
+
 def test_no_bias_and_alpha():
     k = _kernels()
     x = _rand((300, 320), 40)

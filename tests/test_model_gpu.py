@@ -336,6 +336,31 @@ def test_compile_time_gemm_profiling(workdir):
     _close(res, oracle.gemm_rcr(xd, wd, bd, epilogue="fast_gelu"), 1e-2)
 
 
+def test_row_major_b_ops_in_a_graph(workdir):
+    # gemm_rrr_bias -> bmm_rrr (the unfused attention form P @ V uses bmm_rrr in the reference's examples)
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+
+    x = Tensor([IntVar([1, 256], name="m"), 96], name="x", is_input=True)
+    w, b = Tensor([96, 160], name="w"), Tensor([160], name="b")
+    p_ = Tensor([4, 48, 40], name="p", is_input=True)
+    v = Tensor([4, 40, 24], name="v", is_input=True)
+    y = ops.gemm_rrr_bias()(x, w, b)
+    y._attrs["name"], y._attrs["is_output"] = "y", True
+    z = ops.bmm_rrr()(p_, v)
+    z._attrs["name"], z._attrs["is_output"] = "z", True
+    module = compile_model([y, z], detect_target(), workdir, "rrr")
+    wd, bd = _rand((96, 160), 1, 0.1), _rand((160,), 2, 0.1)
+    module.set_many_constants_with_tensors({"w": wd.cuda(), "b": bd.cuda()})
+    pd, vd = _rand((4, 48, 40), 3), _rand((4, 40, 24), 4)
+    for m in (1, 77, 256):
+        xd = _rand((m, 96), 5 + m)
+        outs = {"y": torch.empty((m, 160), dtype=torch.float16, device="cuda"),
+                "z": torch.empty((4, 48, 24), dtype=torch.float16, device="cuda")}
+        res = module.run_with_tensors({"x": xd.cuda(), "p": pd.cuda(), "v": vd.cuda()}, outs)
+        _close(res["y"], oracle.gemm_rrr(xd, wd, bd))
+        _close(res["z"], oracle.bmm_rrr(pd, vd), 2e-2)
+
+
 def test_concurrent_runs_share_the_pool(workdir):
     import threading
 
