@@ -275,11 +275,15 @@ __device__ __forceinline__ void epilogue_direct_store32(const GemmParams& p, con
   }
 }
 
-template <int BN, bool BF16, int EPI, bool PAIR>
+// BMN: B is stored [K, N] (compile-time, so that the [N, K] kernels carry no trace of it). Only instantiated with
+// the generic epilogue (EPI == -1).
+template <int BN, bool BF16, int EPI, bool PAIR, bool BMN = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const __grid_constant__ OutMaps outs, const __grid_constant__ CUtensorMap tma_d0,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_d0,
+               const GemmParams p, const __grid_constant__ OutMaps outs) {
+  // `tma_out` is the (first) destination; `outs.m[1..]` are the extra destinations of a multi-destination store
+  // and sit at the end of the parameter space, out of the way of what every launch reads.
   constexpr bool D0BOX = d0_box_of<EPI, PAIR>();
   using Cfg = TileCfg<BN, PAIR, D0BOX>;
   constexpr int kStages = Cfg::kStages;
@@ -327,8 +331,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
-    if (p.tma_store)
-      for (int i = 0; i < p.num_out; ++i) tma_prefetch_desc(&outs.m[i]);
+    if (p.tma_store) {
+      tma_prefetch_desc(&tma_out);
+      for (int i = 1; i < p.num_out; ++i) tma_prefetch_desc(&outs.m[i]);
+    }
     if (D0BOX && p.tma_d0) tma_prefetch_desc(&tma_d0);
   }
   __syncthreads();
@@ -369,7 +375,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             if (pair_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
             tma_load_3d_pair(sa, &tma_a, leader_bar, kb * kBK, m_blk * kBM, b * p.a_batch_mul);
             const int n0 = n_blk * BN + pair_rank * (BN / 2);
-            if (p.b_mn) {  // [K, N] storage: one box of 64 k-rows x 64 columns per 64-column chunk
+            if (BMN) {  // [K, N] storage: one box of 64 k-rows x 64 columns per 64-column chunk
 #pragma unroll
               for (int ch = 0; ch < Cfg::kBRows / 64; ++ch)
                 tma_load_3d_pair(sa + kABytes + ch * 8192, &tma_b, leader_bar, n0 + ch * 64, kb * kBK,
@@ -380,7 +386,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           } else {
             mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
             tma_load_3d(sa, &tma_a, &full_bar[stage], kb * kBK, m_blk * kBM, b * p.a_batch_mul);
-            if (p.b_mn) {
+            if (BMN) {
 #pragma unroll
               for (int ch = 0; ch < Cfg::kBRows / 64; ++ch)
                 tma_load_3d(sa + kABytes + ch * 8192, &tma_b, &full_bar[stage], n_blk * BN + ch * 64, kb * kBK,
@@ -417,7 +423,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0 && pair_rank == 0) {
-      const uint32_t idesc = umma_idesc_f16(PAIR ? 2 * kBM : kBM, BN, BF16, false, p.b_mn != 0);
+      constexpr uint32_t idesc = umma_idesc_f16(PAIR ? 2 * kBM : kBM, BN, BF16, false, BMN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -441,8 +447,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             const uint64_t adesc = umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
             // [N, K] storage: K-major tile, 32 bytes per k-step. [K, N] storage: MN-major tile, rows are k (128 B
             // each): 16 k-rows = 2048 B per k-step, 64-column chunks 8192 B apart, 8-row groups 1024 B apart.
-            const uint64_t bdesc = p.b_mn ? umma_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
-                                          : umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = BMN ? umma_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
+                                       : umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
             if (PAIR) {
               umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
             } else {
@@ -645,11 +651,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             if (lane == 0 && row0 < p.M) {  // a box that starts past the last row has nothing to write
               const int gcol = colh + (c & ~1) * 32;
               if (p.store_mode == 0) {
-                tma_store_5d(&outs.m[0], box, gcol, row0, b, 0, 0);
+                tma_store_5d(&tma_out, box, gcol, row0, b, 0, 0);
                 for (int i = 1; i < p.num_out; ++i) tma_store_5d(&outs.m[i], box, gcol, row0, b, 0, 0);
               } else {
                 const int cc = gcol / p.d, r_b = row0 / p.t1;
-                for (int i = 0; i < p.num_out; ++i)
+                tma_store_5d(&tma_out, box, gcol - cc * p.d, row0 - r_b * p.t1, cc % p.t3, r_b, cc / p.t3);
+                for (int i = 1; i < p.num_out; ++i)
                   tma_store_5d(&outs.m[i], box, gcol - cc * p.d, row0 - r_b * p.t1, cc % p.t3, r_b, cc / p.t3);
               }
               bulk_commit_group();
@@ -685,23 +692,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   }
 }
 
-template <int BN, bool BF16, int EPI>
+template <int BN, bool BF16, int EPI, bool BMN = false>
 void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout, const GemmParams& p, int grid,
                cudaStream_t stream) {
   using Cfg = TileCfg<BN>;
   static std::atomic<uint64_t> configured{0};
-  opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_tc_kernel<BN, BF16, EPI, false>), Cfg::kSmemBytes);
-  gemm_tc_kernel<BN, BF16, EPI, false><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout, ta, p);
+  opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_tc_kernel<BN, BF16, EPI, false, BMN>),
+                   Cfg::kSmemBytes);
+  gemm_tc_kernel<BN, BF16, EPI, false, BMN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout.m[0], ta, p,
+                                                                                           tout);
   B200AIT_CUDA_CHECK(cudaGetLastError());
 }
 
 // CTA-pair variant: `grid` counts CTAs (twice the number of pairs); launched as clusters of two.
-template <int BN, bool BF16, int EPI>
+template <int BN, bool BF16, int EPI, bool BMN = false>
 void launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout, const CUtensorMap& td0,
                     const GemmParams& p, int grid, cudaStream_t stream) {
   using Cfg = TileCfg<BN, true, d0_box_of<EPI, true>()>;
   static std::atomic<uint64_t> configured{0};
-  auto* kernel = &gemm_tc_kernel<BN, BF16, EPI, true>;
+  auto* kernel = &gemm_tc_kernel<BN, BF16, EPI, true, BMN>;
   opt_in_smem_once(configured, reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
@@ -715,7 +724,7 @@ void launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps&
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  B200AIT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tout, td0, p));
+  B200AIT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tout.m[0], td0, p, tout));
 }
 
 // Epilogues that get their own straight-line instantiation (fp16): bias, relu, gelu, fast_gelu, add,
@@ -752,6 +761,13 @@ void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, 
   template <>                                                                                                  \
   void launch_tc_width<BN_>(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout,  \
                             const GemmParams& p, int grid, cudaStream_t stream) {                              \
+    if (p.b_mn) { /* B stored [K, N]: generic epilogue instantiation only */                                   \
+      if (bf16)                                                                                                \
+        launch_tc<BN_, true, -1, true>(ta, tb, tout, p, grid, stream);                                         \
+      else                                                                                                     \
+        launch_tc<BN_, false, -1, true>(ta, tb, tout, p, grid, stream);                                        \
+      return;                                                                                                  \
+    }                                                                                                          \
     if (bf16) {                                                                                                \
       launch_tc<BN_, true, -1>(ta, tb, tout, p, grid, stream);                                                 \
       return;                                                                                                  \

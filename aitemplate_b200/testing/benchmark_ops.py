@@ -1,4 +1,4 @@
-"""Per-op throughput sweep over the BASELINE configurations (`python bench.py --suite ops`).
+"""Per-op throughput sweep over the benchmark configurations (`python bench.py --suite ops`).
 
 Each row times one op through the C ABI on seeded synthetic inputs: a CUDA graph of `reps` launches
 over a rotation of buffer sets larger than L2 (so no launch finds its operands cached), timed with
@@ -147,7 +147,7 @@ def bench_concat_split(config: str, peaks: Dict) -> List[Dict]:
 
 
 def bench_sd_block(config: str, peaks: Dict) -> Dict:
-    """The whole Stable-Diffusion UNet transformer block of BASELINE configuration 3 through compile_model() and
+    """The whole Stable-Diffusion UNet transformer block of benchmark configuration 3 through compile_model() and
     Model.benchmark_with_tensors() in graph mode (22 kernels per run)."""
     import tempfile
 

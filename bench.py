@@ -31,7 +31,7 @@ BATCH, SEQ, HIDDEN, HEADS, FFN = 64, 384, 768, 12, 3072
 GEMM_DRAM_TRAFFIC_PER_STEP = 547.8e6  # ncu: dram__bytes_read.sum + dram__bytes_write.sum over the 4 launches
 METRIC = "bert_base_layer_seqs_per_sec"
 UNIT = "seq/s"
-WORKLOAD = "BERT-base encoder layer, fp16, batch 64, seq 384, hidden 768, 12 heads x 64, FFN 3072 (BASELINE config 2)"
+WORKLOAD = "BERT-base encoder layer, fp16, batch 64, seq 384, hidden 768, 12 heads x 64, FFN 3072 (benchmark config 2)"
 
 
 def _peaks():
@@ -313,7 +313,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
 
 
 def run_ops_suite(args) -> None:
-    """Per-op sweep over the BASELINE configurations: one JSON line per op (not the driver's contract line)."""
+    """Per-op sweep over the benchmark configurations: one JSON line per op (not the driver's contract line)."""
     import torch
 
     from aitemplate_b200.testing import benchmark_ops
@@ -329,7 +329,7 @@ def flops_of(m: int, n: int, k: int) -> float:
 
 
 def run_nsplit_suite(args, rank: int, world: int, local_rank: int) -> None:
-    """BASELINE config 5 at M = 65536, N = K = 8192 on `world` GPUs, two partitionings:
+    """benchmark config 5 at M = 65536, N = K = 8192 on `world` GPUs, two partitionings:
     M-sharded (rows split, no collective) and N-split (weight rows split, X replicated, one NCCL
     all-gather of the output column shards + re-layout). Rank 0 prints one JSON line."""
     import torch

@@ -2,7 +2,7 @@
 
 Shapes follow tests/unittest/ops/test_attention.py:456-742 ((B16,H4,S8,d=20) and (B16,H16,S1024,d=64)
 scaled to what the host oracle finishes in seconds), :847-1010 (cross attention, Sq != Skv), and the
-BASELINE configurations (BERT S=384 D=64; UNet D=40 with Skv=4096 and Skv=77).
+benchmark configurations (BERT S=384 D=64; UNet D=40 with Skv=4096 and Skv=77).
 The reference's tolerance is 1e-3 against an fp16 torch result; against the fp32 oracle the bound
 is atol = rtol = 1e-2 with a tighter 4e-3 absolute check on top.
 """

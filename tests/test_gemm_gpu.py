@@ -3,7 +3,7 @@
 Shapes follow the reference's tests: tests/unittest/ops/test_gemm_bias.py:43-99 (M 4096/1000, (N,K) in
 {(4,4),(81,1024),(3,256),(64,1024)}, zero sizes), test_gemm_rcr_bias_fast_gelu.py:44-128 (M in
 {1,7,64,127,128}, K=1024, N=64), test_gemm_bias_broadcast.py (8x8x8, 256x128, 1024x512),
-test_bmm.py:32-70, plus the BASELINE configurations.
+test_bmm.py:32-70, plus the benchmark configurations.
 Tolerance: atol = rtol = 1e-2 against the fp32 oracle (fp16 storage, fp32 accumulation).
 """
 import pytest
@@ -318,7 +318,7 @@ def test_reference_signature_entry_points():
 
 
 def test_large_gemm_rows_sampled_against_oracle():
-    # BASELINE config 5 at M = 8192, N = K = 8192: the oracle checks 48 sampled rows (4 GFLOP on the host)
+    # benchmark config 5 at M = 8192, N = K = 8192: the oracle checks 48 sampled rows (4 GFLOP on the host)
     k = _kernels()
     m, n, kk = 8192, 8192, 8192
     g = torch.Generator(device="cuda").manual_seed(5)

@@ -184,7 +184,7 @@ def test_bert_layer_plan_and_memory_plan():
 
 
 def test_sd_transformer_block_plan():
-    # BASELINE configuration 3 lowers to GEMMs, permutes, two attentions and three layernorms; every residual
+    # benchmark configuration 3 lowers to GEMMs, permutes, two attentions and three layernorms; every residual
     # add is fused into the GEMM before it (no stand-alone elementwise kernel is left).
     y = workloads.build_sd_block(2)
     g, plan, blob, consts = _lower([y])

@@ -1,7 +1,7 @@
 """Bit-exact GPU checks of concatenate / split / permute and parity of the element-wise chain.
 
 The reference compares these ops with torch.equal (tests/unittest/ops/test_concatenate.py:74,132,204,
-test_split.py:107,171, test_permute.py); so do these tests. Includes the BASELINE case: four
+test_split.py:107,171, test_permute.py); so do these tests. Includes the benchmark case: four
 [8192, 1024] fp16 tensors concatenated on dim 1 and split back.
 """
 import pytest

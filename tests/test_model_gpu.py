@@ -258,7 +258,7 @@ def test_bert_layer_matches_oracle(workdir, graph_mode):
 
 @pytest.mark.parametrize("tokens", [1024, 4096])
 def test_sd_transformer_block_matches_oracle(workdir, tokens):
-    # BASELINE configuration 3: Stable-Diffusion UNet transformer block, batch 2, dim 320, 8 heads x 40
+    # benchmark configuration 3: Stable-Diffusion UNet transformer block, batch 2, dim 320, 8 heads x 40
     # (head dim 40 = 5 x 8: the tensor-core attention path with a zero-padded head), self-attention over the
     # latent tokens, cross-attention against 77 context tokens of dim 768, GEGLU feed-forward.
     Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()

@@ -2,7 +2,7 @@
 
 Shapes follow tests/unittest/ops/test_layernorm.py:35-205 (batch 50/900/1024, N=1496, gamma/beta None,
 eps 1e-5 and 0.1, multi-dim normalized shape) and test_softmax.py:72-225 (the K list, inner dims,
-zero batch), plus the BASELINE memory-bound sweep shapes. Tolerances are the reference's:
+zero batch), plus the benchmark memory-bound sweep shapes. Tolerances are the reference's:
 1e-3 for layernorm, 1e-2 for softmax.
 """
 import pytest
@@ -105,7 +105,7 @@ def test_softmax_extremes_and_zero_batch():
 
 
 def test_full_size_rows_are_independent_and_normalised():
-    """BASELINE memory-bound sweep at full size: layernorm [65536, 1024] and softmax [64, 1024, 1024]
+    """benchmark memory-bound sweep at full size: layernorm [65536, 1024] and softmax [64, 1024, 1024]
     (one eighth of the batch) checked through size-independent properties plus sampled rows."""
     from aitemplate_b200 import kernels
 
