@@ -113,3 +113,39 @@ def test_bert_layer_oracle_composes_the_op_oracles():
     want = oracle.layernorm(oracle.gemm_rcr(f, p["fc2_weight"], p["fc2_bias"], h1, epilogue="add"),
                             p["ln2_gamma"], p["ln2_beta"], 1e-12).reshape(2, 16, 64)
     assert float((got - want).abs().max()) < 1e-4
+
+
+def test_sd_block_oracle_composes_the_op_oracles():
+    # the Stable-Diffusion transformer block oracle against its own building blocks, on a small instance
+    import math
+
+    import torch
+    import torch.nn.functional as F
+
+    from aitemplate_b200.testing import workloads
+    from oracle import reference_ops as R
+
+    x, ctx, p = workloads.sd_block_inputs(2, tokens=64, dim=64, context_tokens=9, context_dim=48, seed=5)
+    got = R.sd_transformer_block(x, ctx, p, heads=4)
+
+    def attn(name, h, c):
+        def heads_first(t):
+            b, n, _ = t.shape
+            return t.reshape(b, n, 4, 16).permute(0, 2, 1, 3)
+
+        q = heads_first(R.gemm_rcr(h, p[f"{name}_to_q_weight"]))
+        k = heads_first(R.gemm_rcr(c, p[f"{name}_to_k_weight"]))
+        v = heads_first(R.gemm_rcr(c, p[f"{name}_to_v_weight"]))
+        o = R.mem_eff_attention(q, k, v)                       # [B, Sq, H, D]
+        o = o.reshape(o.shape[0], o.shape[1], 64)
+        return R.gemm_rcr(o, p[f"{name}_to_out_weight"], p[f"{name}_to_out_bias"])
+
+    xf = x.float()
+    h = R.layernorm(xf, p["norm1_weight"], p["norm1_bias"])
+    xf = attn("attn1", h, h) + xf
+    xf = attn("attn2", R.layernorm(xf, p["norm2_weight"], p["norm2_bias"]), ctx.float()) + xf
+    h = R.layernorm(xf, p["norm3_weight"], p["norm3_bias"])
+    gate = R.gemm_rcr(h, p["ff_gate_weight"], p["ff_gate_bias"], epilogue="fast_gelu")
+    ff = R.gemm_rcr(R.gemm_rcr(h, p["ff_proj_weight"], p["ff_proj_bias"]) * gate, p["ff_out_weight"], p["ff_out_bias"])
+    want = ff + xf
+    assert torch.allclose(got, want, atol=1e-5, rtol=1e-5)
