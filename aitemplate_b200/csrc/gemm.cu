@@ -289,6 +289,7 @@ void gemm_run(const GemmArgs& g) {
   bool vec = (g.n % 8 == 0) && aligned16(g.c) && (g.c_bs % 8 == 0);
   if (g.bias) vec = vec && aligned16(g.bias);
   B200AIT_REQUIRE(g.num_out >= 1 && g.num_out <= kMaxOut, "gemm: between 1 and 8 output buffers");
+  B200AIT_REQUIRE(g.num_out == 1 || !g.b_mn, "gemm: several output buffers are not built for row-major B");
   for (int i = 1; i < g.num_out; ++i) {
     B200AIT_REQUIRE(g.extra_out[i - 1] != nullptr, "gemm: null extra output buffer");
     vec = vec && aligned16(g.extra_out[i - 1]);

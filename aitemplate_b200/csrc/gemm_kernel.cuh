@@ -275,9 +275,10 @@ __device__ __forceinline__ void epilogue_direct_store32(const GemmParams& p, con
   }
 }
 
-// BMN: B is stored [K, N] (compile-time, so that the [N, K] kernels carry no trace of it). Only instantiated with
-// the generic epilogue (EPI == -1).
-template <int BN, bool BF16, int EPI, bool PAIR, bool BMN = false>
+// BMN: B is stored [K, N]. MULTI: the staged store goes to p.num_out destinations. Both are compile-time, so that
+// the plain [N, K] single-destination kernels carry no trace of them (a run-time flag cost the BERT-layer GEMMs
+// 2-3 %), and both are only instantiated with the generic epilogue (EPI == -1).
+template <int BN, bool BF16, int EPI, bool PAIR, bool BMN = false, bool MULTI = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_d0,
@@ -333,7 +334,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     tma_prefetch_desc(&tma_b);
     if (p.tma_store) {
       tma_prefetch_desc(&tma_out);
-      for (int i = 1; i < p.num_out; ++i) tma_prefetch_desc(&outs.m[i]);
+      if (MULTI)
+        for (int i = 1; i < p.num_out; ++i) tma_prefetch_desc(&outs.m[i]);
     }
     if (D0BOX && p.tma_d0) tma_prefetch_desc(&tma_d0);
   }
@@ -652,12 +654,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               const int gcol = colh + (c & ~1) * 32;
               if (p.store_mode == 0) {
                 tma_store_5d(&tma_out, box, gcol, row0, b, 0, 0);
-                for (int i = 1; i < p.num_out; ++i) tma_store_5d(&outs.m[i], box, gcol, row0, b, 0, 0);
+                if (MULTI)
+                  for (int i = 1; i < p.num_out; ++i) tma_store_5d(&outs.m[i], box, gcol, row0, b, 0, 0);
               } else {
                 const int cc = gcol / p.d, r_b = row0 / p.t1;
                 tma_store_5d(&tma_out, box, gcol - cc * p.d, row0 - r_b * p.t1, cc % p.t3, r_b, cc / p.t3);
-                for (int i = 1; i < p.num_out; ++i)
-                  tma_store_5d(&outs.m[i], box, gcol - cc * p.d, row0 - r_b * p.t1, cc % p.t3, r_b, cc / p.t3);
+                if (MULTI)
+                  for (int i = 1; i < p.num_out; ++i)
+                    tma_store_5d(&outs.m[i], box, gcol - cc * p.d, row0 - r_b * p.t1, cc % p.t3, r_b, cc / p.t3);
               }
               bulk_commit_group();
             }
@@ -692,25 +696,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   }
 }
 
-template <int BN, bool BF16, int EPI, bool BMN = false>
+template <int BN, bool BF16, int EPI, bool BMN = false, bool MULTI = false>
 void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout, const GemmParams& p, int grid,
                cudaStream_t stream) {
   using Cfg = TileCfg<BN>;
   static std::atomic<uint64_t> configured{0};
-  opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_tc_kernel<BN, BF16, EPI, false, BMN>),
+  opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_tc_kernel<BN, BF16, EPI, false, BMN, MULTI>),
                    Cfg::kSmemBytes);
-  gemm_tc_kernel<BN, BF16, EPI, false, BMN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout.m[0], ta, p,
-                                                                                           tout);
+  gemm_tc_kernel<BN, BF16, EPI, false, BMN, MULTI><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
+      ta, tb, tout.m[0], ta, p, tout);
   B200AIT_CUDA_CHECK(cudaGetLastError());
 }
 
 // CTA-pair variant: `grid` counts CTAs (twice the number of pairs); launched as clusters of two.
-template <int BN, bool BF16, int EPI, bool BMN = false>
+template <int BN, bool BF16, int EPI, bool BMN = false, bool MULTI = false>
 void launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout, const CUtensorMap& td0,
                     const GemmParams& p, int grid, cudaStream_t stream) {
   using Cfg = TileCfg<BN, true, d0_box_of<EPI, true>()>;
   static std::atomic<uint64_t> configured{0};
-  auto* kernel = &gemm_tc_kernel<BN, BF16, EPI, true, BMN>;
+  auto* kernel = &gemm_tc_kernel<BN, BF16, EPI, true, BMN, MULTI>;
   opt_in_smem_once(configured, reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
@@ -761,6 +765,13 @@ void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, 
   template <>                                                                                                  \
   void launch_tc_width<BN_>(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout,  \
                             const GemmParams& p, int grid, cudaStream_t stream) {                              \
+    if (p.num_out > 1) { /* several destinations: generic epilogue instantiation only */                       \
+      if (bf16)                                                                                                \
+        launch_tc<BN_, true, -1, false, true>(ta, tb, tout, p, grid, stream);                                  \
+      else                                                                                                     \
+        launch_tc<BN_, false, -1, false, true>(ta, tb, tout, p, grid, stream);                                 \
+      return;                                                                                                  \
+    }                                                                                                          \
     if (p.b_mn) { /* B stored [K, N]: generic epilogue instantiation only */                                   \
       if (bf16)                                                                                                \
         launch_tc<BN_, true, -1, true>(ta, tb, tout, p, grid, stream);                                         \

@@ -10,6 +10,13 @@ namespace b200ait {
 
 void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout,
                        const CUtensorMap& td0, const GemmParams& p, int grid, cudaStream_t stream) {
+  if (p.num_out > 1) {  // several destinations: generic epilogue instantiation only
+    if (bf16)
+      launch_tc_pair<256, true, -1, false, true>(ta, tb, tout, td0, p, grid, stream);
+    else
+      launch_tc_pair<256, false, -1, false, true>(ta, tb, tout, td0, p, grid, stream);
+    return;
+  }
   if (p.b_mn) {  // B stored [K, N]: generic epilogue instantiation only
     if (bf16)
       launch_tc_pair<256, true, -1, true>(ta, tb, tout, td0, p, grid, stream);
