@@ -297,6 +297,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const bool misaligned = (smem_u32(smem) & 1023u) != 0u;
   if (misaligned && threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevBadSmemAlignment);
   const int num_units = misaligned ? 0 : p.num_units;
+  const int splits = PAIR ? 1 : p.splits;  // CTA pairs never split K: their kernels drop the split-K paths
   // Work distribution: a single CTA, or a pair of CTAs (cluster ranks 0 and 1), walks the units.
   const int pair_rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
   const int walker = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
@@ -363,7 +364,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       bool ok = true;
       for (int unit = walker; ok && unit < num_units; unit += num_walkers) {
         int b, m_blk, n_blk;
-        const int tile = unit / p.splits, split = unit - tile * p.splits;
+        const int tile = unit / splits, split = unit - tile * splits;
         decode_tile(p, tile, b, m_blk, n_blk);
         if (PAIR) m_blk = 2 * m_blk + pair_rank;
         const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
@@ -436,7 +437,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        const int split = unit % p.splits;
+        const int split = unit % splits;
         const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kDevWaitFullTimeout);
@@ -503,11 +504,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const int et = threadIdx.x - 64;  // 0..255
     const int code = epilogue_code_of<EPI>(p);
     const bool has_d0 = epi_b1(code) != kBinaryNone;
-    const bool has_bias = p.bias != nullptr && p.splits == 1;
+    const bool has_bias = p.bias != nullptr && splits == 1;
     const bool chunk_contig = p.store_mode == 0 || (p.d % 32 == 0);
-    const bool use_tma = (BN >= 128) && p.tma_store != 0;
+    // Lean kernels (CTA pair + compile-time epilogue) are only launched for alpha = 1, the staged TMA store and,
+    // with a residual, the staged residual boxes: their code carries none of the other paths.
+    constexpr bool kLean = PAIR && EPI >= 0;
+    const bool use_tma = kLean || ((BN >= 128) && p.tma_store != 0);
     // residual through staging boxes: needs the TMA store path and a tensor map over d0
-    const bool box_d0 = D0BOX && use_tma && p.tma_d0 != 0;
+    const bool box_d0 = D0BOX && (kLean || (use_tma && p.tma_d0 != 0));
     uint8_t* my_staging = staging + ew * (Cfg::kBoxesPerWarp * 4096);
     uint64_t* my_d0_bar = d0_bar + 2 * ew;
     uint32_t d0_phase_bits = 0;  // bit i: parity to wait for on my_d0_bar[i]
@@ -518,7 +522,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                                           PAIR ? mapa_shared(smem_u32(&acc_empty[1]), 0) : 0u};
     for (int unit = walker; ok && unit < num_units; unit += num_walkers) {
       int b, m_blk, n_blk;
-      const int tile = unit / p.splits, split = unit - tile * p.splits;
+      const int tile = unit / splits, split = unit - tile * splits;
       decode_tile(p, tile, b, m_blk, n_blk);
       if (PAIR) m_blk = 2 * m_blk + pair_rank;
       const int colh = n_blk * BN + half * (BN / 2);  // first column of this warp's half
@@ -557,7 +561,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           for (int q = 0; q < 4; ++q) d0v[q] = __ldg(reinterpret_cast<const uint4*>(d0_row + col0) + q);
         }
       };
-      if (p.splits == 1 && !box_d0) prefetch_d0(colh);
+      if (splits == 1 && !box_d0) prefetch_d0(colh);
       ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, kDevWaitAccFullTimeout);
       if (!ok) break;
       tc_fence_after();
@@ -577,7 +581,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         for (int q = 0; q < 4; ++q) d0c[q] = d0v[q];
         if (c + 1 < kChunksPerWarp && col0 + 32 < p.N) {  // next chunk's loads go out before this chunk's math
           tmem_ld_32x32b_x32(t_base + static_cast<uint32_t>((c + 1) * 32), nxt);
-          if (p.splits == 1 && !box_d0) prefetch_d0(col0 + 32);
+          if (splits == 1 && !box_d0) prefetch_d0(col0 + 32);
         } else if (!released) {
           released = true;
           tc_fence_before();
@@ -592,7 +596,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(cur[j]);
         const bool full = p.vec_ok && (col0 + 32 <= p.N);
-        if (p.splits > 1) {
+        if (splits > 1) {
           // split-K: raw fp32 partial sums; the reduce kernel applies the epilogue
           if (row_ok) {
             float* dst = p.partial + ((static_cast<long long>(split) * p.batch + b) * p.M + row) * p.N + col0;
@@ -608,7 +612,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           }
           return;
         }
-        if (p.alpha != 1.f) {
+        if (!kLean && p.alpha != 1.f) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
         }
