@@ -297,7 +297,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const bool misaligned = (smem_u32(smem) & 1023u) != 0u;
   if (misaligned && threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevBadSmemAlignment);
   const int num_units = misaligned ? 0 : p.num_units;
-  const int splits = PAIR ? 1 : p.splits;  // CTA pairs never split K: their kernels drop the split-K paths
+  // Lean kernels: a compile-time epilogue on a tile wide enough for the staged TMA store, launched only for
+  // alpha = 1, no split-K, the staged store and (with a residual: CTA pairs only) staged residual boxes. Their
+  // code carries none of the other paths, which is worth several per cent on the short-K GEMMs.
+  constexpr bool kLean = EPI >= 0 && BN >= 128 && (PAIR || epi_b1(EPI < 0 ? 0 : EPI) == kBinaryNone);
+  const int splits = (PAIR || kLean) ? 1 : p.splits;  // CTA pairs never split K either
   // Work distribution: a single CTA, or a pair of CTAs (cluster ranks 0 and 1), walks the units.
   const int pair_rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
   const int walker = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
@@ -506,9 +510,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const bool has_d0 = epi_b1(code) != kBinaryNone;
     const bool has_bias = p.bias != nullptr && splits == 1;
     const bool chunk_contig = p.store_mode == 0 || (p.d % 32 == 0);
-    // Lean kernels (CTA pair + compile-time epilogue) are only launched for alpha = 1, the staged TMA store and,
-    // with a residual, the staged residual boxes: their code carries none of the other paths.
-    constexpr bool kLean = PAIR && EPI >= 0;
     const bool use_tma = kLean || ((BN >= 128) && p.tma_store != 0);
     // residual through staging boxes: needs the TMA store path and a tensor map over d0
     const bool box_d0 = D0BOX && (kLean || (use_tma && p.tma_d0 != 0));
@@ -675,8 +676,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           epilogue_direct_store32<BF16>(p, v, b, row, col0, full, chunk_contig);
         }
       };
-#pragma unroll
-      for (int c = 0; c < kChunksPerWarp; c += 2) {
+#pragma unroll 1
+      for (int c = 0; c < kChunksPerWarp; c += 2) {  // one copy of the two-chunk body: less code to fetch
         chunk_step(c, ra, rb);
         if (c + 1 < kChunksPerWarp) chunk_step(c + 1, rb, ra);
       }
@@ -785,6 +786,13 @@ void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, 
     }                                                                                                          \
     if (bf16) {                                                                                                \
       launch_tc<BN_, true, -1>(ta, tb, tout, p, grid, stream);                                                 \
+      return;                                                                                                  \
+    }                                                                                                          \
+    /* the compile-time-epilogue kernels of the wide tiles are lean (see the kernel): anything else is generic */ \
+    const bool lean_ok = BN_ < 128 || epi_b1(p.epilogue) != kBinaryNone ||                                     \
+                         (p.alpha == 1.f && p.tma_store != 0 && p.splits == 1);                                \
+    if (!lean_ok) {                                                                                            \
+      launch_tc<BN_, false, -1>(ta, tb, tout, p, grid, stream);                                                \
       return;                                                                                                  \
     }                                                                                                          \
     switch (p.epilogue) {                                                                                      \
