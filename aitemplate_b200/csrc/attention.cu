@@ -52,6 +52,32 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 64;     // keys per block
 constexpr int kKvStages = 3;    // K/V ring: blocks j, j+1, j+2 are in flight
 
+// Packed fp32 arithmetic of sm_100 (two lanes per instruction) and the three-input max: the softmax threads are
+// bound by instruction issue, and these halve the count of their FMA / add / max instructions.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <int DCH>
 struct AttnCfg {
   static constexpr int kQBytes = DCH * kBlockM * 128;
@@ -260,8 +286,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
           uint32_t v[32];
           tmem_ld_32x32b_x32(t_addr + c * 32, v);
           tmem_ld_wait();
+          const uint64_t alpha2 = pack2(alpha, alpha);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(v[i]));
+          for (int i = 0; i < 32; i += 2) {
+            const uint64_t r2 = fma2(pack2(o[c * 32 + i], o[c * 32 + i + 1]), alpha2,
+                                     pack2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+            unpack2(r2, o[c * 32 + i], o[c * 32 + i + 1]);
+          }
         }
       }
       tc_fence_before();
@@ -302,10 +333,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
         for (int i = 0; i < 32; i += 2) {
           const float a0 = __uint_as_float(s0[i]), a1 = __uint_as_float(s0[i + 1]);
           const float b0 = __uint_as_float(s1[i]), b1 = __uint_as_float(s1[i + 1]);
-          m0 = fmaxf(m0, (kPlain || i < limit) ? a0 : -INFINITY);
-          m1 = fmaxf(m1, (kPlain || i + 1 < limit) ? a1 : -INFINITY);
-          m2 = fmaxf(m2, (kPlain || 32 + i < limit) ? b0 : -INFINITY);
-          m3 = fmaxf(m3, (kPlain || 33 + i < limit) ? b1 : -INFINITY);
+          if constexpr (kPlain) {
+            m0 = max3(m0, a0, a1);
+            m2 = max3(m2, b0, b1);
+          } else {
+            m0 = fmaxf(m0, (i < limit) ? a0 : -INFINITY);
+            m1 = fmaxf(m1, (i + 1 < limit) ? a1 : -INFINITY);
+            m2 = fmaxf(m2, (32 + i < limit) ? b0 : -INFINITY);
+            m3 = fmaxf(m3, (33 + i < limit) ? b1 : -INFINITY);
+          }
         }
         const float m_blk = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         m_new = fmaxf(m_run, m_blk * p.scale_log2);
@@ -313,20 +349,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
         alpha = exp2f(m_run - m_use);
         // p = exp2(s * scale - m), row sum, P -> swizzled shared memory (16-byte unit u of row r sits
         // at unit u ^ (r & 7))
+        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
+        uint64_t lsum2 = pack2(0.f, 0.f);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const uint32_t(&sv)[32] = h == 0 ? s0 : s1;
           uint32_t packed[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float p0 = exp2f(fmaf(__uint_as_float(sv[i]), p.scale_log2, -m_use));
-            float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -m_use));
+            float x0, x1;
+            unpack2(fma2(pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), scale2, negm2), x0, x1);
+            float p0 = exp2f(x0);
+            float p1 = exp2f(x1);
             if (!kPlain) {
               p0 = (h * 32 + i < limit) ? p0 : 0.f;
               p1 = (h * 32 + i + 1 < limit) ? p1 : 0.f;
             }
-            l0 += p0;
-            l1 += p1;
+            lsum2 = add2(lsum2, pack2(p0, p1));
             packed[i >> 1] = E::from_float2(p0, p1);
           }
 #pragma unroll
@@ -336,6 +375,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
                 make_uint4(packed[u * 4], packed[u * 4 + 1], packed[u * 4 + 2], packed[u * 4 + 3]);
           }
         }
+        unpack2(lsum2, l0, l1);
       };
       if constexpr (NOMASK) {
         softmax_block(std::true_type{});
