@@ -132,6 +132,18 @@ def test_cta_pair_tiles(m, n, kk, epilogue):
     _close(y, oracle.gemm_rcr(x, w, b, *d, epilogue=epilogue))
 
 
+@pytest.mark.parametrize("bsz,m,n,kk", [(3, 300, 520, 512), (8, 256, 256, 1024), (5, 128, 768, 576)])
+def test_cta_pair_tiles_batched(bsz, m, n, kk):
+    # bmm through the CTA-pair kernel (forced): ragged rows per batch, batch index in the TMA coordinates
+    k = _kernels()
+    a, b = _rand((bsz, m, kk), 330, dist="uniform"), _rand((bsz, n, kk), 331, scale=0.1)
+    y = k.bmm_rcr(a.cuda(), b.cuda(), tile_n=512)
+    assert k.device_status() == 0
+    _close(y, oracle.bmm_rcr(a, b))
+    y2 = k.bmm_rcr(a.cuda(), b.cuda(), alpha=0.125, tile_n=512)      # alpha: the generic (non-lean) pair kernel
+    _close(y2, oracle.bmm_rcr(a, b, alpha=0.125))
+
+
 def test_cta_pair_tiles_bf16_and_permuted_store():
     k = _kernels()
     s_, h, dd, bsz = 384, 12, 64, 4
