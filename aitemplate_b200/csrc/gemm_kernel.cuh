@@ -766,6 +766,9 @@ void launch_tc_width<256>(bool, const CUtensorMap&, const CUtensorMap&, const Ou
 void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout,
                        const CUtensorMap& td0, const GemmParams& p, int grid, cudaStream_t stream);
 
+void launch_tc_pair256_bf16_lean(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout,
+                                 const CUtensorMap& td0, const GemmParams& p, int grid, cudaStream_t stream);
+
 #define B200AIT_DEFINE_LAUNCH_TC_WIDTH(BN_)                                                                    \
   template <>                                                                                                  \
   void launch_tc_width<BN_>(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout,  \

@@ -26,11 +26,15 @@ void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, 
   }
   // the compile-time-epilogue kernels are lean: alpha = 1, staged TMA store, residual (if any) through staged boxes
   const bool lean_ok = p.alpha == 1.f && p.tma_store != 0 && (epi_b1(p.epilogue) == kBinaryNone || p.tma_d0 != 0);
-  if (bf16 || !lean_ok) {
+  if (!lean_ok) {
     if (bf16)
       launch_tc_pair<256, true, -1>(ta, tb, tout, td0, p, grid, stream);
     else
       launch_tc_pair<256, false, -1>(ta, tb, tout, td0, p, grid, stream);
+    return;
+  }
+  if (bf16) {  // the bfloat16 lean instantiations live in their own translation unit
+    launch_tc_pair256_bf16_lean(ta, tb, tout, td0, p, grid, stream);
     return;
   }
   switch (p.epilogue) {
