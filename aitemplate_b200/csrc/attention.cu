@@ -52,32 +52,6 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 64;     // keys per block
 constexpr int kKvStages = 3;    // K/V ring: blocks j, j+1, j+2 are in flight
 
-// Packed fp32 arithmetic of sm_100 (two lanes per instruction) and the three-input max: the softmax threads are
-// bound by instruction issue, and these halve the count of their FMA / add / max instructions.
-__device__ __forceinline__ uint64_t pack2(float a, float b) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-
 template <int DCH>
 struct AttnCfg {
   static constexpr int kQBytes = DCH * kBlockM * 128;

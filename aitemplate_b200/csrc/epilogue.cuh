@@ -9,6 +9,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include "ptx.cuh"
+
 namespace b200ait {
 
 enum Unary : int {
@@ -75,10 +77,22 @@ __device__ __forceinline__ void apply_unary_vec(int u, float (&v)[N]) {
 #pragma unroll
       for (int i = 0; i < N; ++i) v[i] = fmaxf(v[i], 0.f);
       break;
-    case kUnaryFastGelu:
+    case kUnaryFastGelu: {
+      // two elements per instruction: x^2, k0k1 x^2 + k0, times x, (MUFU tanh per element), 0.5 x, 0.5 x t + 0.5 x
+      static_assert(N % 2 == 0, "packed path wants an even count");
+      const uint64_t k0 = pack2(0.7978845608028654f, 0.7978845608028654f);
+      const uint64_t k0k1 = pack2(0.7978845608028654f * 0.044715f, 0.7978845608028654f * 0.044715f);
+      const uint64_t half2 = pack2(0.5f, 0.5f);
 #pragma unroll
-      for (int i = 0; i < N; ++i) v[i] = apply_unary(kUnaryFastGelu, v[i]);
+      for (int i = 0; i < N; i += 2) {
+        const uint64_t x = pack2(v[i], v[i + 1]);
+        float u0, u1;
+        unpack2(mul2(x, fma2(mul2(x, x), k0k1, k0)), u0, u1);
+        const uint64_t hx = mul2(x, half2);
+        unpack2(fma2(hx, pack2(tanh_approx(u0), tanh_approx(u1)), hx), v[i], v[i + 1]);
+      }
       break;
+    }
     case kUnaryGelu:
 #pragma unroll
       for (int i = 0; i < N; ++i) v[i] = apply_unary(kUnaryGelu, v[i]);

@@ -622,7 +622,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             const float4 f = *reinterpret_cast<const float4*>(bs + q * 4);
-            v[q * 4] += f.x, v[q * 4 + 1] += f.y, v[q * 4 + 2] += f.z, v[q * 4 + 3] += f.w;
+            unpack2(add2(pack2(v[q * 4], v[q * 4 + 1]), pack2(f.x, f.y)), v[q * 4], v[q * 4 + 1]);
+            unpack2(add2(pack2(v[q * 4 + 2], v[q * 4 + 3]), pack2(f.z, f.w)), v[q * 4 + 2], v[q * 4 + 3]);
           }
         }
         if (use_tma) {
