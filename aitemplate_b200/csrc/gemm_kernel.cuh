@@ -217,7 +217,10 @@ __device__ __forceinline__ void epilogue_math32(const GemmParams& p, float (&v)[
         float f[8];
         unpack8<BF16>(d0v[q], f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[q * 8 + j] = (b1 == kBinaryAdd) ? v[q * 8 + j] + f[j] : v[q * 8 + j] * f[j];
+        for (int j = 0; j < 8; j += 2) {  // two elements per instruction
+          const uint64_t x = pack2(v[q * 8 + j], v[q * 8 + j + 1]), y = pack2(f[j], f[j + 1]);
+          unpack2((b1 == kBinaryAdd) ? add2(x, y) : mul2(x, y), v[q * 8 + j], v[q * 8 + j + 1]);
+        }
       }
     } else {
       const T* d0 = static_cast<const T*>(p.d0) + d_base;
