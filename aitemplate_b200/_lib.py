@@ -46,6 +46,9 @@ def _signatures():
             c_int,
             [c_void_p] * 6 + [c_int64] * 12 + [c_int, c_int, c_float, c_int, c_void_p, c_int64, c_int, c_void_p],
         ),
+        "b200ait_bmm_permute0213": (
+            c_int, [c_void_p] * 3 + [c_int64] * 7 + [c_int, c_int, c_float, c_int, c_void_p],
+        ),
         "b200ait_gemm_rcr_multi_out": (
             c_int,
             [c_void_p] * 4 + [POINTER(c_void_p), c_int] + [c_int64] * 7 + [c_int, c_int, c_float, c_int, c_void_p],

@@ -4,8 +4,8 @@ Same signature and validation as the reference (python/aitemplate/compiler/compi
 where the reference renders C++ per op, runs nvcc and links `test.so`, this build lowers the graph to
 a *plan* for the prebuilt runtime in libb200ait.so:
 
-  toposort -> remove_no_ops -> mark_param_tensor -> fuse_mm_elementwise -> split_to_views -> fuse_strided_cat
-  -> name_graph
+  toposort -> remove_no_ops -> mark_param_tensor -> fuse_mm_elementwise -> split_to_views
+  -> fuse_split_strided -> fuse_strided_cat -> name_graph
   -> memory_planning -> write <workdir>/<test_name>/<dll_name>.plan (+ constants.bin) -> Model(plan)
 
 There is no code generation. Profiling is optional: by default the library's planner picks tile width and
@@ -25,6 +25,7 @@ from .dtype import dtype_str_to_enum
 from .model import Model
 from .transform import (
     fuse_mm_elementwise,
+    fuse_split_strided,
     fuse_strided_cat,
     mark_param_tensor,
     memory_planning,
@@ -250,6 +251,7 @@ def compile_model(
         graph = fuse_mm_elementwise(graph, outputs)
         mark_param_tensor(graph)
         split_to_views(graph)
+        fuse_split_strided(graph)
         fuse_strided_cat(graph)
     name_graph(graph)
     if profile_devs is not None or os.getenv("AIT_B200_PROFILE", "0") == "1":

@@ -3,10 +3,11 @@
 A 2-D operand, or a batch of 1, broadcasts over the other operand's batch."""
 from __future__ import annotations
 
-from typing import Any, Dict, List
+from typing import Any, Dict, List, Tuple
 
 from ...base import IntImm, IntVar, Tensor
 from ...tensor_accessor import TensorAccessor
+from ..common.view_ops import reshape
 from .gemm_rcr import gemm
 
 
@@ -57,7 +58,9 @@ class bmm_rcr(bmm):
 
     def _lower(self) -> Dict[str, Any]:
         a, b = self._attrs["inputs"]
-        return {"kernel": "bmm_rcr", "operands": [a, b], "ints": [], "floats": [float(self._attrs["alpha"])]}
+        # ints[0]: d1 of a "0213" permuted store (bmm_rcr_permute), 0 = plain [B, M, N]
+        return {"kernel": "bmm_rcr", "operands": [a, b], "ints": [int(self._attrs.get("permute_d1", 0))],
+                "floats": [float(self._attrs["alpha"])]}
 
 
 class bmm_rrr(bmm):
@@ -80,4 +83,39 @@ class bmm_rrr(bmm):
 
     def _lower(self) -> Dict[str, Any]:
         a, b = self._attrs["inputs"]
-        return {"kernel": "bmm_rrr", "operands": [a, b], "ints": [], "floats": [float(self._attrs["alpha"])]}
+        return {"kernel": "bmm_rrr", "operands": [a, b], "ints": [int(self._attrs.get("permute_d1", 0))],
+                "floats": [float(self._attrs["alpha"])]}
+
+
+def _permute_variant(base, op_name: str):
+    """bmm whose [B, M, N] result is stored as [B / d1, d1, M, N].permute(0, 2, 1, 3); returns that 4-D tensor
+    [B / d1, M, d1, N] (python/aitemplate/compiler/ops/gemm_universal/bmm_rcr_permute.py:28-116 and
+    bmm_rrr_permute.py; epilogue layout Permute4DBMM_0213)."""
+
+    def __init__(self, shape: Tuple[int, ...], layout: str = "0213") -> None:
+        base.__init__(self)
+        if layout != "0213":
+            raise NotImplementedError(f"{layout} is not implemented!")
+        self._attrs["op"] = op_name
+        self._attrs["shape"] = tuple(shape)
+        self._attrs["layout"] = f"Permute4DBMM_{layout}"
+        self._attrs["permute_shape"] = "_".join(map(str, shape))
+        self._attrs["permute_d1"] = int(shape[0])
+
+    def _get_op_attributes(self):
+        return {"layout": self._attrs["layout"].split("_")[-1], "shape": self._attrs["shape"]}
+
+    def __call__(self, a: Tensor, b: Tensor) -> Tensor:
+        out = base.__call__(self, a, b)
+        batch, m, n = out._attrs["shape"]
+        d1 = self._attrs["permute_d1"]
+        if not isinstance(batch, IntImm) or d1 <= 0 or batch.value() % d1:
+            raise RuntimeError(f"{op_name}: the batch ({batch}) must be static and a multiple of shape[0] = {d1}")
+        return reshape()(out, [batch.value() // d1, m, d1, n])
+
+    return type(op_name, (base,), {"__init__": __init__, "__call__": __call__,
+                                   "_get_op_attributes": _get_op_attributes, "__doc__": _permute_variant.__doc__})
+
+
+bmm_rcr_permute = _permute_variant(bmm_rcr, "bmm_rcr_permute")
+bmm_rrr_permute = _permute_variant(bmm_rrr, "bmm_rrr_permute")

@@ -90,12 +90,16 @@ class gemm(Operator):
         acc = self._attrs["output_accessors"][0]
         n = b._attrs["shape"][0].value()
         out_stride = acc.row_stride() if acc.stride_dim is not None else n
+        # operand A read in place from a column block of a wider buffer (a fused split): the operand tensor is an
+        # alias that starts at the block, so only the row stride is needed; 0 = contiguous rows of K
+        a_acc = self._attrs["input_accessors"][0]
+        a_stride = a_acc.row_stride() if a_acc.stride_dim is not None else 0
         return {
             "kernel": "gemm_rcr",
             "operands": [a, b, bias, d0, d1],
-            # the last two: tile width and split-K picked by the compile-time profiler (0 = the library decides)
+            # ints 7, 8: tile width and split-K picked by the compile-time profiler (0 = the library decides)
             "ints": [epilogue_code(*self._epi), store_mode, t[0], t[1], t[2], acc.offset, out_stride,
-                     int(self._attrs.get("tile_n", 0)), int(self._attrs.get("split_k", 0))],
+                     int(self._attrs.get("tile_n", 0)), int(self._attrs.get("split_k", 0)), a_stride],
             "floats": [float(self._attrs["alpha"])],
         }
 

@@ -87,5 +87,7 @@ class layernorm(Operator):
             n *= d.value()
         acc = self._attrs["output_accessors"][0]
         out_stride = acc.row_stride() if acc.stride_dim is not None else 0  # 0: contiguous rows of n
-        return {"kernel": "layernorm", "operands": [x, gamma, beta], "ints": [n, acc.offset, out_stride],
+        x_acc = self._attrs["input_accessors"][0]
+        in_stride = x_acc.row_stride() if x_acc.stride_dim is not None else 0  # rows of a fused split's input
+        return {"kernel": "layernorm", "operands": [x, gamma, beta], "ints": [n, acc.offset, out_stride, in_stride],
                 "floats": [float(self._attrs["eps"])]}

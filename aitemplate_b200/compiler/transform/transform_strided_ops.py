@@ -67,3 +67,66 @@ def fuse_strided_cat(sorted_graph: List[Tensor]) -> int:
                 fused += 1
             offset += width
     return fused
+
+
+def _strided_reader_slot(op, x) -> bool:
+    """True when `op` can read `x` through a row stride: x is operand A of a 2-D GEMM or the input of a
+    layernorm, and appears nowhere else among the op's inputs."""
+    from ..ops.gemm_universal.bmm import bmm
+    from ..ops.gemm_universal.gemm_rcr import gemm
+    from ..ops.layernorm import layernorm
+
+    ins = op._attrs["inputs"]
+    if sum(1 for y in ins if y is x) != 1 or ins[0] is not x:
+        return False
+    if isinstance(op, bmm):
+        return False
+    return isinstance(op, (gemm, layernorm)) and op._attrs["input_accessors"][0].stride_dim is None
+
+
+def fuse_split_strided(sorted_graph: List[Tensor]) -> int:
+    """The split side of the reference's strided-op pass (python/aitemplate/compiler/transform/
+    transform_strided_ops.py:94-333 together with fuse_split.py): when every consumer of an output of a
+    last-dim split is a GEMM (as operand A) or a layernorm, those kernels read their column block of the
+    split's input in place: the consumer's input TensorAccessor is re-based onto that input (element
+    offset + the wider row stride), the split output becomes an alias of it at the block's byte offset, and
+    the split's output mask for it is cleared. A split whose outputs are all fused launches nothing.
+    Column blocks must start and end on 16-byte boundaries, the alignment the vector loads and the TMA
+    descriptors of the consumers need (the reference checks the same through its alignment attributes).
+    Returns the number of split outputs that were fused."""
+    from ..dtype import get_dtype_size
+    from ..ops.tensor import split
+
+    fused = 0
+    for op in sorted_ops(sorted_graph):
+        if not isinstance(op, split):
+            continue
+        x = op._attrs["inputs"][0]
+        shape = x._attrs["shape"]
+        dim = op._attrs["split_dim"]
+        if dim != len(shape) - 1 or not isinstance(shape[dim], IntImm):
+            continue
+        elem = get_dtype_size(x.dtype())
+        offset = 0
+        for i, (o, width) in enumerate(zip(op._attrs["outputs"], op._attrs["split_sizes"])):
+            readers = list(o._attrs["dst_ops"])
+            ok = (
+                op._attrs["output_masks"][i]
+                and readers
+                and not o._attrs["is_output"]
+                and o._attrs["is_view_of"] is None
+                and width > 0
+                and (offset * elem) % 16 == 0
+                and (width * elem) % 16 == 0
+                and (shape[dim].value() * elem) % 16 == 0
+                and all(_strided_reader_slot(r, o) for r in readers)
+            )
+            if ok:
+                for r in readers:
+                    r._attrs["input_accessors"][0].update_base_tensor(x, dim, offset)
+                o._attrs["is_view_of"] = x   # same storage: the alias starts at the block's first column
+                o._attrs["view_offset_bytes"] = offset * elem
+                op._attrs["output_masks"][i] = False
+                fused += 1
+            offset += width
+    return fused

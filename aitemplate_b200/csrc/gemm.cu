@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const void* a_, const vo
       v = (b2 == kBinaryAdd) ? v + f : v * f;
     }
     v = apply_unary(u2, v);
-    static_cast<T*>(p.out)[static_cast<long long>(b) * p.c_bs + row_offset(p, row) + col_offset(p, col)] =
+    static_cast<T*>(p.out)[batch_offset(p, b) + row_offset(p, row) + col_offset(p, col)] =
         E::from_float(v);
   }
 }
@@ -263,7 +263,20 @@ SplitPlan plan_split_k(long long batch, long long m, long long n, long long k, i
   return sp;
 }
 
-void gemm_run(const GemmArgs& g) {
+void gemm_run(const GemmArgs& g_in) {
+  GemmArgs g = g_in;
+  long long c_bdiv = 0, c_bs_hi = 0;
+  if (g.store_mode == 3) {
+    // Permute4DBMM "0213" of the batched GEMMs: [B / d1, d1, M, N] -> [B / d1, M, d1, N], d1 = t1
+    // (python/aitemplate/compiler/ops/gemm_universal/bmm_rcr_permute.py, bmm_rrr_permute.py; functor
+    // cutlass::layout::Tensor4DPermuteBMM0213 in the reference's CUTLASS fork). Batch b = hi * d1 + lo lands at
+    // hi * M * d1 * N + lo * N and rows are d1 * N apart: a plain strided store with a two-level batch stride.
+    B200AIT_REQUIRE(g.t1 > 0 && g.batch % g.t1 == 0, "bmm permute: the batch must be a multiple of shape[0]");
+    B200AIT_REQUIRE(g.num_out == 1, "bmm permute: one output buffer only");
+    c_bdiv = g.t1, c_bs_hi = g.m * g.t1 * g.n;
+    g.ldc = g.t1 * g.n, g.c_bs = g.n, g.store_mode = 0;
+    if (c_bdiv == 1) c_bdiv = 0, g.c_bs = g.m * g.n;  // d1 = 1: the identity permutation
+  }
   B200AIT_REQUIRE(g.dtype == kDTypeHalf || g.dtype == kDTypeBFloat16, "gemm: dtype must be float16 or bfloat16");
   B200AIT_REQUIRE(g.batch >= 0 && g.m >= 0 && g.n >= 0 && g.k >= 0, "gemm: negative dimension");
   if (g.batch == 0 || g.m == 0 || g.n == 0 || g.k == 0) return;  // reference: zero-size problems launch nothing
@@ -286,6 +299,7 @@ void gemm_run(const GemmArgs& g) {
   p.alpha = g.alpha, p.epilogue = g.epilogue;
   p.store_mode = 0;
   p.t1 = 1, p.t3 = 1, p.d = 1;
+  p.c_bdiv = static_cast<int>(c_bdiv), p.c_bs_hi = c_bs_hi;
   bool vec = (g.n % 8 == 0) && aligned16(g.c) && (g.c_bs % 8 == 0);
   if (g.bias) vec = vec && aligned16(g.bias);
   B200AIT_REQUIRE(g.num_out >= 1 && g.num_out <= kMaxOut, "gemm: between 1 and 8 output buffers");
@@ -358,8 +372,9 @@ void gemm_run(const GemmArgs& g) {
   // when the 256-wide tile was picked automatically, the 256-row tiles still fill every pair once, and K is
   // deep enough for the main loop (not the per-tile epilogue and pair hand-shake) to set the pace.
   const long long pair_tiles = ((g.m + 2 * kBM - 1) / (2 * kBM)) * ((g.n + 255) / 256) * g.batch;
+  B200AIT_REQUIRE(!(force_pair && p.c_bdiv != 0), "bmm permute: the CTA-pair tiles do not take the permuted store");
   const bool pair = force_pair || (g.tile_n == 0 && bn == 256 && sp.splits == 1 && g.k >= 512 &&
-                                   pair_tiles >= sm_count() / 2);
+                                   pair_tiles >= sm_count() / 2 && p.c_bdiv == 0);
   p.splits = sp.splits;
   p.kb_per_split = sp.kb_per_split;
   p.partial = static_cast<float*>(g.workspace);
@@ -378,9 +393,15 @@ void gemm_run(const GemmArgs& g) {
       void* dst = i == 0 ? g.c : g.extra_out[i - 1];
       if (p.store_mode == 0) {
         const long long bs = g.batch > 1 ? g.c_bs : g.m * g.ldc;
-        const long long dims[5] = {g.n, g.m, g.batch, 1, 1};
-        const long long strides[4] = {g.ldc, bs, bs, bs};
-        tout.m[i] = make_out_map(dst, bf16, dims, strides);
+        if (p.c_bdiv != 0) {  // batch coordinate split into (lo, hi)
+          const long long dims[5] = {g.n, g.m, p.c_bdiv, g.batch / p.c_bdiv, 1};
+          const long long strides[4] = {g.ldc, g.c_bs, p.c_bs_hi, p.c_bs_hi};
+          tout.m[i] = make_out_map(dst, bf16, dims, strides);
+        } else {
+          const long long dims[5] = {g.n, g.m, g.batch, 1, 1};
+          const long long strides[4] = {g.ldc, bs, bs, bs};
+          tout.m[i] = make_out_map(dst, bf16, dims, strides);
+        }
         p.tma_store = 1;
       } else if (p.d % 64 == 0 && p.t1 % 32 == 0 && g.batch == 1) {
         // destination [c2][row / t1][c3][row % t1][d]: dims innermost first (d, t1, t3, M / t1, c2 extent)
@@ -469,6 +490,25 @@ B200AIT_EXPORT int b200ait_gemm_rrr(const void* a, const void* b, const void* bi
     g.workspace = workspace;
     g.workspace_bytes = workspace_bytes;
     g.split_k = split_k;
+    gemm_run(g);
+  });
+}
+
+// bmm_rcr_permute / bmm_rrr_permute (python/aitemplate/compiler/ops/gemm_universal/bmm_rcr_permute.py:28-116,
+// bmm_rrr_permute.py; generated signature python/aitemplate/backend/cuda/gemm_universal/bmm_common.py:56-81 with the
+// Permute4DBMM_0213 epilogue of bmm_permute_common.py): c[b] = alpha * a[b] @ op(b[b]) for a [batch, m, k] and
+// b [batch, n, k] (b_row_major = 0) or [batch, k, n] (b_row_major = 1), stored as
+// [batch / d1, d1, m, n].permute(0, 2, 1, 3), i.e. c has the shape [batch / d1, m, d1, n]. A batch stride of 0
+// broadcasts that operand.
+B200AIT_EXPORT int b200ait_bmm_permute0213(const void* a, const void* b, void* c, int64_t batch, int64_t m, int64_t n,
+                                           int64_t k, int64_t a_batch_stride, int64_t b_batch_stride, int64_t d1,
+                                           int b_row_major, int dtype, float alpha, int tile_n, cudaStream_t stream) {
+  return guarded("b200ait_bmm_permute0213", [&] {
+    B200AIT_REQUIRE(d1 > 0, "bmm permute: shape[0] must be positive");
+    GemmArgs g{a, b, nullptr, nullptr, nullptr, c, batch, m, n, k, k, b_row_major ? n : k, n, n,
+               a_batch_stride, b_batch_stride, m * n, m * n, 0, dtype, alpha, 3, d1, 1, 1, tile_n, stream};
+    g.b_mn = b_row_major ? 1 : 0;
+    g.split_k = 1;
     gemm_run(g);
   });
 }

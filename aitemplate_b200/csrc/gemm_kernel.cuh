@@ -38,6 +38,11 @@ struct GemmParams {
   int num_out;    // destinations of the staged store (1 unless the caller passed several output buffers)
   int tma_d0;     // the residual d0 arrives by TMA in the output staging boxes (tensor map `tma_d0`)
   int* status;
+  // batched "0213" store (bmm_*_permute): batch b = hi * c_bdiv + lo lands at hi * c_bs_hi + lo * c_bs, rows ldc
+  // apart, i.e. [B / d1, d1, M, N] -> [B / d1, M, d1, N] with c_bdiv = d1, c_bs = N, ldc = d1 * N, c_bs_hi = M * d1 * N.
+  // 0 = plain batch stride. Only the kernels with a run-time epilogue (EPI < 0) and the CUDA-core kernel honour it.
+  int c_bdiv;
+  long long c_bs_hi;
 };
 
 // Tensor maps of the output: one per destination buffer. More than one destination is how a rank that owns a
@@ -91,6 +96,12 @@ __device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int& 
   n_blk = r / gm;
 }
 
+// offset (in elements) of batch b of the output
+__device__ __forceinline__ long long batch_offset(const GemmParams& p, int b) {
+  if (p.c_bdiv == 0) return static_cast<long long>(b) * p.c_bs;
+  const int hi = b / p.c_bdiv;
+  return hi * p.c_bs_hi + (b - hi * p.c_bdiv) * p.c_bs;
+}
 // offset (in elements) of output element (row, col) relative to the batch base
 __device__ __forceinline__ long long row_offset(const GemmParams& p, int row) {
   if (p.store_mode == 0) return static_cast<long long>(row) * p.ldc;
@@ -174,7 +185,7 @@ __device__ __forceinline__ void epilogue_chunk32(const GemmParams& p, float (&v)
     }
   }
   apply_unary_vec(u2, v);
-  T* out = static_cast<T*>(p.out) + static_cast<long long>(b) * p.c_bs + row_offset(p, row);
+  T* out = static_cast<T*>(p.out) + batch_offset(p, b) + row_offset(p, row);
   if (full) {
     if (p.store_mode == 0) {
 #pragma unroll
@@ -260,7 +271,7 @@ __device__ __forceinline__ void epilogue_direct_store32(const GemmParams& p, con
                                                         int col0, bool full, bool chunk_contig) {
   using E = Elem16<BF16>;
   using T = typename E::T;
-  T* out = static_cast<T*>(p.out) + static_cast<long long>(b) * p.c_bs + row_offset(p, row);
+  T* out = static_cast<T*>(p.out) + batch_offset(p, b) + row_offset(p, row);
   if (full) {
     if (chunk_contig) {
       T* dst = out + col_offset(p, col0);
@@ -662,7 +673,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             if (lane == 0 && row0 < p.M) {  // a box that starts past the last row has nothing to write
               const int gcol = colh + (c & ~1) * 32;
               if (p.store_mode == 0) {
-                tma_store_5d(&tma_out, box, gcol, row0, b, 0, 0);
+                int b_lo = b, b_hi = 0;
+                if (EPI < 0 && p.c_bdiv != 0) b_hi = b / p.c_bdiv, b_lo = b - b_hi * p.c_bdiv;
+                tma_store_5d(&tma_out, box, gcol, row0, b_lo, b_hi, 0);
                 if (MULTI)
                   for (int i = 1; i < p.num_out; ++i) tma_store_5d(&outs.m[i], box, gcol, row0, b, 0, 0);
               } else {
@@ -777,6 +790,13 @@ void launch_tc_pair256_bf16_lean(const CUtensorMap& ta, const CUtensorMap& tb, c
   template <>                                                                                                  \
   void launch_tc_width<BN_>(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout,  \
                             const GemmParams& p, int grid, cudaStream_t stream) {                              \
+    if (p.c_bdiv != 0 && p.num_out == 1 && !p.b_mn) { /* batched 0213 store: generic epilogue only */          \
+      if (bf16)                                                                                                \
+        launch_tc<BN_, true, -1>(ta, tb, tout, p, grid, stream);                                               \
+      else                                                                                                     \
+        launch_tc<BN_, false, -1>(ta, tb, tout, p, grid, stream);                                              \
+      return;                                                                                                  \
+    }                                                                                                          \
     if (p.num_out > 1) { /* several destinations: generic epilogue instantiation only */                       \
       if (bf16)                                                                                                \
         launch_tc<BN_, true, -1, false, true>(ta, tb, tout, p, grid, stream);                                  \

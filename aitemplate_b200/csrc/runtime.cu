@@ -41,6 +41,8 @@ int b200ait_gemm_rcr(const void*, const void*, const void*, const void*, const v
                      int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int, int, float,
                      int, int64_t, int64_t, int64_t, int, void*, int64_t, int, cudaStream_t);
 int b200ait_gemm_rcr_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int, int, int64_t*);
+int b200ait_bmm_permute0213(const void*, const void*, void*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
+                            int64_t, int, int, float, int, cudaStream_t);
 int b200ait_gemm_rrr(const void*, const void*, const void*, const void*, const void*, void*, int64_t, int64_t, int64_t,
                      int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int, int, float, int,
                      void*, int64_t, int, cudaStream_t);
@@ -441,7 +443,9 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     const int tile_hint = op.ints.size() > 8 ? static_cast<int>(op.ints[7]) : 0;
     const int split_hint = op.ints.size() > 8 ? static_cast<int>(op.ints[8]) : 0;
     uint8_t* c = static_cast<uint8_t*>(ptr_of(out0)) + out_off * dtype_size(T[out0].dtype);
-    check(b200ait_gemm_rcr(ptr_of(a), ptr_of(b), ptr_of(bias), ptr_of(d0), ptr_of(d1), c, 1, m, n, k, k, k,
+    // ints[9]: row stride of A when it is a column block of a wider buffer (a split read in place); 0 = K
+    const int64_t lda = op.ints.size() > 9 && op.ints[9] > 0 ? op.ints[9] : k;
+    check(b200ait_gemm_rcr(ptr_of(a), ptr_of(b), ptr_of(bias), ptr_of(d0), ptr_of(d1), c, 1, m, n, k, lda, k,
                            out_stride, n, 0, 0, 0, 0, static_cast<int>(op.ints[0]), T[a].dtype,
                            static_cast<float>(op.floats[0]), static_cast<int>(op.ints[1]), op.ints[2], op.ints[3],
                            op.ints[4], tile_hint, workspace_, workspace_bytes_, split_hint, stream),
@@ -462,7 +466,8 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     if (!launch) return;
     const int64_t out_off = op.ints[5], out_stride = op.ints[6];
     uint8_t* c = static_cast<uint8_t*>(ptr_of(out0)) + out_off * dtype_size(T[out0].dtype);
-    check(b200ait_gemm_rrr(ptr_of(a), ptr_of(b), ptr_of(bias), ptr_of(d0), ptr_of(d1), c, 1, m, n, k, k, n, out_stride,
+    const int64_t lda = op.ints.size() > 9 && op.ints[9] > 0 ? op.ints[9] : k;
+    check(b200ait_gemm_rrr(ptr_of(a), ptr_of(b), ptr_of(bias), ptr_of(d0), ptr_of(d1), c, 1, m, n, k, lda, n, out_stride,
                            n, 0, 0, 0, 0, static_cast<int>(op.ints[0]), T[a].dtype, static_cast<float>(op.floats[0]),
                            static_cast<int>(op.ints[7]), workspace_, workspace_bytes_, static_cast<int>(op.ints[8]),
                            stream),
@@ -480,9 +485,17 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     const int64_t batch = std::max(ba, bb);
     bind_shape(out0, {batch, m, n}, "bmm output");
     if (!launch) return;
+    // ints[0]: d1 of the "0213" permuted store of bmm_rrr_permute ([B / d1, M, d1, N]); 0 = plain
+    const int64_t a_bs = (ba == 1 && batch > 1) ? 0 : m * k, b_bs = (bb == 1 && batch > 1) ? 0 : n * k;
+    if (!op.ints.empty() && op.ints[0] > 0) {
+      check(b200ait_bmm_permute0213(ptr_of(a), ptr_of(b), ptr_of(out0), batch, m, n, k, a_bs, b_bs, op.ints[0], 1,
+                                    T[a].dtype, static_cast<float>(op.floats[0]), 0, stream),
+            op);
+      return;
+    }
     check(b200ait_gemm_rrr(ptr_of(a), ptr_of(b), nullptr, nullptr, nullptr, ptr_of(out0), batch, m, n, k, k, n, n, n,
-                           (ba == 1 && batch > 1) ? 0 : m * k, (bb == 1 && batch > 1) ? 0 : n * k, m * n, m * n, 0,
-                           T[a].dtype, static_cast<float>(op.floats[0]), 0, nullptr, 0, 1, stream),
+                           a_bs, b_bs, m * n, m * n, 0, T[a].dtype, static_cast<float>(op.floats[0]), 0, nullptr, 0,
+                           1, stream),
           op);
     return;
   }
@@ -497,9 +510,17 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     const int64_t batch = std::max(ba, bb);
     bind_shape(out0, {batch, m, n}, "bmm output");
     if (!launch) return;
+    // ints[0]: d1 of the "0213" permuted store of bmm_rcr_permute ([B / d1, M, d1, N]); 0 = plain
+    const int64_t a_bs = (ba == 1 && batch > 1) ? 0 : m * k, b_bs = (bb == 1 && batch > 1) ? 0 : n * k;
+    if (!op.ints.empty() && op.ints[0] > 0) {
+      check(b200ait_bmm_permute0213(ptr_of(a), ptr_of(b), ptr_of(out0), batch, m, n, k, a_bs, b_bs, op.ints[0], 0,
+                                    T[a].dtype, static_cast<float>(op.floats[0]), 0, stream),
+            op);
+      return;
+    }
     check(b200ait_gemm_rcr(ptr_of(a), ptr_of(b), nullptr, nullptr, nullptr, ptr_of(out0), batch, m, n, k, k, k, n, n,
-                           (ba == 1 && batch > 1) ? 0 : m * k, (bb == 1 && batch > 1) ? 0 : n * k, m * n, m * n, 0,
-                           T[a].dtype, static_cast<float>(op.floats[0]), 0, 1, 1, 1, 0, nullptr, 0, 1, stream),
+                           a_bs, b_bs, m * n, m * n, 0, T[a].dtype, static_cast<float>(op.floats[0]), 0, 1, 1, 1, 0,
+                           nullptr, 0, 1, stream),
           op);
     return;
   }
@@ -527,9 +548,11 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     // ints[1], ints[2]: element offset and row stride of the output when it is a column block of a wider
     // buffer (a layernorm fused into a concatenate); 0 stride = contiguous rows
     const int64_t out_off = op.ints.size() > 2 ? op.ints[1] : 0, out_stride = op.ints.size() > 2 ? op.ints[2] : 0;
+    // ints[3]: row stride of the input when it is a column block of a wider buffer (a split read in place)
+    const int64_t in_stride = op.ints.size() > 3 ? op.ints[3] : 0;
     uint8_t* y = static_cast<uint8_t*>(ptr_of(out0)) + out_off * dtype_size(T[out0].dtype);
-    check(b200ait_layernorm(y, ptr_of(x), ptr_of(in(1)), ptr_of(in(2)), m, n, static_cast<float>(op.floats[0]), 0,
-                            out_stride, T[x].dtype, stream),
+    check(b200ait_layernorm(y, ptr_of(x), ptr_of(in(1)), ptr_of(in(2)), m, n, static_cast<float>(op.floats[0]),
+                            in_stride, out_stride, T[x].dtype, stream),
           op);
     return;
   }

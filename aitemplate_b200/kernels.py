@@ -208,6 +208,30 @@ def bmm_rrr(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, tile_n: int = 
     return out
 
 
+def bmm_permute(a: torch.Tensor, b: torch.Tensor, d1: int, b_row_major: bool = False, alpha: float = 1.0,
+                tile_n: int = 0) -> torch.Tensor:
+    """bmm_rcr_permute (b [B, N, K]) / bmm_rrr_permute (b [B, K, N], b_row_major): the [B, M, N] product stored as
+    [B / d1, d1, M, N].permute(0, 2, 1, 3); returns the [B / d1, M, d1, N] tensor."""
+    _check_cuda(a, b)
+    a3 = a if a.dim() == 3 else a.unsqueeze(0)
+    b3 = b if b.dim() == 3 else b.unsqueeze(0)
+    ba, m, k = a3.shape
+    bb = b3.shape[0]
+    k2, n = (b3.shape[1], b3.shape[2]) if b_row_major else (b3.shape[2], b3.shape[1])
+    if k != k2 or not (ba == bb or ba == 1 or bb == 1):
+        raise ValueError(f"bmm_permute: incompatible shapes {tuple(a.shape)} and {tuple(b.shape)}")
+    batch = max(ba, bb)
+    if d1 <= 0 or batch % d1:
+        raise ValueError(f"bmm_permute: batch {batch} is not a multiple of d1 = {d1}")
+    out = torch.empty((batch // d1, m, d1, n), dtype=a.dtype, device=a.device)
+    code = _lib.load().b200ait_bmm_permute0213(
+        _ptr(a3), _ptr(b3), _ptr(out), batch, m, n, k,
+        0 if (ba == 1 and batch > 1) else m * k, 0 if (bb == 1 and batch > 1) else n * k, d1, int(b_row_major),
+        _dtype_code(a), c_float(alpha), tile_n, _stream())
+    _lib.check(code, "b200ait_bmm_permute0213")
+    return out
+
+
 def gemm_workspace_bytes(batch: int, m: int, n: int, k: int, tile_n: int = 0, split_k: int = 0) -> int:
     """Bytes of fp32 split-K scratch the library would use for this problem (0 = it would not split)."""
     out = c_int64(0)

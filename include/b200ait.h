@@ -66,6 +66,14 @@ int b200ait_gemm_rrr(const void* a, const void* b, const void* bias, const void*
                      int64_t ldd, int64_t a_batch_stride, int64_t b_batch_stride, int64_t c_batch_stride,
                      int64_t d_batch_stride, int epilogue, int dtype, float alpha, int tile_n, void* workspace,
                      int64_t workspace_bytes, int split_k, b200ait_stream_t stream);
+/* bmm_rcr_permute / bmm_rrr_permute (python/aitemplate/compiler/ops/gemm_universal/bmm_rcr_permute.py:28-116,
+ * bmm_rrr_permute.py; generated function python/aitemplate/backend/cuda/gemm_universal/bmm_common.py:56-81 with the
+ * Permute4DBMM_0213 epilogue): c[b] = alpha * a[b] @ b[b]^T for b [batch, n, k] (b_row_major = 0), or a[b] @ b[b]
+ * for b [batch, k, n] (b_row_major = 1), stored as [batch / d1, d1, m, n].permute(0, 2, 1, 3): c has the shape
+ * [batch / d1, m, d1, n]. A batch stride of 0 broadcasts that operand; batch must be a multiple of d1. */
+int b200ait_bmm_permute0213(const void* a, const void* b, void* c, int64_t batch, int64_t m, int64_t n, int64_t k,
+                            int64_t a_batch_stride, int64_t b_batch_stride, int64_t d1, int b_row_major, int dtype,
+                            float alpha, int tile_n, b200ait_stream_t stream);
 /* No counterpart in the reference (it is single-GPU: no communication backend anywhere under python/aitemplate
  * or static/). The same GEMM with its result written to num_out buffers of identical shape and strides
  * (1 <= num_out <= 8) by the epilogue's TMA stores. outs[0] is normally this GPU's buffer and the others

@@ -109,6 +109,14 @@ def bmm_rrr(a, b, alpha: float = 1.0) -> torch.Tensor:
     return torch.matmul(a, b) * alpha
 
 
+def bmm_permute(a, b, d1: int, b_row_major: bool = False, alpha: float = 1.0) -> torch.Tensor:
+    """tests/unittest/ops/test_bmm_permute.py: Y = bmm(A, B^T) (rcr) or bmm(A, B) (rrr), then
+    Y.reshape(B // D1, D1, M, N).permute(0, 2, 1, 3)."""
+    y = bmm_rrr(a, b, alpha) if b_row_major else bmm_rcr(a, b, alpha)
+    bsz, m, n = y.shape
+    return y.reshape(bsz // d1, d1, m, n).permute(0, 2, 1, 3).contiguous()
+
+
 def gemm_rcr_bias_permute(x, w, bias, shape: Sequence[int], layout: str = "20314") -> torch.Tensor:
     """tests/unittest/ops/test_gemm_bias_permute.py:74-75 and test_attention.py:146-149:
     linear -> reshape [M/t1, t1, t2, t3, N/t2/t3] -> permute (2, 0, 3, 1, 4)."""

@@ -46,6 +46,8 @@ CASES = [
     ("bmm_rrr", "bmm_rrr", {}, [[16, 384, 384], [16, 384, 64]], {}),
     ("bmm_rrr_dynamic_batch", "bmm_rrr", {}, [[[1, 64], 48, 40], [[1, 64], 40, 24]], {}),
     ("bmm_rrr_broadcast_b", "bmm_rrr", {}, [[5, 32, 256], [1, 256, 72]], {}),
+    ("bmm_rcr_permute", "bmm_rcr_permute", {"shape": [12]}, [[24, 80, 88], [24, 64, 88]], {}),
+    ("bmm_rrr_permute", "bmm_rrr_permute", {"shape": [10]}, [[100, 88, 64], [100, 64, 88]], {}),
     ("mem_eff_attention", "mem_eff_attention", {"causal": False}, [[64, 12, 384, 64]] * 3, {}),
     ("mem_eff_attention_cross", "mem_eff_attention", {"causal": False},
      [[2, 8, 4096, 40], [2, 8, 77, 40], [2, 8, 77, 40]], {}),
@@ -115,9 +117,9 @@ def run_case(ops, Tensor, IntVar, FuncEnum, case):
         out = op(*tensors)
     outs = list(out) if isinstance(out, (tuple, list)) else [out]
     src = list(outs[0]._attrs["src_ops"])[0]
-    # gemm_rcr_bias_permute / gemm_rcr_permute return a reshape of the GEMM output: record the GEMM's attrs
+    # the *_permute GEMMs return a reshape of the GEMM output: record the GEMM's attrs
     node = src
-    if src._attrs["op"] == "reshape" and op_name.endswith("permute") and op_name.startswith("gemm"):
+    if src._attrs["op"] == "reshape" and op_name.endswith("permute") and op_name.startswith(("gemm", "bmm")):
         node = list(src._attrs["inputs"][0]._attrs["src_ops"])[0]
     attrs = {}
     for k in ATTR_KEYS:

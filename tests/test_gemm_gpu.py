@@ -300,6 +300,31 @@ def test_bmm_rcr_broadcast_and_zero_batch():
     assert tuple(z.shape) == (0, 8, 8)
 
 
+# shapes of tests/unittest/ops/test_bmm_permute.py:67-71 and :110-114 (B 24 / 100 / 10240, M 80 / 88, d1 12 / 10),
+# plus tile-aligned ones that take the staged TMA store with the two-level batch coordinate
+@pytest.mark.parametrize("bsz,m,n,kk,d1", [(24, 80, 64, 88, 12), (100, 88, 64, 88, 10), (10240, 88, 64, 88, 10),
+                                           (48, 256, 256, 64, 12), (16, 384, 128, 128, 4), (6, 130, 200, 72, 1)])
+@pytest.mark.parametrize("row_major_b", [False, True])
+def test_bmm_permute(bsz, m, n, kk, d1, row_major_b):
+    k = _kernels()
+    a = _rand((bsz, m, kk), 90, "uniform")
+    b = _rand((bsz, kk, n) if row_major_b else (bsz, n, kk), 91, "uniform")
+    y = k.bmm_permute(a.cuda(), b.cuda(), d1, b_row_major=row_major_b)
+    assert k.device_status() == 0
+    assert tuple(y.shape) == (bsz // d1, m, d1, n)
+    _close(y, oracle.bmm_permute(a, b, d1, b_row_major=row_major_b))
+
+
+def test_bmm_permute_alpha_bf16_and_errors():
+    k = _kernels()
+    a = _rand((8, 128, 64), 92, "uniform", dtype=torch.bfloat16)
+    b = _rand((8, 256, 64), 93, "uniform", dtype=torch.bfloat16)
+    y = k.bmm_permute(a.cuda(), b.cuda(), 4, alpha=0.25)
+    _close(y, oracle.bmm_permute(a, b, 4, alpha=0.25), atol=4e-2, rtol=4e-2)
+    with pytest.raises(ValueError):
+        k.bmm_permute(a.cuda(), b.cuda(), 3)           # 8 is not a multiple of 3
+
+
 def test_reference_signature_entry_points():
     """The per-op entry points that take the reference's generated argument list."""
     import ctypes

@@ -8,6 +8,7 @@ from aitemplate_b200.compiler.base import IntImm, IntVar, Tensor
 from aitemplate_b200.compiler.ops import FuncEnum
 from aitemplate_b200.compiler.transform import (
     fuse_mm_elementwise,
+    fuse_split_strided,
     fuse_strided_cat,
     mark_param_tensor,
     memory_planning,
@@ -31,6 +32,7 @@ def _lower(outs, fuse=True):
         g = fuse_mm_elementwise(g, outs)
         mark_param_tensor(g)
         split_to_views(g)
+        fuse_split_strided(g)
         fuse_strided_cat(g)
     name_graph(g)
     copies = C._assign_storage(g, outs)
@@ -213,7 +215,7 @@ def test_strided_cat_fusion_plan():
     gemms = [_parse_op(l) for l in lines if l.startswith("op gemm_rcr")]
     assert [g_["ints"][5:7] for g_ in gemms] == [[0, 288], [96 + 24, 288]]   # (offset, row stride) in elements
     lnl = _parse_op(next(l for l in lines if l.startswith("op layernorm")))
-    assert lnl["ints"] == [128, 96 + 24 + 40, 288]
+    assert lnl["ints"] == [128, 96 + 24 + 40, 288, 0]                       # n, out offset, out stride, in stride
     # the producers' tensors alias the concat output, which is emitted before them
     tl = [l.split() for l in lines if l.startswith("tensor ")]
     idx_y = next(i for i, t in enumerate(tl) if t[1] == "y")
@@ -330,3 +332,66 @@ def test_target_rejects_fp16_accumulation():
     assert t.name() == "cuda" and t._kwargs["no_tf32"] is True
     with pytest.raises(NotImplementedError):
         detect_target(use_fp16_acc=True)
+
+
+def test_split_strided_input_fusion_plan():
+    # the split side of the reference's strided-op pass (tests/unittest/compiler/test_split_bmm_fusion.py,
+    # test_strided_layernorm.py): GEMMs (operand A) and layernorms read their column block of the split's input
+    # in place; a block with another kind of reader, or an unaligned one, keeps its copy
+    m = IntVar([1, 64], name="m")
+    x = Tensor([m, 128 + 64 + 32 + 24], name="x", is_input=True)
+    w1, w2 = Tensor([48, 128], name="w1"), Tensor([16, 64], name="w2")
+    p0, p1, p2, p3 = ops.split()(x, [128, 64, 32, 24], dim=-1)
+    g1 = _out(ops.gemm_rcr()(p0, w1), "g1")
+    ln0 = _out(ops.layernorm()(p0, None, None, [IntImm(128)], 1e-5), "ln0")   # two readers of one block
+    g2 = _out(ops.gemm_rcr()(p1, w2), "g2")
+    e2 = _out(ops.elementwise(FuncEnum.RELU)(p2), "e2")                       # not a strided reader
+    ln3 = _out(ops.layernorm()(p3, None, None, [IntImm(24)], 1e-5), "ln3")
+    g, plan, blob, consts = _lower([g1, ln0, g2, e2, ln3])
+    lines = plan.splitlines()
+    sp = _parse_op(next(l for l in lines if l.startswith("op split")))
+    assert sp["ints"] == [1, 4, 128, 64, 32, 24, 0, 0, 1, 0]                   # masks: only the relu's block is copied
+    gemms = {l.split()[2]: _parse_op(l) for l in lines if l.startswith("op gemm_rcr")}
+    assert sorted(g_["ints"][9] for g_ in gemms.values()) == [248, 248]
+    lns = [_parse_op(l) for l in lines if l.startswith("op layernorm")]
+    assert sorted(l_["ints"][3] for l_ in lns) == [248, 248]
+    tl = [l.split() for l in lines if l.startswith("tensor ")]
+    idx_x = next(i for i, t in enumerate(tl) if t[1] == "x")
+    views = sorted(int(t[5]) for t in tl if t[3] == "4" and int(t[6]) == idx_x)
+    assert views == [0, 256, 2 * (128 + 64 + 32)]                              # byte offsets of the aliased blocks
+
+
+def test_split_strided_input_fusion_is_skipped_when_illegal():
+    x = Tensor([8, 100], name="x", is_input=True)
+    w = Tensor([16, 50], name="w")
+    a, b = ops.split()(x, 50, dim=1)                      # blocks of 100 bytes: not 16-byte aligned
+    y0 = _out(ops.gemm_rcr()(a, w), "y0")
+    y1 = _out(ops.gemm_rcr()(b, w), "y1")
+    _, plan, _, _ = _lower([y0, y1])
+    assert _parse_op(next(l for l in plan.splitlines() if l.startswith("op split")))["ints"][-2:] == [1, 1]
+    x2 = Tensor([8, 64], name="x2", is_input=True)
+    c, d = ops.split()(x2, 32, dim=1)
+    y3 = _out(ops.gemm_rrr()(Tensor([4, 8], name="x4", is_input=True), c), "y3")   # operand B: not fused
+    y4 = _out(d, "d")                                                              # a graph output keeps its copy
+    _, plan, _, _ = _lower([y3, y4])
+    assert _parse_op(next(l for l in plan.splitlines() if l.startswith("op split")))["ints"][-2:] == [1, 1]
+
+
+def test_bmm_permute_nodes():
+    # bmm_rcr_permute / bmm_rrr_permute keep the reference's attributes (layout "Permute4DBMM_0213", shape (d1,)),
+    # return the [B / d1, M, d1, N] view and carry d1 to the runtime in the plan
+    a, b = Tensor([24, 80, 88], name="a", is_input=True), Tensor([24, 64, 88], name="b", is_input=True)
+    c = Tensor([24, 88, 64], name="c", is_input=True)
+    op = ops.bmm_rcr_permute(shape=(12,))
+    assert op._attrs["layout"] == "Permute4DBMM_0213" and op._get_op_attributes() == {"layout": "0213", "shape": (12,)}
+    y0 = _out(op(a, b), "y0")
+    y1 = _out(ops.bmm_rrr_permute(shape=(12,))(a, c), "y1")
+    assert [d.value() for d in y0._attrs["shape"]] == [2, 80, 12, 64]
+    _, plan, _, _ = _lower([y0, y1])
+    lines = plan.splitlines()
+    assert _parse_op(next(l for l in lines if l.startswith("op bmm_rcr")))["ints"] == [12]
+    assert _parse_op(next(l for l in lines if l.startswith("op bmm_rrr")))["ints"] == [12]
+    with pytest.raises(RuntimeError):
+        ops.bmm_rcr_permute(shape=(5,))(a, b)            # 24 is not a multiple of 5
+    with pytest.raises(NotImplementedError):
+        ops.bmm_rcr_permute(shape=(12,), layout="0123")

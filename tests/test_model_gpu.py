@@ -310,6 +310,69 @@ def test_strided_output_fusion_into_concat(workdir, m):
     assert torch.equal(res[:, 96:116].cpu(), zd)  # the copied block is bit-exact
 
 
+@pytest.mark.parametrize("m", [48, 1000])
+def test_strided_input_fusion_from_split(workdir, m):
+    # GEMMs (operand A) and layernorms read their column blocks of a last-dim split's input in place
+    # (tests/unittest/compiler/test_split_bmm_fusion.py, test_strided_layernorm.py in the reference); the block with
+    # an elementwise reader is still copied by the split kernel
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    from aitemplate_b200.compiler.ops import FuncEnum
+    from aitemplate_b200.frontend import IntImm
+
+    widths = [256, 64, 32, 72]
+    x = Tensor([m, sum(widths)], name="x", is_input=True)
+    w1, b1 = Tensor([136, 256], name="w1"), Tensor([136], name="b1")
+    w2 = Tensor([264, 64], name="w2")
+    p0, p1, p2, p3 = ops.split()(x, widths, dim=-1)
+    outs = {
+        "g1": ops.gemm_rcr_bias_relu()(p0, w1, b1),
+        "ln0": ops.layernorm()(p0, None, None, [IntImm(256)], 1e-5),
+        "g2": ops.gemm_rcr()(p1, w2),
+        "e2": ops.elementwise(FuncEnum.RELU)(p2),
+        "ln3": ops.layernorm()(p3, None, None, [IntImm(72)], 1e-5),
+    }
+    for name, t in outs.items():
+        t._attrs["name"], t._attrs["is_output"] = name, True
+    module = compile_model(list(outs.values()), detect_target(), workdir, "strided_split")
+    plan = open(os.path.join(workdir, "strided_split", "test.so.plan")).read()
+    split_line = next(l for l in plan.splitlines() if l.startswith("op split")).split()
+    assert split_line[-5:-1] == ["0", "0", "1", "0"]
+    xd = _rand((m, sum(widths)), 1)
+    w1d, b1d, w2d = _rand((136, 256), 3, 0.05), _rand((136,), 4, 0.1), _rand((264, 64), 5, 0.05)
+    module.set_many_constants_with_tensors({"w1": w1d.cuda(), "b1": b1d.cuda(), "w2": w2d.cuda()})
+    bufs = {"g1": (m, 136), "ln0": (m, 256), "g2": (m, 264), "e2": (m, 32), "ln3": (m, 72)}
+    res = module.run_with_tensors(
+        {"x": xd.cuda()}, {k: torch.full(v, 9.0, dtype=torch.float16, device="cuda") for k, v in bufs.items()})
+    c0, c1, c2, c3 = torch.split(xd, widths, dim=1)
+    _close(res["g1"], oracle.gemm_rcr(c0, w1d, b1d, epilogue="relu"), 1e-2)
+    _close(res["ln0"], oracle.layernorm(c0, None, None), 1e-2)
+    _close(res["g2"], oracle.gemm_rcr(c1, w2d), 1e-2)
+    assert torch.equal(res["e2"].cpu(), torch.relu(c2))
+    _close(res["ln3"], oracle.layernorm(c3, None, None), 1e-2)
+
+
+def test_bmm_permute_ops_in_a_graph(workdir):
+    # bmm_rcr_permute / bmm_rrr_permute (tests/unittest/ops/test_bmm_permute.py): the 0213 permutation is fused into
+    # the batched GEMM's store and the node returns the [B / d1, M, d1, N] view
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    bsz, m, n, kk, d1 = 24, 80, 64, 88, 12
+    a = Tensor([bsz, m, kk], name="a", is_input=True)
+    b = Tensor([bsz, n, kk], name="b", is_input=True)
+    c = Tensor([bsz, kk, n], name="c", is_input=True)
+    y0 = ops.bmm_rcr_permute(shape=(d1,))(a, b)
+    op1 = ops.bmm_rrr_permute(shape=(d1,))
+    y1 = ops.bmm_rrr_permute(**op1._get_op_attributes())(a, c)
+    for name, t in (("y0", y0), ("y1", y1)):
+        t._attrs["name"], t._attrs["is_output"] = name, True
+    assert [d.value() for d in y0._attrs["shape"]] == [bsz // d1, m, d1, n]
+    module = compile_model([y0, y1], detect_target(), workdir, "bmm_permute")
+    ad, bd, cd = _rand((bsz, m, kk), 1), _rand((bsz, n, kk), 2), _rand((bsz, kk, n), 3)
+    outs = {k: torch.empty((bsz // d1, m, d1, n), dtype=torch.float16, device="cuda") for k in ("y0", "y1")}
+    res = module.run_with_tensors({"a": ad.cuda(), "b": bd.cuda(), "c": cd.cuda()}, outs)
+    _close(res["y0"], oracle.bmm_permute(ad, bd, d1), 1e-2)
+    _close(res["y1"], oracle.bmm_permute(ad, cd, d1, b_row_major=True), 1e-2)
+
+
 def test_compile_time_gemm_profiling(workdir):
     # profile_devs given: every GEMM of the graph is timed over the launch configurations, the winners go into the
     # plan and a cache file, and the model still matches the oracle

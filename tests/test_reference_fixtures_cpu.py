@@ -48,7 +48,7 @@ def _run(case):
         out = op(*tensors)
     outs = list(out) if isinstance(out, (tuple, list)) else [out]
     node = list(outs[0]._attrs["src_ops"])[0]
-    if node._attrs["op"] == "reshape" and name.startswith("gemm") and name.endswith("permute"):
+    if node._attrs["op"] == "reshape" and name.startswith(("gemm", "bmm")) and name.endswith("permute"):
         node = list(node._attrs["inputs"][0]._attrs["src_ops"])[0]
     return outs, node
 
