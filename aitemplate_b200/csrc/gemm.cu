@@ -59,6 +59,28 @@ __global__ void __launch_bounds__(256) gemm_splitk_reduce_kernel(const GemmParam
   epilogue_chunk32<BF16>(p, v, b, row, col0, true);
 }
 
+// The fused epilogue on one fp32 accumulator: alpha, bias, activation, residual(s), activation, one rounding.
+template <bool BF16>
+__device__ __forceinline__ void epilogue_scalar_store(const GemmParams& p, float acc, int b, int row, int col) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  const int u1 = epi_u1(p.epilogue), b1 = epi_b1(p.epilogue), b2 = epi_b2(p.epilogue), u2 = epi_u2(p.epilogue);
+  float v = acc * p.alpha;
+  if (p.bias) v += E::to_float(static_cast<const T*>(p.bias)[col]);
+  v = apply_unary(u1, v);
+  const long long di = static_cast<long long>(b) * p.d_bs + static_cast<long long>(row) * p.ldd + col;
+  if (b1 != kBinaryNone) {
+    const float f = E::to_float(static_cast<const T*>(p.d0)[di]);
+    v = (b1 == kBinaryAdd) ? v + f : v * f;
+  }
+  if (b2 != kBinaryNone) {
+    const float f = E::to_float(static_cast<const T*>(p.d1)[di]);
+    v = (b2 == kBinaryAdd) ? v + f : v * f;
+  }
+  v = apply_unary(u2, v);
+  static_cast<T*>(p.out)[batch_offset(p, b) + row_offset(p, row) + col_offset(p, col)] = E::from_float(v);
+}
+
 // ------------------------------------------------------------------------------------------------
 // CUDA-core kernel for shapes TMA cannot address. 32x32 output tile per block, K staged in smem.
 template <bool BF16>
@@ -93,26 +115,70 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const void* a_, const vo
   }
   const int col = col0 + tx;
   if (col >= p.N) return;
-  const int u1 = epi_u1(p.epilogue), b1 = epi_b1(p.epilogue), b2 = epi_b2(p.epilogue), u2 = epi_u2(p.epilogue);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int row = row0 + ty + i * 8;
-    if (row >= p.M) continue;
-    float v = acc[i] * p.alpha;
-    if (p.bias) v += E::to_float(static_cast<const T*>(p.bias)[col]);
-    v = apply_unary(u1, v);
-    const long long di = static_cast<long long>(b) * p.d_bs + static_cast<long long>(row) * p.ldd + col;
-    if (b1 != kBinaryNone) {
-      const float f = E::to_float(static_cast<const T*>(p.d0)[di]);
-      v = (b1 == kBinaryAdd) ? v + f : v * f;
+    if (row < p.M) epilogue_scalar_store<BF16>(p, acc[i], b, row, col);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Weight-streaming kernel for M <= 4 (a GEMV per row of X): the run time is the time to read W once, and a
+// handful of rows leaves nothing for the tensor core to amortise. One block of 32 warps per SM holds X in
+// shared memory and owns a contiguous share of the rows of W; each warp streams one row at a time with
+// 16-byte loads that do not allocate in L1 (8 in flight per lane), multiplies on the FMA pipe in fp32 and
+// reduces across the lanes. No workspace, no second pass.
+constexpr int kRowDotMaxM = 4;
+constexpr int kRowDotThreads = 1024;
+template <bool BF16, int MR>
+__global__ void __launch_bounds__(kRowDotThreads, 1) gemm_rowdot_kernel(const void* a_, const void* b_,
+                                                                         const GemmParams p) {
+  using T = typename Elem16<BF16>::T;
+  extern __shared__ __align__(16) uint8_t rowdot_smem[];
+  uint4* xs = reinterpret_cast<uint4*>(rowdot_smem);  // [MR][K / 8]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int nvec = p.K >> 3;
+  for (int i = threadIdx.x; i < MR * nvec; i += blockDim.x) {
+    const int m = i / nvec, v = i - m * nvec;
+    xs[i] = (m < p.M) ? __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(a_) + static_cast<long long>(m) * p.lda) + v)
+                      : make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  // rows [n_begin, n_end) of W belong to this block
+  const int per = (p.N + gridDim.x - 1) / gridDim.x;
+  const int n_begin = blockIdx.x * per, n_end = min(p.N, n_begin + per);
+  constexpr int kUnroll = 8;
+  for (int n = n_begin + warp; n < n_end; n += nwarps) {
+    const uint4* w = reinterpret_cast<const uint4*>(static_cast<const T*>(b_) + static_cast<long long>(n) * p.ldb);
+    float acc[MR];
+#pragma unroll
+    for (int m = 0; m < MR; ++m) acc[m] = 0.f;
+    for (int v0 = lane; v0 < nvec; v0 += 32 * kUnroll) {
+      uint4 wq[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        wq[u] = (v0 + 32 * u < nvec) ? __ldcs(w + v0 + 32 * u) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int v = min(v0 + 32 * u, nvec - 1);  // past the end the weights above are zero
+        float wf[8];
+        unpack8<BF16>(wq[u], wf);
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+          float xf[8];
+          unpack8<BF16>(xs[m * nvec + v], xf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[m] = fmaf(xf[j], wf[j], acc[m]);
+        }
+      }
     }
-    if (b2 != kBinaryNone) {
-      const float f = E::to_float(static_cast<const T*>(p.d1)[di]);
-      v = (b2 == kBinaryAdd) ? v + f : v * f;
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+      float t = acc[m];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      if (lane == m && m < p.M) epilogue_scalar_store<BF16>(p, t, 0, m, n);
     }
-    v = apply_unary(u2, v);
-    static_cast<T*>(p.out)[batch_offset(p, b) + row_offset(p, row) + col_offset(p, col)] =
-        E::from_float(v);
   }
 }
 
@@ -353,6 +419,27 @@ void gemm_run(const GemmArgs& g_in) {
   const bool tma_ok = (g.k % 8 == 0) && (g.lda % 8 == 0) && (g.ldb % 8 == 0) && aligned16(g.a) && aligned16(g.b) &&
                       (g.a_bs % 8 == 0) && (g.b_bs % 8 == 0) && g.batch < 65536 * 32;
   B200AIT_REQUIRE(tma_ok || g.num_out == 1, "gemm: several output buffers need TMA-addressable operands");
+  // M <= 4, deep K, the caller left tile width and split-K to the library: stream W once on the CUDA cores
+  const long long rowdot_smem = (g.m <= 1 ? 1 : g.m <= 2 ? 2 : 4) * g.k * 2;
+  if (tma_ok && g.batch == 1 && g.m <= kRowDotMaxM && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0 &&
+      g.k >= 1024 && g.n >= 64 && rowdot_smem <= 160 * 1024) {
+    const unsigned grid = static_cast<unsigned>(std::min<long long>(sm_count(), (g.n + 3) / 4));
+    const int smem = static_cast<int>(rowdot_smem);
+#define B200AIT_ROWDOT(BF, MR)                                                                                 \
+  do {                                                                                                         \
+    static std::atomic<uint64_t> configured{0};                                                                \
+    opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_rowdot_kernel<BF, MR>), 160 * 1024);      \
+    gemm_rowdot_kernel<BF, MR><<<grid, kRowDotThreads, smem, g.stream>>>(g.a, g.b, p);                         \
+  } while (0)
+    if (bf16) {
+      if (g.m <= 1) B200AIT_ROWDOT(true, 1); else if (g.m <= 2) B200AIT_ROWDOT(true, 2); else B200AIT_ROWDOT(true, 4);
+    } else {
+      if (g.m <= 1) B200AIT_ROWDOT(false, 1); else if (g.m <= 2) B200AIT_ROWDOT(false, 2); else B200AIT_ROWDOT(false, 4);
+    }
+#undef B200AIT_ROWDOT
+    B200AIT_CUDA_CHECK(cudaGetLastError());
+    return;
+  }
   if (!tma_ok) {
     dim3 grid(static_cast<unsigned>((g.n + 31) / 32), static_cast<unsigned>((g.m + 31) / 32),
               static_cast<unsigned>(g.batch));

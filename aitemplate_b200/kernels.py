@@ -106,7 +106,11 @@ def gemm_rcr(
 ) -> torch.Tensor:
     """y = epilogue(x @ w.T + bias, d0, d1); x [..., K] (leading dims fold into M), w [N, K].
     split_k: 0 lets the library decide, 1 disables split-K, n allows at most n splits."""
-    _check_cuda(x, w, bias, d0, d1, out)
+    _check_cuda(x, w, bias, d0, d1)
+    if out is not None and not out.is_cuda:
+        raise ValueError("tensors must be CUDA tensors")
+    if out is not None and not out.is_contiguous() and not (permute_shape is None and out.dim() == 2):
+        raise ValueError("tensors must be contiguous")
     k = x.shape[-1]
     m = x.numel() // k if k else math.prod(x.shape[:-1])
     n = w.shape[0]
@@ -126,8 +130,13 @@ def gemm_rcr(
             raise ValueError(f"unknown permute layout {permute_layout}")
     else:
         out_shape = list(x.shape[:-1]) + [n]
+    ldc = n
     if out is None:
         out = torch.empty(out_shape, dtype=x.dtype, device=x.device)
+    elif store_mode == 0 and out.dim() == 2:
+        if out.stride(1) != 1:
+            raise ValueError("gemm_rcr: the rows of `out` must be contiguous")
+        ldc = out.stride(0)          # a column block of a wider buffer is written in place
     ws = None
     if split_k != 1 and m and n and k:
         ws_bytes = gemm_workspace_bytes(1, m, n, k, tile_n, split_k)
@@ -135,7 +144,7 @@ def gemm_rcr(
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     code = _lib.load().b200ait_gemm_rcr(
         _ptr(x), _ptr(w), _ptr(bias), _ptr(d0), _ptr(d1), _ptr(out),
-        1, m, n, k, k, k, n, n, 0, 0, 0, 0,
+        1, m, n, k, k, k, ldc, n, 0, 0, 0, 0,
         epilogue_code(epilogue), _dtype_code(x), c_float(alpha), store_mode, t1, t2, t3, tile_n,
         _ptr(ws), ws.numel() if ws is not None else 0, split_k, _stream(),
     )

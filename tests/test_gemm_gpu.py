@@ -325,6 +325,40 @@ def test_bmm_permute_alpha_bf16_and_errors():
         k.bmm_permute(a.cuda(), b.cuda(), 3)           # 8 is not a multiple of 3
 
 
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 13, 16])
+@pytest.mark.parametrize("n,kk,epilogue", [(8192, 8192, "relu"), (1000, 1024, "fast_gelu"), (64, 1024, ""),
+                                           (4104, 2056, "add"), (72, 4096, "mul_add"), (520, 7176, "mul_add")])
+def test_weight_streaming_rows(m, n, kk, epilogue):
+    # M <= 4 with deep K runs on the weight-streaming CUDA-core kernel (benchmark configuration 5, M = 1), larger M
+    # on the split-K tensor-core path; ragged N, K not a multiple of the unrolled step, residual epilogues
+    k = _kernels()
+    x = _rand((m, kk), 500, dist="uniform")
+    w = _rand((n, kk), 501, scale=0.02)
+    b = _rand((n,), 502, scale=0.1)
+    nres = {"add": 1, "mul_add": 2}.get(epilogue, 0)
+    d = [_rand((m, n), 503 + i) for i in range(nres)]
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), *[t.cuda() for t in d], epilogue=epilogue)
+    assert k.device_status() == 0
+    want = oracle.gemm_rcr(x, w, b, *d, epilogue=epilogue)
+    _close(y, want)
+    y256 = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), *[t.cuda() for t in d], epilogue=epilogue, tile_n=256)
+    _close(y256, want)                                # the tensor-core path on the same problem
+
+
+def test_weight_streaming_rows_bf16_strided_and_permuted():
+    k = _kernels()
+    x = _rand((2, 2048), 510, dist="uniform", dtype=torch.bfloat16)
+    w = _rand((512, 2048), 511, scale=0.02, dtype=torch.bfloat16)
+    _close(k.gemm_rcr(x.cuda(), w.cuda(), None, alpha=0.5), oracle.gemm_rcr(x, w, None, alpha=0.5), atol=4e-2, rtol=4e-2)
+    xh, wh, bh = x.half(), w.half(), _rand((512,), 512)
+    buf = torch.full((2, 1024), 3.0, dtype=torch.float16, device="cuda")     # write into a column block of a wider row
+    k.gemm_rcr(xh.cuda(), wh.cuda(), bh.cuda(), out=buf[:, 256:768])
+    _close(buf[:, 256:768], oracle.gemm_rcr(xh, wh, bh))
+    assert bool((buf[:, :256] == 3.0).all()) and bool((buf[:, 768:] == 3.0).all())
+    y = k.gemm_rcr(xh.cuda(), wh.cuda(), bh.cuda(), permute_shape=(1, 2, 4))  # Permute5D store of the same rows
+    _close(y, oracle.gemm_rcr_bias_permute(xh, wh, bh, (1, 2, 4)))
+
+
 def test_reference_signature_entry_points():
     """The per-op entry points that take the reference's generated argument list."""
     import ctypes
