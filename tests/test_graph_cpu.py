@@ -8,6 +8,7 @@ from aitemplate_b200.compiler.base import IntImm, IntVar, Tensor
 from aitemplate_b200.compiler.ops import FuncEnum
 from aitemplate_b200.compiler.transform import (
     fuse_mm_elementwise,
+    fuse_gemm_permute0213,
     fuse_split_strided,
     fuse_strided_cat,
     mark_param_tensor,
@@ -30,6 +31,7 @@ def _lower(outs, fuse=True):
     mark_param_tensor(g)
     if fuse:
         g = fuse_mm_elementwise(g, outs)
+        g = fuse_gemm_permute0213(g, outs)
         mark_param_tensor(g)
         split_to_views(g)
         fuse_split_strided(g)
@@ -191,6 +193,7 @@ def test_sd_transformer_block_plan():
     y = workloads.build_sd_block(2)
     g, plan, blob, consts = _lower([y])
     kernels = [line.split()[1] for line in plan.splitlines() if line.startswith("op ") and line.split()[1] != "view"]
+    # (head size 40: the heads-first permutes stay copy kernels, see fuse_gemm_permute0213)
     attn = ["gemm_rcr", "permute"] * 3 + ["mem_eff_attention", "gemm_rcr"]
     assert kernels == ["layernorm"] + attn + ["layernorm"] + attn + ["layernorm", "gemm_rcr", "gemm_rcr", "gemm_rcr"]
     assert consts >= 2 * (4 * 320 * 320 + 2 * 320 * 768 + 2 * 320 * 320 + 3 * 1280 * 320)
@@ -395,3 +398,25 @@ def test_bmm_permute_nodes():
         ops.bmm_rcr_permute(shape=(5,))(a, b)            # 24 is not a multiple of 5
     with pytest.raises(NotImplementedError):
         ops.bmm_rcr_permute(shape=(12,), layout="0123")
+
+
+def test_gemm_permute0213_fusion_and_its_limits():
+    # gemm -> reshape [B, S, H, d] -> permute (0, 2, 1, 3): the GEMM takes the reference's gemm_rcr_permute layout
+    # (shape (S, H), "0213") and the permute's output becomes a view; with another reader of the GEMM result, a head
+    # size the staged store cannot box (not a multiple of 64), or a graph output in between, the copy kernel stays
+    x = Tensor([2 * 64, 64], name="x", is_input=True)
+    w, b = Tensor([4 * 64, 64], name="w"), Tensor([4 * 64], name="b")
+    q = ops.gemm_rcr_bias()(x, w, b)
+    y = _out(ops.permute()(ops.reshape()(q, [2, 64, 4, 64]), [0, 2, 1, 3]), "y")
+    g, plan, _, _ = _lower([y])
+    lines = plan.splitlines()
+    assert not any(l.startswith("op permute") for l in lines)
+    assert _parse_op(next(l for l in lines if l.startswith("op gemm_rcr")))["ints"][1:4] == [2, 64, 4]
+    assert [d.value() for d in next(t for t in g if t._attrs["name"] == "y")._attrs["shape"]] == [2, 4, 64, 64]
+    q2 = ops.gemm_rcr()(x, w)
+    y2 = _out(ops.permute()(ops.reshape()(q2, [2, 64, 4, 64]), [0, 2, 1, 3]), "y2")
+    z2 = _out(ops.elementwise(FuncEnum.RELU)(q2), "z2")                       # a second reader of the GEMM result
+    w3 = Tensor([4 * 40, 64], name="w3")
+    y3 = _out(ops.permute()(ops.reshape()(ops.gemm_rcr()(x, w3), [2, 64, 4, 40]), [0, 2, 1, 3]), "y3")   # d = 40
+    _, plan, _, _ = _lower([y2, z2, y3])
+    assert sum(l.startswith("op permute") for l in plan.splitlines()) == 2

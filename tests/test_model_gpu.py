@@ -373,6 +373,25 @@ def test_bmm_permute_ops_in_a_graph(workdir):
     _close(res["y1"], oracle.bmm_permute(ad, cd, d1, b_row_major=True), 1e-2)
 
 
+def test_gemm_permute0213_fusion_matches_oracle(workdir):
+    # q-projection -> [B, S, H, d] -> heads first: the permute is folded into the GEMM's staged store
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    bsz, seq, heads, d, kdim = 3, 160, 4, 64, 192
+    x = Tensor([bsz * seq, kdim], name="x", is_input=True)
+    w, b = Tensor([heads * d, kdim], name="w"), Tensor([heads * d], name="b")
+    y = ops.permute()(ops.reshape()(ops.gemm_rcr_bias()(x, w, b), [bsz, seq, heads, d]), [0, 2, 1, 3])
+    y._attrs["name"], y._attrs["is_output"] = "y", True
+    module = compile_model(y, detect_target(), workdir, "gemm_permute0213")
+    plan = open(os.path.join(workdir, "gemm_permute0213", "test.so.plan")).read()
+    assert "op permute" not in plan
+    xd, wd, bd = _rand((bsz * seq, kdim), 1), _rand((heads * d, kdim), 2, 0.05), _rand((heads * d,), 3, 0.1)
+    module.set_many_constants_with_tensors({"w": wd.cuda(), "b": bd.cuda()})
+    out = torch.empty((bsz, heads, seq, d), dtype=torch.float16, device="cuda")
+    res = module.run_with_tensors({"x": xd.cuda()}, {"y": out})["y"]
+    want = oracle.gemm_rcr(xd, wd, bd).reshape(bsz, seq, heads, d).permute(0, 2, 1, 3)
+    _close(res, want, 1e-2)
+
+
 def test_compile_time_gemm_profiling(workdir):
     # profile_devs given: every GEMM of the graph is timed over the launch configurations, the winners go into the
     # plan and a cache file, and the model still matches the oracle
