@@ -31,6 +31,18 @@ class bmm(gemm):
         raise RuntimeError(f"bmm operand A and B should have same batch_size, or batch_size = 1! "
                            f"Current shape A: {a_shape} shape B: {b_shape} .")
 
+    def _plan_ints(self) -> List[int]:
+        """[d1, lda, ldb, out_offset, ldc]: d1 of a "0213" permuted store (bmm_*_permute; 0 = plain [B, M, N]);
+        row strides of A and B when they are column blocks of a wider buffer (a split read in place; 0 =
+        contiguous); element offset and row stride of the output when it is a column block of a concatenate's
+        buffer (0 stride = contiguous). The batch strides follow as rows x row stride."""
+        acc_a, acc_b = self._attrs["input_accessors"][:2]
+        out = self._attrs["output_accessors"][0]
+        return [int(self._attrs.get("permute_d1", 0)),
+                acc_a.row_stride() if acc_a.stride_dim is not None else 0,
+                acc_b.row_stride() if acc_b.stride_dim is not None else 0,
+                out.offset, out.row_stride() if out.stride_dim is not None else 0]
+
     def _sanity_check(self, a: Tensor, b: Tensor) -> None:
         for name, t in (("A", a), ("B", b)):
             if len(t._attrs["shape"]) not in (2, 3):
@@ -58,8 +70,7 @@ class bmm_rcr(bmm):
 
     def _lower(self) -> Dict[str, Any]:
         a, b = self._attrs["inputs"]
-        # ints[0]: d1 of a "0213" permuted store (bmm_rcr_permute), 0 = plain [B, M, N]
-        return {"kernel": "bmm_rcr", "operands": [a, b], "ints": [int(self._attrs.get("permute_d1", 0))],
+        return {"kernel": "bmm_rcr", "operands": [a, b], "ints": self._plan_ints(),
                 "floats": [float(self._attrs["alpha"])]}
 
 
@@ -83,7 +94,7 @@ class bmm_rrr(bmm):
 
     def _lower(self) -> Dict[str, Any]:
         a, b = self._attrs["inputs"]
-        return {"kernel": "bmm_rrr", "operands": [a, b], "ints": [int(self._attrs.get("permute_d1", 0))],
+        return {"kernel": "bmm_rrr", "operands": [a, b], "ints": self._plan_ints(),
                 "floats": [float(self._attrs["alpha"])]}
 
 

@@ -7,7 +7,7 @@ buffer, and the concat's input mask for it is cleared so the copy kernel skips i
 all fused launches nothing. This is the "cat pattern" of the reference's pass
 (python/aitemplate/compiler/transform/transform_strided_ops.py:94-333, with the accessor arithmetic of
 python/aitemplate/compiler/tensor_accessor.py:349-404), restricted to the producers of this path whose kernels
-take an output offset and row stride: the gemm_rcr family without a permuted store, and layernorm.
+take an output offset and row stride: the gemm and bmm families without a permuted store, and layernorm.
 """
 from __future__ import annotations
 
@@ -69,25 +69,29 @@ def fuse_strided_cat(sorted_graph: List[Tensor]) -> int:
     return fused
 
 
-def _strided_reader_slot(op, x) -> bool:
-    """True when `op` can read `x` through a row stride: x is operand A of a 2-D GEMM or the input of a
-    layernorm, and appears nowhere else among the op's inputs."""
+def _strided_reader_slot(op, x):
+    """Index of the input accessor through which `op` can read `x` with a row stride, or None: x is operand A of
+    a 2-D GEMM, either operand of a bmm without a permuted store, or the input of a layernorm, and appears
+    nowhere else among the op's inputs."""
     from ..ops.gemm_universal.bmm import bmm
     from ..ops.gemm_universal.gemm_rcr import gemm
     from ..ops.layernorm import layernorm
 
     ins = op._attrs["inputs"]
-    if sum(1 for y in ins if y is x) != 1 or ins[0] is not x:
-        return False
+    if sum(1 for y in ins if y is x) != 1:
+        return None
+    idx = next(i for i, y in enumerate(ins) if y is x)
     if isinstance(op, bmm):
-        return False
-    return isinstance(op, (gemm, layernorm)) and op._attrs["input_accessors"][0].stride_dim is None
+        ok = idx in (0, 1) and op._attrs.get("layout") is None
+    else:
+        ok = idx == 0 and isinstance(op, (gemm, layernorm))
+    return idx if ok and op._attrs["input_accessors"][idx].stride_dim is None else None
 
 
 def fuse_split_strided(sorted_graph: List[Tensor]) -> int:
     """The split side of the reference's strided-op pass (python/aitemplate/compiler/transform/
     transform_strided_ops.py:94-333 together with fuse_split.py): when every consumer of an output of a
-    last-dim split is a GEMM (as operand A) or a layernorm, those kernels read their column block of the
+    last-dim split is a GEMM (as operand A), a bmm (either operand) or a layernorm, those kernels read their column block of the
     split's input in place: the consumer's input TensorAccessor is re-based onto that input (element
     offset + the wider row stride), the split output becomes an alias of it at the block's byte offset, and
     the split's output mask for it is cleared. A split whose outputs are all fused launches nothing.
@@ -119,11 +123,11 @@ def fuse_split_strided(sorted_graph: List[Tensor]) -> int:
                 and (offset * elem) % 16 == 0
                 and (width * elem) % 16 == 0
                 and (shape[dim].value() * elem) % 16 == 0
-                and all(_strided_reader_slot(r, o) for r in readers)
+                and all(_strided_reader_slot(r, o) is not None for r in readers)
             )
             if ok:
                 for r in readers:
-                    r._attrs["input_accessors"][0].update_base_tensor(x, dim, offset)
+                    r._attrs["input_accessors"][_strided_reader_slot(r, o)].update_base_tensor(x, dim, offset)
                 o._attrs["is_view_of"] = x   # same storage: the alias starts at the block's first column
                 o._attrs["view_offset_bytes"] = offset * elem
                 op._attrs["output_masks"][i] = False

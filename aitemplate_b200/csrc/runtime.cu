@@ -485,16 +485,22 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     const int64_t batch = std::max(ba, bb);
     bind_shape(out0, {batch, m, n}, "bmm output");
     if (!launch) return;
-    // ints[0]: d1 of the "0213" permuted store of bmm_rrr_permute ([B / d1, M, d1, N]); 0 = plain
-    const int64_t a_bs = (ba == 1 && batch > 1) ? 0 : m * k, b_bs = (bb == 1 && batch > 1) ? 0 : n * k;
-    if (!op.ints.empty() && op.ints[0] > 0) {
-      check(b200ait_bmm_permute0213(ptr_of(a), ptr_of(b), ptr_of(out0), batch, m, n, k, a_bs, b_bs, op.ints[0], 1,
+    // ints: [d1, lda, ldb, out offset, ldc]. d1 > 0: the "0213" permuted store of bmm_rrr_permute
+    // ([B / d1, M, d1, N]). lda / ldb: row strides of operands that are column blocks of a wider buffer (a split
+    // read in place). out offset / ldc: the output is a column block of a concatenate's buffer. 0 = contiguous.
+    const auto opt = [&](size_t i) { return op.ints.size() > i ? op.ints[i] : 0; };
+    const int64_t lda = opt(1) > 0 ? opt(1) : k, ldb = opt(2) > 0 ? opt(2) : n, ldc = opt(4) > 0 ? opt(4) : n;
+    const int64_t a_bs = (ba == 1 && batch > 1) ? 0 : m * lda, b_bs = (bb == 1 && batch > 1) ? 0 : k * ldb;
+    if (opt(0) > 0) {
+      if (opt(1) > 0 || opt(2) > 0 || opt(4) > 0) throw Error("bmm '" + op.name + "': permuted store with strided operands");
+      check(b200ait_bmm_permute0213(ptr_of(a), ptr_of(b), ptr_of(out0), batch, m, n, k, a_bs, b_bs, opt(0), 1,
                                     T[a].dtype, static_cast<float>(op.floats[0]), 0, stream),
             op);
       return;
     }
-    check(b200ait_gemm_rrr(ptr_of(a), ptr_of(b), nullptr, nullptr, nullptr, ptr_of(out0), batch, m, n, k, k, n, n, n,
-                           a_bs, b_bs, m * n, m * n, 0, T[a].dtype, static_cast<float>(op.floats[0]), 0, nullptr, 0,
+    uint8_t* c = static_cast<uint8_t*>(ptr_of(out0)) + opt(3) * dtype_size(T[out0].dtype);
+    check(b200ait_gemm_rrr(ptr_of(a), ptr_of(b), nullptr, nullptr, nullptr, c, batch, m, n, k, lda, ldb, ldc, n,
+                           a_bs, b_bs, m * ldc, m * n, 0, T[a].dtype, static_cast<float>(op.floats[0]), 0, nullptr, 0,
                            1, stream),
           op);
     return;
@@ -510,16 +516,20 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     const int64_t batch = std::max(ba, bb);
     bind_shape(out0, {batch, m, n}, "bmm output");
     if (!launch) return;
-    // ints[0]: d1 of the "0213" permuted store of bmm_rcr_permute ([B / d1, M, d1, N]); 0 = plain
-    const int64_t a_bs = (ba == 1 && batch > 1) ? 0 : m * k, b_bs = (bb == 1 && batch > 1) ? 0 : n * k;
-    if (!op.ints.empty() && op.ints[0] > 0) {
-      check(b200ait_bmm_permute0213(ptr_of(a), ptr_of(b), ptr_of(out0), batch, m, n, k, a_bs, b_bs, op.ints[0], 0,
+    // ints: [d1, lda, ldb, out offset, ldc], as for bmm_rrr above
+    const auto opt = [&](size_t i) { return op.ints.size() > i ? op.ints[i] : 0; };
+    const int64_t lda = opt(1) > 0 ? opt(1) : k, ldb = opt(2) > 0 ? opt(2) : k, ldc = opt(4) > 0 ? opt(4) : n;
+    const int64_t a_bs = (ba == 1 && batch > 1) ? 0 : m * lda, b_bs = (bb == 1 && batch > 1) ? 0 : n * ldb;
+    if (opt(0) > 0) {
+      if (opt(1) > 0 || opt(2) > 0 || opt(4) > 0) throw Error("bmm '" + op.name + "': permuted store with strided operands");
+      check(b200ait_bmm_permute0213(ptr_of(a), ptr_of(b), ptr_of(out0), batch, m, n, k, a_bs, b_bs, opt(0), 0,
                                     T[a].dtype, static_cast<float>(op.floats[0]), 0, stream),
             op);
       return;
     }
-    check(b200ait_gemm_rcr(ptr_of(a), ptr_of(b), nullptr, nullptr, nullptr, ptr_of(out0), batch, m, n, k, k, k, n, n,
-                           a_bs, b_bs, m * n, m * n, 0, T[a].dtype, static_cast<float>(op.floats[0]), 0, 1, 1, 1, 0,
+    uint8_t* c = static_cast<uint8_t*>(ptr_of(out0)) + opt(3) * dtype_size(T[out0].dtype);
+    check(b200ait_gemm_rcr(ptr_of(a), ptr_of(b), nullptr, nullptr, nullptr, c, batch, m, n, k, lda, ldb, ldc, n,
+                           a_bs, b_bs, m * ldc, m * n, 0, T[a].dtype, static_cast<float>(op.floats[0]), 0, 1, 1, 1, 0,
                            nullptr, 0, 1, stream),
           op);
     return;

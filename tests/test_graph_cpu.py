@@ -392,8 +392,8 @@ def test_bmm_permute_nodes():
     assert [d.value() for d in y0._attrs["shape"]] == [2, 80, 12, 64]
     _, plan, _, _ = _lower([y0, y1])
     lines = plan.splitlines()
-    assert _parse_op(next(l for l in lines if l.startswith("op bmm_rcr")))["ints"] == [12]
-    assert _parse_op(next(l for l in lines if l.startswith("op bmm_rrr")))["ints"] == [12]
+    assert _parse_op(next(l for l in lines if l.startswith("op bmm_rcr")))["ints"] == [12, 0, 0, 0, 0]
+    assert _parse_op(next(l for l in lines if l.startswith("op bmm_rrr")))["ints"] == [12, 0, 0, 0, 0]
     with pytest.raises(RuntimeError):
         ops.bmm_rcr_permute(shape=(5,))(a, b)            # 24 is not a multiple of 5
     with pytest.raises(NotImplementedError):
@@ -420,3 +420,23 @@ def test_gemm_permute0213_fusion_and_its_limits():
     y3 = _out(ops.permute()(ops.reshape()(ops.gemm_rcr()(x, w3), [2, 64, 4, 40]), [0, 2, 1, 3]), "y3")   # d = 40
     _, plan, _, _ = _lower([y2, z2, y3])
     assert sum(l.startswith("op permute") for l in plan.splitlines()) == 2
+
+
+def test_bmm_strided_cat_and_split_plan():
+    # tests/unittest/compiler/test_split_bmm_fusion.py and test_strided_op_cat_pattern.py in the reference: bmm
+    # operands read column blocks of a last-dim split in place, and bmm outputs land in the concatenate's buffer
+    x = Tensor([4, 32, 48], name="x", is_input=True)
+    w = Tensor([4, 24, 32], name="w", is_input=True)
+    xa, xb = ops.split()(x, [16, 32], dim=2)         # xb has no strided reader: the split still copies it
+    wa, wb = ops.split()(w, 16, dim=2)
+    y0 = ops.bmm_rcr()(xa, wa)                       # A and B are column blocks: lda 48, ldb 32
+    y1 = ops.bmm_rcr()(xa, wb)
+    y = _out(ops.concatenate()([y0, y1], dim=2), "y")
+    z = _out(ops.elementwise(FuncEnum.RELU)(xb), "z")
+    _, plan, _, _ = _lower([y, z])
+    lines = plan.splitlines()
+    bmms = [_parse_op(l)["ints"] for l in lines if l.startswith("op bmm_rcr")]
+    assert bmms == [[0, 48, 32, 0, 48], [0, 48, 32, 24, 48]]                  # [d1, lda, ldb, out offset, ldc]
+    assert _parse_op(next(l for l in lines if l.startswith("op concatenate")))["ints"][-2:] == [0, 0]
+    masks = sorted(_parse_op(l)["ints"][-2:] for l in lines if l.startswith("op split"))
+    assert masks == [[0, 0], [0, 1]]

@@ -392,6 +392,31 @@ def test_gemm_permute0213_fusion_matches_oracle(workdir):
     _close(res, want, 1e-2)
 
 
+@pytest.mark.parametrize("bsz,m", [(4, 96), (3, 300)])
+def test_bmm_reads_split_blocks_and_writes_concat_blocks(workdir, bsz, m):
+    # tests/unittest/compiler/test_split_bmm_fusion.py, test_strided_op_cat_pattern.py in the reference: both bmm
+    # operands are column blocks of last-dim splits and both results are column blocks of one concatenate
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    k1, k2, n1, n2 = 64, 136, 72, 264
+    x = Tensor([bsz, m, k1 + k2], name="x", is_input=True)
+    w = Tensor([bsz, n1, k1 + k2], name="w", is_input=True)
+    v = Tensor([bsz, k2, n2], name="v", is_input=True)
+    xa, xb = ops.split()(x, [k1, k2], dim=2)
+    wa, wb = ops.split()(w, [k1, k2], dim=2)
+    y = ops.concatenate()([ops.bmm_rcr()(xa, wa), ops.bmm_rrr()(xb, v), ops.bmm_rcr()(xb, wb)], dim=2)
+    y._attrs["name"], y._attrs["is_output"] = "y", True
+    module = compile_model(y, detect_target(), workdir, "bmm_strided")
+    plan = open(os.path.join(workdir, "bmm_strided", "test.so.plan")).read()
+    assert [l.split()[-4:-1] for l in plan.splitlines() if l.startswith("op concatenate")] == [["0", "0", "0"]]
+    assert all(l.split()[-3:-1] == ["0", "0"] for l in plan.splitlines() if l.startswith("op split"))
+    xd, wd, vd = _rand((bsz, m, k1 + k2), 1), _rand((bsz, n1, k1 + k2), 2, 0.1), _rand((bsz, k2, n2), 3, 0.1)
+    out = torch.full((bsz, m, n1 + n2 + n1), 9.0, dtype=torch.float16, device="cuda")
+    res = module.run_with_tensors({"x": xd.cuda(), "w": wd.cuda(), "v": vd.cuda()}, {"y": out})["y"]
+    want = torch.cat([oracle.bmm_rcr(xd[:, :, :k1], wd[:, :, :k1]), oracle.bmm_rrr(xd[:, :, k1:], vd),
+                      oracle.bmm_rcr(xd[:, :, k1:], wd[:, :, k1:])], dim=2)
+    _close(res, want, 1e-2)
+
+
 def test_compile_time_gemm_profiling(workdir):
     # profile_devs given: every GEMM of the graph is timed over the launch configurations, the winners go into the
     # plan and a cache file, and the model still matches the oracle
