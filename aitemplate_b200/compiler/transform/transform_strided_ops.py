@@ -23,7 +23,8 @@ def _fusible_producer(op) -> bool:
 
     if isinstance(op, gemm):
         return op._attrs.get("layout") is None
-    return isinstance(op, layernorm)
+    # a layernorm over several trailing dims has rows that span more than the last dim: not a column block
+    return isinstance(op, layernorm) and len(op._attrs["normalized_shape"]) == 1
 
 
 def fuse_strided_cat(sorted_graph: List[Tensor]) -> int:
@@ -83,8 +84,10 @@ def _strided_reader_slot(op, x):
     idx = next(i for i, y in enumerate(ins) if y is x)
     if isinstance(op, bmm):
         ok = idx in (0, 1) and op._attrs.get("layout") is None
+    elif isinstance(op, layernorm):
+        ok = idx == 0 and len(op._attrs["normalized_shape"]) == 1
     else:
-        ok = idx == 0 and isinstance(op, (gemm, layernorm))
+        ok = idx == 0 and isinstance(op, gemm)
     return idx if ok and op._attrs["input_accessors"][idx].stride_dim is None else None
 
 

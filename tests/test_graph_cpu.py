@@ -440,3 +440,16 @@ def test_bmm_strided_cat_and_split_plan():
     assert _parse_op(next(l for l in lines if l.startswith("op concatenate")))["ints"][-2:] == [0, 0]
     masks = sorted(_parse_op(l)["ints"][-2:] for l in lines if l.startswith("op split"))
     assert masks == [[0, 0], [0, 1]]
+
+
+def test_strided_fusion_skips_layernorm_over_several_dims():
+    # rows of a layernorm over [S, W] span more than the last dim: neither its input nor its output is a column block
+    x = Tensor([4, 8, 64], name="x", is_input=True)
+    a, b = ops.split()(x, 32, dim=2)
+    la = ops.layernorm()(a, None, None, [IntImm(8), IntImm(32)], 1e-5)
+    lb = ops.layernorm()(b, None, None, [IntImm(32)], 1e-5)
+    y = _out(ops.concatenate()([la, lb], dim=2), "y")
+    _, plan, _, _ = _lower([y])
+    lines = plan.splitlines()
+    assert _parse_op(next(l for l in lines if l.startswith("op split")))["ints"][-2:] == [1, 0]
+    assert _parse_op(next(l for l in lines if l.startswith("op concatenate")))["ints"][-2:] == [1, 0]
