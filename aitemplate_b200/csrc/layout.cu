@@ -34,10 +34,23 @@ __global__ void __launch_bounds__(256) copy2d_kernel(const CopyBatch batch) {
   const CopyJob j = batch.job[blockIdx.y];
   const long long total = batch.rows * j.row_vecs;
   const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
-    const long long r = i / j.row_vecs, c = i - r * j.row_vecs;
-    const V v = *reinterpret_cast<const V*>(j.src + r * j.src_row_stride + c * sizeof(V));
-    *reinterpret_cast<V*>(j.dst + r * j.dst_row_stride + c * sizeof(V)) = v;
+  // four independent loads go out before the first store: the copy is bound by the bytes in flight per SM
+  constexpr int kUnroll = 4;
+  for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += kUnroll * step) {
+    V v[kUnroll];
+    long long dst_off[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long i = i0 + u * step;
+      if (i < total) {
+        const long long r = i / j.row_vecs, c = i - r * j.row_vecs;
+        v[u] = __ldcs(reinterpret_cast<const V*>(j.src + r * j.src_row_stride + c * sizeof(V)));
+        dst_off[u] = r * j.dst_row_stride + c * sizeof(V);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (i0 + u * step < total) *reinterpret_cast<V*>(j.dst + dst_off[u]) = v[u];
   }
 }
 
@@ -141,6 +154,35 @@ __global__ void __launch_bounds__(256) transpose_kernel(const V* __restrict__ sr
   }
 }
 
+// The same transpose for 16-bit elements with even R and C: 64 x 64 tiles moved with 32-bit accesses, so that a
+// warp reads and writes full 128-byte lines (the 32 x 32 kernel above moves 64-byte half lines of 16-bit data).
+__global__ void __launch_bounds__(256) transpose16_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst,
+                                                          long long R, long long C) {
+  __shared__ __align__(4) uint16_t tile[64][66];
+  const long long b = blockIdx.z;
+  const uint16_t* s = src + b * R * C;
+  uint16_t* d = dst + b * R * C;
+  const long long r0 = static_cast<long long>(blockIdx.y) * 64, c0 = static_cast<long long>(blockIdx.x) * 64;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = ty + i * 8;
+    const long long r = r0 + row, c = c0 + 2 * tx;
+    if (r < R && c < C)
+      *reinterpret_cast<uint32_t*>(&tile[row][2 * tx]) = __ldcs(reinterpret_cast<const uint32_t*>(s + r * C + c));
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int oc = ty + i * 8;  // column of the tile = row of the output
+    const long long c = c0 + oc, r = r0 + 2 * tx;
+    if (c < C && r < R) {
+      const uint32_t w = static_cast<uint32_t>(tile[2 * tx][oc]) | (static_cast<uint32_t>(tile[2 * tx + 1][oc]) << 16);
+      *reinterpret_cast<uint32_t*>(d + c * R + r) = w;
+    }
+  }
+}
+
 void permute_run(const void* src, void* dst, const int64_t* in_shape, const int64_t* perm, int rank, int elem_size,
                  cudaStream_t stream) {
   B200AIT_REQUIRE(rank >= 1 && rank <= kMaxRank, "permute: rank must be in [1, 8]");
@@ -190,7 +232,11 @@ void permute_run(const void* src, void* dst, const int64_t* in_shape, const int6
     const long long B = (r == 3) ? od[0] : 1, C = od[r - 2], R = od[r - 1];
     if (B < 65536 && (R + 31) / 32 < 65536) {
       dim3 grid(static_cast<unsigned>((C + 31) / 32), static_cast<unsigned>((R + 31) / 32), static_cast<unsigned>(B));
-      if (elem_size == 2)
+      if (elem_size == 2 && R % 2 == 0 && C % 2 == 0 && R >= 64 && C >= 64 &&
+          (reinterpret_cast<uintptr_t>(src) & 3) == 0 && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+        dim3 grid64(static_cast<unsigned>((C + 63) / 64), static_cast<unsigned>((R + 63) / 64), static_cast<unsigned>(B));
+        transpose16_kernel<<<grid64, 256, 0, stream>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), R, C);
+      } else if (elem_size == 2)
         transpose_kernel<uint16_t><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), R, C);
       else
         transpose_kernel<uint32_t><<<grid, 256, 0, stream>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), R, C);

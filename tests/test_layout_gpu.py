@@ -78,6 +78,10 @@ def test_split_by_chunk_size_with_ragged_tail(size, dim, shape):
         ((3, 5, 7), (1, 0, 2)),
         ((3, 5, 7), (2, 1, 0)),
         ((64, 100), (1, 0)),
+        ((200, 66), (1, 0)),               # 16-bit: 64 x 64 tiles with 32-bit accesses, ragged in both directions
+        ((3, 130, 258), (0, 2, 1)),
+        ((5, 64, 384), (0, 2, 1)),
+        ((2, 65, 128), (0, 2, 1)),         # odd R: the 32 x 32 kernel
         ((2, 3, 4, 5, 6), (4, 0, 3, 1, 2)),
         ((7, 1, 9), (2, 1, 0)),
         ((4, 6), (0, 1)),
