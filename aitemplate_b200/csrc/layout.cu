@@ -114,16 +114,19 @@ struct PermuteParams {
   long long total;
 };
 
-template <typename V>
+// I: type of the index arithmetic. 32-bit when every index fits (a 64-bit division costs several times a 32-bit
+// one, and a thread does one per dimension for each 16-byte vector it moves).
+template <typename V, typename I>
 __global__ void __launch_bounds__(256) permute_gather_kernel(const PermuteParams p) {
   const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.total; i += step) {
-    long long rem = i, off = 0;
+    I rem = static_cast<I>(i), off = 0;
 #pragma unroll
     for (int d = kMaxRank - 1; d >= 0; --d) {
       if (d < p.rank) {
-        const long long q = rem / p.out_dims[d];
-        off += (rem - q * p.out_dims[d]) * p.in_strides[d];
+        const I dim = static_cast<I>(p.out_dims[d]);
+        const I q = rem / dim;
+        off += (rem - q * dim) * static_cast<I>(p.in_strides[d]);
         rem = q;
       }
     }
@@ -266,13 +269,22 @@ void permute_run(const void* src, void* dst, const int64_t* in_shape, const int6
   if (epv > 1) p.out_dims[r - 1] = od[r - 1] / epv;
   p.total = total / epv;
   const unsigned grid = static_cast<unsigned>(std::min<long long>((p.total + 255) / 256, 148 * 32));
+  const bool small = total < (1ll << 31);  // element count bounds every index and every input offset
+#define B200AIT_GATHER(V)                                                   \
+  do {                                                                      \
+    if (small)                                                              \
+      permute_gather_kernel<V, uint32_t><<<grid, 256, 0, stream>>>(p);      \
+    else                                                                    \
+      permute_gather_kernel<V, long long><<<grid, 256, 0, stream>>>(p);     \
+  } while (0)
   switch (vec) {
-    case 16: permute_gather_kernel<uint4><<<grid, 256, 0, stream>>>(p); break;
-    case 8: permute_gather_kernel<uint2><<<grid, 256, 0, stream>>>(p); break;
-    case 4: permute_gather_kernel<uint32_t><<<grid, 256, 0, stream>>>(p); break;
-    case 2: permute_gather_kernel<uint16_t><<<grid, 256, 0, stream>>>(p); break;
-    default: permute_gather_kernel<uint8_t><<<grid, 256, 0, stream>>>(p); break;
+    case 16: B200AIT_GATHER(uint4); break;
+    case 8: B200AIT_GATHER(uint2); break;
+    case 4: B200AIT_GATHER(uint32_t); break;
+    case 2: B200AIT_GATHER(uint16_t); break;
+    default: B200AIT_GATHER(uint8_t); break;
   }
+#undef B200AIT_GATHER
   B200AIT_CUDA_CHECK(cudaGetLastError());
 }
 
