@@ -42,7 +42,26 @@ __global__ void __launch_bounds__(256) gemm_splitk_reduce_kernel(const GemmParam
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = 0.f;
   const bool full = p.vec_ok && col0 + 32 <= p.N;
-  for (int s = 0; s < p.splits; ++s) {
+  const long long split_stride = static_cast<long long>(p.batch) * p.M * p.N;
+  int s0 = 0;
+  if (full) {
+    // two splits' 128 bytes per thread are requested before either is added: few threads run here when M is
+    // small, so the pass is bound by how many loads each of them keeps in flight
+    const float* base = p.partial + (static_cast<long long>(b) * p.M + row) * p.N + col0;
+    for (; s0 + 1 < p.splits; s0 += 2) {
+      float4 f[2][8];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) f[h][q] = __ldcs(reinterpret_cast<const float4*>(base + (s0 + h) * split_stride + q * 4));
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          v[q * 4] += f[h][q].x, v[q * 4 + 1] += f[h][q].y, v[q * 4 + 2] += f[h][q].z, v[q * 4 + 3] += f[h][q].w;
+    }
+  }
+  for (int s = s0; s < p.splits; ++s) {
     const float* src = p.partial + ((static_cast<long long>(s) * p.batch + b) * p.M + row) * p.N + col0;
     if (full) {
 #pragma unroll
