@@ -5,14 +5,19 @@ use as ground truth for each op of the path. It is imported only by tests/, by
 __graft_entry__.smoke() and by bench.py's cpu_baseline / --impl reference legs, always as the
 checker or the timed CPU baseline and never by the product path (aitemplate_b200/ never imports it).
 
-Pinning. The reference ships no golden vectors or known-answer files for these ops: every test
-compares the compiled kernel with a PyTorch expression on the same inputs. Each function below is
-that expression (file:line given per function), evaluated in fp32 on inputs that were first rounded
-to fp16, so the oracle is pinned by construction to the reference's test oracle. What the
-reference's tests pin only loosely is noted where it matters: test_gemm_rcr_bias_fast_gelu.py
-checks fast_gelu against erf-GELU at atol=rtol=1e-1, so below 1e-1 the tanh form is pinned by the
-kernel source (custom_math.cuh:828-851), not by a test. tests/golden/ additionally holds fixtures
-produced by importing the reference's Python graph layer (shape inference and op attributes).
+Pinning. The reference ships no golden vectors for these ops: every one of its tests compares the
+compiled kernel with a PyTorch expression on the same inputs. Each function below restates that
+expression (file:line per function), in fp32 on inputs first rounded to fp16, and is PINNED to the
+reference's own text: tests/golden/make_reference_numeric_fixtures.py imports the reference's
+tests/unittest/ops/test_attention.py (attention_ref_math, attention_pt, ref_cross_attention,
+ref_attention_bmhk) and evaluates the cited source lines of the other reference tests on seeded
+inputs; tests/test_oracle_pinned_cpu.py requires every function here to reproduce those recorded
+outputs to 1e-6. Not pinned by a reference-computed vector: the tanh form of fast_gelu
+(test_gemm_rcr_bias_fast_gelu.py compares with erf-GELU at atol=rtol=1e-1, so below 1e-1 the tanh
+form is pinned by the kernel source custom_math.cuh:828-851 only), and the whole-block functions
+bert_layer / sd_transformer_block, which are checked to equal the composition of the pinned
+single-op functions. tests/golden/ additionally holds fixtures produced by importing the
+reference's Python graph layer (shape inference and op attributes).
 
 Inputs may be fp16/bf16/fp32 tensors on any device; they are moved to the CPU and up-cast.
 """
@@ -33,7 +38,7 @@ def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
 def _unary(name: str, x: torch.Tensor) -> torch.Tensor:
     if name == "identity":
         return x
-    if name == "relu":  # tests/unittest/ops/test_gemm_bias_relu.py:63-64
+    if name == "relu":  # tests/unittest/ops/test_gemm_bias_relu.py:64-65
         return torch.relu(x)
     if name == "gelu":  # tests/unittest/ops/test_gemm_rcr_bias_fast_gelu.py:96 (torch.nn.GELU())
         return F.gelu(x)
@@ -74,7 +79,7 @@ EPILOGUES = {
 
 def gemm_rcr(x, w, bias=None, d0=None, d1=None, epilogue: str = "", alpha: float = 1.0) -> torch.Tensor:
     """F.linear(X, W, bias) then the epilogue: tests/unittest/ops/test_gemm_bias.py:69,
-    test_gemm_bias_relu.py:63-64, test_gemm_rcr_bias_fast_gelu.py:96, test_gemm_bias_broadcast.py:216-219."""
+    test_gemm_bias_relu.py:64-65, test_gemm_rcr_bias_fast_gelu.py:96, test_gemm_bias_broadcast.py:216-219."""
     x, w, bias, d0, d1 = map(_f32, (x, w, bias, d0, d1))
     y = F.linear(x, w) * alpha
     if bias is not None:
