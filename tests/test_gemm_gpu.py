@@ -118,6 +118,9 @@ def test_forced_tile_width_many_tiles(tile_n):
         (2048, 1024, 512, "add"),
         (2048, 1024, 512, "add_add"),  # second residual: register path next to the staged first one
         (4096, 768, 3072, "add"),    # many tiles per pair: every ring stage and both accumulators wrap
+        (512, 512, 256, "fast_gelu"),
+        (4096, 3072, 768, "fast_gelu"),  # the lean pair fast_gelu kernel of the BERT FFN1 launch
+        (300, 520, 192, "fast_gelu"),
     ],
 )
 def test_cta_pair_tiles(m, n, kk, epilogue):
