@@ -36,6 +36,8 @@ def _signatures():
         "b200ait_last_error": (c_char_p, []),
         "b200ait_version": (c_int, []),
         "b200ait_device_status": (c_int, [POINTER(c_int)]),
+        "b200ait_kernel_launch_count": (c_int, [I64P]),
+        "b200ait_selftest_bounded_wait": (c_int, [I64P, c_void_p]),
         "b200ait_gemm_rcr": (
             c_int,
             [c_void_p] * 6 + [c_int64] * 12 + [c_int, c_int, c_float, c_int, c_int64, c_int64, c_int64, c_int,
@@ -121,6 +123,13 @@ def load() -> ctypes.CDLL:
             fn.argtypes = args
         _lib = lib
         return lib
+
+
+def kernel_launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    n = c_int64(0)
+    check(load().b200ait_kernel_launch_count(ctypes.byref(n)), "b200ait_kernel_launch_count")
+    return int(n.value)
 
 
 def last_error() -> str:

@@ -495,7 +495,7 @@ void launch_attn_variant(const void* q, const void* k, const void* v, const Attn
   AttnParams pp = p;
   pp.num_items = static_cast<int>(items);
   const long long grid = std::min<long long>(items, static_cast<long long>(sm_count()) * (DCH == 1 ? 2 : 1));
-  attention_tc_kernel<DCH, BF16, NOMASK><<<static_cast<unsigned>(grid), kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv,
+  ::b200ait::count_launch(), attention_tc_kernel<DCH, BF16, NOMASK><<<static_cast<unsigned>(grid), kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv,
                                                                                                                  pp);
   B200AIT_CUDA_CHECK(cudaGetLastError());
 }
@@ -563,9 +563,9 @@ B200AIT_EXPORT int b200ait_mem_eff_attention(void* output, const void* query, co
       const unsigned grid = static_cast<unsigned>((rows + 3) / 4);
       const size_t sh = 4 * static_cast<size_t>(p.D) * sizeof(float);
       if (bf16)
-        attention_simt_kernel<true><<<grid, 128, sh, stream>>>(query, key, value, p);
+        ::b200ait::count_launch(), attention_simt_kernel<true><<<grid, 128, sh, stream>>>(query, key, value, p);
       else
-        attention_simt_kernel<false><<<grid, 128, sh, stream>>>(query, key, value, p);
+        ::b200ait::count_launch(), attention_simt_kernel<false><<<grid, 128, sh, stream>>>(query, key, value, p);
       B200AIT_CUDA_CHECK(cudaGetLastError());
     }
   });

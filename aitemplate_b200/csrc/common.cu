@@ -6,6 +6,8 @@
 
 namespace b200ait {
 
+std::atomic<uint64_t> g_kernel_launches{0};
+
 namespace {
 thread_local std::string g_last_error;
 constexpr int kMaxDevices = 64;
@@ -77,6 +79,14 @@ B200AIT_EXPORT int b200ait_device_status(int* status_out) {
 }
 
 B200AIT_EXPORT int b200ait_version() { return 1; }
+
+// Number of kernels this library has launched in this process so far (all devices, all threads).
+B200AIT_EXPORT int b200ait_kernel_launch_count(int64_t* count_out) {
+  return guarded("b200ait_kernel_launch_count", [&] {
+    B200AIT_REQUIRE(count_out, "count_out is null");
+    *count_out = static_cast<int64_t>(g_kernel_launches.load(std::memory_order_relaxed));
+  });
+}
 
 // ------------------------------------------------------------------------------------------------
 // Peer buffers for multi-GPU runs (one process per GPU on one node): a buffer allocated here can be opened by

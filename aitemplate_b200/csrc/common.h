@@ -19,6 +19,11 @@ const std::string& last_error();
 // device pointer to this device's int status word (allocated on first use, zeroed)
 int* device_status_word();
 
+// Process-wide count of kernels this library has launched (every launch site calls count_launch();
+// a launch made while a stream is being captured counts once, at capture).
+extern std::atomic<uint64_t> g_kernel_launches;
+inline void count_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
+
 // number of SMs of the current device (cached per device)
 int sm_count();
 

@@ -448,7 +448,7 @@ void gemm_run(const GemmArgs& g_in) {
   do {                                                                                                         \
     static std::atomic<uint64_t> configured{0};                                                                \
     opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_rowdot_kernel<BF, MR>), 160 * 1024);      \
-    gemm_rowdot_kernel<BF, MR><<<grid, kRowDotThreads, smem, g.stream>>>(g.a, g.b, p);                         \
+    ::b200ait::count_launch(), gemm_rowdot_kernel<BF, MR><<<grid, kRowDotThreads, smem, g.stream>>>(g.a, g.b, p);                         \
   } while (0)
     if (bf16) {
       if (g.m <= 1) B200AIT_ROWDOT(true, 1); else if (g.m <= 2) B200AIT_ROWDOT(true, 2); else B200AIT_ROWDOT(true, 4);
@@ -464,9 +464,9 @@ void gemm_run(const GemmArgs& g_in) {
               static_cast<unsigned>(g.batch));
     B200AIT_REQUIRE(grid.y < 65536 && grid.z < 65536, "gemm: unaligned problem too large for the CUDA-core kernel");
     if (bf16)
-      gemm_simt_kernel<true><<<grid, 256, 0, g.stream>>>(g.a, g.b, p);
+      ::b200ait::count_launch(), gemm_simt_kernel<true><<<grid, 256, 0, g.stream>>>(g.a, g.b, p);
     else
-      gemm_simt_kernel<false><<<grid, 256, 0, g.stream>>>(g.a, g.b, p);
+      ::b200ait::count_launch(), gemm_simt_kernel<false><<<grid, 256, 0, g.stream>>>(g.a, g.b, p);
     B200AIT_CUDA_CHECK(cudaGetLastError());
     return;
   }
@@ -556,9 +556,9 @@ void gemm_run(const GemmArgs& g_in) {
     const long long total = static_cast<long long>(p.batch) * p.M * ((p.N + 31) / 32);
     const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
     if (bf16)
-      gemm_splitk_reduce_kernel<true><<<blocks, 256, 0, g.stream>>>(p);
+      ::b200ait::count_launch(), gemm_splitk_reduce_kernel<true><<<blocks, 256, 0, g.stream>>>(p);
     else
-      gemm_splitk_reduce_kernel<false><<<blocks, 256, 0, g.stream>>>(p);
+      ::b200ait::count_launch(), gemm_splitk_reduce_kernel<false><<<blocks, 256, 0, g.stream>>>(p);
     B200AIT_CUDA_CHECK(cudaGetLastError());
   }
 }
@@ -843,10 +843,20 @@ B200AIT_EXPORT int b200ait_gemm_rcr_static_scratch(const void* a, const void* b,
                                                    cudaStream_t stream) {
   return guarded("b200ait_gemm_rcr_static_scratch", [&] {
     B200AIT_REQUIRE(batch >= 0 && m >= 0 && n >= 0 && k >= 0, "gemm: negative dimension");
-    const long long need = 2ll * batch * m * n * 4;
-    if (need > kStaticScratchBytes) {
+    // limit check without forming the product first: 2 * batch * m * n * 4 can leave int64 for absurd
+    // dimensions and would then slip under the limit
+    const long long cap_elems = kStaticScratchBytes / 8;  // fp32 partial sums of two splits
+    bool fits = true;
+    long long elems = 1;
+    for (long long d : {(long long)batch, (long long)m, (long long)n}) {
+      if (d == 0) { elems = 0; break; }
+      if (elems > cap_elems / d) { fits = false; break; }
+      elems *= d;
+    }
+    if (!fits || elems > cap_elems) {
+      const std::string need = fits ? std::to_string(elems * 8) : std::string("more than 2^40");
       throw Error("problem too large for the static scratch: two splits of " + std::to_string(batch) + " x " +
-                  std::to_string(m) + " x " + std::to_string(n) + " fp32 partial sums need " + std::to_string(need) +
+                  std::to_string(m) + " x " + std::to_string(n) + " fp32 partial sums need " + need +
                   " bytes, the limit is " + std::to_string(kStaticScratchBytes) +
                   "; call b200ait_gemm_rcr with a caller-provided workspace instead");
     }

@@ -725,7 +725,7 @@ void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tout
   static std::atomic<uint64_t> configured{0};
   opt_in_smem_once(configured, reinterpret_cast<const void*>(&gemm_tc_kernel<BN, BF16, EPI, false, BMN, MULTI>),
                    Cfg::kSmemBytes);
-  gemm_tc_kernel<BN, BF16, EPI, false, BMN, MULTI><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
+  ::b200ait::count_launch(), gemm_tc_kernel<BN, BF16, EPI, false, BMN, MULTI><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
       ta, tb, tout.m[0], ta, p, tout);
   B200AIT_CUDA_CHECK(cudaGetLastError());
 }
@@ -750,6 +750,7 @@ void launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps&
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  ::b200ait::count_launch();
   B200AIT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tout.m[0], td0, p, tout));
 }
 

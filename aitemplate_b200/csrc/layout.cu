@@ -93,11 +93,11 @@ void run_copies(const std::vector<HostCopy>& copies, long long rows, cudaStream_
     const unsigned gx = static_cast<unsigned>(std::min<long long>((max_vecs + per_block - 1) / per_block, 148 * 16));
     dim3 grid(std::max(gx, 1u), n);
     switch (vec) {
-      case 16: copy2d_kernel<uint4><<<grid, 256, 0, stream>>>(b); break;
-      case 8: copy2d_kernel<uint2><<<grid, 256, 0, stream>>>(b); break;
-      case 4: copy2d_kernel<uint32_t><<<grid, 256, 0, stream>>>(b); break;
-      case 2: copy2d_kernel<uint16_t><<<grid, 256, 0, stream>>>(b); break;
-      default: copy2d_kernel<uint8_t><<<grid, 256, 0, stream>>>(b); break;
+      case 16: ::b200ait::count_launch(), copy2d_kernel<uint4><<<grid, 256, 0, stream>>>(b); break;
+      case 8: ::b200ait::count_launch(), copy2d_kernel<uint2><<<grid, 256, 0, stream>>>(b); break;
+      case 4: ::b200ait::count_launch(), copy2d_kernel<uint32_t><<<grid, 256, 0, stream>>>(b); break;
+      case 2: ::b200ait::count_launch(), copy2d_kernel<uint16_t><<<grid, 256, 0, stream>>>(b); break;
+      default: ::b200ait::count_launch(), copy2d_kernel<uint8_t><<<grid, 256, 0, stream>>>(b); break;
     }
     B200AIT_CUDA_CHECK(cudaGetLastError());
   }
@@ -238,11 +238,11 @@ void permute_run(const void* src, void* dst, const int64_t* in_shape, const int6
       if (elem_size == 2 && R % 2 == 0 && C % 2 == 0 && R >= 64 && C >= 64 &&
           (reinterpret_cast<uintptr_t>(src) & 3) == 0 && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
         dim3 grid64(static_cast<unsigned>((C + 63) / 64), static_cast<unsigned>((R + 63) / 64), static_cast<unsigned>(B));
-        transpose16_kernel<<<grid64, 256, 0, stream>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), R, C);
+        ::b200ait::count_launch(), transpose16_kernel<<<grid64, 256, 0, stream>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), R, C);
       } else if (elem_size == 2)
-        transpose_kernel<uint16_t><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), R, C);
+        ::b200ait::count_launch(), transpose_kernel<uint16_t><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), R, C);
       else
-        transpose_kernel<uint32_t><<<grid, 256, 0, stream>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), R, C);
+        ::b200ait::count_launch(), transpose_kernel<uint32_t><<<grid, 256, 0, stream>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), R, C);
       B200AIT_CUDA_CHECK(cudaGetLastError());
       return;
     }
@@ -273,9 +273,9 @@ void permute_run(const void* src, void* dst, const int64_t* in_shape, const int6
 #define B200AIT_GATHER(V)                                                   \
   do {                                                                      \
     if (small)                                                              \
-      permute_gather_kernel<V, uint32_t><<<grid, 256, 0, stream>>>(p);      \
+      ::b200ait::count_launch(), permute_gather_kernel<V, uint32_t><<<grid, 256, 0, stream>>>(p);      \
     else                                                                    \
-      permute_gather_kernel<V, long long><<<grid, 256, 0, stream>>>(p);     \
+      ::b200ait::count_launch(), permute_gather_kernel<V, long long><<<grid, 256, 0, stream>>>(p);     \
   } while (0)
   switch (vec) {
     case 16: B200AIT_GATHER(uint4); break;
@@ -574,9 +574,9 @@ B200AIT_EXPORT int b200ait_elementwise(void* output, const int64_t* out_shape, i
     const long long work = vec ? p.total / 8 : p.total;
     const unsigned grid = static_cast<unsigned>(std::min<long long>((work + 255) / 256, 148 * 32));
     if (dtype == kDTypeBFloat16)
-      elementwise_kernel<true><<<grid, 256, 0, stream>>>(p);
+      ::b200ait::count_launch(), elementwise_kernel<true><<<grid, 256, 0, stream>>>(p);
     else
-      elementwise_kernel<false><<<grid, 256, 0, stream>>>(p);
+      ::b200ait::count_launch(), elementwise_kernel<false><<<grid, 256, 0, stream>>>(p);
     B200AIT_CUDA_CHECK(cudaGetLastError());
   });
 }

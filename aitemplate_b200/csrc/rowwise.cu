@@ -169,7 +169,7 @@ void layernorm_launch(const LayerNormParams& p, cudaStream_t stream) {
     const int wpb = (vpl <= 4) ? 8 : 4;  // warps per block
     const unsigned grid = static_cast<unsigned>((p.m + wpb - 1) / wpb);
     const int threads = wpb * 32;
-#define B200AIT_LN(V) layernorm_warp_kernel<V, BF16><<<grid, threads, 0, stream>>>(p)
+#define B200AIT_LN(V) ::b200ait::count_launch(), layernorm_warp_kernel<V, BF16><<<grid, threads, 0, stream>>>(p)
     if (vpl <= 1)
       B200AIT_LN(1);
     else if (vpl <= 2)
@@ -190,7 +190,7 @@ void layernorm_launch(const LayerNormParams& p, cudaStream_t stream) {
   } else {
     B200AIT_REQUIRE(p.m < (1ll << 31), "layernorm: too many rows");
     const int threads = p.n >= 2048 ? 512 : (p.n >= 512 ? 256 : 128);
-    layernorm_block_kernel<BF16><<<static_cast<unsigned>(p.m), threads, 0, stream>>>(p);
+    ::b200ait::count_launch(), layernorm_block_kernel<BF16><<<static_cast<unsigned>(p.m), threads, 0, stream>>>(p);
   }
   B200AIT_CUDA_CHECK(cudaGetLastError());
 }
@@ -299,13 +299,13 @@ template <bool BF16>
 void softmax_launch(const SoftmaxParams& p, cudaStream_t stream) {
   if (p.inner > 1) {
     const long long total = p.outer * p.inner;
-    softmax_strided_kernel<BF16><<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(p);
+    ::b200ait::count_launch(), softmax_strided_kernel<BF16><<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(p);
   } else if (p.k % 8 == 0 && p.k <= 4096 && al16(p.x) && al16(p.y)) {
     const int vpl = (p.k / 8 + 31) / 32;
     const int wpb = (vpl <= 4) ? 8 : 4;
     const unsigned grid = static_cast<unsigned>((p.outer + wpb - 1) / wpb);
     const int threads = wpb * 32;
-#define B200AIT_SM(V) softmax_warp_kernel<V, BF16><<<grid, threads, 0, stream>>>(p)
+#define B200AIT_SM(V) ::b200ait::count_launch(), softmax_warp_kernel<V, BF16><<<grid, threads, 0, stream>>>(p)
     if (vpl <= 1)
       B200AIT_SM(1);
     else if (vpl <= 2)
@@ -320,7 +320,7 @@ void softmax_launch(const SoftmaxParams& p, cudaStream_t stream) {
   } else {
     B200AIT_REQUIRE(p.outer < (1ll << 31), "softmax: too many rows");
     const int threads = p.k >= 2048 ? 512 : (p.k >= 256 ? 256 : (p.k >= 64 ? 64 : 32));
-    softmax_block_kernel<BF16><<<static_cast<unsigned>(p.outer), threads, 0, stream>>>(p);
+    ::b200ait::count_launch(), softmax_block_kernel<BF16><<<static_cast<unsigned>(p.outer), threads, 0, stream>>>(p);
   }
   B200AIT_CUDA_CHECK(cudaGetLastError());
 }

@@ -275,14 +275,24 @@ class Executor {
       const TensorInfo& a = plan.tensors[op.operands[0]];
       const TensorInfo& b = plan.tensors[op.operands[1]];
       if (a.dims.empty() || b.dims.size() != 2 || !b.dims[0].is_static || !a.dims.back().is_static) continue;
-      for (int bound = 0; bound < 2; ++bound) {
-        int64_t m = 1;
-        for (size_t i = 0; i + 1 < a.dims.size(); ++i)
-          m *= a.dims[i].is_static ? a.dims[i].v : (bound ? plan.dims[a.dims[i].v].hi : plan.dims[a.dims[i].v].lo);
+      // Split-K demand is not monotonic in M (none once the tiles fill the SMs, little at M = 1, most
+      // around M = 128..512), so a dynamic M is sampled: both bounds, then every multiple of 128 up to 2048
+      // and powers of two above, inside [lo, hi].
+      int64_t m_lo = 1, m_hi = 1;
+      for (size_t i = 0; i + 1 < a.dims.size(); ++i) {
+        m_lo *= a.dims[i].is_static ? a.dims[i].v : plan.dims[a.dims[i].v].lo;
+        m_hi *= a.dims[i].is_static ? a.dims[i].v : plan.dims[a.dims[i].v].hi;
+      }
+      std::vector<int64_t> ms{m_lo, m_hi};
+      for (int64_t m = 128; m < m_hi && m <= 2048; m += 128)
+        if (m > m_lo) ms.push_back(m);
+      for (int64_t m = 4096; m < m_hi; m *= 2)
+        if (m > m_lo) ms.push_back(m);
+      // ints[7], ints[8]: tile width and split-K chosen by the compile-time profiler (0 = library decides)
+      const int tile_hint = op.ints.size() > 8 ? static_cast<int>(op.ints[7]) : 0;
+      const int split_hint = op.ints.size() > 8 ? static_cast<int>(op.ints[8]) : 0;
+      for (int64_t m : ms) {
         int64_t bytes = 0;
-        // ints[7], ints[8]: tile width and split-K chosen by the compile-time profiler (0 = library decides)
-        const int tile_hint = op.ints.size() > 8 ? static_cast<int>(op.ints[7]) : 0;
-        const int split_hint = op.ints.size() > 8 ? static_cast<int>(op.ints[8]) : 0;
         if (b200ait_gemm_rcr_workspace_bytes(1, m, b.dims[0].v, a.dims.back().v, tile_hint, split_hint, &bytes) == 0)
           workspace_bytes_ = std::max(workspace_bytes_, bytes);
       }
@@ -367,6 +377,18 @@ class Executor {
   void profile(cudaStream_t stream, size_t iters, const std::string& filename, uint8_t* constants);
 
   cudaEvent_t run_finished() const { return run_finished_; }
+  // Orders a new run on `stream` after this executor's previous run (which may still be in flight on
+  // another stream and owns the same blob and workspace) without blocking the host.
+  void order_after_previous_run(cudaStream_t stream) {
+    if (has_run_ && stream != last_stream_) B200AIT_CUDA_CHECK(cudaStreamWaitEvent(stream, run_finished_, 0));
+    last_stream_ = stream;
+    has_run_ = true;
+  }
+  // Marks the end of whatever an aborted run managed to enqueue, so that the next run of this
+  // executor is still ordered after those kernels.
+  void mark_run_finished(cudaStream_t stream) noexcept {
+    if (cudaEventRecord(run_finished_, stream) != cudaSuccess) cudaGetLastError();
+  }
 
  private:
   void check(int code, const OpInfo& op) {
@@ -382,6 +404,8 @@ class Executor {
   RunState st_;
   std::vector<void*> ptrs_;
   cudaEvent_t run_finished_ = nullptr;
+  cudaStream_t last_stream_ = nullptr;
+  bool has_run_ = false;
   cudaStream_t graph_stream_ = nullptr;
   struct GraphEntry {
     std::vector<int64_t> key;
@@ -966,12 +990,13 @@ class ModelContainer {
            bool graph_mode, int64_t** output_shapes_out) {
     std::shared_lock<std::shared_mutex> clock(constants_mutex_);
     check_constants_ready();
-    Executor* ex = acquire();
+    Executor* ex = acquire(stream);
     try {
       prepare(*ex, inputs, num_in, outputs, num_out);
       ex->run(stream, graph_mode, constants_[active_]);
       write_output_shapes(*ex, output_shapes_out);
     } catch (...) {
+      ex->mark_run_finished(stream);  // an op that threw mid-plan leaves earlier kernels queued
       release(ex);
       throw;
     }
@@ -1025,11 +1050,12 @@ class ModelContainer {
     if (!filename) throw Error("filename is null");
     std::shared_lock<std::shared_mutex> clock(constants_mutex_);
     check_constants_ready();
-    Executor* ex = acquire();
+    Executor* ex = acquire(stream);
     try {
       prepare(*ex, inputs, num_in, outputs, num_out);
       ex->profile(stream, iters, filename, constants_[active_]);
     } catch (...) {
+      ex->mark_run_finished(stream);
       release(ex);
       throw;
     }
@@ -1165,14 +1191,21 @@ class ModelContainer {
     for (auto& e : executors_) B200AIT_CUDA_CHECK(cudaEventSynchronize(e->run_finished()));
   }
 
-  Executor* acquire() {
+  // An executor is held only while a run is being ENQUEUED (its host state is the per-run shapes and
+  // pointers); reuse of its blob by the next run is ordered on the device, so the host can queue any
+  // number of runs ahead of the GPU.
+  Executor* acquire(cudaStream_t stream) {
     std::unique_lock<std::mutex> lock(pool_mutex_);
     pool_cv_.wait(lock, [&] { return !available_.empty(); });
     Executor* ex = available_.front();
     available_.pop_front();
     lock.unlock();
-    // the executor's previous run may still be in flight on another stream; its blob is reused
-    B200AIT_CUDA_CHECK(cudaEventSynchronize(ex->run_finished()));
+    try {
+      ex->order_after_previous_run(stream);
+    } catch (...) {
+      release(ex);
+      throw;
+    }
     return ex;
   }
   void release(Executor* ex) {

@@ -4,6 +4,10 @@ Each row times one op through the C ABI on seeded synthetic inputs: a CUDA graph
 over a rotation of buffer sets larger than L2 (so no launch finds its operands cached), timed with
 CUDA events, best of `iters` replays. Reported: microseconds per launch, TFLOP/s or GB/s from the
 ALGORITHMIC flops / bytes of the op, and that as a fraction of the measured and of the nominal peak.
+Each row also carries a `_sample`: a slice of the op's independent units (rows, batches, heads) with
+the inputs that produced it and the kernel's output for it, plus the factor by which the whole op is
+larger. The caller (bench.py) evaluates its CPU checker on the sample, which gives the row its
+cpu_ms and its error columns; this package itself never touches a CPU implementation.
 The reference's analogue is the per-op profiler loop (python/aitemplate/backend/cuda/gemm_universal/
 common.py:439-568: warm-up, timed launches over a rotating memory pool sized to defeat L2).
 """
@@ -69,8 +73,16 @@ def _gen(seed: int) -> torch.Generator:
     return torch.Generator(device="cuda").manual_seed(seed)
 
 
+def _unit_sample(n: int, take: int) -> torch.Tensor:
+    """`take` unit indices out of n: the first, the last, the rest spread evenly (device tensor)."""
+    if take >= n:
+        return torch.arange(n, device="cuda")
+    idx = torch.linspace(0, n - 1, take, device="cuda").round().long()
+    return torch.unique(idx)
+
+
 def bench_gemm(config: str, m: int, n: int, k: int, epilogue: str, peaks: Dict, residual: bool = False,
-               w_scale: float = 0.02, permute=None, seed: int = 1) -> Dict:
+               w_scale: float = 0.02, permute=None, seed: int = 1, sample_flops: float = 1.2e12) -> Dict:
     g = _gen(seed)
     nbytes = 2 * (m * k + n * k + n + m * n * (2 if residual else 1))
     sets = _rot(nbytes)
@@ -88,7 +100,28 @@ def bench_gemm(config: str, m: int, n: int, k: int, epilogue: str, peaks: Dict, 
     ms = _time_graph(fn, reps=2 * sets)
     bound = "tensor" if 2.0 * m * n * k / nbytes > 250 else "hbm"
     name = "gemm_rcr_bias" + ("_" + epilogue if epilogue else "") + ("_permute" if permute else "")
-    return _row(config, name, f"{m}x{n}x{k}", ms, 2.0 * m * n * k, nbytes, bound, peaks)
+    row = _row(config, name, f"{m}x{n}x{k}", ms, 2.0 * m * n * k, nbytes, bound, peaks)
+    # the vendor library on the same buffers, for comparison only: F.linear = cuBLAS GEMM + bias, WITHOUT the
+    # activation / residual / permuted store this op fuses
+    ms_lib = _time_graph(lambda i: torch.nn.functional.linear(xs[i % sets], w, b), reps=2 * sets, iters=3)
+    row["cublas_linear_us"] = round(ms_lib * 1e3, 2)
+    fn(0)
+    torch.cuda.synchronize()
+    if permute is None:
+        take = min(m, max(1, int(sample_flops // (2.0 * n * k))))
+        rows = _unit_sample(m, take)
+        row["_sample"] = {"kind": "gemm", "x": xs[0][rows], "w": w, "b": b, "d0": ds[0][rows] if residual else None,
+                          "epilogue": epilogue, "got": outs[0][rows], "scale": m / take,
+                          "note": f"{take} of {m} rows"}
+    else:  # whole sequences (t1 rows each) so that the permuted output can be sliced along its batch dim
+        t1 = permute[0]
+        nseq = m // t1
+        take = min(nseq, max(1, int(sample_flops // (2.0 * t1 * n * k))))
+        seqs = _unit_sample(nseq, take)
+        rows = (seqs[:, None] * t1 + torch.arange(t1, device="cuda")[None, :]).reshape(-1)
+        row["_sample"] = {"kind": "gemm_permute", "x": xs[0][rows], "w": w, "b": b, "shape": permute,
+                          "got": outs[0][:, seqs], "scale": nseq / take, "note": f"{take} of {nseq} sequences"}
+    return row
 
 
 def bench_bmm(config: str, batch: int, m: int, n: int, k: int, peaks: Dict) -> Dict:
@@ -98,7 +131,14 @@ def bench_bmm(config: str, batch: int, m: int, n: int, k: int, peaks: Dict) -> D
     a = [(torch.rand((batch, m, k), generator=g, device="cuda") * 2 - 1).half() for _ in range(sets)]
     b = [(torch.rand((batch, n, k), generator=g, device="cuda") * 2 - 1).half() for _ in range(sets)]
     ms = _time_graph(lambda i: K.bmm_rcr(a[i % sets], b[i % sets]), reps=2 * sets)
-    return _row(config, "bmm_rcr", f"{batch}x[{m}x{k}].[{n}x{k}]^T", ms, 2.0 * batch * m * n * k, nbytes, "hbm", peaks)
+    row = _row(config, "bmm_rcr", f"{batch}x[{m}x{k}].[{n}x{k}]^T", ms, 2.0 * batch * m * n * k, nbytes, "hbm", peaks)
+    ms_lib = _time_graph(lambda i: torch.bmm(a[i % sets], b[i % sets].transpose(1, 2)), reps=2 * sets, iters=3)
+    row["cublas_bmm_us"] = round(ms_lib * 1e3, 2)
+    y = K.bmm_rcr(a[0], b[0])
+    idx = _unit_sample(batch, min(batch, 128))
+    row["_sample"] = {"kind": "bmm", "a": a[0][idx], "b": b[0][idx], "got": y[idx], "scale": batch / idx.numel(),
+                      "note": f"{idx.numel()} of {batch} batches"}
+    return row
 
 
 def bench_attention(config: str, b: int, h: int, sq: int, skv: int, d: int, peaks: Dict) -> Dict:
@@ -109,8 +149,13 @@ def bench_attention(config: str, b: int, h: int, sq: int, skv: int, d: int, peak
     k = [torch.randn((b, h, skv, d), generator=g, device="cuda").half() for _ in range(sets)]
     v = [torch.randn((b, h, skv, d), generator=g, device="cuda").half() for _ in range(sets)]
     ms = _time_graph(lambda i: K.mem_eff_attention(q[i % sets], k[i % sets], v[i % sets]), reps=2 * sets)
-    return _row(config, "mem_eff_attention", f"B{b} H{h} Sq{sq} Skv{skv} D{d}", ms, 4.0 * b * h * sq * skv * d, nbytes,
-                "tensor", peaks)
+    row = _row(config, "mem_eff_attention", f"B{b} H{h} Sq{sq} Skv{skv} D{d}", ms, 4.0 * b * h * sq * skv * d, nbytes,
+               "tensor", peaks)
+    o = K.mem_eff_attention(q[0], k[0], v[0])  # [B, Sq, H, D]
+    idx = _unit_sample(b, min(b, max(1, int(6e9 // (4.0 * h * sq * skv * d)))))
+    row["_sample"] = {"kind": "attention", "q": q[0][idx], "k": k[0][idx], "v": v[0][idx], "got": o[idx],
+                      "scale": b / idx.numel(), "note": f"{idx.numel()} of {b} batches"}
+    return row
 
 
 def bench_layernorm(config: str, m: int, n: int, eps: float, peaks: Dict) -> Dict:
@@ -121,7 +166,12 @@ def bench_layernorm(config: str, m: int, n: int, eps: float, peaks: Dict) -> Dic
     gamma = (torch.rand((n,), generator=g, device="cuda") + 0.5).half()
     beta = (torch.randn((n,), generator=g, device="cuda") * 0.1).half()
     ms = _time_graph(lambda i: K.layernorm(xs[i % sets], gamma, beta, eps=eps), reps=2 * sets)
-    return _row(config, "layernorm", f"{m}x{n}", ms, 0.0, nbytes, "hbm", peaks)
+    row = _row(config, "layernorm", f"{m}x{n}", ms, 0.0, nbytes, "hbm", peaks)
+    y = K.layernorm(xs[0], gamma, beta, eps=eps)
+    rows = _unit_sample(m, min(m, 8192))
+    row["_sample"] = {"kind": "layernorm", "x": xs[0][rows], "gamma": gamma, "beta": beta, "eps": eps, "got": y[rows],
+                      "scale": m / rows.numel(), "note": f"{rows.numel()} of {m} rows"}
+    return row
 
 
 def bench_softmax(config: str, shape, peaks: Dict) -> Dict:
@@ -131,7 +181,13 @@ def bench_softmax(config: str, shape, peaks: Dict) -> Dict:
     sets = 2
     xs = [torch.randn(shape, generator=g, device="cuda").mul_(2).half() for _ in range(sets)]
     ms = _time_graph(lambda i: K.softmax(xs[i % sets], -1), reps=4)
-    return _row(config, "softmax", "x".join(map(str, shape)), ms, 0.0, nbytes, "hbm", peaks)
+    row = _row(config, "softmax", "x".join(map(str, shape)), ms, 0.0, nbytes, "hbm", peaks)
+    y = K.softmax(xs[0], -1)
+    take = max(1, shape[0] // 8)
+    idx = _unit_sample(shape[0], take)
+    row["_sample"] = {"kind": "softmax", "x": xs[0][idx], "got": y[idx], "scale": shape[0] / idx.numel(),
+                      "note": f"{idx.numel()} of {shape[0]} outer slices"}
+    return row
 
 
 def bench_concat_split(config: str, peaks: Dict) -> List[Dict]:
@@ -142,8 +198,13 @@ def bench_concat_split(config: str, peaks: Dict) -> List[Dict]:
     nbytes = 2 * 2 * 8192 * 4096
     ms_c = _time_graph(lambda i: K.concatenate(parts[i % sets], 1), reps=2 * sets)
     ms_s = _time_graph(lambda i: K.split(cats[i % sets], [1024] * 4, 1), reps=2 * sets)
-    return [_row(config, "concatenate", "4x[8192x1024] dim 1", ms_c, 0.0, nbytes, "hbm", peaks),
-            _row(config, "split", "[8192x4096] -> 4 parts", ms_s, 0.0, nbytes, "hbm", peaks)]
+    r_c = _row(config, "concatenate", "4x[8192x1024] dim 1", ms_c, 0.0, nbytes, "hbm", peaks)
+    r_s = _row(config, "split", "[8192x4096] -> 4 parts", ms_s, 0.0, nbytes, "hbm", peaks)
+    r_c["_sample"] = {"kind": "concatenate", "parts": parts[0], "dim": 1, "got": K.concatenate(parts[0], 1),
+                      "scale": 1.0, "note": "whole tensor, bit-exact"}
+    r_s["_sample"] = {"kind": "split", "x": cats[0], "sections": [1024] * 4, "dim": 1,
+                      "got": K.split(cats[0], [1024] * 4, 1), "scale": 1.0, "note": "whole tensor, bit-exact"}
+    return [r_c, r_s]
 
 
 def bench_sd_block(config: str, peaks: Dict) -> Dict:
@@ -173,32 +234,42 @@ def bench_sd_block(config: str, peaks: Dict) -> Dict:
     tf = (gemm + attn) / (mean_ms * 1e-3) / 1e12
     row.update(tflops=round(tf, 1), frac_measured=round(tf / peaks["tflops_burst"], 3),
                frac_nominal=round(tf / NOMINAL_TFLOPS, 3))
+    res = module.run_with_tensors(ins, {"output_0": out}, graph_mode=True)
+    row["_sample"] = {"kind": "sd_block", "x": x, "context": context, "params": params, "got": res["output_0"],
+                      "scale": 1.0, "note": "whole block"}
     return row
 
 
-def run_suite(peaks: Dict) -> List[Dict]:
-    rows: List[Dict] = []
-    rows.append(bench_gemm("1", 256, 3072, 768, "fast_gelu", peaks))
+def run_suite(peaks: Dict, quick: bool = False):
+    """Yields one row per op of the benchmark configurations. quick=True shrinks the CPU-side samples (not the GPU
+    problems) so that the whole sweep, CPU checks included, stays within about a minute."""
+    sf = 2.5e11 if quick else 1.2e12
+    for r in _suite_rows(peaks, sf):
+        yield r
+
+
+def _suite_rows(peaks: Dict, sf: float):
+    yield bench_gemm("1", 256, 3072, 768, "fast_gelu", peaks)
     m2 = 64 * 384
-    rows.append(bench_gemm("2", m2, 2304, 768, "", peaks, permute=(384, 3, 12)))
-    rows.append(bench_attention("2", 64, 12, 384, 384, 64, peaks))
-    rows.append(bench_gemm("2", m2, 768, 768, "add", peaks, residual=True))
-    rows.append(bench_layernorm("2", m2, 768, 1e-12, peaks))
-    rows.append(bench_gemm("2", m2, 3072, 768, "fast_gelu", peaks))
-    rows.append(bench_gemm("2", m2, 768, 3072, "add", peaks, residual=True))
+    yield bench_gemm("2", m2, 2304, 768, "", peaks, permute=(384, 3, 12))
+    yield bench_attention("2", 64, 12, 384, 384, 64, peaks)
+    yield bench_gemm("2", m2, 768, 768, "add", peaks, residual=True)
+    yield bench_layernorm("2", m2, 768, 1e-12, peaks)
+    yield bench_gemm("2", m2, 3072, 768, "fast_gelu", peaks)
+    yield bench_gemm("2", m2, 768, 3072, "add", peaks, residual=True)
     for n in (768, 1024, 4096):
-        rows.append(bench_layernorm("3", 65536, n, 1e-5, peaks))
-    rows.append(bench_softmax("3", (512, 1024, 1024), peaks))
-    rows.extend(bench_concat_split("3", peaks))
-    rows.append(bench_attention("4", 2, 8, 4096, 4096, 40, peaks))
-    rows.append(bench_attention("4", 2, 8, 4096, 77, 40, peaks))
-    rows.append(bench_gemm("4", 8192, 320, 320, "", peaks))
-    rows.append(bench_gemm("4", 8192, 2560, 320, "", peaks))
-    rows.append(bench_gemm("4", 8192, 1280, 320, "mul", peaks, residual=True))
-    rows.append(bench_gemm("4", 8192, 320, 1280, "add", peaks, residual=True))
-    rows.append(bench_layernorm("4", 8192, 320, 1e-5, peaks))
-    rows.append(bench_sd_block("4", peaks))
-    rows.append(bench_bmm("5", 1024, 512, 512, 64, peaks))
+        yield bench_layernorm("3", 65536, n, 1e-5, peaks)
+    yield bench_softmax("3", (512, 1024, 1024), peaks)
+    yield from bench_concat_split("3", peaks)
+    yield bench_attention("4", 2, 8, 4096, 4096, 40, peaks)
+    yield bench_attention("4", 2, 8, 4096, 77, 40, peaks)
+    yield bench_gemm("4", 8192, 320, 320, "", peaks)
+    yield bench_gemm("4", 8192, 2560, 320, "", peaks)
+    yield bench_gemm("4", 8192, 1280, 320, "mul", peaks, residual=True)
+    yield bench_gemm("4", 8192, 320, 1280, "add", peaks, residual=True)
+    yield bench_layernorm("4", 8192, 320, 1e-5, peaks)
+    yield bench_sd_block("4", peaks)
+    yield bench_bmm("5", 1024, 512, 512, 64, peaks)
     for m in (1, 16, 128, 1024, 8192, 65536):  # the seconds-long cases last: they leave the GPU power-capped
-        rows.append(bench_gemm("5", m, 8192, 8192, "relu", peaks, w_scale=0.01))
-    return rows
+        yield bench_gemm("5", m, 8192, 8192, "relu", peaks, w_scale=0.01, sample_flops=sf)
+

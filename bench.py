@@ -28,7 +28,6 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 BATCH, SEQ, HIDDEN, HEADS, FFN = 64, 384, 768, 12, 3072
-GEMM_DRAM_TRAFFIC_PER_STEP = 551.8e6  # ncu: dram__bytes_read.sum + dram__bytes_write.sum over the 4 launches
 METRIC = "bert_base_layer_seqs_per_sec"
 UNIT = "seq/s"
 WORKLOAD = "BERT-base encoder layer, fp16, batch 64, seq 384, hidden 768, 12 heads x 64, FFN 3072 (benchmark config 2)"
@@ -189,9 +188,39 @@ def run_reference(args, rank: int, world: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+PREHEAT_MS = 300.0   # untimed graph replays before the first barrier: clocks idle at ~340 MHz when a box is leased
+LEAD_IN_STEPS = 5    # untimed steps right after the barrier, so the host runs ahead of the GPU in the timed steps
+
+
+def _gather_rows(dist, row):
+    """All ranks contribute one list of floats; every rank gets the [world, len] table."""
+    import torch
+
+    t = torch.tensor(row, device="cuda", dtype=torch.float64)
+    if dist is None:
+        return [t.tolist()]
+    out = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, t)
+    return [o.tolist() for o in out]
+
+
+def _load_gemm_traffic():
+    """DRAM bytes (read + write) of the four GEMM launches of one step, from the committed ncu summary."""
+    path = os.path.join(ROOT, "profiles", "gemm_tc_kernel_bert_layer.md")
+    try:
+        with open(path) as f:
+            for line in f:
+                if line.startswith("traffic_bytes_per_step:"):
+                    return float(line.split(":", 1)[1].split()[0]), "from_profile"
+    except OSError:
+        pass
+    return None, "no profile summary found"
+
+
 def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     import torch
 
+    from aitemplate_b200 import _lib
     from aitemplate_b200.compiler import compile_model
     from aitemplate_b200.testing import detect_target, workloads
 
@@ -200,6 +229,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     if world > 1:
         import torch.distributed as dist
 
+        # in-switch reduction is not needed for a barrier and an all-gather, and ranks here open each other's
+        # buffers for the N-split exchange: keep NCCL on plain peer transfers
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = _peaks()
     x_cpu, params = workloads.bert_layer_inputs(BATCH, SEQ, HIDDEN, FFN, seed=1334 + rank)
@@ -214,13 +246,24 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     out = torch.empty((BATCH, SEQ, HIDDEN), dtype=torch.float16, device="cuda")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # > 126 MB L2
     stream = torch.cuda.current_stream()
+    warmup = max(args.warmup, 3)
 
     def step(i: int, graph: bool = True):
         model.run_with_tensors({"hidden_states": xs[i % n_rot]}, {"output_0": out}, sync=False, graph_mode=graph)
 
-    for i in range(max(args.warmup, 3)):
+    for i in range(warmup):
         step(i)
     torch.cuda.synchronize()
+    launches_before = _lib.kernel_launch_count()
+    step(0, graph=False)  # one eager step: counts the kernels a step launches (a graph replay re-issues the same nodes)
+    torch.cuda.synchronize()
+    launches_per_step = _lib.kernel_launch_count() - launches_before
+    # preheat: raise the clocks and settle the power state before anything is timed
+    t_pre = time.perf_counter()
+    while (time.perf_counter() - t_pre) * 1000.0 < PREHEAT_MS:
+        for i in range(20):
+            step(i)
+        torch.cuda.synchronize()
 
     def barrier():
         if dist is not None:
@@ -230,23 +273,35 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     # ---- device-resident throughput: K steps, each bracketed by events, L2 flushed between steps
     sampler = ClockSampler(local_rank)
     barrier()
+    wall0 = time.perf_counter()
     sampler.start()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    for i in range(LEAD_IN_STEPS):
+        flush.zero_()
+        step(i)
     for i in range(args.steps):
         flush.zero_()
         starts[i].record(stream)
         step(i)
         ends[i].record(stream)
+    enqueue_s = time.perf_counter() - wall0
     barrier()
+    wall_s = time.perf_counter() - wall0
     clocks = sampler.stop()
-    step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    step_ms = sorted(s.elapsed_time(e) for s, e in zip(starts, ends))
     total_ms = sum(step_ms)
-    if dist is not None:
-        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+    med_ms = statistics.median(step_ms)
+    table = _gather_rows(dist, [total_ms, step_ms[0], med_ms, step_ms[int(0.9 * (len(step_ms) - 1))], step_ms[-1],
+                                wall_s * 1000.0, enqueue_s * 1000.0, clocks.get("sm_mhz") or 0.0,
+                                float(len(clocks.get("reasons", [])))])
+    slowest = max(range(world), key=lambda r: table[r][0])
+    total_ms = table[slowest][0]
     value = world * BATCH * args.steps / (total_ms / 1000.0)
+    per_rank = [{"rank": r, "sum_ms": round(t[0], 3), "step_ms_min": round(t[1], 4), "step_ms_median": round(t[2], 4),
+                 "step_ms_p90": round(t[3], 4), "step_ms_max": round(t[4], 4), "wall_ms_between_barriers": round(t[5], 2),
+                 "host_enqueue_ms": round(t[6], 2), "sm_mhz_median": t[7], "clock_reasons_seen": int(t[8])}
+                for r, t in enumerate(table)]
 
     # ---- end to end through the public API: every step copies its input from pinned host memory to the
     # device, runs Model.run_with_tensors and copies the output back to pinned host memory. The three
@@ -297,114 +352,239 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     e1.record(stream)
     barrier()
     e2e_ms = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_table = _gather_rows(dist, [e2e_ms])
+    e2e_ms = max(t[0] for t in e2e_table)
     y_pin = y_pins[(args.steps - 1) % NB]
     x_pin = x_pins[0]
+    h2d_bytes, d2h_bytes = x_pin.numel() * 2, y_pin.numel() * 2
     e2e_value = world * BATCH * args.steps / (e2e_ms / 1000.0)
     checksum = float(y_pin.float().abs().mean())
+    for r, t in enumerate(e2e_table):
+        per_rank[r]["e2e_ms_per_step"] = round(t[0] / args.steps, 4)
+        per_rank[r]["e2e_h2d_gbs"] = round(h2d_bytes * args.steps / (t[0] / 1000.0) / 1e9, 2)
+        per_rank[r]["e2e_d2h_gbs"] = round(d2h_bytes * args.steps / (t[0] / 1000.0) / 1e9, 2)
 
-    line = None
-    if rank == 0:
-        # ---- roofline of the dominant kernel (the tcgen05 GEMM, 4 launches per step): per-op CUDA-event
-        # times from the runtime's profiler (each op timed alone after an L2 flush)
-        prof_path = os.path.join(workdir, "profile.json")
-        model.profile_with_tensors({"hidden_states": xs[0]}, {"output_0": out}, 20, prof_path)
-        with open(prof_path) as f:
-            prof = json.load(f)
-        gemm_ms, gemm_fl, per_op = 0.0, 0.0, {}
-        for name, rec in prof.items():
-            per_op[name] = round(rec["ms_per_iter"] * 1000.0, 2)
-            if name.startswith("gemm_rcr"):
-                ins = rec["input_sizes"]
-                mm, kk = int(ins[0][0]), int(ins[0][1])
-                nn_ = int(ins[1][0])
-                gemm_fl += 2.0 * mm * nn_ * kk
-                gemm_ms += rec["ms_per_iter"]
-        achieved = gemm_fl / (gemm_ms / 1000.0) / 1e12 if gemm_ms > 0 else None
-        cpu_value, cores, runs = _cpu_layer_seqs_per_sec(8, 10.0, 6)
-        ms_per_step = total_ms / args.steps
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "l2": "256 MB flush between timed steps; inputs rotate over 4 buffers",
-                       "graph_mode": True, "sharding": f"{world} x batch {BATCH}, no collective"},
-            "layer_tflops": workloads.bert_layer_flops(BATCH, SEQ, HIDDEN, HEADS, FFN) / (ms_per_step / 1000.0) / 1e12,
-            "roofline": {"kernel": "gemm_tc_kernel (4 launches per step)", "bound": "tensor", "achieved": achieved,
-                         "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["tflops_burst"] if achieved else None,
-                         "peak_source": peaks["source"] + " burst (each kernel timed alone)",
-                         # DRAM read + write bytes of the four GEMM launches of one step, from the committed
-                         # ncu capture of this workload (profiles/gemm_tc_kernel_bert_layer.md); the algorithmic
-                         # bytes of the same four launches are 693.6e6.
-                         "traffic": GEMM_DRAM_TRAFFIC_PER_STEP, "traffic_unit": "bytes per step (4 launches)",
-                         "per_op_us": per_op},
-            "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
-                             "sample": f"8 of {BATCH} sequences x {runs} runs, fp32 torch oracle, all host threads"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_pin.numel() * 2,
-                    "d2h_bytes_per_step": y_pin.numel() * 2, "ms_per_step": e2e_ms / args.steps,
-                    "pipeline": "3 streams (upload / run / download), ring of 3 device buffers",
-                    "output_abs_mean": checksum},
-            "gpu_launches": 7 * args.steps,
-            "clocks": clocks,
-        }
-    model.close()
+    # ---- N-split variant of the large GEMM (weight rows split over the ranks, one exchange step), once, on a
+    # reduced M so that it fits the run: attached to the line so that every multi-GPU run carries it
+    nsplit = None
+    if world > 1:
+        try:
+            nsplit = nsplit_forms(dist, rank, world, m=8192, n=8192, k=8192, iters=3)
+        except Exception as e:  # never lose the headline line to the side measurement
+            nsplit = {"error": f"{type(e).__name__}: {e}"}
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
-    if line is not None:
-        print(json.dumps(line), flush=True)
+    if rank != 0:
+        model.close()
+        return
+
+    # ---- rank 0 alone from here on (the other ranks have left; nothing below is inside a timed region)
+    # roofline of the dominant kernel (the tcgen05 GEMM, 4 launches per step): per-op CUDA-event times from the
+    # runtime's profiler (each op timed alone after an L2 flush)
+    prof_path = os.path.join(workdir, "profile.json")
+    model.profile_with_tensors({"hidden_states": xs[0]}, {"output_0": out}, 20, prof_path)
+    with open(prof_path) as f:
+        prof = json.load(f)
+    gemm_ms, gemm_fl, per_op = 0.0, 0.0, {}
+    for name, rec in prof.items():
+        per_op[name] = round(rec["ms_per_iter"] * 1000.0, 2)
+        if name.startswith("gemm_rcr"):
+            ins = rec["input_sizes"]
+            mm, kk = int(ins[0][0]), int(ins[0][1])
+            nn_ = int(ins[1][0])
+            gemm_fl += 2.0 * mm * nn_ * kk
+            gemm_ms += rec["ms_per_iter"]
+    achieved = gemm_fl / (gemm_ms / 1000.0) / 1e12 if gemm_ms > 0 else None
+    # parity of THIS run's batch-64 output: three of its sequences against the CPU oracle
+    from oracle import reference_ops
+
+    model.run_with_tensors({"hidden_states": xs[0]}, {"output_0": out}, sync=True, graph_mode=True)
+    picks = [0, BATCH // 2 + 5, BATCH - 1]
+    want = reference_ops.bert_layer(x_cpu[picks], params, HEADS)
+    got = out[picks].float().cpu()
+    err = (got - want).abs()
+    parity = {"checked": f"sequences {picks} of the batch-{BATCH} graph-mode output vs the fp32 CPU oracle",
+              "max_abs_err": float(err.max()), "max_rel_err": float((err / want.abs().clamp_min(1e-2)).max()),
+              "tolerance": "atol = rtol = 2e-2 on the whole layer (1e-2 per op)",
+              "pass": bool((err <= 2e-2 + 2e-2 * want.abs()).all())}
+    cpu_value, cores, runs = _cpu_layer_seqs_per_sec(8, 10.0, 6)
+    ops_digest = None
+    if world == 1 and not args.no_ops:
+        try:
+            ops_digest = [compact_op_row(r) for r in ops_rows(peaks, quick=True)]
+        except Exception as e:
+            ops_digest = [{"error": f"{type(e).__name__}: {e}"}]
+    traffic, traffic_src = _load_gemm_traffic()
+    ms_per_step = total_ms / args.steps
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": "256 MB flush between timed steps; inputs rotate over 4 buffers",
+                   "graph_mode": True, "sharding": f"{world} x batch {BATCH}, no collective",
+                   "preheat_ms": PREHEAT_MS, "lead_in_steps": LEAD_IN_STEPS},
+        "ms_per_step_median_slowest_rank": table[slowest][2], "slowest_rank": slowest,
+        "layer_tflops": workloads.bert_layer_flops(BATCH, SEQ, HIDDEN, HEADS, FFN) / (ms_per_step / 1000.0) / 1e12,
+        "roofline": {"kernel": "gemm_tc_kernel (4 launches per step)", "bound": "tensor", "achieved": achieved,
+                     "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["tflops_burst"] if achieved else None,
+                     "frac_nominal": achieved / 2250.0 if achieved else None,
+                     "peak_source": peaks["source"] + " burst (each kernel timed alone)",
+                     "traffic": traffic, "traffic_source": traffic_src,
+                     "traffic_unit": "DRAM read + write bytes per step (4 launches); algorithmic bytes 693.6e6",
+                     "per_op_us": per_op},
+        "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"8 of {BATCH} sequences x {runs} runs, fp32 torch oracle, all host threads"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
+                "d2h_bytes_per_step": d2h_bytes, "ms_per_step": e2e_ms / args.steps,
+                "pipeline": "3 streams (upload / run / download), ring of 3 device buffers",
+                "output_abs_mean": checksum},
+        "parity": parity,
+        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches_per_step": launches_per_step,
+        "clocks": clocks,
+        "per_rank": per_rank,
+    }
+    if nsplit is not None:
+        line["nsplit"] = nsplit
+    if ops_digest is not None:
+        line["ops"] = ops_digest
+    model.close()
+    print(json.dumps(line), flush=True)
+
+
+def _check_sample(sample):
+    """Evaluates the CPU oracle on a row's sample. Returns (cpu_ms for the sample, max_abs_err, max_rel_err, pass).
+    Inputs are moved to the host first; only the oracle call is timed (median of up to 3 runs, 1 when slow)."""
+    import torch
+
+    from oracle import reference_ops as R
+
+    kind = sample["kind"]
+    cpu = lambda t: None if t is None else t.detach().float().cpu()  # noqa: E731
+    exact = False
+    atol = rtol = 1e-2
+    if kind == "gemm":
+        args = [cpu(sample[k]) for k in ("x", "w", "b", "d0")]
+        fn = lambda: R.gemm_rcr(*args, epilogue=sample["epilogue"])  # noqa: E731
+    elif kind == "gemm_permute":
+        args = [cpu(sample[k]) for k in ("x", "w", "b")]
+        fn = lambda: R.gemm_rcr_bias_permute(*args, sample["shape"], "20314")  # noqa: E731
+    elif kind == "bmm":
+        a, b = cpu(sample["a"]), cpu(sample["b"])
+        fn = lambda: R.bmm_rcr(a, b)  # noqa: E731
+    elif kind == "attention":
+        q, k, v = cpu(sample["q"]), cpu(sample["k"]), cpu(sample["v"])
+        fn = lambda: R.mem_eff_attention(q, k, v)  # noqa: E731
+    elif kind == "layernorm":
+        x, g, bb = cpu(sample["x"]), cpu(sample["gamma"]), cpu(sample["beta"])
+        fn = lambda: R.layernorm(x, g, bb, sample["eps"])  # noqa: E731
+        atol = rtol = 2e-3
+    elif kind == "softmax":
+        x = cpu(sample["x"])
+        fn = lambda: R.softmax(x, -1)  # noqa: E731
+    elif kind == "concatenate":
+        parts = [t.cpu() for t in sample["parts"]]
+        fn = lambda: R.concatenate(parts, sample["dim"])  # noqa: E731
+        exact = True
+    elif kind == "split":
+        x = sample["x"].cpu()
+        fn = lambda: R.split(x, sample["sections"], sample["dim"])  # noqa: E731
+        exact = True
+    elif kind == "sd_block":
+        fn = lambda: R.sd_transformer_block(sample["x"], sample["context"], sample["params"])  # noqa: E731
+        atol = rtol = 3e-2
+    else:
+        raise KeyError(kind)
+    times = []
+    want = None
+    for _ in range(3):
+        t0 = time.perf_counter()
+        want = fn()
+        times.append(time.perf_counter() - t0)
+        if sum(times) > 4.0:
+            break
+    cpu_ms = statistics.median(times) * 1000.0
+    got = sample["got"]
+    if exact:
+        if isinstance(want, (list, tuple)):
+            same = all(torch.equal(g.cpu(), w) for g, w in zip(got, want))
+        else:
+            same = torch.equal(got.cpu(), want)
+        return cpu_ms, 0.0 if same else float("nan"), 0.0 if same else float("nan"), bool(same), len(times)
+    g = got.detach().float().cpu()
+    err = (g - want).abs()
+    ok = bool((err <= atol + rtol * want.abs()).all()) and bool(torch.isfinite(g).all())
+    return cpu_ms, float(err.max()), float((err / want.abs().clamp_min(atol)).max()), ok, len(times)
+
+
+def ops_rows(peaks, quick: bool = False):
+    """Per-op rows of the benchmark configurations: GPU time and roofline fractions from the package's sweep, CPU
+    time (the oracle expression in fp32 on all host cores, on the row's sample, scaled to the whole op) and the
+    error of the kernel's output against that oracle."""
+    import torch
+
+    from aitemplate_b200.testing import benchmark_ops
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    for row in benchmark_ops.run_suite(peaks, quick=quick):
+        sample = row.pop("_sample", None)
+        row["gpu_ms"] = round(row.pop("us") / 1000.0, 5)
+        if sample is not None:
+            cpu_ms, abs_err, rel_err, ok, runs = _check_sample(sample)
+            row.update(cpu_ms=round(cpu_ms * sample["scale"], 2), cpu_cores=cores,
+                       cpu_sample=f"{sample['note']} x {runs} run(s), scaled x{sample['scale']:g}",
+                       max_abs_err=abs_err, max_rel_err=rel_err)
+            row["pass"] = ok
+        del sample
+        torch.cuda.empty_cache()
+        yield row
+
+
+def compact_op_row(row):
+    keep = ("config", "op", "shape", "gpu_ms", "cpu_ms", "cpu_cores", "tflops", "gbs", "frac_measured", "frac_nominal",
+            "cublas_linear_us", "cublas_bmm_us", "max_abs_err", "max_rel_err", "pass")
+    return {k: row[k] for k in keep if k in row}
 
 
 def run_ops_suite(args) -> None:
     """Per-op sweep over the benchmark configurations: one JSON line per op (not the driver's contract line)."""
     import torch
 
-    from aitemplate_b200.testing import benchmark_ops
-
     torch.cuda.set_device(0)
     peaks = _peaks()
-    for row in benchmark_ops.run_suite(peaks):
+    for row in ops_rows(peaks, quick=False):
         print(json.dumps(row), flush=True)
 
 
-def flops_of(m: int, n: int, k: int) -> float:
-    return 2.0 * m * n * k
-
-
-def run_nsplit_suite(args, rank: int, world: int, local_rank: int) -> None:
-    """benchmark config 5 at M = 65536, N = K = 8192 on `world` GPUs, two partitionings:
-    M-sharded (rows split, no collective) and N-split (weight rows split, X replicated, one NCCL
-    all-gather of the output column shards + re-layout). Rank 0 prints one JSON line."""
+def nsplit_forms(dist, rank: int, world: int, m: int, n: int, k: int, iters: int):
+    """gemm_rcr_bias_relu [m, k] x [n, k] on `world` GPUs in three partitionings; needs an initialised process group
+    when world > 1. Returns the result dict (same on every rank).
+      m_sharded      rows split, no collective;
+      n_split        weight rows split, X replicated, one NCCL all-gather of the output column shards + re-layout;
+      n_split_fused  the GEMM epilogue's TMA stores write every tile into all ranks' row-major Y (peer pointers)."""
     import torch
-    import torch.distributed as dist
 
     from aitemplate_b200 import kernels as K
     from aitemplate_b200 import sharding
 
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    m, n, k = 65536, 8192, 8192
     g = torch.Generator(device="cuda").manual_seed(500 + rank)
     w = (torch.randn((n, k), generator=g, device="cuda") * 0.01).half()
     b = (torch.randn((n,), generator=g, device="cuda") * 0.01).half()
     start, stop = sharding.shard_range(m, world, rank)
     x_rows = (torch.rand((stop - start, k), generator=g, device="cuda") * 2 - 1).half()
     y_rows = torch.empty((stop - start, n), dtype=torch.float16, device="cuda")
-    w_r, b_r = sharding.split_weight_columns(w, b, world, rank)
     x_full = (torch.rand((m, k), generator=g, device="cuda") * 2 - 1).half()
     if world > 1:  # the N-split forms need the same X, W and bias on every rank
         for t in (x_full, w, b):
             dist.broadcast(t, 0)
-        w_r, b_r = sharding.split_weight_columns(w, b, world, rank)
+    w_r, b_r = sharding.split_weight_columns(w, b, world, rank)
     y_cols = torch.empty((m, n // world), dtype=torch.float16, device="cuda")
     gathered = torch.empty((world * m, n // world), dtype=torch.float16, device="cuda")
 
-    def timed(fn, iters):
+    def timed(fn):
         for _ in range(2):
             fn()
         if world > 1:
@@ -423,43 +603,54 @@ def run_nsplit_suite(args, rank: int, world: int, local_rank: int) -> None:
             ms = float(t.item())
         return ms
 
-    iters = max(args.steps // 5, 3)
-    ms_m = timed(lambda: K.gemm_rcr(x_rows, w, b, epilogue="relu", out=y_rows), iters)
-    ms_gemm = timed(lambda: K.gemm_rcr(x_full, w_r, b_r, epilogue="relu", out=y_cols), iters)
+    ms_m = timed(lambda: K.gemm_rcr(x_rows, w, b, epilogue="relu", out=y_rows))
+    ms_gemm = timed(lambda: K.gemm_rcr(x_full, w_r, b_r, epilogue="relu", out=y_cols))
     if world > 1:
-        ms_gather = timed(lambda: sharding.gather_columns(y_cols, world, gathered=gathered), iters)
+        ms_gather = timed(lambda: sharding.gather_columns(y_cols, world, gathered=gathered))
         ms_total = timed(lambda: sharding.gather_columns(
-            K.gemm_rcr(x_full, w_r, b_r, epilogue="relu", out=y_cols), world, gathered=gathered), iters)
+            K.gemm_rcr(x_full, w_r, b_r, epilogue="relu", out=y_cols), world, gathered=gathered))
     else:
         ms_gather, ms_total = 0.0, ms_gemm
-    # fused form: the GEMM epilogue's TMA stores write every tile into all ranks' row-major Y (peer pointers),
-    # so there is no gather pass; a rank's timed kernel ends when its own remote stores have completed
     fused = None
+    flops = 2.0 * m * n * k
     if world > 1:
+        # a rank's timed kernel ends when its own remote stores have completed; no flag or spin between ranks
         ybuf = sharding.PeerBuffer(m, n, torch.float16, rank, world)
-        ms_fused = timed(lambda: sharding.gemm_rcr_nsplit_fused(x_full, w_r, b_r, ybuf, "relu"), iters)
+        ms_fused = timed(lambda: sharding.gemm_rcr_nsplit_fused(x_full, w_r, b_r, ybuf, "relu"))
         dist.barrier()
         torch.cuda.synchronize()
         want = sharding.gather_columns(K.gemm_rcr(x_full, w_r, b_r, epilogue="relu", out=y_cols), world,
                                        gathered=gathered)
         same = torch.tensor([1 if torch.equal(ybuf.local, want) else 0], device="cuda")
         dist.all_reduce(same, op=dist.ReduceOp.MIN)
-        fused = {"total_ms": ms_fused, "tflops_total": flops_of(m, n, k) / (ms_fused / 1e3) / 1e12,
+        fused = {"total_ms": ms_fused, "tflops_total": flops / (ms_fused / 1e3) / 1e12,
                  "remote_store_bytes_per_rank": (world - 1) * m * (n // world) * 2,
                  "collective": "none: epilogue TMA stores into peer memory over NVLink",
                  "matches_all_gather_bitwise": bool(same.item())}
         dist.barrier()
         ybuf.close()
-    flops = 2.0 * m * n * k
+    return {
+        "workload": f"gemm_rcr_bias_relu M={m} N={n} K={k} fp16", "n_gpus": world,
+        "m_sharded": {"ms": ms_m, "tflops_total": flops / (ms_m / 1e3) / 1e12, "collective": None},
+        "n_split": {"gemm_ms": ms_gemm, "all_gather_relayout_ms": ms_gather, "total_ms": ms_total,
+                    "tflops_total": flops / (ms_total / 1e3) / 1e12,
+                    "gathered_bytes_per_rank": (world - 1) * m * (n // world) * 2, "collective": "ncclAllGather"},
+        "n_split_fused": fused,
+        "matches_all_gather_bitwise": fused["matches_all_gather_bitwise"] if fused else None,
+    }
+
+
+def run_nsplit_suite(args, rank: int, world: int, local_rank: int) -> None:
+    """benchmark config 5 at M = 65536, N = K = 8192 on `world` GPUs (see nsplit_forms). Rank 0 prints one JSON line."""
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    res = nsplit_forms(dist if world > 1 else None, rank, world, 65536, 8192, 8192, max(args.steps // 5, 3))
     if rank == 0:
-        print(json.dumps({
-            "suite": "nsplit", "workload": "gemm_rcr_bias_relu M=65536 N=K=8192 fp16", "n_gpus": world,
-            "m_sharded": {"ms": ms_m, "tflops_total": flops / (ms_m / 1e3) / 1e12, "collective": None},
-            "n_split": {"gemm_ms": ms_gemm, "all_gather_relayout_ms": ms_gather, "total_ms": ms_total,
-                        "tflops_total": flops / (ms_total / 1e3) / 1e12,
-                        "gathered_bytes_per_rank": (world - 1) * m * (n // world) * 2, "collective": "ncclAllGather"},
-            "n_split_fused": fused,
-        }), flush=True)
+        print(json.dumps({"suite": "nsplit", **res}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -471,6 +662,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-ops", action="store_true",
+                    help="layer suite: leave the per-op digest (GPU time, CPU time, error per op) out of the line")
     ap.add_argument("--suite", choices=["layer", "ops", "nsplit"], default="layer",
                     help="layer: the contract benchmark (default); ops: per-op sweep; nsplit: config 5 on N GPUs")
     args = ap.parse_args()

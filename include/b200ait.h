@@ -39,6 +39,16 @@ int b200ait_version(void);
 /* Synchronises the device, then reads and clears the kernel status word (0 = clean). A non-zero
  * value means a bounded wait inside a kernel gave up and that kernel's output is invalid. */
 int b200ait_device_status(int* status_out);
+/* Number of kernels the library has launched in this process so far (a launch made during a stream
+ * capture counts once, at capture). No counterpart in the reference; used to report launch counts. */
+int b200ait_kernel_launch_count(int64_t* count_out);
+/* Exercises the bounded wait of the pipeline kernels: one CTA waits, with a 1 ms limit, on an mbarrier
+ * nobody arrives on, gives up and returns. out[0] = result of that wait (0 = gave up), out[1] = result of a
+ * later wait in the same CTA (0 = returned at once), out[2] = ns spent. Leaves code 5 in the status word
+ * for b200ait_device_status to report and clear. The reference has no device-side waits to bound
+ * (its kernels are single-pass CUTLASS launches); host-side it maps to DeviceCheckLastError,
+ * static/include/model.h:22-32. */
+int b200ait_selftest_bounded_wait(int64_t* out, void* stream);
 
 /* Generic GEMM: c[b] = epilogue(alpha * a[b] . b[b]^T + bias, d0, d1); a [batch, m, k] (row stride lda),
  * b [batch, n, k] (row stride ldb), c / d0 / d1 [batch, m, n] (row strides ldc / ldd). A batch stride
