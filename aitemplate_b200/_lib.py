@@ -74,6 +74,14 @@ def _signatures():
             c_int,
             [c_void_p] * 4 + [c_int64] * 3 + [c_int] * 3 + [c_float, c_int, POINTER(c_int32), POINTER(c_int32), c_int, c_void_p],
         ),
+        "b200ait_mem_eff_attention_strided": (
+            c_int,
+            [c_void_p] * 4 + [c_int64] * 3 + [c_int] * 3 + [I64P, I64P, I64P, c_float, c_int, c_int, c_void_p],
+        ),
+        "b200ait_flash_attention": (
+            c_int,
+            [c_void_p] * 5 + [c_int] * 4 + [c_float, c_float, c_int, c_int, c_int64, c_int, c_void_p],
+        ),
         "b200ait_layernorm": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_float, c_int64, c_int64, c_int, c_void_p]),
         "b200ait_softmax": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
         "b200ait_concatenate": (

@@ -4,7 +4,7 @@ Same signature and validation as the reference (python/aitemplate/compiler/compi
 where the reference renders C++ per op, runs nvcc and links `test.so`, this build lowers the graph to
 a *plan* for the prebuilt runtime in libb200ait.so:
 
-  toposort -> remove_no_ops -> mark_param_tensor -> fuse_mm_elementwise -> fuse_gemm_permute0213 -> split_to_views
+  toposort -> remove_no_ops -> mark_param_tensor -> fuse_mm_elementwise -> fuse_gemm_permute0213 -> fuse_permute_into_attention -> split_to_views
   -> fuse_split_strided -> fuse_strided_cat -> name_graph
   -> memory_planning -> write <workdir>/<test_name>/<dll_name>.plan (+ constants.bin) -> Model(plan)
 
@@ -26,6 +26,7 @@ from .model import Model
 from .transform import (
     fuse_mm_elementwise,
     fuse_gemm_permute0213,
+    fuse_permute_into_attention,
     fuse_split_strided,
     fuse_strided_cat,
     mark_param_tensor,
@@ -251,6 +252,7 @@ def compile_model(
     if do_optimize_graph:
         graph = fuse_mm_elementwise(graph, outputs)
         graph = fuse_gemm_permute0213(graph, outputs)
+        graph = fuse_permute_into_attention(graph, outputs)
         mark_param_tensor(graph)
         split_to_views(graph)
         fuse_split_strided(graph)

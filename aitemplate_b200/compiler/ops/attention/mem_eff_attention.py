@@ -59,5 +59,8 @@ class mem_eff_attention(Operator):
 
     def _lower(self) -> Dict[str, Any]:
         d = self._attrs["head_size"]
+        # input_layouts: set by fuse_permute_into_attention; "bshd" = the operand is stored [B, S, H, D] and read in place
+        layouts = self._attrs.get("input_layouts", ["bhsd"] * 3)
         return {"kernel": "mem_eff_attention", "operands": list(self._attrs["inputs"]),
-                "ints": [1 if self._attrs["causal"] else 0], "floats": [1.0 / math.sqrt(d) if d else 1.0]}
+                "ints": [1 if self._attrs["causal"] else 0] + [1 if l == "bshd" else 0 for l in layouts],
+                "floats": [1.0 / math.sqrt(d) if d else 1.0]}

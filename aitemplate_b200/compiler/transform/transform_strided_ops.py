@@ -204,3 +204,46 @@ def fuse_gemm_permute0213(sorted_graph: List[Tensor], outputs: List[Tensor]) -> 
             changed = True
             break
     return sorted_graph
+
+
+def fuse_permute_into_attention(sorted_graph: List[Tensor], outputs: List[Tensor]) -> List[Tensor]:
+    """permute (0, 2, 1, 3) -> mem_eff_attention becomes the attention alone: the kernel reads an operand stored
+    [B, S, H, D] in place through strided tensor maps (row stride H*D, head stride D), so the copy that only
+    reorders heads and rows disappears. This is the input-TensorAccessor side of the reference's strided-op fusion
+    (python/aitemplate/compiler/transform/transform_strided_ops.py:94-224; the reference's kernel takes q / k / v
+    strides, python/aitemplate/backend/cuda/attention/mem_eff_attention.py:160-171) applied to the pattern its
+    attention front ends emit (python/aitemplate/frontend/nn/attention.py:360-368: reshape [B, S, H, D] then
+    permute). Legal when the permute's output feeds nothing but that attention, is not a graph output, and the
+    head size is a multiple of 8 (the strided maps need 16-byte strides). Records `input_layouts` on the op:
+    "bshd" for a folded operand, "bhsd" otherwise. Returns the re-sorted graph."""
+    from ..ops.attention.mem_eff_attention import mem_eff_attention
+    from ..ops.tensor.tensor_ops import _permute_base
+    from .toposort import toposort
+
+    changed = False
+    for op in sorted_ops(sorted_graph):
+        if not isinstance(op, mem_eff_attention):
+            continue
+        layouts = list(op._attrs.get("input_layouts", ["bhsd"] * 3))
+        for i, t in enumerate(list(op._attrs["inputs"][:3])):
+            if layouts[i] != "bhsd":
+                continue
+            src = list(t._attrs["src_ops"])
+            if len(src) != 1 or not isinstance(src[0], _permute_base) or list(src[0]._attrs["dims"]) != [0, 2, 1, 3]:
+                continue
+            if t._attrs["is_output"] or set(t._attrs["dst_ops"]) != {op}:
+                continue
+            if sum(1 for y in op._attrs["inputs"] if y is t) != 1:
+                continue
+            head = t._attrs["shape"][3]
+            if not isinstance(head, IntImm) or head.value() % 8 != 0 or head.value() > 128:
+                continue
+            x = src[0]._attrs["inputs"][0]  # stored [B, S, H, D]
+            op.replace_input_tensor(t, x)
+            x._attrs["dst_ops"].add(op)
+            t._attrs["dst_ops"].discard(op)
+            op._attrs["input_accessors"][i] = type(op._attrs["input_accessors"][i])(x)
+            layouts[i] = "bshd"
+            changed = True
+        op._attrs["input_layouts"] = layouts
+    return toposort(outputs) if changed else sorted_graph

@@ -12,10 +12,14 @@
 //   warp 0      TMA producer: the item's Q tile, then K/V blocks of kBlockN keys into a 3-stage ring;
 //               the next item's Q streams in while the current item drains
 //   warp 1      MMA issuer:   S = Q K^T  (tcgen05.mma, fp32 accumulator in TMEM)
-//                             T = P V    (P from shared memory, V as an MN-major B operand)
-//               S, P and T are double-buffered: the MMAs of key block j+1 overlap the softmax of block j
+//                             O += P V   (P from shared memory, V as an MN-major B operand); O stays in TMEM for
+//                             the whole item and every key block accumulates into it
+//               S and P are double-buffered: the MMAs of key block j+1 overlap the softmax of block j; O is
+//               double-buffered across items
 //   warps 2-5   one thread per query row: TMEM -> registers, mask (skipped for full, unmasked blocks),
-//               running max / sum, exp2, P -> swizzled shared memory, O (registers) = O * alpha + T
+//               reference max / row sum, exp2, P -> swizzled shared memory; O is touched only when a row's
+//               maximum outgrows the reference by more than 2^8 (then O and the row sum are rescaled in
+//               TMEM) and once at the end of the item (O / row sum -> global memory)
 // Two CTAs share an SM (head dim <= 64) so one CTA's softmax also overlaps the other's MMAs.
 // Head dims that are not a multiple of 8, or larger than 128, run on a CUDA-core kernel.
 #include <cuda.h>
@@ -43,14 +47,29 @@ struct AttnParams {
   int num_items;  // B * H * q_blocks work items of 128 query rows
   float scale_log2;  // softmax scale * log2(e)
   int causal;
-  void* out;  // [B, Sq, H, Dv]
+  void* out;  // [B, Sq, H, Dv], or [total, H, Dv] with cu_seqlens
   int* status;
+  // Variable-length ("packed") mode: sequence b owns rows cu_seqlens[b] .. cu_seqlens[b+1] of q, k, v and out, and
+  // Sq = Skv = the longest sequence. Null: every sequence has Sq query and Skv key rows and its own batch coordinate.
+  const int* cu_seqlens;
+  // coordinate order of each tensor map: 0 = (channel, row, head, batch), 1 = (channel, head, row, batch); the host
+  // picks whichever keeps the map's strides ascending
+  int q_order, k_order, v_order;
+};
+
+// One operand (q, k or v) as the kernel addresses it: element strides of a [batch, head, row, channel] view with
+// unit channel stride. [B, H, S, D] contiguous is {D, S*D, H*S*D}; the q part of a packed [total, 3, H, D] tensor
+// is {3*H*D, D, -} with a single batch; a [B, S, H, D] tensor read in place is {H*D, D, S*H*D}.
+struct AttnOperand {
+  const void* ptr;
+  long long row_stride, head_stride, batch_stride;
 };
 
 constexpr int kAttnThreads = 192;
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 64;     // keys per block
 constexpr int kKvStages = 3;    // K/V ring: blocks j, j+1, j+2 are in flight
+constexpr float kRescaleLog2 = 8.f;  // a row's reference maximum may lag its true maximum by this much (log2 units)
 
 template <int DCH>
 struct AttnCfg {
@@ -60,19 +79,25 @@ struct AttnCfg {
   static constexpr int kDataBytes = kQBytes + kKvStages * 2 * kKBytes + 2 * kPBytes;
   // the dynamic shared-memory window is declared 1024-byte aligned, so no slack is reserved:
   // two CTAs of the 64-wide configuration (96 KB each) must fit one SM
-  static constexpr int kSmemBytes = kDataBytes + 128;
-  static constexpr int kTWidth = DCH * 64;                       // columns of one T = P V accumulator
-  static constexpr int kTmemCols = (DCH == 1) ? 256 : 512;       // S x2 (64 each) then T x2
+  static constexpr int kBarrierBytes = 256;  // 19 mbarriers + the TMEM slot + the abort flag (160 bytes), padded
+  static constexpr int kSmemBytes = kDataBytes + kBarrierBytes;
+  static constexpr int kTWidth = DCH * 64;                       // columns of one O accumulator
+  static constexpr int kTmemCols = (DCH == 1) ? 256 : 512;       // S x2 (64 each) then O x2 (item parity)
 };
 
 // Persistent CTAs: each walks work items (one item = 128 query rows of one (batch, head)) with stride
 // gridDim.x, so barrier set-up, TMEM allocation and the load latency of the first tiles are paid once
 // and the next item's Q / K / V stream in while the current item drains.
-// Pipeline (key blocks numbered globally g = 0, 1, .. across items; everything double-buffered on g & 1):
-//   MMA warp:      S(0), S(1); then for each j: wait P(j) -> T(j) = P(j) V(j) -> S(j+2)
-//   softmax warps: wait S(j) -> max / exp2 / row sum -> P(j) -> signal; then fold T(j-1) into O
-// so the tensor core computes S(j+1), S(j+2) and T(j-1) while the softmax threads work on block j,
-// and the softmax threads never wait for an MMA that was not issued a whole block earlier.
+// Pipeline (key blocks numbered globally g = 0, 1, .. across items; S and P double-buffered on g & 1, O on the
+// item's parity):
+//   MMA warp:      S(0), S(1); then for each j: wait P(j) -> O += P(j) V(j) -> S(j+2)
+//   softmax warps: wait S(j) -> max / exp2 / row sum -> P(j) -> signal; at the item's end O / row sum -> global
+// so the tensor core computes S(j+1), S(j+2) and P(j-1) V(j-1) while the softmax threads work on block j.
+// The softmax is "lazy" about the running maximum: a row keeps a reference maximum m_ref and evaluates
+// p = exp2(s * scale - m_ref); m_ref is raised (and O and the row sum rescaled by exp2(m_ref_old - m_ref_new))
+// only when the block's maximum exceeds it by more than kRescaleLog2, so p never exceeds 2^kRescaleLog2 and the
+// final O / l is the same quotient the reference forms with the exact running maximum
+// (attention_scaling_coefs_updater.h:85-165), up to the rounding of P at a different power-of-two-ish scale.
 // NOMASK: no causal mask and a key length that is a multiple of the block: every key block is "plain", and the
 // kernel is compiled without the masked softmax body (the lean variant is measurably faster than a run-time test).
 template <int DCH, bool BF16, bool NOMASK>
@@ -93,21 +118,56 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
   uint64_t* kv_empty = kv_full + kKvStages;
   uint64_t* s_full = kv_empty + kKvStages;  // [2]
   uint64_t* p_full = s_full + 2;            // [2]
-  uint64_t* t_full = p_full + 2;            // [2]
-  uint64_t* drain_bar = t_full + 2;
+  uint64_t* pv_done = p_full + 2;           // [2] P(g) V(g) has been accumulated into O (per key block, g & 1)
+  uint64_t* o_full = pv_done + 2;           // [2] every P V of the item has completed (item parity)
+  uint64_t* o_empty = o_full + 2;           // [2] the softmax threads have read the item's O out of TMEM
+  uint64_t* drain_bar = o_empty + 2;
   uint64_t* q_empty = drain_bar + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  static_assert((1 + 2 * kKvStages + 2 * 5 + 2) * 8 + 8 <= Cfg::kBarrierBytes, "barrier block overflows its shared memory");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // work item -> (batch*head index, first query row, visible key count, key blocks)
-  auto decode_item = [&](int item, int& bh, int& q0, int& kv_len, int& n_blocks) {
+  // work item -> where its rows live and how many key blocks it walks. n_blocks == 0 (a query tile past the end of
+  // a short sequence in packed mode) means the item is skipped by every role alike.
+  struct Item {
+    int h, b4;      // head and batch coordinates of the tensor maps
+    int row0;       // first row of the sequence in the maps' row dimension (0 unless packed)
+    int q0;         // first query row of the tile inside its sequence
+    int q_len;      // query rows of the sequence
+    int kv_len;     // keys visible to this tile
+    int n_blocks;
+    long long out_row0;  // first output row of the sequence
+  };
+  auto decode_item = [&](int item) {
+    Item w;
     const int q_blk = item % p.q_blocks;
-    bh = item / p.q_blocks;
-    q0 = q_blk * kBlockM;
-    kv_len = p.Skv;
-    if (!NOMASK && p.causal) kv_len = min(kv_len, q0 + kBlockM);
-    n_blocks = (kv_len + kBlockN - 1) / kBlockN;
+    const int bh = item / p.q_blocks;
+    const int b = bh / p.H;
+    w.h = bh - b * p.H;
+    w.q0 = q_blk * kBlockM;
+    if (p.cu_seqlens) {
+      const int lo = __ldg(p.cu_seqlens + b), hi = __ldg(p.cu_seqlens + b + 1);
+      w.b4 = 0;
+      w.row0 = lo;
+      w.q_len = w.kv_len = max(hi - lo, 0);
+      w.out_row0 = lo;
+    } else {
+      w.b4 = b;
+      w.row0 = 0;
+      w.q_len = p.Sq;
+      w.kv_len = p.Skv;
+      w.out_row0 = static_cast<long long>(b) * p.Sq;
+    }
+    if (!NOMASK && p.causal) w.kv_len = min(w.kv_len, w.q0 + kBlockM);
+    w.n_blocks = (w.q0 < w.q_len) ? (w.kv_len + kBlockN - 1) / kBlockN : 0;
+    return w;
+  };
+  auto load_rows = [&](void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int row, const Item& w, int order) {
+    if (order == 0)
+      tma_load_4d(dst, map, bar, c0, row, w.h, w.b4);
+    else
+      tma_load_4d(dst, map, bar, c0, w.h, row, w.b4);
   };
   const int dsteps = (p.D + 15) / 16;  // k-steps of Q K^T
 
@@ -120,7 +180,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 128);
-      mbar_init(&t_full[i], 1);
+      mbar_init(&pv_done[i], 1);
+      mbar_init(&o_full[i], 1);
+      mbar_init(&o_empty[i], 128);
     }
     mbar_init(drain_bar, 1);
     mbar_init(q_empty, 1);
@@ -140,23 +202,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base;        // S(j) at + (j & 1) * 64
-  const uint32_t tmem_t = tmem_base + 128;  // T(j) at + (j & 1) * kTWidth
+  const uint32_t tmem_o = tmem_base + 128;  // O of item it at + (it & 1) * kTWidth
 
   if (warp == 0) {
     if (lane == 0) {
       bool ok = true;
       int g = 0;  // global key-block counter (K/V ring position)
       int it = 0;
-      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++it) {
-        int bh, q0, kv_len, n_blocks;
-        decode_item(item, bh, q0, kv_len, n_blocks);
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        const Item w = decode_item(item);
+        if (w.n_blocks == 0) continue;
         // the Q tile is free once the previous item's last S = Q K^T has completed
         ok = mbar_wait(q_empty, (it & 1) ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
         if (!ok) break;
         mbar_arrive_expect_tx(q_full, Cfg::kQBytes);
 #pragma unroll
-        for (int c = 0; c < DCH; ++c) tma_load_3d(sQ + c * kBlockM * 128, &tma_q, q_full, c * 64, q0, bh);
-        for (int j = 0; j < n_blocks; ++j, ++g) {
+        for (int c = 0; c < DCH; ++c) load_rows(sQ + c * kBlockM * 128, &tma_q, q_full, c * 64, w.row0 + w.q0, w, p.q_order);
+        for (int j = 0; j < w.n_blocks; ++j, ++g) {
           const int st = g % kKvStages;
           const uint32_t ph = (g / kKvStages) & 1;
           ok = mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
@@ -166,10 +228,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
           mbar_arrive_expect_tx(&kv_full[st], 2 * Cfg::kKBytes);
 #pragma unroll
           for (int c = 0; c < DCH; ++c) {
-            tma_load_3d(sK + c * kBlockN * 128, &tma_k, &kv_full[st], c * 64, j * kBlockN, bh);
-            tma_load_3d(sV + c * kBlockN * 128, &tma_v, &kv_full[st], c * 64, j * kBlockN, bh);
+            load_rows(sK + c * kBlockN * 128, &tma_k, &kv_full[st], c * 64, w.row0 + j * kBlockN, w, p.k_order);
+            load_rows(sV + c * kBlockN * 128, &tma_v, &kv_full[st], c * 64, w.row0 + j * kBlockN, w, p.v_order);
           }
         }
+        ++it;
       }
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();
@@ -201,13 +264,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
       };
       int gb = 0;  // global index of the item's first key block
       int it = 0;
-      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++it) {
-        int bh, q0, kv_len, n_blocks;
-        decode_item(item, bh, q0, kv_len, n_blocks);
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        const Item w = decode_item(item);
+        const int n_blocks = w.n_blocks;
+        if (n_blocks == 0) continue;
         ok = mbar_wait(q_full, it & 1, abort_flag, p.status, kDevWaitFullTimeout);
         if (ok) ok = issue_s(gb);
         if (ok && n_blocks > 1) ok = issue_s(gb + 1);
         if (ok && n_blocks <= 2) umma_commit(q_empty);  // every S of this item has been issued
+        // this item's O buffer was last used by item it - 2: its rows must have been read out
+        if (ok) ok = mbar_wait(&o_empty[it & 1], ((it >> 1) & 1) ^ 1u, abort_flag, p.status, kDevWaitAccEmptyTimeout);
+        const uint32_t o_addr = tmem_o + static_cast<uint32_t>((it & 1) * Cfg::kTWidth);
         for (int j = 0; ok && j < n_blocks; ++j) {
           const int g = gb + j;
           ok = mbar_wait(&p_full[g & 1], (g >> 1) & 1, abort_flag, p.status, kDevWaitOtherTimeout);
@@ -222,16 +289,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
             // V block rows are keys (128 B each): 16 keys per step = 2048 B; 64-wide d chunks are
             // kBlockN*128 B apart (leading byte offset), 8-key groups 1024 B apart (stride byte offset)
             const uint64_t bdesc = umma_smem_desc_sw128(v_addr + k * 2048, kBlockN * 128, 1024);
-            umma_f16_ss(tmem_t + static_cast<uint32_t>((g & 1) * Cfg::kTWidth), adesc, bdesc, idesc_t, k != 0 ? 1u : 0u);
+            umma_f16_ss(o_addr, adesc, bdesc, idesc_t, (j != 0 || k != 0) ? 1u : 0u);
           }
-          umma_commit(&t_full[g & 1]);
+          umma_commit(&pv_done[g & 1]);
           umma_commit(&kv_empty[st]);
+          if (j + 1 == n_blocks) umma_commit(&o_full[it & 1]);
           if (j + 2 < n_blocks) {
             ok = issue_s(g + 2);
             if (ok && j + 3 == n_blocks) umma_commit(q_empty);
           }
         }
         gb += n_blocks;
+        ++it;
       }
       if (!ok) {
         umma_commit(drain_bar);
@@ -247,143 +316,168 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;  // row inside the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    float o[DCH * 64];
     bool ok = true;
-    // O = O * alpha + T(g)
-    auto fold_t = [&](int g, float alpha) -> bool {
-      if (!mbar_wait(&t_full[g & 1], (g >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout)) return false;
-      tc_fence_after();
-      const uint32_t t_addr = tmem_t + lane_addr + static_cast<uint32_t>((g & 1) * Cfg::kTWidth);
-#pragma unroll
-      for (int c = 0; c < DCH * 2; ++c) {
-        if (c * 32 < p.Dv) {  // warp-uniform
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(t_addr + c * 32, v);
-          tmem_ld_wait();
-          const uint64_t alpha2 = pack2(alpha, alpha);
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const uint64_t r2 = fma2(pack2(o[c * 32 + i], o[c * 32 + i + 1]), alpha2,
-                                     pack2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
-            unpack2(r2, o[c * 32 + i], o[c * 32 + i + 1]);
-          }
-        }
-      }
-      tc_fence_before();
-      return true;
-    };
     int gb = 0;  // global index of the item's first key block
+    int it = 0;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
-      int bh, q0, kv_len, n_blocks;
-      decode_item(item, bh, q0, kv_len, n_blocks);
-      const int q_idx = q0 + r;
-#pragma unroll
-      for (int i = 0; i < DCH * 64; ++i) o[i] = 0.f;
-      float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+      const Item w = decode_item(item);
+      const int n_blocks = w.n_blocks, kv_len = w.kv_len;
+      if (n_blocks == 0) continue;
+      const int q_idx = w.q0 + r;
+      const uint32_t o_addr = tmem_o + lane_addr + static_cast<uint32_t>((it & 1) * Cfg::kTWidth);
+      float m_ref = -INFINITY, l_run = 0.f;
       for (int j = 0; ok && j < n_blocks; ++j) {
         const int g = gb + j;
         ok = mbar_wait(&s_full[g & 1], (g >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout);
         if (!ok) break;
         tc_fence_after();
         const uint32_t s_addr = tmem_s + lane_addr + static_cast<uint32_t>((g & 1) * kBlockN);
-      const int key0 = j * kBlockN;
-      int limit = kv_len - key0;  // keys [0, limit) of this block are visible to this row
-      if (!NOMASK && p.causal) limit = min(limit, q_idx - key0 + 1);
-      // A key block is "plain" when every key of it is visible to every row of this warp: then both
-      // passes run without per-element masks (only the last block of a ragged or causal sequence
-      // needs them).
-      const bool plain = NOMASK || __reduce_min_sync(0xffffffffu, limit) >= kBlockN;
-      uint32_t s0[32], s1[32];
-      tmem_ld_32x32b_x32(s_addr, s0);
-      tmem_ld_32x32b_x32(s_addr + 32, s1);
-      tmem_ld_wait();
-      uint8_t* row_base = sP + (g & 1) * Cfg::kPBytes + r * 128;
-      float alpha, m_new, l0 = 0.f, l1 = 0.f;
-      // One body, compiled twice: kPlain drops every per-element mask.
-      auto softmax_block = [&](auto plain_tag) {
-        constexpr bool kPlain = decltype(plain_tag)::value;
-        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+        const int key0 = j * kBlockN;
+        int limit = kv_len - key0;  // keys [0, limit) of this block are visible to this row
+        if (!NOMASK && p.causal) limit = min(limit, q_idx - key0 + 1);
+        // A key block is "plain" when every key of it is visible to every row of this warp: then both
+        // passes run without per-element masks (only the last block of a ragged or causal sequence
+        // needs them).
+        const bool plain = NOMASK || __reduce_min_sync(0xffffffffu, limit) >= kBlockN;
+        uint32_t s0[32], s1[32];
+        tmem_ld_32x32b_x32(s_addr, s0);
+        tmem_ld_32x32b_x32(s_addr + 32, s1);
+        tmem_ld_wait();
+        uint8_t* row_base = sP + (g & 1) * Cfg::kPBytes + r * 128;
+        float l0 = 0.f, l1 = 0.f;
+        // One body, compiled twice: kPlain drops every per-element mask.
+        auto softmax_block = [&](auto plain_tag) {
+          constexpr bool kPlain = decltype(plain_tag)::value;
+          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float a0 = __uint_as_float(s0[i]), a1 = __uint_as_float(s0[i + 1]);
-          const float b0 = __uint_as_float(s1[i]), b1 = __uint_as_float(s1[i + 1]);
-          if constexpr (kPlain) {
-            m0 = max3(m0, a0, a1);
-            m2 = max3(m2, b0, b1);
-          } else {
-            m0 = fmaxf(m0, (i < limit) ? a0 : -INFINITY);
-            m1 = fmaxf(m1, (i + 1 < limit) ? a1 : -INFINITY);
-            m2 = fmaxf(m2, (32 + i < limit) ? b0 : -INFINITY);
-            m3 = fmaxf(m3, (33 + i < limit) ? b1 : -INFINITY);
-          }
-        }
-        const float m_blk = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-        m_new = fmaxf(m_run, m_blk * p.scale_log2);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        alpha = exp2f(m_run - m_use);
-        // p = exp2(s * scale - m), row sum, P -> swizzled shared memory (16-byte unit u of row r sits
-        // at unit u ^ (r & 7))
-        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
-        uint64_t lsum2 = pack2(0.f, 0.f);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint32_t(&sv)[32] = h == 0 ? s0 : s1;
-          uint32_t packed[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0, x1;
-            unpack2(fma2(pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), scale2, negm2), x0, x1);
-            float p0 = exp2f(x0);
-            float p1 = exp2f(x1);
-            if (!kPlain) {
-              p0 = (h * 32 + i < limit) ? p0 : 0.f;
-              p1 = (h * 32 + i + 1 < limit) ? p1 : 0.f;
+          for (int i = 0; i < 32; i += 4) {
+            const float a0 = __uint_as_float(s0[i]), a1 = __uint_as_float(s0[i + 1]);
+            const float a2 = __uint_as_float(s0[i + 2]), a3 = __uint_as_float(s0[i + 3]);
+            const float b0 = __uint_as_float(s1[i]), b1 = __uint_as_float(s1[i + 1]);
+            const float b2 = __uint_as_float(s1[i + 2]), b3 = __uint_as_float(s1[i + 3]);
+            if constexpr (kPlain) {
+              m0 = max3(m0, a0, a1);
+              m1 = max3(m1, a2, a3);
+              m2 = max3(m2, b0, b1);
+              m3 = max3(m3, b2, b3);
+            } else {
+              m0 = max3(m0, (i < limit) ? a0 : -INFINITY, (i + 1 < limit) ? a1 : -INFINITY);
+              m1 = max3(m1, (i + 2 < limit) ? a2 : -INFINITY, (i + 3 < limit) ? a3 : -INFINITY);
+              m2 = max3(m2, (32 + i < limit) ? b0 : -INFINITY, (33 + i < limit) ? b1 : -INFINITY);
+              m3 = max3(m3, (34 + i < limit) ? b2 : -INFINITY, (35 + i < limit) ? b3 : -INFINITY);
             }
-            lsum2 = add2(lsum2, pack2(p0, p1));
-            packed[i >> 1] = E::from_float2(p0, p1);
           }
+          const float m_blk = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scale_log2;
+          // Raise the reference maximum only when some row of this warp outgrew it by more than the slack
+          // (always on an item's first block, where nothing has been accumulated yet). The TMEM accesses of
+          // the rescale are warp-wide, so the decision is too; rows that did not move get alpha = 1.
+          if (__any_sync(0xffffffffu, m_blk > m_ref + kRescaleLog2)) {
+            const float m_new = fmaxf(m_ref, m_blk);
+            if (j > 0) {
+              // O holds blocks 0 .. j-1 once P(j-1) V(j-1) is done; P(j) V(j) cannot start before this
+              // thread's arrival on p_full below
+              if (!mbar_wait(&pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout)) {
+                ok = false;
+              } else {
+                tc_fence_after();
+                const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_ref - m_new);  // m_ref = -inf: O is 0 anyway
+                const uint64_t alpha2 = pack2(alpha, alpha);
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int unit = (h * 4 + u) ^ (r & 7);
-            *reinterpret_cast<uint4*>(row_base + unit * 16) =
-                make_uint4(packed[u * 4], packed[u * 4 + 1], packed[u * 4 + 2], packed[u * 4 + 3]);
+                for (int c = 0; c < DCH * 4; ++c) {
+                  if (c * 16 < p.Dv) {  // warp-uniform
+                    uint32_t v[16];
+                    tmem_ld_32x32b_x16(o_addr + c * 16, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                      float x0, x1;
+                      unpack2(mul2(pack2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), alpha2), x0, x1);
+                      v[i] = __float_as_uint(x0);
+                      v[i + 1] = __float_as_uint(x1);
+                    }
+                    tmem_st_32x32b_x16(o_addr + c * 16, v);
+                  }
+                }
+                tmem_st_wait();
+                l_run *= alpha;
+              }
+            }
+            m_ref = m_new;
           }
-        }
-        unpack2(lsum2, l0, l1);
-      };
-      if constexpr (NOMASK) {
-        softmax_block(std::true_type{});
-      } else {
-        if (plain)
+          const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+          // p = exp2(s * scale - m_ref), row sum, P -> swizzled shared memory (16-byte unit u of row r sits
+          // at unit u ^ (r & 7))
+          const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
+          uint64_t lsum2 = pack2(0.f, 0.f);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t(&sv)[32] = h == 0 ? s0 : s1;
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float x0, x1;
+              unpack2(fma2(pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), scale2, negm2), x0, x1);
+              float p0 = exp2f(x0);
+              float p1 = exp2f(x1);
+              if (!kPlain) {
+                p0 = (h * 32 + i < limit) ? p0 : 0.f;
+                p1 = (h * 32 + i + 1 < limit) ? p1 : 0.f;
+              }
+              lsum2 = add2(lsum2, pack2(p0, p1));
+              packed[i >> 1] = E::from_float2(p0, p1);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int unit = (h * 4 + u) ^ (r & 7);
+              *reinterpret_cast<uint4*>(row_base + unit * 16) =
+                  make_uint4(packed[u * 4], packed[u * 4 + 1], packed[u * 4 + 2], packed[u * 4 + 3]);
+            }
+          }
+          unpack2(lsum2, l0, l1);
+        };
+        if constexpr (NOMASK) {
           softmax_block(std::true_type{});
-        else
-          softmax_block(std::false_type{});
+        } else {
+          if (plain)
+            softmax_block(std::true_type{});
+          else
+            softmax_block(std::false_type{});
+        }
+        l_run += l0 + l1;
+        tc_fence_before();
+        fence_proxy_async_smem();
+        mbar_arrive(&p_full[g & 1]);
       }
-      l_run = l_run * alpha + (l0 + l1);
-      m_run = m_new;
-      tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(&p_full[g & 1]);
-      // fold the previous block's P V into O while the tensor core works on this block's
-        if (j > 0) ok = fold_t(g - 1, alpha_prev);
-        alpha_prev = alpha;
-      }
-      if (ok) ok = fold_t(gb + n_blocks - 1, alpha_prev);
       gb += n_blocks;
-      if (ok && q_idx < p.Sq) {
+      // the item's O is complete once its last P V has been accumulated
+      if (ok) ok = mbar_wait(&o_full[it & 1], (it >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout);
+      if (ok) {
+        tc_fence_after();
         const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
-        const int b = bh / p.H, h = bh - b * p.H;
-        T* out = static_cast<T*>(p.out) + ((static_cast<long long>(b) * p.Sq + q_idx) * p.H + h) * p.Dv;
+        T* out = static_cast<T*>(p.out) + ((w.out_row0 + q_idx) * p.H + w.h) * p.Dv;
 #pragma unroll
-        for (int c = 0; c < DCH * 8; ++c) {
-          if (c * 8 < p.Dv) {
-            float f[8];
+        for (int c = 0; c < DCH * 2; ++c) {
+          if (c * 32 < p.Dv) {  // warp-uniform
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(o_addr + c * 32, v);
+            tmem_ld_wait();
+            if (q_idx < w.q_len) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = o[c * 8 + i] * inv;
-            *reinterpret_cast<uint4*>(out + c * 8) = pack8<BF16>(f);
+              for (int u = 0; u < 4; ++u) {
+                if (c * 32 + u * 8 < p.Dv) {
+                  float f[8];
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[u * 8 + i]) * inv;
+                  *reinterpret_cast<uint4*>(out + c * 32 + u * 8) = pack8<BF16>(f);
+                }
+              }
+            }
           }
         }
+        tc_fence_before();
+        mbar_arrive(&o_empty[it & 1]);
       }
+      ++it;
     }
   }
 
@@ -466,15 +560,25 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(const void* q_, con
   }
 }
 
-// [BH, S, D] map, box [1, box_rows, 64], 128-byte swizzle; a box wider than D zero-fills
-static CUtensorMap make_attn_map(const void* base, bool bf16, int d, int s, long long bh, int box_rows) {
+// 4-D map over one operand with the operand's element strides, 128-byte swizzle, box = 64 channels x box_rows rows
+// of one head of one batch; a box wider than D, or reaching past the last row, zero-fills. The row and head
+// dimensions are emitted in ascending-stride order: order 0 = (channel, row, head, batch), 1 = (channel, head, row, batch).
+static int attn_map_order(const AttnOperand& op) { return op.head_stride < op.row_stride ? 1 : 0; }
+static CUtensorMap make_attn_map(const AttnOperand& op, bool bf16, int d, long long rows, int heads, int batches,
+                                 int box_rows) {
   CUtensorMap m;
-  cuuint64_t dims[3] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(s), static_cast<cuuint64_t>(bh)};
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(d) * 2, static_cast<cuuint64_t>(d) * s * 2};
-  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = get_encode_fn()(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                               const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const int order = attn_map_order(op);
+  const cuuint64_t row_dim = static_cast<cuuint64_t>(rows), head_dim = static_cast<cuuint64_t>(heads);
+  const cuuint64_t row_str = static_cast<cuuint64_t>(op.row_stride) * 2, head_str = static_cast<cuuint64_t>(op.head_stride) * 2;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), order ? head_dim : row_dim, order ? row_dim : head_dim,
+                        static_cast<cuuint64_t>(batches)};
+  cuuint64_t strides[3] = {order ? head_str : row_str, order ? row_str : head_str,
+                           static_cast<cuuint64_t>(op.batch_stride) * 2};
+  const cuuint32_t br = static_cast<cuuint32_t>(box_rows);
+  cuuint32_t box[4] = {64, order ? 1u : br, order ? br : 1u, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = get_encode_fn()(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                               const_cast<void*>(op.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) throw Error("attention: cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(r)));
@@ -482,18 +586,20 @@ static CUtensorMap make_attn_map(const void* base, bool bf16, int d, int s, long
 }
 
 template <int DCH, bool BF16, bool NOMASK>
-void launch_attn_variant(const void* q, const void* k, const void* v, const AttnParams& p, cudaStream_t stream) {
+void launch_attn_variant(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, const AttnParams& p,
+                         long long q_rows, long long kv_rows, cudaStream_t stream) {
   using Cfg = AttnCfg<DCH>;
   static std::atomic<uint64_t> configured{0};
   opt_in_smem_once(configured, reinterpret_cast<const void*>(&attention_tc_kernel<DCH, BF16, NOMASK>), Cfg::kSmemBytes);
-  const long long bh = static_cast<long long>(p.B) * p.H;
-  CUtensorMap tq = make_attn_map(q, BF16, p.D, p.Sq, bh, kBlockM);
-  CUtensorMap tk = make_attn_map(k, BF16, p.D, p.Skv, bh, kBlockN);
-  CUtensorMap tv = make_attn_map(v, BF16, p.Dv, p.Skv, bh, kBlockN);
-  const long long items = bh * p.q_blocks;
+  const int map_batches = p.cu_seqlens ? 1 : p.B;
+  CUtensorMap tq = make_attn_map(q, BF16, p.D, q_rows, p.H, map_batches, kBlockM);
+  CUtensorMap tk = make_attn_map(k, BF16, p.D, kv_rows, p.H, map_batches, kBlockN);
+  CUtensorMap tv = make_attn_map(v, BF16, p.Dv, kv_rows, p.H, map_batches, kBlockN);
+  const long long items = static_cast<long long>(p.B) * p.H * p.q_blocks;
   B200AIT_REQUIRE(items < (1ll << 31), "attention: too many work items");
   AttnParams pp = p;
   pp.num_items = static_cast<int>(items);
+  pp.q_order = attn_map_order(q), pp.k_order = attn_map_order(k), pp.v_order = attn_map_order(v);
   const long long grid = std::min<long long>(items, static_cast<long long>(sm_count()) * (DCH == 1 ? 2 : 1));
   ::b200ait::count_launch(), attention_tc_kernel<DCH, BF16, NOMASK><<<static_cast<unsigned>(grid), kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv,
                                                                                                                  pp);
@@ -501,11 +607,57 @@ void launch_attn_variant(const void* q, const void* k, const void* v, const Attn
 }
 
 template <int DCH, bool BF16>
-void launch_attn(const void* q, const void* k, const void* v, const AttnParams& p, cudaStream_t stream) {
-  if (!p.causal && p.Skv % kBlockN == 0)
-    launch_attn_variant<DCH, BF16, true>(q, k, v, p, stream);
+void launch_attn(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, const AttnParams& p,
+                 long long q_rows, long long kv_rows, cudaStream_t stream) {
+  if (!p.causal && !p.cu_seqlens && p.Skv % kBlockN == 0)
+    launch_attn_variant<DCH, BF16, true>(q, k, v, p, q_rows, kv_rows, stream);
   else
-    launch_attn_variant<DCH, BF16, false>(q, k, v, p, stream);
+    launch_attn_variant<DCH, BF16, false>(q, k, v, p, q_rows, kv_rows, stream);
+}
+
+static bool operand_ok_for_tma(const AttnOperand& o) {
+  return (reinterpret_cast<uintptr_t>(o.ptr) & 15u) == 0 && o.row_stride % 8 == 0 && o.head_stride % 8 == 0 &&
+         o.batch_stride % 8 == 0 && o.row_stride > 0 && o.head_stride > 0 && o.batch_stride > 0;
+}
+
+// Shared body of the attention entry points. q_rows / kv_rows: extent of the row dimension of the operands
+// (Sq / Skv, or the packed total). The tensor-core kernel takes every layout whose strides are multiples of 8
+// elements; the CUDA-core kernel needs contiguous [B, H, S, D] operands.
+static void attention_run(void* output, const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, AttnParams p,
+                          long long q_rows, long long kv_rows, bool contiguous_bhsd, bool bf16, cudaStream_t stream) {
+  p.q_blocks = (p.Sq + kBlockM - 1) / kBlockM;
+  p.out = output;
+  p.status = device_status_word();
+  const bool tc_ok = p.D % 8 == 0 && p.Dv % 8 == 0 && p.D <= 128 && p.Dv <= 128 && operand_ok_for_tma(q) &&
+                     operand_ok_for_tma(k) && operand_ok_for_tma(v) &&
+                     (reinterpret_cast<uintptr_t>(output) & 15u) == 0;
+  if (tc_ok) {
+    const bool two = p.D > 64 || p.Dv > 64;
+    if (two) {
+      if (bf16)
+        launch_attn<2, true>(q, k, v, p, q_rows, kv_rows, stream);
+      else
+        launch_attn<2, false>(q, k, v, p, q_rows, kv_rows, stream);
+    } else {
+      if (bf16)
+        launch_attn<1, true>(q, k, v, p, q_rows, kv_rows, stream);
+      else
+        launch_attn<1, false>(q, k, v, p, q_rows, kv_rows, stream);
+    }
+    return;
+  }
+  B200AIT_REQUIRE(contiguous_bhsd && !p.cu_seqlens,
+                  "attention: this layout needs head sizes that are multiples of 8 (at most 128) and 16-byte aligned, "
+                  "8-element-strided operands");
+  B200AIT_REQUIRE(p.Dv <= 256, "attention: head_size_v > 256 is not supported");
+  const long long rows = static_cast<long long>(p.B) * p.H * p.Sq;
+  const unsigned grid = static_cast<unsigned>((rows + 3) / 4);
+  const size_t sh = 4 * static_cast<size_t>(p.D) * sizeof(float);
+  if (bf16)
+    ::b200ait::count_launch(), attention_simt_kernel<true><<<grid, 128, sh, stream>>>(q.ptr, k.ptr, v.ptr, p);
+  else
+    ::b200ait::count_launch(), attention_simt_kernel<false><<<grid, 128, sh, stream>>>(q.ptr, k.ptr, v.ptr, p);
+  B200AIT_CUDA_CHECK(cudaGetLastError());
 }
 
 }  // namespace b200ait
@@ -535,38 +687,87 @@ B200AIT_EXPORT int b200ait_mem_eff_attention(void* output, const void* query, co
     p.B = static_cast<int>(batch_size), p.H = num_heads;
     p.Sq = static_cast<int>(seq_len_q), p.Skv = static_cast<int>(seq_len_kv);
     p.D = head_size, p.Dv = head_size_v;
-    p.q_blocks = (p.Sq + kBlockM - 1) / kBlockM;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.causal = is_causal ? 1 : 0;
-    p.out = output;
-    p.status = device_status_word();
-    const bool bf16 = dtype == kDTypeBFloat16;
-    auto al = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) == 0; };
-    const bool tc_ok = head_size % 8 == 0 && head_size_v % 8 == 0 && head_size <= 128 && head_size_v <= 128 &&
-                       al(query) && al(key) && al(value) && al(output);
-    if (tc_ok) {
-      const bool two = head_size > 64 || head_size_v > 64;
-      if (two) {
-        if (bf16)
-          launch_attn<2, true>(query, key, value, p, stream);
-        else
-          launch_attn<2, false>(query, key, value, p, stream);
-      } else {
-        if (bf16)
-          launch_attn<1, true>(query, key, value, p, stream);
-        else
-          launch_attn<1, false>(query, key, value, p, stream);
-      }
-    } else {
-      B200AIT_REQUIRE(head_size_v <= 256, "attention: head_size_v > 256 is not supported");
-      const long long rows = static_cast<long long>(p.B) * p.H * p.Sq;
-      const unsigned grid = static_cast<unsigned>((rows + 3) / 4);
-      const size_t sh = 4 * static_cast<size_t>(p.D) * sizeof(float);
-      if (bf16)
-        ::b200ait::count_launch(), attention_simt_kernel<true><<<grid, 128, sh, stream>>>(query, key, value, p);
-      else
-        ::b200ait::count_launch(), attention_simt_kernel<false><<<grid, 128, sh, stream>>>(query, key, value, p);
-      B200AIT_CUDA_CHECK(cudaGetLastError());
-    }
+    p.cu_seqlens = nullptr;
+    const long long h = num_heads;
+    const AttnOperand q{query, head_size, seq_len_q * head_size, h * seq_len_q * head_size};
+    const AttnOperand k{key, head_size, seq_len_kv * head_size, h * seq_len_kv * head_size};
+    const AttnOperand v{value, head_size_v, seq_len_kv * head_size_v, h * seq_len_kv * head_size_v};
+    attention_run(output, q, k, v, p, seq_len_q, seq_len_kv, true, dtype == kDTypeBFloat16, stream);
+  });
+}
+
+// mem_eff_attention over operands that are strided views: each of q, k, v is addressed as [batch, head, row, channel]
+// with the element strides given (channel stride 1), e.g. a [B, S, H, D] projection output read in place
+// ({H*D, D, S*H*D}) instead of through a permute copy. Output [B, Sq, H, Dv] contiguous. Strides must be positive
+// multiples of 8 elements and head sizes multiples of 8 up to 128 (the tensor-core kernel is the only one that
+// takes strided operands). Counterpart of the reference's input TensorAccessors on this op
+// (python/aitemplate/backend/cuda/attention/mem_eff_attention.py:160-171 pass q/k/v strides to the kernel).
+B200AIT_EXPORT int b200ait_mem_eff_attention_strided(void* output, const void* query, const void* key,
+                                                     const void* value, int64_t batch_size, int64_t seq_len_kv,
+                                                     int64_t seq_len_q, int num_heads, int head_size, int head_size_v,
+                                                     const int64_t* q_strides, const int64_t* k_strides,
+                                                     const int64_t* v_strides, float softmax_scale, int is_causal,
+                                                     int dtype, cudaStream_t stream) {
+  return guarded("b200ait_mem_eff_attention_strided", [&] {
+    B200AIT_REQUIRE(dtype == kDTypeHalf || dtype == kDTypeBFloat16, "attention: dtype must be float16 or bfloat16");
+    B200AIT_REQUIRE(q_strides && k_strides && v_strides, "attention: strides are null");
+    B200AIT_REQUIRE(batch_size >= 0 && seq_len_kv >= 0 && seq_len_q >= 0 && num_heads >= 0 && head_size >= 0 &&
+                        head_size_v >= 0,
+                    "attention: negative dimension");
+    if (batch_size == 0 || seq_len_q == 0 || num_heads == 0 || head_size_v == 0) return;
+    B200AIT_REQUIRE(output && query && key && value, "attention: null pointer with non-zero size");
+    B200AIT_REQUIRE(seq_len_kv > 0 && head_size > 0, "attention: empty key sequence or head");
+    B200AIT_REQUIRE(seq_len_q < (1 << 30) && seq_len_kv < (1 << 30), "attention: sequence too long");
+    AttnParams p{};
+    p.B = static_cast<int>(batch_size), p.H = num_heads;
+    p.Sq = static_cast<int>(seq_len_q), p.Skv = static_cast<int>(seq_len_kv);
+    p.D = head_size, p.Dv = head_size_v;
+    p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    p.causal = is_causal ? 1 : 0;
+    p.cu_seqlens = nullptr;
+    const AttnOperand q{query, q_strides[0], q_strides[1], q_strides[2]};
+    const AttnOperand k{key, k_strides[0], k_strides[1], k_strides[2]};
+    const AttnOperand v{value, v_strides[0], v_strides[1], v_strides[2]};
+    attention_run(output, q, k, v, p, seq_len_q, seq_len_kv, false, dtype == kDTypeBFloat16, stream);
+  });
+}
+
+// flash_attention: packed-QKV variable-length attention. qkv is [total, 3, num_heads, head_size]; cu_seqlens
+// (device, int32, batch_size + 1 entries) gives each sequence's first row; output [total, num_heads, head_size].
+// Argument order follows the reference's generated function
+// (python/aitemplate/backend/cuda/attention/flash_attention.py:199-215); softmax_lse, o_tmp and loop are its
+// kernel's scratch and scheduling arguments and are ignored here (may be null), p_dropout must be 0. `total` rows
+// are read from cu_seqlens on the device, so the host only needs seq_len = the longest sequence's length (an upper
+// bound is enough) and total_rows = the row extent of qkv.
+B200AIT_EXPORT int b200ait_flash_attention(void* output, const void* qkv, const int* cu_seqlens, float* softmax_lse,
+                                           float* o_tmp, int batch_size, int seq_len, int num_heads, int head_size,
+                                           float p_dropout, float softmax_scale, int is_causal, int loop,
+                                           int64_t total_rows, int dtype, cudaStream_t stream) {
+  (void)softmax_lse, (void)o_tmp, (void)loop;
+  return guarded("b200ait_flash_attention", [&] {
+    B200AIT_REQUIRE(dtype == kDTypeHalf || dtype == kDTypeBFloat16, "attention: dtype must be float16 or bfloat16");
+    B200AIT_REQUIRE(p_dropout == 0.f, "flash_attention: dropout is not supported (inference only)");
+    B200AIT_REQUIRE(batch_size >= 0 && seq_len >= 0 && num_heads >= 0 && head_size >= 0 && total_rows >= 0,
+                    "attention: negative dimension");
+    if (batch_size == 0 || seq_len == 0 || num_heads == 0 || head_size == 0 || total_rows == 0) return;
+    B200AIT_REQUIRE(output && qkv && cu_seqlens, "attention: null pointer with non-zero size");
+    B200AIT_REQUIRE(head_size % 8 == 0 && head_size <= 128, "flash_attention: head size must be a multiple of 8, at most 128");
+    B200AIT_REQUIRE(total_rows < (1ll << 30), "attention: too many rows");
+    AttnParams p{};
+    p.B = batch_size, p.H = num_heads;
+    p.Sq = p.Skv = seq_len;
+    p.D = p.Dv = head_size;
+    p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    p.causal = is_causal ? 1 : 0;
+    p.cu_seqlens = cu_seqlens;
+    const long long hd = static_cast<long long>(num_heads) * head_size;
+    const size_t esz = 2;
+    const uint8_t* base = static_cast<const uint8_t*>(qkv);
+    const AttnOperand q{base, 3 * hd, head_size, 3 * hd * total_rows};
+    const AttnOperand k{base + hd * esz, 3 * hd, head_size, 3 * hd * total_rows};
+    const AttnOperand v{base + 2 * hd * esz, 3 * hd, head_size, 3 * hd * total_rows};
+    attention_run(output, q, k, v, p, total_rows, total_rows, false, dtype == kDTypeBFloat16, stream);
   });
 }

@@ -48,6 +48,10 @@ int b200ait_gemm_rrr(const void*, const void*, const void*, const void*, const v
                      void*, int64_t, int, cudaStream_t);
 int b200ait_mem_eff_attention(void*, const void*, const void*, const void*, int64_t, int64_t, int64_t, int, int, int,
                               float, int, const int32_t*, const int32_t*, int, cudaStream_t);
+int b200ait_mem_eff_attention_strided(void*, const void*, const void*, const void*, int64_t, int64_t, int64_t, int, int,
+                                      int, const int64_t*, const int64_t*, const int64_t*, float, int, int, cudaStream_t);
+int b200ait_flash_attention(void*, const void*, const int*, float*, float*, int, int, int, int, float, float, int, int,
+                            int64_t, int, cudaStream_t);
 int b200ait_layernorm(void*, const void*, const void*, const void*, int64_t, int64_t, float, int64_t, int64_t, int,
                       cudaStream_t);
 int b200ait_softmax(const void*, void*, int64_t, int64_t, int64_t, int, cudaStream_t);
@@ -559,14 +563,54 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     return;
   }
   if (op.kernel == "mem_eff_attention") {
+    // ints: causal, then one flag per operand: 1 = the operand is stored [B, S, H, D] (a permute (0, 2, 1, 3) that the
+    // compiler folded into this op) and is read in place through strides
     const int q = in(0), k = in(1), v = in(2);
-    const auto qs = shape_of(q), ks = shape_of(k), vs = shape_of(v);
+    const bool qt = op.ints.size() > 1 && op.ints[1], kt = op.ints.size() > 2 && op.ints[2],
+               vt = op.ints.size() > 3 && op.ints[3];
+    auto bhsd = [&](int t, bool stored_bshd) {  // logical [B, H, S, D] dims of an operand
+      auto s = shape_of(t);
+      if (stored_bshd) std::swap(s[1], s[2]);
+      return s;
+    };
+    const auto qs = bhsd(q, qt), ks = bhsd(k, kt), vs = bhsd(v, vt);
     bind_shape(out0, {qs[0], qs[2], qs[1], vs[3]}, "attention output");
     if (!launch) return;
-    check(b200ait_mem_eff_attention(ptr_of(out0), ptr_of(q), ptr_of(k), ptr_of(v), qs[0], ks[2], qs[2],
-                                    static_cast<int>(qs[1]), static_cast<int>(qs[3]), static_cast<int>(vs[3]),
-                                    static_cast<float>(op.floats[0]), static_cast<int>(op.ints[0]), nullptr, nullptr,
-                                    T[q].dtype, stream),
+    if (!qt && !kt && !vt) {
+      check(b200ait_mem_eff_attention(ptr_of(out0), ptr_of(q), ptr_of(k), ptr_of(v), qs[0], ks[2], qs[2],
+                                      static_cast<int>(qs[1]), static_cast<int>(qs[3]), static_cast<int>(vs[3]),
+                                      static_cast<float>(op.floats[0]), static_cast<int>(op.ints[0]), nullptr, nullptr,
+                                      T[q].dtype, stream),
+            op);
+      return;
+    }
+    auto strides = [](const std::vector<int64_t>& s, bool stored_bshd, int64_t* out) {
+      const int64_t h = s[1], rows = s[2], d = s[3];
+      if (stored_bshd) {
+        out[0] = h * d, out[1] = d, out[2] = rows * h * d;
+      } else {
+        out[0] = d, out[1] = rows * d, out[2] = h * rows * d;
+      }
+    };
+    int64_t sq[3], sk[3], sv[3];
+    strides(qs, qt, sq), strides(ks, kt, sk), strides(vs, vt, sv);
+    check(b200ait_mem_eff_attention_strided(ptr_of(out0), ptr_of(q), ptr_of(k), ptr_of(v), qs[0], ks[2], qs[2],
+                                            static_cast<int>(qs[1]), static_cast<int>(qs[3]), static_cast<int>(vs[3]),
+                                            sq, sk, sv, static_cast<float>(op.floats[0]), static_cast<int>(op.ints[0]),
+                                            T[q].dtype, stream),
+          op);
+    return;
+  }
+  if (op.kernel == "flash_attention") {  // ints: causal, batch_size, max_seq_len; floats: scale
+    const int x = in(0), cu = in(1);
+    const auto xs = shape_of(x);  // [total, 3, H, D]
+    bind_shape(out0, {xs[0], xs[2], xs[3]}, "flash_attention output");
+    if (!launch) return;
+    check(b200ait_flash_attention(ptr_of(out0), ptr_of(x), static_cast<const int*>(ptr_of(cu)), nullptr, nullptr,
+                                  static_cast<int>(op.ints[1]), static_cast<int>(op.ints[2]),
+                                  static_cast<int>(xs[2]), static_cast<int>(xs[3]), 0.f,
+                                  static_cast<float>(op.floats[0]), static_cast<int>(op.ints[0]), 0, xs[0], T[x].dtype,
+                                  stream),
           op);
     return;
   }

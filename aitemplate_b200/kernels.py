@@ -287,6 +287,55 @@ def mem_eff_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal:
     return out
 
 
+def _bhsd_strides(t: torch.Tensor):
+    """(row, head, batch) element strides of a [B, H, S, D] view; the channel stride must be 1."""
+    if t.dim() != 4 or t.stride(3) != 1:
+        raise ValueError("attention operands must be 4-D [B, H, S, D] views with unit channel stride")
+    row, head = t.stride(2), t.stride(1)
+    batch = t.stride(0) if t.shape[0] > 1 else max(row * t.shape[2], head * t.shape[1])
+    return _i64([row, head, batch])
+
+
+def mem_eff_attention_strided(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
+                              scale: Optional[float] = None) -> torch.Tensor:
+    """mem_eff_attention on [B, H, S, D] VIEWS that need not be contiguous (e.g. `x.view(B, S, H, D).permute(0, 2,
+    1, 3)` of a projection output): the kernel reads them in place through strided tensor maps."""
+    for t in (q, k, v):
+        if t is not None and not t.is_cuda:
+            raise ValueError("inputs must be on GPU")
+    bsz, h, sq, d = q.shape
+    skv, dv = k.shape[2], v.shape[3]
+    out = torch.empty((bsz, sq, h, dv), dtype=q.dtype, device=q.device)
+    if scale is None:
+        scale = 1.0 / math.sqrt(d) if d else 1.0
+    code = _lib.load().b200ait_mem_eff_attention_strided(
+        _ptr(out), q.data_ptr(), k.data_ptr(), v.data_ptr(), bsz, skv, sq, h, d, dv, _bhsd_strides(q),
+        _bhsd_strides(k), _bhsd_strides(v), c_float(scale), int(causal), _dtype_code(q), _stream(),
+    )
+    _lib.check(code, "b200ait_mem_eff_attention_strided")
+    return out
+
+
+def flash_attention(qkv: torch.Tensor, cu_seqlens: torch.Tensor, max_seq_len: int, causal: bool = False,
+                    scale: Optional[float] = None) -> torch.Tensor:
+    """qkv [total, 3, H, D] packed, cu_seqlens int32 [batch + 1] -> [total, H, D]."""
+    _check_cuda(qkv, cu_seqlens)
+    if cu_seqlens.dtype != torch.int32:
+        raise ValueError("cu_seqlens must be int32")
+    total, three, h, d = qkv.shape
+    if three != 3:
+        raise ValueError("qkv must be [total, 3, num_heads, head_size]")
+    out = torch.empty((total, h, d), dtype=qkv.dtype, device=qkv.device)
+    if scale is None:
+        scale = 1.0 / math.sqrt(d) if d else 1.0
+    code = _lib.load().b200ait_flash_attention(
+        _ptr(out), _ptr(qkv), _ptr(cu_seqlens), None, None, cu_seqlens.numel() - 1, int(max_seq_len), h, d,
+        c_float(0.0), c_float(scale), int(causal), 0, total, _dtype_code(qkv), _stream(),
+    )
+    _lib.check(code, "b200ait_flash_attention")
+    return out
+
+
 def layernorm(x: torch.Tensor, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor], eps: float = 1e-5,
               normalized_ndim: int = 1) -> torch.Tensor:
     _check_cuda(x, gamma, beta)

@@ -51,7 +51,8 @@ class BertEncoderLayer(nn.Module):
     def __init__(self, batch: int, seq: int, hidden: int = 768, heads: int = 12, ffn: int = 3072,
                  eps: float = 1e-12) -> None:
         super().__init__()
-        self.attn = nn.MultiheadAttention(hidden, batch, seq, num_heads=heads, qkv_bias=True, has_residual=True)
+        self.attn = nn.MultiheadAttention(hidden, batch, seq, num_heads=heads, qkv_bias=True, has_residual=True,
+                                              use_mem_eff=True)
         self.ln1 = nn.LayerNorm(hidden, eps=eps)
         self.fc1 = nn.Linear(hidden, ffn, specialization="fast_gelu")
         self.fc2 = nn.Linear(ffn, hidden, specialization="add")

@@ -258,7 +258,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     step(0, graph=False)  # one eager step: counts the kernels a step launches (a graph replay re-issues the same nodes)
     torch.cuda.synchronize()
     launches_per_step = _lib.kernel_launch_count() - launches_before
-    # preheat: raise the clocks and settle the power state before anything is timed
+    # preheat: raise the clocks and settle the power state before anything is timed. The clock sampler runs from
+    # here to the end of the timed region: the same kernels at the same rate, so its median is the clock under load.
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     t_pre = time.perf_counter()
     while (time.perf_counter() - t_pre) * 1000.0 < PREHEAT_MS:
         for i in range(20):
@@ -271,10 +274,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         torch.cuda.synchronize()
 
     # ---- device-resident throughput: K steps, each bracketed by events, L2 flushed between steps
-    sampler = ClockSampler(local_rank)
     barrier()
     wall0 = time.perf_counter()
-    sampler.start()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     for i in range(LEAD_IN_STEPS):

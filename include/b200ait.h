@@ -175,6 +175,27 @@ int b200ait_mem_eff_attention(void* output, const void* query, const void* key, 
                               const int32_t* lengths_kv, const int32_t* lengths_q, int dtype,
                               b200ait_stream_t stream);
 
+/* mem_eff_attention whose q, k, v are strided views: each is addressed as [batch, head, row, channel] with unit
+ * channel stride and the three element strides {row, head, batch} given, e.g. {H*D, D, S*H*D} reads a [B, S, H, D]
+ * projection output in place. Strides: positive multiples of 8 elements; head sizes: multiples of 8, at most 128.
+ * Output [B, Sq, H, Dv] contiguous. Counterpart of the q/k/v strides the reference passes to its kernel through
+ * the op's input TensorAccessors (python/aitemplate/backend/cuda/attention/mem_eff_attention.py:160-171). */
+int b200ait_mem_eff_attention_strided(void* output, const void* query, const void* key, const void* value,
+                                      int64_t batch_size, int64_t seq_len_kv, int64_t seq_len_q, int num_heads,
+                                      int head_size, int head_size_v, const int64_t* q_strides,
+                                      const int64_t* k_strides, const int64_t* v_strides, float softmax_scale,
+                                      int is_causal, int dtype, b200ait_stream_t stream);
+
+/* flash_attention: qkv [total, 3, num_heads, head_size] (all sequences' rows back to back), cu_seqlens int32
+ * [batch_size + 1] on the device, output [total, num_heads, head_size]; sequence b attends within rows
+ * cu_seqlens[b] .. cu_seqlens[b+1]. seq_len = (an upper bound of) the longest sequence, total_rows = row extent of
+ * qkv. softmax_lse, o_tmp and loop belong to the reference kernel and are ignored; p_dropout must be 0.
+ * (python/aitemplate/backend/cuda/attention/flash_attention.py:199-215; total_rows and dtype are appended) */
+int b200ait_flash_attention(void* output, const void* qkv, const int* cu_seqlens, float* softmax_lse, float* o_tmp,
+                            int batch_size, int seq_len, int num_heads, int head_size, float p_dropout,
+                            float softmax_scale, int is_causal, int loop, int64_t total_rows, int dtype,
+                            b200ait_stream_t stream);
+
 /* layernorm over the last n elements of each of m rows; gamma / beta may be NULL; a row stride of 0
  * means n (python/aitemplate/backend/cuda/layernorm_sigmoid_mul/layernorm_sigmoid_mul.py:72-83) */
 int b200ait_layernorm(void* out, const void* in, const void* gamma, const void* beta, int64_t m, int64_t n,

@@ -88,3 +88,53 @@ def test_zero_batch():
 
     z = torch.zeros((0, 4, 16, 64), dtype=torch.float16, device="cuda")
     assert tuple(kernels.mem_eff_attention(z, z, z).shape) == (0, 16, 4, 64)
+
+
+# ---- packed variable-length attention (ops.flash_attention): tests/unittest/ops/test_attention.py:200-330 builds
+# qkv [total, 3, H, D] + cu_seqlens and compares with attention_ref per sequence
+@pytest.mark.parametrize("lengths,h,d,causal", [
+    ([384] * 4, 12, 64, False),            # the BERT case: equal lengths
+    ([384, 100, 1, 257, 130], 4, 64, False),
+    ([384, 100, 1, 257, 130], 4, 64, True),
+    ([77, 300, 128], 3, 32, False),
+    ([512, 129], 2, 128, False),
+    ([64, 0, 200], 2, 16, False),           # an empty sequence in the middle
+])
+def test_flash_attention_packed_variable_length(lengths, h, d, causal):
+    from aitemplate_b200 import kernels
+
+    total = sum(lengths)
+    qkv = _rand((total, 3, h, d), 21)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
+    out = kernels.flash_attention(qkv.cuda(), cu.cuda(), max(lengths), causal=causal)
+    assert kernels.device_status() == 0
+    assert tuple(out.shape) == (total, h, d)
+    got = out.float().cpu()
+    for b, n in enumerate(lengths):
+        if n == 0:
+            continue
+        lo = int(cu[b])
+        q, k, v = (qkv[lo:lo + n, i].permute(1, 0, 2).unsqueeze(0) for i in range(3))  # [1, H, n, D]
+        want = oracle.mem_eff_attention(q, k, v, causal=causal)[0]  # [n, H, D]
+        err = (got[lo:lo + n] - want).abs()
+        assert bool((err <= 1e-2 + 1e-2 * want.abs()).all()) and float(err.max()) < 4e-3, (b, float(err.max()))
+
+
+@pytest.mark.parametrize("b,h,sq,skv,d,causal", [(2, 8, 1024, 1024, 40, False), (2, 8, 512, 77, 40, False),
+                                                  (3, 4, 200, 200, 64, True), (1, 2, 130, 260, 96, False)])
+def test_strided_operands_read_in_place(b, h, sq, skv, d, causal):
+    """q, k, v stored [B, S, H, D] (a projection output) and handed over as permuted views: no copy is made."""
+    from aitemplate_b200 import kernels
+
+    qs, ks, vs = _rand((b, sq, h, d), 31), _rand((b, skv, h, d), 32), _rand((b, skv, h, d), 33)
+    qd, kd, vd = qs.cuda(), ks.cuda(), vs.cuda()
+    out = kernels.mem_eff_attention_strided(qd.permute(0, 2, 1, 3), kd.permute(0, 2, 1, 3), vd.permute(0, 2, 1, 3),
+                                            causal=causal)
+    assert kernels.device_status() == 0
+    want = oracle.mem_eff_attention(qs.permute(0, 2, 1, 3), ks.permute(0, 2, 1, 3), vs.permute(0, 2, 1, 3), causal=causal)
+    err = (out.float().cpu() - want).abs()
+    assert bool((err <= 1e-2 + 1e-2 * want.abs()).all()) and float(err.max()) < 4e-3, float(err.max())
+    # mixed: q in place, k and v contiguous [B, H, S, D]
+    out2 = kernels.mem_eff_attention_strided(qd.permute(0, 2, 1, 3), kd.permute(0, 2, 1, 3).contiguous(),
+                                             vd.permute(0, 2, 1, 3).contiguous(), causal=causal)
+    assert torch.equal(out2, out)

@@ -32,6 +32,7 @@ def _lower(outs, fuse=True):
     if fuse:
         g = fuse_mm_elementwise(g, outs)
         g = fuse_gemm_permute0213(g, outs)
+        g = C.fuse_permute_into_attention(g, outs)
         mark_param_tensor(g)
         split_to_views(g)
         fuse_split_strided(g)
@@ -193,9 +194,12 @@ def test_sd_transformer_block_plan():
     y = workloads.build_sd_block(2)
     g, plan, blob, consts = _lower([y])
     kernels = [line.split()[1] for line in plan.splitlines() if line.startswith("op ") and line.split()[1] != "view"]
-    # (head size 40: the heads-first permutes stay copy kernels, see fuse_gemm_permute0213)
-    attn = ["gemm_rcr", "permute"] * 3 + ["mem_eff_attention", "gemm_rcr"]
+    # (head size 40: no permuted GEMM store, see fuse_gemm_permute0213; instead the attention reads the
+    # [B, S, H, D] projections in place, fuse_permute_into_attention, so no permute kernel is left)
+    attn = ["gemm_rcr"] * 3 + ["mem_eff_attention", "gemm_rcr"]
     assert kernels == ["layernorm"] + attn + ["layernorm"] + attn + ["layernorm", "gemm_rcr", "gemm_rcr", "gemm_rcr"]
+    attn_ops = [_parse_op(l) for l in plan.splitlines() if l.startswith("op mem_eff_attention")]
+    assert [o["ints"] for o in attn_ops] == [[0, 1, 1, 1], [0, 1, 1, 1]]
     assert consts >= 2 * (4 * 320 * 320 + 2 * 320 * 768 + 2 * 320 * 320 + 3 * 1280 * 320)
     assert blob >= 2 * 4096 * 1280 * 2
 
@@ -321,7 +325,9 @@ def test_nn_modules_name_parameters():
     layer = workloads.BertEncoderLayer(2, 384)
     layer.name_parameter_tensor()
     names = sorted(p.tensor()._attrs["name"] for p in layer.parameters())
-    assert names == sorted(workloads.BERT_PARAM_NAMES.keys())
+    # cu_length belongs to nn.MultiheadAttention as in the reference (frontend/nn/attention.py:147-148); only the
+    # packed flash_attention path reads it
+    assert names == sorted(list(workloads.BERT_PARAM_NAMES.keys()) + ["attn_cu_length"])
     lin = nn.Linear(8, 16, specialization="relu")
     assert lin._op_name == "gemm_rcr_bias_relu"
     with pytest.raises(NotImplementedError):

@@ -503,3 +503,36 @@ def test_concurrent_runs_share_the_pool(workdir):
     assert not errors, errors
     for y in results:
         _close(y, want, 2e-2)
+
+
+def test_multihead_attention_default_flash_path_matches_oracle(workdir):
+    """nn.MultiheadAttention as the reference's BERT example uses it (examples/03_bert/modeling/bert.py:55-66): the
+    packed flash_attention path with the cu_length constant, written with `aitemplate.*` imports only."""
+    from aitemplate.compiler import compile_model
+    from aitemplate.frontend import nn, Tensor
+    from aitemplate.testing import detect_target
+
+    batch, seq, hidden, heads = 3, 384, 768, 12
+    attn = nn.MultiheadAttention(dim=hidden, batch_size=batch, seq_len=seq, num_heads=heads, qkv_bias=True,
+                                 has_residual=True)
+    attn.name_parameter_tensor()
+    x = Tensor([batch, seq, hidden], name="hidden_states", is_input=True)
+    y = attn(x, x)
+    y._attrs["name"], y._attrs["is_output"] = "output_0", True
+    module = compile_model(y, detect_target(), workdir, "mha_flash")
+    g = torch.Generator().manual_seed(77)
+    r = lambda *s, sc=1.0: (torch.randn(*s, generator=g) * sc).half()  # noqa: E731
+    p = {"qkv_weight": r(3 * hidden, hidden, sc=0.02), "qkv_bias": r(3 * hidden, sc=0.02),
+         "proj_weight": r(hidden, hidden, sc=0.02), "proj_bias": r(hidden, sc=0.02)}
+    xh = r(batch, seq, hidden)
+    cu = torch.arange(batch + 1, dtype=torch.int32) * seq
+    module.set_many_constants_with_tensors({**{k: v.cuda() for k, v in p.items()}, "cu_length": cu.cuda()})
+    out = torch.empty((batch, seq, hidden), dtype=torch.float16, device="cuda")
+    x2 = xh.float().reshape(batch * seq, hidden)
+    qkv = oracle.gemm_rcr_bias_permute(x2, p["qkv_weight"], p["qkv_bias"], (seq, 3, heads), "20314")
+    a = oracle.mem_eff_attention(qkv[0], qkv[1], qkv[2]).reshape(batch * seq, hidden)
+    want = oracle.gemm_rcr(a.half(), p["proj_weight"], p["proj_bias"], x2, epilogue="add").reshape(batch, seq, hidden)
+    for graph_mode in (False, True, True):
+        res = module.run_with_tensors({"hidden_states": xh.cuda()}, {"output_0": out}, graph_mode=graph_mode)
+        _close(res["output_0"], want, 2e-2)
+    module.close()

@@ -5,7 +5,7 @@ oracle/_ref/libref_kernels.so is the reference's softmax.cuh and permute.cuh com
 oracle/build_ref.py (entry points in oracle/ref_kernels.cu, which holds no kernel code of its own).
 It is built where a reference checkout exists and travels with the tree as a built file; without it
 these tests skip. permute must agree bit for bit; softmax, which both sides evaluate in fp32 and
-round once to fp16, within one fp16 unit in the last place of a value in [0, 1] (2^-11 relative),
+round once to fp16, within one fp16 unit in the last place (at most 2^-10 relative, 2^-24 absolute for subnormals),
 and both within the reference's own tolerance (1e-2) of the CPU oracle.
 """
 import ctypes
@@ -53,7 +53,7 @@ def test_softmax_matches_reference_kernel(ref, m, k):
     torch.cuda.synchronize()
     g, w = got.float().cpu(), want.float().cpu()
     err = (g - w).abs()
-    assert bool((err <= 2.0 ** -11 * torch.maximum(w, g) + 1e-7).all()), float(err.max())
+    assert bool((err <= 2.0 ** -10 * torch.maximum(w, g) + 2.0 ** -24).all()), float(err.max())
     o = oracle.softmax(x, -1)
     for t in (g, w):
         assert bool(((t - o).abs() <= 1e-2 + 1e-2 * o).all())
