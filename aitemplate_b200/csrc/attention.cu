@@ -11,16 +11,20 @@
 // Persistent CTAs walk work items of 128 query rows of one (batch, head):
 //   warp 0      TMA producer: the item's Q tile, then K/V blocks of kBlockN keys into a 3-stage ring;
 //               the next item's Q streams in while the current item drains
-//   warp 1      MMA issuer:   S = Q K^T  (tcgen05.mma, fp32 accumulator in TMEM)
-//                             O += P V   (P from shared memory, V as an MN-major B operand); O stays in TMEM for
-//                             the whole item and every key block accumulates into it
+//   warp 6      MMA issuer:   S = Q K^T  (tcgen05.mma, fp32 accumulator in TMEM)
+//   warp 1      MMA issuer:   O += P V   (P read from TMEM, where the softmax threads put it over the S columns
+//                             they have consumed; V as an MN-major B operand from shared memory); O stays in
+//                             TMEM for the whole item and every key block accumulates into it
 //               S and P are double-buffered: the MMAs of key block j+1 overlap the softmax of block j; O is
 //               double-buffered across items
 //   warps 2-5   one thread per query row: TMEM -> registers, mask (skipped for full, unmasked blocks),
-//               reference max / row sum, exp2, P -> swizzled shared memory; O is touched only when a row's
+//               reference max / row sum, exp2, P (16-bit pairs) -> TMEM; O is touched only when a row's
 //               maximum outgrows the reference by more than 2^8 (then O and the row sum are rescaled in
 //               TMEM) and once at the end of the item (O / row sum -> global memory)
 // Two CTAs share an SM (head dim <= 64) so one CTA's softmax also overlaps the other's MMAs.
+// Shared-memory bandwidth is what the MMAs of this kernel run into (a 128 x 64 x 16 MMA with both operands in
+// shared memory reads 6 KB and issues every 48 cycles = 128 B / clk, the whole bandwidth of an SM), which is why P
+// never goes through shared memory: that removed a 16 KB write and a 16 KB read per key block.
 // Head dims that are not a multiple of 8, or larger than 128, run on a CUDA-core kernel.
 #include <cuda.h>
 
@@ -34,6 +38,34 @@
 #include "ptx.cuh"
 
 namespace b200ait {
+
+// Cycle probes for tuning (compiled only with -DB200AIT_ATTN_PROBE; never part of the shipped library): CTA 0 adds
+// the clock64() time its softmax warp 2 / its MMA thread spend in each phase to g_attn_probe[slot].
+#ifdef B200AIT_ATTN_PROBE
+__device__ long long g_attn_probe[32];
+#define ATTN_PROBE_DECL(cond)                \
+  const bool probe_on = (cond);              \
+  long long probe_acc[4] = {0, 0, 0, 0};     \
+  long long probe_t = clock64();
+// phase times are kept in registers (slot & 3) and flushed once by ATTN_PROBE_FLUSH(base)
+#define ATTN_PROBE(slot)                                   \
+  if (probe_on) {                                          \
+    const long long probe_now = clock64();                 \
+    probe_acc[(slot) & 3] += probe_now - probe_t;          \
+    probe_t = probe_now;                                   \
+  }
+#define ATTN_PROBE_SKIP() \
+  if (probe_on) probe_t = clock64();
+#define ATTN_PROBE_FLUSH(base)                                                  \
+  if (probe_on) {                                                               \
+    for (int pi = 0; pi < 4; ++pi) g_attn_probe[(base) + pi] += probe_acc[pi];  \
+  }
+#else
+#define ATTN_PROBE_DECL(cond)
+#define ATTN_PROBE(slot)
+#define ATTN_PROBE_SKIP()
+#define ATTN_PROBE_FLUSH(base)
+#endif
 
 // defined in gemm.cu
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -65,18 +97,21 @@ struct AttnOperand {
   long long row_stride, head_stride, batch_stride;
 };
 
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 224;  // producer, P V issuer, 4 softmax warps, S issuer
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 64;     // keys per block
-constexpr int kKvStages = 3;    // K/V ring: blocks j, j+1, j+2 are in flight
 constexpr float kRescaleLog2 = 8.f;  // a row's reference maximum may lag its true maximum by this much (log2 units)
 
 template <int DCH>
 struct AttnCfg {
   static constexpr int kQBytes = DCH * kBlockM * 128;
   static constexpr int kKBytes = DCH * kBlockN * 128;  // one K (or V) block
-  static constexpr int kPBytes = kBlockM * 128;        // one P block: 128 rows x 64 keys
-  static constexpr int kDataBytes = kQBytes + kKvStages * 2 * kKBytes + 2 * kPBytes;
+  // K/V ring. A block's load is issued when the block kKvStages before it has been consumed and is needed two block
+  // periods before its own P V, so the ring gives (kKvStages - 2) block periods of lead (six stages measured the
+  // same as four, also on short sequences whose K / V come from DRAM).
+  static constexpr int kKvStages = 4;
+  static constexpr int kQBufs = (DCH == 1) ? 2 : 1;   // Q tiles in shared memory: the next item's Q loads an item ahead
+  static constexpr int kDataBytes = kQBufs * kQBytes + kKvStages * 2 * kKBytes;
   // the dynamic shared-memory window is declared 1024-byte aligned, so no slack is reserved:
   // two CTAs of the 64-wide configuration (96 KB each) must fit one SM
   static constexpr int kBarrierBytes = 256;  // 19 mbarriers + the TMEM slot + the abort flag (160 bytes), padded
@@ -111,21 +146,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
     return;
   }
   uint8_t* sQ = smem;
-  uint8_t* sKV = sQ + Cfg::kQBytes;  // stage s: K at sKV + s*2*kKBytes, V right after K
-  uint8_t* sP = sKV + kKvStages * 2 * Cfg::kKBytes;  // two P blocks
-  uint64_t* q_full = reinterpret_cast<uint64_t*>(sP + 2 * Cfg::kPBytes);
-  uint64_t* kv_full = q_full + 1;
-  uint64_t* kv_empty = kv_full + kKvStages;
-  uint64_t* s_full = kv_empty + kKvStages;  // [2]
+  uint8_t* sKV = sQ + Cfg::kQBufs * Cfg::kQBytes;  // stage s: K at sKV + s*2*kKBytes, V right after K
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(sKV + Cfg::kKvStages * 2 * Cfg::kKBytes);  // [2]
+  uint64_t* kv_full = q_full + 2;
+  uint64_t* kv_empty = kv_full + Cfg::kKvStages;
+  uint64_t* s_full = kv_empty + Cfg::kKvStages;  // [2]
   uint64_t* p_full = s_full + 2;            // [2]
-  uint64_t* pv_done = p_full + 2;           // [2] P(g) V(g) has been accumulated into O (per key block, g & 1)
-  uint64_t* o_full = pv_done + 2;           // [2] every P V of the item has completed (item parity)
-  uint64_t* o_empty = o_full + 2;           // [2] the softmax threads have read the item's O out of TMEM
-  uint64_t* drain_bar = o_empty + 2;
-  uint64_t* q_empty = drain_bar + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_empty + 1);
+  // "P(g) V(g) has been accumulated into O" is the same event as "K/V stage g % Cfg::kKvStages is free": the softmax
+  // threads wait on kv_empty for it (before a rescale of O, and for the item's last block before reading O out),
+  // which spares two tcgen05.commit per key block; a commit costs the MMA thread as much as an MMA
+  uint64_t* o_empty = p_full + 2;           // [2] the softmax threads have read the item's O out of TMEM
+  uint64_t* drain_bar = o_empty + 2;         // [2] one per issuing thread, used only when a wait has given up
+  uint64_t* q_empty = drain_bar + 2;          // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  static_assert((1 + 2 * kKvStages + 2 * 5 + 2) * 8 + 8 <= Cfg::kBarrierBytes, "barrier block overflows its shared memory");
+  static_assert((2 + 2 * Cfg::kKvStages + 2 * 3 + 4) * 8 + 8 <= Cfg::kBarrierBytes, "barrier block overflows its shared memory");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // work item -> where its rows live and how many key blocks it walks. n_blocks == 0 (a query tile past the end of
@@ -173,19 +208,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < kKvStages; ++s) {
+    mbar_init(q_full + 1, 1);
+    for (int s = 0; s < Cfg::kKvStages; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 128);
-      mbar_init(&pv_done[i], 1);
-      mbar_init(&o_full[i], 1);
       mbar_init(&o_empty[i], 128);
     }
     mbar_init(drain_bar, 1);
+    mbar_init(drain_bar + 1, 1);
     mbar_init(q_empty, 1);
+    mbar_init(q_empty + 1, 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tma_q);
@@ -201,7 +237,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;        // S(j) at + (j & 1) * 64
+  const uint32_t tmem_s = tmem_base;        // S(j) at + (j & 1) * 64; P(j) as 16-bit pairs over its first 32 columns
   const uint32_t tmem_o = tmem_base + 128;  // O of item it at + (it & 1) * kTWidth
 
   if (warp == 0) {
@@ -212,15 +248,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
         const Item w = decode_item(item);
         if (w.n_blocks == 0) continue;
-        // the Q tile is free once the previous item's last S = Q K^T has completed
-        ok = mbar_wait(q_empty, (it & 1) ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
+        // Q buffer qb is free once the last S = Q K^T of the item that used it before has completed
+        const int qb = it % Cfg::kQBufs;
+        const uint32_t qph = static_cast<uint32_t>(it / Cfg::kQBufs) & 1u;
+        ok = mbar_wait(&q_empty[qb], qph ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
         if (!ok) break;
-        mbar_arrive_expect_tx(q_full, Cfg::kQBytes);
+        mbar_arrive_expect_tx(&q_full[qb], Cfg::kQBytes);
 #pragma unroll
-        for (int c = 0; c < DCH; ++c) load_rows(sQ + c * kBlockM * 128, &tma_q, q_full, c * 64, w.row0 + w.q0, w, p.q_order);
+        for (int c = 0; c < DCH; ++c)
+          load_rows(sQ + qb * Cfg::kQBytes + c * kBlockM * 128, &tma_q, &q_full[qb], c * 64, w.row0 + w.q0, w, p.q_order);
         for (int j = 0; j < w.n_blocks; ++j, ++g) {
-          const int st = g % kKvStages;
-          const uint32_t ph = (g / kKvStages) & 1;
+          const int st = g % Cfg::kKvStages;
+          const uint32_t ph = (g / Cfg::kKvStages) & 1;
           ok = mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
           if (!ok) break;
           uint8_t* sK = sKV + st * 2 * Cfg::kKBytes;
@@ -240,68 +279,49 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
         }
       }
     }
+#ifndef B200AIT_ATTN_NO_SYNCWARP
     __syncwarp();
+#endif
   } else if (warp == 1) {
+    // P V issuer: O(item) += P(g) V(g) as soon as the softmax threads have put P(g) into TMEM
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_f16(kBlockM, kBlockN, BF16, false, false);
       constexpr uint32_t idesc_t = umma_idesc_f16(kBlockM, Cfg::kTWidth, BF16, false, true);  // V is MN-major
-      const uint32_t q_addr = smem_u32(sQ);
       bool ok = true;
-      // S(g) = Q K(g)^T into S buffer g & 1 (g = global key-block index)
-      auto issue_s = [&](int g) -> bool {
-        const int st = g % kKvStages;
-        if (!mbar_wait(&kv_full[st], (g / kKvStages) & 1, abort_flag, p.status, kDevWaitFullTimeout)) return false;
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(sKV + st * 2 * Cfg::kKBytes);
-        for (int k = 0; k < dsteps; ++k) {
-          const int c = k >> 2, kk = k & 3;
-          const uint64_t adesc = umma_smem_desc_sw128(q_addr + c * kBlockM * 128 + kk * 32, 16, 1024);
-          const uint64_t bdesc = umma_smem_desc_sw128(k_addr + c * kBlockN * 128 + kk * 32, 16, 1024);
-          umma_f16_ss(tmem_s + static_cast<uint32_t>((g & 1) * kBlockN), adesc, bdesc, idesc_s, k != 0 ? 1u : 0u);
-        }
-        umma_commit(&s_full[g & 1]);
-        return true;
-      };
+      ATTN_PROBE_DECL(blockIdx.x == 0)
       int gb = 0;  // global index of the item's first key block
       int it = 0;
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
         const Item w = decode_item(item);
         const int n_blocks = w.n_blocks;
         if (n_blocks == 0) continue;
-        ok = mbar_wait(q_full, it & 1, abort_flag, p.status, kDevWaitFullTimeout);
-        if (ok) ok = issue_s(gb);
-        if (ok && n_blocks > 1) ok = issue_s(gb + 1);
-        if (ok && n_blocks <= 2) umma_commit(q_empty);  // every S of this item has been issued
         // this item's O buffer was last used by item it - 2: its rows must have been read out
-        if (ok) ok = mbar_wait(&o_empty[it & 1], ((it >> 1) & 1) ^ 1u, abort_flag, p.status, kDevWaitAccEmptyTimeout);
+        ok = mbar_wait(&o_empty[it & 1], ((it >> 1) & 1) ^ 1u, abort_flag, p.status, kDevWaitAccEmptyTimeout);
         const uint32_t o_addr = tmem_o + static_cast<uint32_t>((it & 1) * Cfg::kTWidth);
         for (int j = 0; ok && j < n_blocks; ++j) {
           const int g = gb + j;
+          ATTN_PROBE(1)  // loop bookkeeping
           ok = mbar_wait(&p_full[g & 1], (g >> 1) & 1, abort_flag, p.status, kDevWaitOtherTimeout);
           if (!ok) break;
           tc_fence_after();
-          const int st = g % kKvStages;
-          const uint32_t p_addr = smem_u32(sP + (g & 1) * Cfg::kPBytes);
+          ATTN_PROBE(2)  // wait for P
+          const int st = g % Cfg::kKvStages;
+          const uint32_t p_tmem = tmem_s + static_cast<uint32_t>((g & 1) * kBlockN);
           const uint32_t v_addr = smem_u32(sKV + st * 2 * Cfg::kKBytes + Cfg::kKBytes);
 #pragma unroll
           for (int k = 0; k < kBlockN / 16; ++k) {
-            const uint64_t adesc = umma_smem_desc_sw128(p_addr + k * 32, 16, 1024);
+            // A = P from TMEM: 16 keys of a row are 8 columns of 16-bit pairs.
             // V block rows are keys (128 B each): 16 keys per step = 2048 B; 64-wide d chunks are
             // kBlockN*128 B apart (leading byte offset), 8-key groups 1024 B apart (stride byte offset)
             const uint64_t bdesc = umma_smem_desc_sw128(v_addr + k * 2048, kBlockN * 128, 1024);
-            umma_f16_ss(o_addr, adesc, bdesc, idesc_t, (j != 0 || k != 0) ? 1u : 0u);
+            umma_f16_ts(o_addr, p_tmem + k * 8, bdesc, idesc_t, (j != 0 || k != 0) ? 1u : 0u);
           }
-          umma_commit(&pv_done[g & 1]);
-          umma_commit(&kv_empty[st]);
-          if (j + 1 == n_blocks) umma_commit(&o_full[it & 1]);
-          if (j + 2 < n_blocks) {
-            ok = issue_s(g + 2);
-            if (ok && j + 3 == n_blocks) umma_commit(q_empty);
-          }
+          umma_commit(&kv_empty[st]);  // K/V stage free; also "P(g) V(g) is in O" for the softmax threads and the S issuer
+          ATTN_PROBE(0)  // issue of the 4 P V MMAs + commit
         }
         gb += n_blocks;
         ++it;
       }
+      ATTN_PROBE_FLUSH(16)
       if (!ok) {
         umma_commit(drain_bar);
         const uint64_t t0 = globaltimer_ns();
@@ -309,7 +329,62 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
         }
       }
     }
+#ifndef B200AIT_ATTN_NO_SYNCWARP
     __syncwarp();
+#endif
+  } else if (warp == 6) {
+    // S issuer: S(g) = Q K(g)^T into S buffer g & 1 (g = global key-block index). A second issuing thread, so that
+    // waiting for P and issuing P V never delays the scores of the blocks ahead (and the other way round): one
+    // thread issuing both spent as long on its own waits and commits as the softmax threads on a block.
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_f16(kBlockM, kBlockN, BF16, false, false);
+      bool ok = true;
+      int gb = 0;
+      int it = 0;
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        const Item w = decode_item(item);
+        const int n_blocks = w.n_blocks;
+        if (n_blocks == 0) continue;
+        const int qb = it % Cfg::kQBufs;
+        const uint32_t q_addr = smem_u32(sQ + qb * Cfg::kQBytes);
+        ok = mbar_wait(&q_full[qb], static_cast<uint32_t>(it / Cfg::kQBufs) & 1u, abort_flag, p.status, kDevWaitFullTimeout);
+        for (int j = 0; ok && j < n_blocks; ++j) {
+          const int g = gb + j;
+          const int st = g % Cfg::kKvStages;
+          // S buffer g & 1 still holds P(g - 2) until P(g - 2) V(g - 2) has completed (un-aliasing P, so that the
+          // scores only wait for the softmax threads to have loaded S(g - 2), was measured: no faster)
+          if (g >= 2)
+            ok = mbar_wait(&kv_empty[(g - 2) % Cfg::kKvStages], ((g - 2) / Cfg::kKvStages) & 1, abort_flag, p.status,
+                           kDevWaitAccEmptyTimeout);
+          if (ok) ok = mbar_wait(&kv_full[st], (g / Cfg::kKvStages) & 1, abort_flag, p.status, kDevWaitFullTimeout);
+          if (!ok) break;
+          tc_fence_after();
+#ifdef B200AIT_ATTN_PROBE
+          if (blockIdx.x == 0) g_attn_probe[20] += 1;  // S tiles issued
+#endif
+          const uint32_t k_addr = smem_u32(sKV + st * 2 * Cfg::kKBytes);
+          for (int k = 0; k < dsteps; ++k) {
+            const int c = k >> 2, kk = k & 3;
+            const uint64_t adesc = umma_smem_desc_sw128(q_addr + c * kBlockM * 128 + kk * 32, 16, 1024);
+            const uint64_t bdesc = umma_smem_desc_sw128(k_addr + c * kBlockN * 128 + kk * 32, 16, 1024);
+            umma_f16_ss(tmem_s + static_cast<uint32_t>((g & 1) * kBlockN), adesc, bdesc, idesc_s, k != 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[g & 1]);
+          if (j + 1 == n_blocks) umma_commit(&q_empty[qb]);  // every S of this item has been issued: its Q may be replaced
+        }
+        gb += n_blocks;
+        ++it;
+      }
+      if (!ok) {
+        umma_commit(drain_bar + 1);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(drain_bar + 1, 0) && globaltimer_ns() - t0 < 1000000ull) {
+        }
+      }
+    }
+#ifndef B200AIT_ATTN_NO_SYNCWARP
+    __syncwarp();
+#endif
   } else {
     using E = Elem16<BF16>;
     using T = typename E::T;
@@ -319,6 +394,49 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
     bool ok = true;
     int gb = 0;  // global index of the item's first key block
     int it = 0;
+    ATTN_PROBE_DECL(blockIdx.x == 0 && threadIdx.x == 64)
+    // The read-out of an item's O (wait for its last P V, O / row sum -> global memory) is deferred until this thread
+    // has handed the NEXT item's first P block to the tensor core: by then the last P V has long completed, so the
+    // thread never waits for it, and its TMEM loads and stores overlap the other warps' exponentials. O is
+    // double-buffered on the item's parity, which is what makes the deferral legal.
+    struct Pending {
+      bool valid = false;
+      int it = 0, last_g = 0;   // item counter (selects the O buffer) and global index of its last key block
+      float inv_l = 0.f;
+      T* out = nullptr;         // this row's output; null when the row lies past the end of its sequence
+    } pend;
+    auto flush_pending = [&]() -> bool {
+      if (!pend.valid) return true;
+      pend.valid = false;
+      // the item's O is complete once its last P V has been accumulated
+      if (!mbar_wait(&kv_empty[pend.last_g % Cfg::kKvStages], (pend.last_g / Cfg::kKvStages) & 1, abort_flag, p.status,
+                     kDevWaitAccFullTimeout))
+        return false;
+      tc_fence_after();
+      const uint32_t o_prev = tmem_o + lane_addr + static_cast<uint32_t>((pend.it & 1) * Cfg::kTWidth);
+#pragma unroll
+      for (int c = 0; c < DCH * 2; ++c) {
+        if (c * 32 < p.Dv) {  // warp-uniform
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(o_prev + c * 32, v);
+          tmem_ld_wait();
+          if (pend.out != nullptr) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (c * 32 + u * 8 < p.Dv) {
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[u * 8 + i]) * pend.inv_l;
+                *reinterpret_cast<uint4*>(pend.out + c * 32 + u * 8) = pack8<BF16>(f);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&o_empty[pend.it & 1]);
+      return true;
+    };
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
       const Item w = decode_item(item);
       const int n_blocks = w.n_blocks, kv_len = w.kv_len;
@@ -331,6 +449,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
         ok = mbar_wait(&s_full[g & 1], (g >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout);
         if (!ok) break;
         tc_fence_after();
+        ATTN_PROBE(0)  // wait for S (and whatever the loop does before it)
         const uint32_t s_addr = tmem_s + lane_addr + static_cast<uint32_t>((g & 1) * kBlockN);
         const int key0 = j * kBlockN;
         int limit = kv_len - key0;  // keys [0, limit) of this block are visible to this row
@@ -343,7 +462,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
         tmem_ld_32x32b_x32(s_addr, s0);
         tmem_ld_32x32b_x32(s_addr + 32, s1);
         tmem_ld_wait();
-        uint8_t* row_base = sP + (g & 1) * Cfg::kPBytes + r * 128;
+        ATTN_PROBE(1)  // S from TMEM
         float l0 = 0.f, l1 = 0.f;
         // One body, compiled twice: kPlain drops every per-element mask.
         auto softmax_block = [&](auto plain_tag) {
@@ -376,7 +495,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
             if (j > 0) {
               // O holds blocks 0 .. j-1 once P(j-1) V(j-1) is done; P(j) V(j) cannot start before this
               // thread's arrival on p_full below
-              if (!mbar_wait(&pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout)) {
+              if (!mbar_wait(&kv_empty[(g - 1) % Cfg::kKvStages], ((g - 1) / Cfg::kKvStages) & 1, abort_flag, p.status,
+                             kDevWaitAccFullTimeout)) {
                 ok = false;
               } else {
                 tc_fence_after();
@@ -404,35 +524,35 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
             }
             m_ref = m_new;
           }
+          ATTN_PROBE(2)  // row max (+ rescale when it happens)
           const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-          // p = exp2(s * scale - m_ref), row sum, P -> swizzled shared memory (16-byte unit u of row r sits
-          // at unit u ^ (r & 7))
+          // p = exp2(s * scale - m_ref), row sum, P rounded to 16 bits (kernel_forward.h:785-824) and written as
+          // pairs over the first 32 columns of this S buffer: every S value of the row is in registers by now
           const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
           uint64_t lsum2 = pack2(0.f, 0.f);
+          uint32_t packed[32];
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const uint32_t(&sv)[32] = h == 0 ? s0 : s1;
-            uint32_t packed[16];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
               float x0, x1;
               unpack2(fma2(pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), scale2, negm2), x0, x1);
+#ifdef B200AIT_ATTN_EXP_SKIP  // tuning experiment: no exponentials, to expose the MMA side's own pace
+              float p0 = x0, p1 = x1;
+#else
               float p0 = exp2f(x0);
               float p1 = exp2f(x1);
+#endif
               if (!kPlain) {
                 p0 = (h * 32 + i < limit) ? p0 : 0.f;
                 p1 = (h * 32 + i + 1 < limit) ? p1 : 0.f;
               }
               lsum2 = add2(lsum2, pack2(p0, p1));
-              packed[i >> 1] = E::from_float2(p0, p1);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int unit = (h * 4 + u) ^ (r & 7);
-              *reinterpret_cast<uint4*>(row_base + unit * 16) =
-                  make_uint4(packed[u * 4], packed[u * 4 + 1], packed[u * 4 + 2], packed[u * 4 + 3]);
+              packed[h * 16 + (i >> 1)] = E::from_float2(p0, p1);
             }
           }
+          tmem_st_32x32b_x32(s_addr, packed);
           unpack2(lsum2, l0, l1);
         };
         if constexpr (NOMASK) {
@@ -444,41 +564,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
             softmax_block(std::false_type{});
         }
         l_run += l0 + l1;
+        tmem_st_wait();  // P is in TMEM
         tc_fence_before();
-        fence_proxy_async_smem();
         mbar_arrive(&p_full[g & 1]);
+        ATTN_PROBE(3)  // exp2 pass, P to TMEM, fence, arrive
+        if (j == 0 && ok) ok = flush_pending();  // the previous item's O, now that this item's first P is on its way
       }
       gb += n_blocks;
-      // the item's O is complete once its last P V has been accumulated
-      if (ok) ok = mbar_wait(&o_full[it & 1], (it >> 1) & 1, abort_flag, p.status, kDevWaitAccFullTimeout);
       if (ok) {
-        tc_fence_after();
-        const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
-        T* out = static_cast<T*>(p.out) + ((w.out_row0 + q_idx) * p.H + w.h) * p.Dv;
-#pragma unroll
-        for (int c = 0; c < DCH * 2; ++c) {
-          if (c * 32 < p.Dv) {  // warp-uniform
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(o_addr + c * 32, v);
-            tmem_ld_wait();
-            if (q_idx < w.q_len) {
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                if (c * 32 + u * 8 < p.Dv) {
-                  float f[8];
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[u * 8 + i]) * inv;
-                  *reinterpret_cast<uint4*>(out + c * 32 + u * 8) = pack8<BF16>(f);
-                }
-              }
-            }
-          }
-        }
-        tc_fence_before();
-        mbar_arrive(&o_empty[it & 1]);
+        pend.valid = true;
+        pend.it = it;
+        pend.last_g = gb - 1;
+        pend.inv_l = (l_run > 0.f) ? 1.f / l_run : 0.f;
+        pend.out = (q_idx < w.q_len) ? static_cast<T*>(p.out) + ((w.out_row0 + q_idx) * p.H + w.h) * p.Dv : nullptr;
       }
+      ATTN_PROBE(0)  // item bookkeeping (booked with the wait for S)
       ++it;
     }
+    if (ok) ok = flush_pending();  // the last item of this CTA
+    ATTN_PROBE_FLUSH(0)
   }
 
   tc_fence_before();
@@ -600,7 +704,11 @@ void launch_attn_variant(const AttnOperand& q, const AttnOperand& k, const AttnO
   AttnParams pp = p;
   pp.num_items = static_cast<int>(items);
   pp.q_order = attn_map_order(q), pp.k_order = attn_map_order(k), pp.v_order = attn_map_order(v);
+#ifdef B200AIT_ATTN_ONE_CTA  // tuning experiment: one CTA per SM
+  const long long grid = std::min<long long>(items, static_cast<long long>(sm_count()));
+#else
   const long long grid = std::min<long long>(items, static_cast<long long>(sm_count()) * (DCH == 1 ? 2 : 1));
+#endif
   ::b200ait::count_launch(), attention_tc_kernel<DCH, BF16, NOMASK><<<static_cast<unsigned>(grid), kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv,
                                                                                                                  pp);
   B200AIT_CUDA_CHECK(cudaGetLastError());
@@ -771,3 +879,15 @@ B200AIT_EXPORT int b200ait_flash_attention(void* output, const void* qkv, const 
     attention_run(output, q, k, v, p, total_rows, total_rows, false, dtype == kDTypeBFloat16, stream);
   });
 }
+
+#ifdef B200AIT_ATTN_PROBE
+// tuning builds only: copies the probe counters to the host and clears them
+B200AIT_EXPORT int b200ait_attn_probe_read(long long* out32) {
+  return guarded("b200ait_attn_probe_read", [&] {
+    B200AIT_CUDA_CHECK(cudaDeviceSynchronize());
+    B200AIT_CUDA_CHECK(cudaMemcpyFromSymbol(out32, g_attn_probe, sizeof(long long) * 32));
+    long long zero[32] = {};
+    B200AIT_CUDA_CHECK(cudaMemcpyToSymbol(g_attn_probe, zero, sizeof(zero)));
+  });
+}
+#endif
