@@ -536,3 +536,35 @@ def test_multihead_attention_default_flash_path_matches_oracle(workdir):
         res = module.run_with_tensors({"hidden_states": xh.cuda()}, {"output_0": out}, graph_mode=graph_mode)
         _close(res["output_0"], want, 2e-2)
     module.close()
+
+
+def test_dynamic_m_reserves_split_k_workspace_for_interior_sizes(workdir):
+    """Split-K demand is not monotonic in M (nothing at M = 1, nothing once the tiles fill the SMs, most in
+    between), so a dynamic M in [1, 4096] must reserve scratch for the interior sizes, not only for its bounds;
+    otherwise M = 256 silently runs unsplit."""
+    import ctypes
+
+    from aitemplate_b200 import kernels
+    from aitemplate_b200.compiler import AITemplateAllocatorKind
+
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    k, n = 8192, 1024
+    need = kernels.gemm_workspace_bytes(1, 256, n, k)
+    assert need > 0, "M = 256 is meant to split K"
+    assert kernels.gemm_workspace_bytes(1, 4096, n, k) == 0 or kernels.gemm_workspace_bytes(1, 4096, n, k) < need
+    X = Tensor(shape=[IntVar([1, 4096], name="m"), k], dtype="float16", name="input_0", is_input=True)
+    W = Tensor(shape=[n, k], dtype="float16", name="input_1", is_input=True)
+    B = Tensor(shape=[n], dtype="float16", name="input_2", is_input=True)
+    Y = ops.gemm_rcr_bias_relu()(X, W, B)
+    Y._attrs["name"], Y._attrs["is_output"] = "output_0", True
+    module = compile_model(Y, detect_target(), workdir, "dyn_m_workspace", allocator_kind=AITemplateAllocatorKind.TRACKING)
+    nbytes = ctypes.c_size_t(0)
+    module.DLL.AITemplateTrackingAllocatorGetNumBytes(module.allocator_handle, ctypes.byref(nbytes))
+    assert nbytes.value >= need, (nbytes.value, need)
+    w, b = _rand((n, k), 2, 0.02), _rand((n,), 3)
+    for m in (1, 256, 300, 4096):
+        x = _rand((m, k), 10 + m)
+        y = torch.empty((4096, n), dtype=torch.float16, device="cuda")
+        res = module.run_with_tensors({"input_0": x.cuda(), "input_1": w.cuda(), "input_2": b.cuda()}, [y])
+        _close(res["output_0"], oracle.gemm_rcr(x, w, b, epilogue="relu"))
+    module.close()
