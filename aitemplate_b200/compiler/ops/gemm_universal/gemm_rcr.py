@@ -97,9 +97,12 @@ class gemm(Operator):
         return {
             "kernel": "gemm_rcr",
             "operands": [a, b, bias, d0, d1],
-            # ints 7, 8: tile width and split-K picked by the compile-time profiler (0 = the library decides)
+            # ints 7, 8: tile width and split-K picked by the compile-time profiler; 0 = the library decides at run
+            # time from the actual M. The `split_k` attribute's default of 1 is the reference's placeholder for "not
+            # profiled yet" (gemm_common.py:579-594), not a request to never split.
             "ints": [epilogue_code(*self._epi), store_mode, t[0], t[1], t[2], acc.offset, out_stride,
-                     int(self._attrs.get("tile_n", 0)), int(self._attrs.get("split_k", 0)), a_stride],
+                     int(self._attrs.get("tile_n", 0)) if self._attrs.get("profiled") else 0,
+                     int(self._attrs.get("split_k", 0)) if self._attrs.get("profiled") else 0, a_stride],
             "floats": [float(self._attrs["alpha"])],
         }
 

@@ -69,6 +69,7 @@ def profile_gemms(sorted_graph: List[Tensor], cache, timer: Optional[Callable] =
                              split_k, us)
         if best is not None:
             op._attrs["tile_n"], op._attrs["split_k"] = best
+            op._attrs["profiled"] = True
             chosen[op._attrs["name"] or op._attrs["op"]] = best
     if dirty:
         cache.save()

@@ -193,6 +193,34 @@ PREHEAT_MS = 120.0   # untimed steps (flush + graph replay, the timed pattern) b
 LEAD_IN_STEPS = 5    # untimed steps right after the barrier, so the host runs ahead of the GPU in the timed steps
 
 
+def _bind_to_gpu_numa_node(local_rank: int):
+    """Pins this process to the CPUs NVML reports as local to its GPU (read-only query), so that the pinned host
+    buffers of the end-to-end pipeline are allocated on that NUMA node: with several ranks per box, copies from a
+    remote node share one inter-socket link. Returns the previous affinity (restore it before CPU-side timing)."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        phys = local_rank
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if visible:
+            ids = [v for v in visible.split(",") if v.strip()]
+            if local_rank < len(ids) and ids[local_rank].strip().isdigit():
+                phys = int(ids[local_rank])
+        handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = {64 * i + b for i, w in enumerate(mask) for b in range(64) if (w >> b) & 1}
+        old = os.sched_getaffinity(0)
+        cpus &= old
+        if cpus and cpus != old:
+            os.sched_setaffinity(0, cpus)
+            return old
+    except Exception:
+        pass
+    return None
+
+
 def _gather_rows(dist, row):
     """All ranks contribute one list of floats; every rank gets the [world, len] table."""
     import torch
@@ -226,6 +254,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     from aitemplate_b200.testing import detect_target, workloads
 
     torch.cuda.set_device(local_rank)
+    old_affinity = _bind_to_gpu_numa_node(local_rank) if world > 1 else None
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -297,13 +326,13 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     med_ms = statistics.median(step_ms)
     table = _gather_rows(dist, [total_ms, step_ms[0], med_ms, step_ms[int(0.9 * (len(step_ms) - 1))], step_ms[-1],
                                 wall_s * 1000.0, enqueue_s * 1000.0, clocks.get("sm_mhz") or 0.0,
-                                float(len(clocks.get("reasons", [])))])
+                                float(len(clocks.get("reasons", []))), float(len(os.sched_getaffinity(0)))])
     slowest = max(range(world), key=lambda r: table[r][0])
     total_ms = table[slowest][0]
     value = world * BATCH * args.steps / (total_ms / 1000.0)
     per_rank = [{"rank": r, "sum_ms": round(t[0], 3), "step_ms_min": round(t[1], 4), "step_ms_median": round(t[2], 4),
                  "step_ms_p90": round(t[3], 4), "step_ms_max": round(t[4], 4), "wall_ms_between_barriers": round(t[5], 2),
-                 "host_enqueue_ms": round(t[6], 2), "sm_mhz_median": t[7], "clock_reasons_seen": int(t[8])}
+                 "host_enqueue_ms": round(t[6], 2), "sm_mhz_median": t[7], "clock_reasons_seen": int(t[8]), "host_cpus_bound": int(t[9])}
                 for r, t in enumerate(table)]
 
     # ---- end to end through the public API: every step copies its input from pinned host memory to the
@@ -383,6 +412,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         return
 
     # ---- rank 0 alone from here on (the other ranks have left; nothing below is inside a timed region)
+    if old_affinity is not None:
+        os.sched_setaffinity(0, old_affinity)  # the CPU baseline uses every host core
     # roofline of the dominant kernel (the tcgen05 GEMM, 4 launches per step): per-op CUDA-event times from the
     # runtime's profiler (each op timed alone after an L2 flush)
     prof_path = os.path.join(workdir, "profile.json")
