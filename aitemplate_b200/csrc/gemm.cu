@@ -100,6 +100,35 @@ __device__ __forceinline__ void epilogue_scalar_store(const GemmParams& p, float
   static_cast<T*>(p.out)[batch_offset(p, b) + row_offset(p, row) + col_offset(p, col)] = E::from_float(v);
 }
 
+// The fused epilogue on 8 consecutive columns of one row whose 16-byte accesses are legal; the bias is already
+// in registers. Kept small on purpose: the weight-streaming kernel runs it once, at its very end, from a cold
+// instruction cache.
+template <bool BF16>
+__device__ __forceinline__ void epilogue_row8_store(const GemmParams& p, float (&v)[8], const float (&bias_v)[8],
+                                                    int row, int col0) {
+  using T = typename Elem16<BF16>::T;
+  const int u1 = epi_u1(p.epilogue), b1 = epi_b1(p.epilogue), b2 = epi_b2(p.epilogue), u2 = epi_u2(p.epilogue);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = v[e] * p.alpha + bias_v[e];
+  apply_unary_vec(u1, v);
+  const long long d_base = static_cast<long long>(row) * p.ldd + col0;
+  if (b1 != kBinaryNone) {
+    float f[8];
+    unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.d0) + d_base)), f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = (b1 == kBinaryAdd) ? v[e] + f[e] : v[e] * f[e];
+  }
+  if (b2 != kBinaryNone) {
+    float f[8];
+    unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.d1) + d_base)), f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = (b2 == kBinaryAdd) ? v[e] + f[e] : v[e] * f[e];
+  }
+  apply_unary_vec(u2, v);
+  T* out = static_cast<T*>(p.out) + row_offset(p, row) + col_offset(p, col0);
+  *reinterpret_cast<uint4*>(out) = pack8<BF16>(v);
+}
+
 // ------------------------------------------------------------------------------------------------
 // CUDA-core kernel for shapes TMA cannot address. 32x32 output tile per block, K staged in smem.
 template <bool BF16>
@@ -199,6 +228,300 @@ __global__ void __launch_bounds__(kRowDotThreads, 1) gemm_rowdot_kernel(const vo
       if (lane == m && m < p.M) epilogue_scalar_store<BF16>(p, t, 0, m, n);
     }
   }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Weight-streaming tensor-core kernel for 5 <= M <= 32 with the operands swapped: Y^T = W X^T.
+// The run time of such a GEMM is the time to read W once. Here the rows of W sit on the 128 MMA rows and the few
+// rows of X are the MMA's N (16 or 32), so a CTA consumes 16 KB of weights per four short MMAs, and W is
+// partitioned so that every byte is read by exactly one CTA: a cluster of two CTAs owns a slab of 128 weight rows,
+// rank r streams half r of K through an 8-stage TMA ring, and rank 1 hands its 128 x MX fp32 partial sums to
+// rank 0 through the cluster's shared-memory window. No global workspace, no second pass (the 128 x 256 tiles +
+// split-K + reduce kernel this replaces ran at 0.54 of the copy rate for these shapes).
+//   warp 0: TMA producer   warp 1: MMA issuer   warps 2-5: epilogue (TMEM lane = weight row = output column)
+constexpr int kSwapThreads = 192;
+constexpr int kSwapMaxM = 128;
+template <int MX>
+struct SwapCfg {
+  static constexpr int kWBytes = 128 * kBK * 2;     // 16 KB: 128 weight rows x 64 k
+  static constexpr int kXBytes = MX * kBK * 2;      // MX rows of X x 64 k
+  static constexpr int kStageBytes = kWBytes + kXBytes;
+  static constexpr int kPartialBytes = 128 * (MX / 2) * 4;  // the half of the peer's sums this rank finishes
+  static constexpr int kStages = MX <= 64 ? 8 : 6;  // what fits beside the partial sums: 144 to 192 KB in flight
+  static constexpr int kAccCols = MX < 32 ? 32 : MX;  // TMEM columns of one accumulator
+  static constexpr int kTmemCols = 2 * kAccCols;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kPartialBytes + 256;
+  static_assert(kSmemBytes <= 227 * 1024, "swapped-operand kernel: shared memory");
+};
+
+template <int N>
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[N]) {
+  static_assert(N == 8 || N == 16 || N == 32, "TMEM load width");
+  if constexpr (N == 8) {
+    tmem_ld_32x32b_x8(taddr, r);
+  } else if constexpr (N == 16) {
+    tmem_ld_32x32b_x16(taddr, r);
+  } else {
+    tmem_ld_32x32b_x32(taddr, r);
+  }
+}
+
+template <bool BF16, int MX>
+__global__ void __launch_bounds__(kSwapThreads, 1)
+gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
+                   const GemmParams p, const int num_slabs) {
+  using Cfg = SwapCfg<MX>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const bool misaligned = (smem_u32(smem) & 1023u) != 0u;
+  if (misaligned && threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevBadSmemAlignment);
+  float* partial = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);  // [MX / 2][128], written by the peer
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes);
+  uint64_t* empty_bar = full_bar + Cfg::kStages;
+  uint64_t* acc_full = empty_bar + Cfg::kStages;   // [2]
+  uint64_t* acc_empty = acc_full + 2;             // [2]
+  uint64_t* partial_ready = acc_empty + 2;        // the peer's partial sums are in `partial`
+  uint64_t* partial_taken = partial_ready + 1;    // the peer has read the sums this CTA sent
+  uint64_t* drain_bar = partial_taken + 1;
+  uint64_t* tile_summed = drain_bar + 1;          // every thread has added its own sums into `partial`
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_summed + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  static_assert((2 * Cfg::kStages + 8) * 8 + 8 <= 256, "barrier area too small");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());
+  const int walker = blockIdx.x >> 1, num_walkers = gridDim.x >> 1;
+  const int my_slabs = misaligned ? 0 : num_slabs;
+  // this rank's half of the k-blocks
+  const int kb_total = (p.K + kBK - 1) / kBK;
+  const int kb_half = (kb_total + 1) / 2;
+  const int kb0 = rank == 0 ? 0 : kb_half, kb1 = rank == 0 ? kb_half : kb_total;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 128);
+    }
+    mbar_init(partial_ready, 128);
+    mbar_init(partial_taken, 128);
+    mbar_init(drain_bar, 1);
+    mbar_init(tile_summed, 128);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tma_w);
+    tma_prefetch_desc(&tma_x);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);  // two accumulators
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int slab = walker; ok && slab < my_slabs; slab += num_walkers) {
+        // Every CTA reads the same rows of X. Walking the k-blocks from a different starting point in every
+        // cluster keeps the CTAs from asking L2 for the same lines of X at the same moment.
+        const int nkb = kb1 - kb0;
+        const int rot = nkb > 0 ? static_cast<int>((static_cast<unsigned>(slab) * 11u) % static_cast<unsigned>(nkb)) : 0;
+        for (int i = 0; i < nkb; ++i) {
+          const int kb = kb0 + (i + rot >= nkb ? i + rot - nkb : i + rot);
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
+          if (!ok) break;
+          uint8_t* sw = smem + stage * Cfg::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          tma_load_3d(sw, &tma_w, &full_bar[stage], kb * kBK, slab * 128, 0);
+          tma_load_3d(sw + Cfg::kWBytes, &tma_x, &full_bar[stage], kb * kBK, 0, 0);
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(128, MX, BF16, false, false);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int slab = walker; ok && slab < my_slabs; slab += num_walkers) {
+        ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, kDevWaitAccEmptyTimeout);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * Cfg::kAccCols);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kDevWaitFullTimeout);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t w_addr = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t x_addr = w_addr + Cfg::kWBytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t adesc = umma_smem_desc_sw128(w_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = umma_smem_desc_sw128(x_addr + k * 32, 16, 1024);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      if (!ok) {
+        umma_commit(drain_bar);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 1000000ull) {
+        }
+      }
+    }
+  } else {
+    // Both ranks finish half of the slab's rows of X: rank r keeps rows [r * MX/2, (r + 1) * MX/2) of its own
+    // sums, sends the other half to its peer's `partial`, adds what the peer sent and writes its rows out.
+    constexpr int kHalf = MX / 2;
+    constexpr int kChunk = kHalf < 32 ? kHalf : 32;  // TMEM columns per load
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // weight row inside the slab == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t peer = static_cast<uint32_t>(rank ^ 1);
+    const uint32_t peer_partial = mapa_shared(smem_u32(partial), peer);
+    const uint32_t peer_ready = mapa_shared(smem_u32(partial_ready), peer);
+    const uint32_t peer_taken = mapa_shared(smem_u32(partial_taken), peer);
+    const int my_row0 = rank * kHalf, peer_row0 = (rank ^ 1) * kHalf;
+    const int my_rows = p.M - my_row0 < 0 ? 0 : (p.M - my_row0 < kHalf ? p.M - my_row0 : kHalf);
+    const bool peer_has_rows = p.M > peer_row0;
+    const int et = static_cast<int>(threadIdx.x) - 64;  // 0..127 over the four epilogue warps
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int it = 0;
+    bool ok = true;
+    for (int slab = walker; ok && slab < my_slabs; slab += num_walkers, ++it) {
+      // The tile goes out row by row: a thread takes 8 consecutive columns (one 16-byte store), 16 threads one
+      // row of the slab. A thread keeps the same columns for every row, so it fetches their bias once, early.
+      const int col0 = slab * 128 + (et & 15) * 8;
+      const bool vec = p.vec_ok && col0 + 8 <= p.N;
+      float bias_v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (vec && p.bias != nullptr && my_rows > 0)
+        unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(static_cast<const typename Elem16<BF16>::T*>(p.bias) + col0)),
+                      bias_v);
+      ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, kDevWaitAccFullTimeout);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + lane_addr + static_cast<uint32_t>(acc * Cfg::kAccCols);
+      // the peer must have read what this CTA sent for the previous slab before it is overwritten
+      if (it > 0) ok = mbar_wait_cluster(partial_taken, (it - 1) & 1, abort_flag, p.status, kDevWaitOtherTimeout);
+#pragma unroll
+      for (int c = 0; c < kHalf / kChunk; ++c) {
+        uint32_t v[kChunk];
+        tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(peer_row0 + c * kChunk), v);
+        tmem_ld_wait();
+        if (ok && peer_has_rows) {
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j)
+            st_shared_cluster_f32(peer_partial + static_cast<uint32_t>(((c * kChunk + j) * 128 + row) * 4),
+                                  __uint_as_float(v[j]));
+        }
+      }
+      if (ok) mbar_arrive_cluster(peer_ready);  // release at cluster scope: the stores above are visible to the waiter
+      if (ok) ok = mbar_wait_cluster(partial_ready, it & 1, abort_flag, p.status, kDevWaitOtherTimeout);
+#pragma unroll
+      for (int c = 0; c < kHalf / kChunk; ++c) {
+        uint32_t v[kChunk];
+        tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(my_row0 + c * kChunk), v);
+        tmem_ld_wait();
+        if (ok && my_rows > 0) {
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) partial[(c * kChunk + j) * 128 + row] += __uint_as_float(v[j]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+      if (ok) {
+        mbar_arrive(tile_summed);
+        ok = mbar_wait(tile_summed, it & 1, abort_flag, p.status, kDevWaitOtherTimeout);
+      }
+      if (ok) {
+        // two rows (j and j + 8) per trip: two independent chains for the one warp each scheduler has
+        for (int j = et >> 4; j < my_rows; j += 16) {
+          const bool two = j + 8 < my_rows;
+          const float* src0 = partial + j * 128 + (et & 15) * 8;
+          const float* src1 = src0 + (two ? 8 * 128 : 0);
+          if (vec) {
+            const float4 a0 = *reinterpret_cast<const float4*>(src0), a1 = *reinterpret_cast<const float4*>(src0 + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(src1), b1 = *reinterpret_cast<const float4*>(src1 + 4);
+            float oa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            float ob[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            epilogue_row8_store<BF16>(p, oa, bias_v, my_row0 + j, col0);
+            if (two) epilogue_row8_store<BF16>(p, ob, bias_v, my_row0 + j + 8, col0);
+          } else {
+#pragma unroll 1
+            for (int e = 0; e < 8; ++e)
+              if (col0 + e < p.N) {
+                epilogue_scalar_store<BF16>(p, src0[e], 0, my_row0 + j, col0 + e);
+                if (two) epilogue_scalar_store<BF16>(p, src1[e], 0, my_row0 + j + 8, col0 + e);
+              }
+          }
+        }
+        mbar_arrive_cluster(peer_taken);  // this thread is done reading: the peer may send the next slab's sums
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while its peer can still write to it or signal it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <bool BF16, int MX>
+static void launch_swapab(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int num_slabs,
+                          cudaStream_t stream) {
+  using Cfg = SwapCfg<MX>;
+  static std::atomic<uint64_t> configured{0};
+  auto* kernel = &gemm_swapab_kernel<BF16, MX>;
+  opt_in_smem_once(configured, reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * std::min(num_slabs, sm_count() / 2)));
+  cfg.blockDim = dim3(kSwapThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  ::b200ait::count_launch();
+  B200AIT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, tw, tx, p, num_slabs));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -457,6 +780,25 @@ void gemm_run(const GemmArgs& g_in) {
     }
 #undef B200AIT_ROWDOT
     B200AIT_CUDA_CHECK(cudaGetLastError());
+    return;
+  }
+  // 5 <= M <= 128 against a big weight matrix, tile width and split-K left to the library: stream W once with the
+  // operands swapped (W rows on the MMA rows), K halved across a cluster of two, no workspace
+  if (tma_ok && g.batch == 1 && g.m <= kSwapMaxM && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0 &&
+      g.k >= 2048 && g.n >= 2048) {
+    const int num_slabs = static_cast<int>((g.n + 127) / 128);
+    const int mx = g.m <= 16 ? 16 : g.m <= 32 ? 32 : g.m <= 64 ? 64 : 128;
+    CUtensorMap tw = make_tile_map(g.b, bf16, g.k, g.n, 1, g.ldb, 0, 128);
+    CUtensorMap tx = make_tile_map(g.a, bf16, g.k, g.m, 1, g.lda, 0, mx);
+#define B200AIT_SWAP(MX)                                                   \
+  do {                                                                     \
+    if (bf16)                                                              \
+      launch_swapab<true, MX>(tw, tx, p, num_slabs, g.stream);             \
+    else                                                                   \
+      launch_swapab<false, MX>(tw, tx, p, num_slabs, g.stream);            \
+  } while (0)
+    if (mx == 16) B200AIT_SWAP(16); else if (mx == 32) B200AIT_SWAP(32); else if (mx == 64) B200AIT_SWAP(64); else B200AIT_SWAP(128);
+#undef B200AIT_SWAP
     return;
   }
   if (!tma_ok) {
@@ -876,3 +1218,4 @@ B200AIT_EXPORT int b200ait_gemm_rcr_static_scratch(const void* a, const void* b,
       B200AIT_CUDA_CHECK(cudaMemcpyAsync(status_out, status, sizeof(int), cudaMemcpyDeviceToDevice, stream));
   });
 }
+

@@ -53,6 +53,30 @@ struct OutMaps {
 };
 
 constexpr int kBM = 128;
+// Cycle probes for tuning (compiled only with -DB200AIT_GEMM_PROBE; never part of the shipped library): CTA 0's MMA
+// thread and first epilogue warp add the clock64() time they spend in each phase to g_gemm_probe[slot].
+#ifdef B200AIT_GEMM_PROBE
+static __device__ long long g_gemm_probe[32];  // one copy per translation unit (no relocatable device code)
+#define GEMM_PROBE_DECL(cond)            \
+  const bool probe_on = (cond);          \
+  long long probe_acc[4] = {0, 0, 0, 0}; \
+  long long probe_t = clock64();
+#define GEMM_PROBE(slot)                          \
+  if (probe_on) {                                 \
+    const long long probe_now = clock64();        \
+    probe_acc[(slot) & 3] += probe_now - probe_t; \
+    probe_t = probe_now;                          \
+  }
+#define GEMM_PROBE_FLUSH(base)                                                  \
+  if (probe_on) {                                                               \
+    for (int pi = 0; pi < 4; ++pi) g_gemm_probe[(base) + pi] += probe_acc[pi];  \
+  }
+#else
+#define GEMM_PROBE_DECL(cond)
+#define GEMM_PROBE(slot)
+#define GEMM_PROBE_FLUSH(base)
+#endif
+
 constexpr int kBK = 64;
 constexpr int kGroupM = 8;
 constexpr int kEpiWarps = 8;                      // two per TMEM lane quarter, each takes half of the columns
@@ -335,6 +359,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + kBK - 1) / kBK;
+#ifdef B200AIT_GEMM_PROBE
+  if (blockIdx.x == 0 && threadIdx.x == 0) g_gemm_probe[15] = clock64();  // kernel start
+#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -450,17 +477,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      GEMM_PROBE_DECL(blockIdx.x == 0)
       for (int unit = walker; ok && unit < num_units; unit += num_walkers) {
+        GEMM_PROBE(3)  // other
         ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, kDevWaitAccEmptyTimeout);
         if (!ok) break;
         tc_fence_after();
+        GEMM_PROBE(0)  // waiting for a free accumulator
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         const int split = unit % splits;
         const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
+          GEMM_PROBE(2)  // issuing MMAs and commits
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kDevWaitFullTimeout);
           if (!ok) break;
           tc_fence_after();
+          GEMM_PROBE(1)  // waiting for operands
           const uint32_t a_addr = smem_u32(smem + stage * kStageBytes);
           const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
@@ -494,7 +526,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
+        GEMM_PROBE(2)
       }
+      GEMM_PROBE_FLUSH(0)
+#ifdef B200AIT_GEMM_PROBE
+      if (blockIdx.x == 0) g_gemm_probe[16] = clock64();  // end of the MMA thread's work
+#endif
       if (!ok) {
         // let MMAs that were already issued finish before TMEM is released
         if (PAIR) {
@@ -535,7 +572,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     bool ok = true;
     const uint32_t acc_empty_leader[2] = {PAIR ? mapa_shared(smem_u32(&acc_empty[0]), 0) : 0u,
                                           PAIR ? mapa_shared(smem_u32(&acc_empty[1]), 0) : 0u};
+    GEMM_PROBE_DECL(blockIdx.x == 0 && threadIdx.x == 64)
     for (int unit = walker; ok && unit < num_units; unit += num_walkers) {
+      GEMM_PROBE(3)  // epilogue warp: other
       int b, m_blk, n_blk;
       const int tile = unit / splits, split = unit - tile * splits;
       decode_tile(p, tile, b, m_blk, n_blk);
@@ -577,9 +616,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         }
       };
       if (splits == 1 && !box_d0) prefetch_d0(colh);
+      GEMM_PROBE(0)  // tile set-up: residual boxes issued, bias staged, epilogue barrier
       ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, kDevWaitAccFullTimeout);
       if (!ok) break;
       tc_fence_after();
+      GEMM_PROBE(1)  // waiting for the accumulator
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                               static_cast<uint32_t>(acc * BN + half * (BN / 2));
       // Two register buffers alternate between "being read" and "being loaded", so that a chunk is used where
@@ -701,7 +742,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       if (!ok) break;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+      GEMM_PROBE(2)  // the tile's chunks: TMEM loads, residual, math, staging, stores
     }
+    GEMM_PROBE_FLUSH(4)
+#ifdef B200AIT_GEMM_PROBE
+    if (blockIdx.x == 0 && threadIdx.x == 64) g_gemm_probe[17] = clock64();
+#endif
     if (use_tma && lane == 0) bulk_wait_group0();  // shared memory must outlive the stores that read it
   }
 

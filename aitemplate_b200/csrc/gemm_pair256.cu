@@ -45,3 +45,13 @@ void launch_tc_pair256(bool bf16, const CUtensorMap& ta, const CUtensorMap& tb, 
 }
 #undef B200AIT_CASE_PAIR
 }  // namespace b200ait
+
+#ifdef B200AIT_GEMM_PROBE
+// tuning builds only: the probe counters of the CTA-pair kernels of this translation unit
+extern "C" __attribute__((visibility("default"))) int b200ait_gemm_probe_read(long long* out32) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+  if (cudaMemcpyFromSymbol(out32, b200ait::g_gemm_probe, sizeof(long long) * 32) != cudaSuccess) return 1;
+  long long zero[32] = {};
+  return cudaMemcpyToSymbol(b200ait::g_gemm_probe, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
+}
+#endif
