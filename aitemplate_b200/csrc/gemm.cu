@@ -241,17 +241,21 @@ __global__ void __launch_bounds__(kRowDotThreads, 1) gemm_rowdot_kernel(const vo
 //   warp 0: TMA producer   warp 1: MMA issuer   warps 2-5: epilogue (TMEM lane = weight row = output column)
 constexpr int kSwapThreads = 192;
 constexpr int kSwapMaxM = 128;
-template <int MX>
+template <int MX, int R>
 struct SwapCfg {
+  static_assert(R == 2 || R == 4, "cluster size");
+  static constexpr int kPart = MX / R;              // rows of X each rank finishes
+  static_assert(kPart >= 8, "a rank finishes at least 8 rows");
   static constexpr int kWBytes = 128 * kBK * 2;     // 16 KB: 128 weight rows x 64 k
   static constexpr int kXBytes = MX * kBK * 2;      // MX rows of X x 64 k
   static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kPartialBytes = 128 * (MX / 2) * 4;  // the half of the peer's sums this rank finishes
-  static constexpr int kStages = MX <= 64 ? 8 : 6;  // what fits beside the partial sums: 144 to 192 KB in flight
+  static constexpr int kPartialBytes = (R - 1) * kPart * 128 * 4;  // one slot per peer: its sums for this rank's rows
+  static constexpr int kFit = (227 * 1024 - 256 - kPartialBytes) / kStageBytes;
+  static constexpr int kStages = kFit < 8 ? kFit : 8;  // 144 to 192 KB in flight
   static constexpr int kAccCols = MX < 32 ? 32 : MX;  // TMEM columns of one accumulator
   static constexpr int kTmemCols = 2 * kAccCols;
   static constexpr int kSmemBytes = kStages * kStageBytes + kPartialBytes + 256;
-  static_assert(kSmemBytes <= 227 * 1024, "swapped-operand kernel: shared memory");
+  static_assert(kStages >= 4 && kSmemBytes <= 227 * 1024, "swapped-operand kernel: shared memory");
 };
 
 template <int N>
@@ -266,21 +270,21 @@ __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[N]) 
   }
 }
 
-template <bool BF16, int MX>
+template <bool BF16, int MX, int R>
 __global__ void __launch_bounds__(kSwapThreads, 1)
 gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
                    const GemmParams p, const int num_slabs) {
-  using Cfg = SwapCfg<MX>;
+  using Cfg = SwapCfg<MX, R>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const bool misaligned = (smem_u32(smem) & 1023u) != 0u;
   if (misaligned && threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevBadSmemAlignment);
-  float* partial = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);  // [MX / 2][128], written by the peer
+  float* partial = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);  // [R - 1][MX / R][128], a slot per peer
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes);
   uint64_t* empty_bar = full_bar + Cfg::kStages;
   uint64_t* acc_full = empty_bar + Cfg::kStages;   // [2]
   uint64_t* acc_empty = acc_full + 2;             // [2]
-  uint64_t* partial_ready = acc_empty + 2;        // the peer's partial sums are in `partial`
-  uint64_t* partial_taken = partial_ready + 1;    // the peer has read the sums this CTA sent
+  uint64_t* partial_ready = acc_empty + 2;        // every peer's partial sums are in `partial`
+  uint64_t* partial_taken = partial_ready + 1;    // every peer has read the sums it was sent
   uint64_t* drain_bar = partial_taken + 1;
   uint64_t* tile_summed = drain_bar + 1;          // every thread has added its own sums into `partial`
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_summed + 1);
@@ -289,12 +293,13 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(cluster_ctarank());
-  const int walker = blockIdx.x >> 1, num_walkers = gridDim.x >> 1;
+  const int walker = blockIdx.x / R, num_walkers = gridDim.x / R;
   const int my_slabs = misaligned ? 0 : num_slabs;
-  // this rank's half of the k-blocks
+  // this rank's share of the k-blocks (the host sends no problem with fewer k-blocks than ranks)
   const int kb_total = (p.K + kBK - 1) / kBK;
-  const int kb_half = (kb_total + 1) / 2;
-  const int kb0 = rank == 0 ? 0 : kb_half, kb1 = rank == 0 ? kb_half : kb_total;
+  const int kb_share = (kb_total + R - 1) / R;
+  const int kb0 = rank * kb_share < kb_total ? rank * kb_share : kb_total;
+  const int kb1 = kb0 + kb_share < kb_total ? kb0 + kb_share : kb_total;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -305,8 +310,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], 128);
     }
-    mbar_init(partial_ready, 128);
-    mbar_init(partial_taken, 128);
+    mbar_init(partial_ready, 128 * (R - 1));
+    mbar_init(partial_taken, 128 * (R - 1));
     mbar_init(drain_bar, 1);
     mbar_init(tile_summed, 128);
     *abort_flag = 0;
@@ -399,20 +404,16 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       }
     }
   } else {
-    // Both ranks finish half of the slab's rows of X: rank r keeps rows [r * MX/2, (r + 1) * MX/2) of its own
-    // sums, sends the other half to its peer's `partial`, adds what the peer sent and writes its rows out.
-    constexpr int kHalf = MX / 2;
-    constexpr int kChunk = kHalf < 32 ? kHalf : 32;  // TMEM columns per load
+    // Every rank finishes MX / R of the slab's rows of X: rank r keeps rows [r * MX/R, (r + 1) * MX/R) of its own
+    // sums, sends the others to the rank that finishes them (slot "sender" of that rank's `partial`), adds what
+    // its peers sent and writes its rows out.
+    constexpr int kPart = Cfg::kPart;
+    constexpr int kChunk = kPart < 32 ? kPart : 32;  // TMEM columns per load
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // weight row inside the slab == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t peer = static_cast<uint32_t>(rank ^ 1);
-    const uint32_t peer_partial = mapa_shared(smem_u32(partial), peer);
-    const uint32_t peer_ready = mapa_shared(smem_u32(partial_ready), peer);
-    const uint32_t peer_taken = mapa_shared(smem_u32(partial_taken), peer);
-    const int my_row0 = rank * kHalf, peer_row0 = (rank ^ 1) * kHalf;
-    const int my_rows = p.M - my_row0 < 0 ? 0 : (p.M - my_row0 < kHalf ? p.M - my_row0 : kHalf);
-    const bool peer_has_rows = p.M > peer_row0;
+    const int my_row0 = rank * kPart;
+    const int my_rows = p.M - my_row0 < 0 ? 0 : (p.M - my_row0 < kPart ? p.M - my_row0 : kPart);
     const int et = static_cast<int>(threadIdx.x) - 64;  // 0..127 over the four epilogue warps
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -431,30 +432,43 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + lane_addr + static_cast<uint32_t>(acc * Cfg::kAccCols);
-      // the peer must have read what this CTA sent for the previous slab before it is overwritten
+      // the peers must have read what this CTA sent for the previous slab before it is overwritten
       if (it > 0) ok = mbar_wait_cluster(partial_taken, (it - 1) & 1, abort_flag, p.status, kDevWaitOtherTimeout);
 #pragma unroll
-      for (int c = 0; c < kHalf / kChunk; ++c) {
-        uint32_t v[kChunk];
-        tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(peer_row0 + c * kChunk), v);
-        tmem_ld_wait();
-        if (ok && peer_has_rows) {
+      for (int q = 0; q < R; ++q) {
+        if (q == rank) continue;
+        const int slot = rank < q ? rank : rank - 1;  // where this rank's sums go in rank q's buffer
+        const uint32_t dst = mapa_shared(smem_u32(partial), static_cast<uint32_t>(q)) +
+                             static_cast<uint32_t>((slot * kPart * 128 + row) * 4);
+        const bool q_has_rows = p.M > q * kPart;
 #pragma unroll
-          for (int j = 0; j < kChunk; ++j)
-            st_shared_cluster_f32(peer_partial + static_cast<uint32_t>(((c * kChunk + j) * 128 + row) * 4),
-                                  __uint_as_float(v[j]));
+        for (int c = 0; c < kPart / kChunk; ++c) {
+          uint32_t v[kChunk];
+          tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(q * kPart + c * kChunk), v);
+          tmem_ld_wait();
+          if (ok && q_has_rows) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j)
+              st_shared_cluster_f32(dst + static_cast<uint32_t>((c * kChunk + j) * 128 * 4), __uint_as_float(v[j]));
+          }
         }
+        // release at cluster scope: the stores above are visible to the waiter
+        if (ok) mbar_arrive_cluster(mapa_shared(smem_u32(partial_ready), static_cast<uint32_t>(q)));
       }
-      if (ok) mbar_arrive_cluster(peer_ready);  // release at cluster scope: the stores above are visible to the waiter
       if (ok) ok = mbar_wait_cluster(partial_ready, it & 1, abort_flag, p.status, kDevWaitOtherTimeout);
 #pragma unroll
-      for (int c = 0; c < kHalf / kChunk; ++c) {
+      for (int c = 0; c < kPart / kChunk; ++c) {
         uint32_t v[kChunk];
         tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(my_row0 + c * kChunk), v);
         tmem_ld_wait();
         if (ok && my_rows > 0) {
 #pragma unroll
-          for (int j = 0; j < kChunk; ++j) partial[(c * kChunk + j) * 128 + row] += __uint_as_float(v[j]);
+          for (int j = 0; j < kChunk; ++j) {
+            float sum = __uint_as_float(v[j]);
+#pragma unroll
+            for (int sl = 0; sl < R - 1; ++sl) sum += partial[(sl * kPart + c * kChunk + j) * 128 + row];
+            partial[(c * kChunk + j) * 128 + row] = sum;  // slot 0 becomes the finished tile
+          }
         }
       }
       tc_fence_before();
@@ -485,7 +499,10 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
               }
           }
         }
-        mbar_arrive_cluster(peer_taken);  // this thread is done reading: the peer may send the next slab's sums
+        // this thread is done reading: the peers may send the next slab's sums
+#pragma unroll
+        for (int q = 0; q < R; ++q)
+          if (q != rank) mbar_arrive_cluster(mapa_shared(smem_u32(partial_taken), static_cast<uint32_t>(q)));
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
@@ -501,25 +518,35 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   }
 }
 
-template <bool BF16, int MX>
+template <bool BF16, int MX, int R>
 static void launch_swapab(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int num_slabs,
                           cudaStream_t stream) {
-  using Cfg = SwapCfg<MX>;
+  using Cfg = SwapCfg<MX, R>;
   static std::atomic<uint64_t> configured{0};
-  auto* kernel = &gemm_swapab_kernel<BF16, MX>;
+  auto* kernel = &gemm_swapab_kernel<BF16, MX, R>;
   opt_in_smem_once(configured, reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(2 * std::min(num_slabs, sm_count() / 2)));
+  cfg.gridDim = dim3(static_cast<unsigned>(R * (sm_count() / R)));
   cfg.blockDim = dim3(kSwapThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.x = R;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  // one walker per cluster the GPU can hold at once (clusters do not straddle GPCs, so this can be fewer than
+  // SMs / R): a cluster left for a second wave would start when the first is already done streaming
+  static std::atomic<int> resident{0};
+  int walkers = resident.load(std::memory_order_relaxed);
+  if (walkers == 0) {
+    B200AIT_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&walkers, kernel, &cfg));
+    B200AIT_REQUIRE(walkers > 0, "gemm: the weight-streaming kernel's cluster does not fit this GPU");
+    resident.store(walkers, std::memory_order_relaxed);
+  }
+  cfg.gridDim = dim3(static_cast<unsigned>(R * std::min(num_slabs, walkers)));
   ::b200ait::count_launch();
   B200AIT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, tw, tx, p, num_slabs));
 }
@@ -783,21 +810,27 @@ void gemm_run(const GemmArgs& g_in) {
     return;
   }
   // 5 <= M <= 128 against a big weight matrix, tile width and split-K left to the library: stream W once with the
-  // operands swapped (W rows on the MMA rows), K halved across a cluster of two, no workspace
+  // operands swapped (W rows on the MMA rows), K split across a cluster of two or four, no workspace
   if (tma_ok && g.batch == 1 && g.m <= kSwapMaxM && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0 &&
-      g.k >= 2048 && g.n >= 2048) {
+      g.k >= 512 && g.n >= 512) {
     const int num_slabs = static_cast<int>((g.n + 127) / 128);
-    const int mx = g.m <= 16 ? 16 : g.m <= 32 ? 32 : g.m <= 64 ? 64 : 128;
+    // few slabs (N <= 128 * SMs / 4): K goes four ways, so that most SMs stream
+    const bool quad = num_slabs <= sm_count() / 4;
+    const int mx = g.m <= 16 && !quad ? 16 : g.m <= 32 ? 32 : g.m <= 64 ? 64 : 128;
     CUtensorMap tw = make_tile_map(g.b, bf16, g.k, g.n, 1, g.ldb, 0, 128);
     CUtensorMap tx = make_tile_map(g.a, bf16, g.k, g.m, 1, g.lda, 0, mx);
-#define B200AIT_SWAP(MX)                                                   \
+#define B200AIT_SWAP(MX, R)                                                \
   do {                                                                     \
     if (bf16)                                                              \
-      launch_swapab<true, MX>(tw, tx, p, num_slabs, g.stream);             \
+      launch_swapab<true, MX, R>(tw, tx, p, num_slabs, g.stream);          \
     else                                                                   \
-      launch_swapab<false, MX>(tw, tx, p, num_slabs, g.stream);            \
+      launch_swapab<false, MX, R>(tw, tx, p, num_slabs, g.stream);         \
   } while (0)
-    if (mx == 16) B200AIT_SWAP(16); else if (mx == 32) B200AIT_SWAP(32); else if (mx == 64) B200AIT_SWAP(64); else B200AIT_SWAP(128);
+    if (quad) {
+      if (mx == 32) B200AIT_SWAP(32, 4); else if (mx == 64) B200AIT_SWAP(64, 4); else B200AIT_SWAP(128, 4);
+    } else {
+      if (mx == 16) B200AIT_SWAP(16, 2); else if (mx == 32) B200AIT_SWAP(32, 2); else if (mx == 64) B200AIT_SWAP(64, 2); else B200AIT_SWAP(128, 2);
+    }
 #undef B200AIT_SWAP
     return;
   }
