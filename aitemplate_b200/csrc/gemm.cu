@@ -249,12 +249,14 @@ struct SwapCfg {
   static constexpr int kWBytes = 128 * kBK * 2;     // 16 KB: 128 weight rows x 64 k
   static constexpr int kXBytes = MX * kBK * 2;      // MX rows of X x 64 k
   static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kPartialBytes = (R - 1) * kPart * 128 * 4;  // one slot per peer: its sums for this rank's rows
-  static constexpr int kFit = (227 * 1024 - 256 - kPartialBytes) / kStageBytes;
+  static constexpr int kSlotBytes = 128 * kPart * 4;               // [128 weight rows][kPart rows of X] fp32
+  static constexpr int kPartialBytes = (R - 1) * kSlotBytes;       // one slot per peer: its sums for this rank's rows
+  static constexpr int kTileBytes = kSlotBytes;                    // the finished tile, [kPart][128]
+  static constexpr int kFit = (227 * 1024 - 256 - kPartialBytes - kTileBytes) / kStageBytes;
   static constexpr int kStages = kFit < 8 ? kFit : 8;  // 144 to 192 KB in flight
   static constexpr int kAccCols = MX < 32 ? 32 : MX;  // TMEM columns of one accumulator
   static constexpr int kTmemCols = 2 * kAccCols;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kPartialBytes + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kPartialBytes + kTileBytes + 256;
   static_assert(kStages >= 4 && kSmemBytes <= 227 * 1024, "swapped-operand kernel: shared memory");
 };
 
@@ -279,14 +281,16 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   const bool misaligned = (smem_u32(smem) & 1023u) != 0u;
   if (misaligned && threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevBadSmemAlignment);
   float* partial = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);  // [R - 1][MX / R][128], a slot per peer
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes);
+  float* tile = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes);  // [MX / R][128]
+  uint64_t* full_bar =
+      reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes + Cfg::kTileBytes);
   uint64_t* empty_bar = full_bar + Cfg::kStages;
   uint64_t* acc_full = empty_bar + Cfg::kStages;   // [2]
   uint64_t* acc_empty = acc_full + 2;             // [2]
-  uint64_t* partial_ready = acc_empty + 2;        // every peer's partial sums are in `partial`
+  uint64_t* partial_ready = acc_empty + 2;        // every peer's partial sums are in `partial` (counts their bytes)
   uint64_t* partial_taken = partial_ready + 1;    // every peer has read the sums it was sent
   uint64_t* drain_bar = partial_taken + 1;
-  uint64_t* tile_summed = drain_bar + 1;          // every thread has added its own sums into `partial`
+  uint64_t* tile_summed = drain_bar + 1;          // every thread has put its sums into `tile`
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_summed + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   static_assert((2 * Cfg::kStages + 8) * 8 + 8 <= 256, "barrier area too small");
@@ -310,15 +314,41 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], 128);
     }
-    mbar_init(partial_ready, 128 * (R - 1));
+    mbar_init(partial_ready, 1);
     mbar_init(partial_taken, 128 * (R - 1));
     mbar_init(drain_bar, 1);
     mbar_init(tile_summed, 128);
     *abort_flag = 0;
     fence_mbar_init();
+    fence_proxy_async_smem();  // this thread's own TMA loads, issued below, signal the barriers just initialised
     tma_prefetch_desc(&tma_w);
     tma_prefetch_desc(&tma_x);
   }
+  // The TMA producer (thread 0). Every CTA reads the same rows of X: walking the k-blocks from a different starting
+  // point in every cluster keeps the CTAs from asking L2 for the same lines of X at the same moment.
+  const int nkb = kb1 - kb0;
+  int prod_stage = 0;
+  uint32_t prod_phase = 0;
+  auto produce = [&](int slab, int i0, int i1) -> bool {
+    const int rot = nkb > 0 ? static_cast<int>((static_cast<unsigned>(slab) * 11u) % static_cast<unsigned>(nkb)) : 0;
+    for (int i = i0; i < i1; ++i) {
+      const int kb = kb0 + (i + rot >= nkb ? i + rot - nkb : i + rot);
+      if (!mbar_wait(&empty_bar[prod_stage], prod_phase ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout)) return false;
+      uint8_t* sw = smem + prod_stage * Cfg::kStageBytes;
+      mbar_arrive_expect_tx(&full_bar[prod_stage], Cfg::kStageBytes);
+      tma_load_3d(sw, &tma_w, &full_bar[prod_stage], kb * kBK, slab * 128, 0);
+      tma_load_3d(sw + Cfg::kWBytes, &tma_x, &full_bar[prod_stage], kb * kBK, 0, 0);
+      if (++prod_stage == Cfg::kStages) {
+        prod_stage = 0;
+        prod_phase ^= 1u;
+      }
+    }
+    return true;
+  };
+  // The first ring-full of loads needs this CTA's barriers only: it leaves before the TMEM allocation and the
+  // cluster-wide sync, which then cost nothing on top of the first trip to DRAM.
+  const int prefill = nkb < Cfg::kStages ? nkb : Cfg::kStages;
+  if (threadIdx.x == 0 && walker < my_slabs) produce(walker, 0, prefill);
   __syncthreads();
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);  // two accumulators
@@ -329,31 +359,13 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  bool epi_arrived = false;  // this thread has arrived at the closing cluster barrier
 
   if (warp == 0) {
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
       bool ok = true;
-      for (int slab = walker; ok && slab < my_slabs; slab += num_walkers) {
-        // Every CTA reads the same rows of X. Walking the k-blocks from a different starting point in every
-        // cluster keeps the CTAs from asking L2 for the same lines of X at the same moment.
-        const int nkb = kb1 - kb0;
-        const int rot = nkb > 0 ? static_cast<int>((static_cast<unsigned>(slab) * 11u) % static_cast<unsigned>(nkb)) : 0;
-        for (int i = 0; i < nkb; ++i) {
-          const int kb = kb0 + (i + rot >= nkb ? i + rot - nkb : i + rot);
-          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout);
-          if (!ok) break;
-          uint8_t* sw = smem + stage * Cfg::kStageBytes;
-          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          tma_load_3d(sw, &tma_w, &full_bar[stage], kb * kBK, slab * 128, 0);
-          tma_load_3d(sw + Cfg::kWBytes, &tma_x, &full_bar[stage], kb * kBK, 0, 0);
-          if (++stage == Cfg::kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-      }
+      for (int slab = walker; ok && slab < my_slabs; slab += num_walkers)
+        ok = produce(slab, slab == walker ? prefill : 0, nkb);
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) {
@@ -405,8 +417,10 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
   } else {
     // Every rank finishes MX / R of the slab's rows of X: rank r keeps rows [r * MX/R, (r + 1) * MX/R) of its own
-    // sums, sends the others to the rank that finishes them (slot "sender" of that rank's `partial`), adds what
-    // its peers sent and writes its rows out.
+    // sums and sends the others to the rank that finishes them (slot "sender" of that rank's `partial`; a warp's
+    // store covers 128 consecutive bytes). The stores are asynchronous and credit their bytes to the receiver's
+    // `partial_ready`: nobody waits for a store to land except the thread that needs the data. Then the rank
+    // adds what its peers sent into `tile` and writes its rows out.
     constexpr int kPart = Cfg::kPart;
     constexpr int kChunk = kPart < 32 ? kPart : 32;  // TMEM columns per load
     const int quarter = warp & 3;
@@ -420,6 +434,9 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     int it = 0;
     bool ok = true;
     for (int slab = walker; ok && slab < my_slabs; slab += num_walkers, ++it) {
+      const bool last = slab + num_walkers >= my_slabs;
+      // what the peers will send for this slab (a rank with no valid row of X is sent nothing and waits for nothing)
+      if (et == 0 && my_rows > 0) mbar_arrive_expect_tx(partial_ready, (R - 1) * Cfg::kSlotBytes);
       // The tile goes out row by row: a thread takes 8 consecutive columns (one 16-byte store), 16 threads one
       // row of the slab. A thread keeps the same columns for every row, so it fetches their bias once, early.
       const int col0 = slab * 128 + (et & 15) * 8;
@@ -436,38 +453,41 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       if (it > 0) ok = mbar_wait_cluster(partial_taken, (it - 1) & 1, abort_flag, p.status, kDevWaitOtherTimeout);
 #pragma unroll
       for (int q = 0; q < R; ++q) {
-        if (q == rank) continue;
+        if (q == rank || p.M <= q * kPart) continue;
         const int slot = rank < q ? rank : rank - 1;  // where this rank's sums go in rank q's buffer
         const uint32_t dst = mapa_shared(smem_u32(partial), static_cast<uint32_t>(q)) +
                              static_cast<uint32_t>((slot * kPart * 128 + row) * 4);
-        const bool q_has_rows = p.M > q * kPart;
+        const uint32_t dst_bar = mapa_shared(smem_u32(partial_ready), static_cast<uint32_t>(q));
 #pragma unroll
         for (int c = 0; c < kPart / kChunk; ++c) {
           uint32_t v[kChunk];
           tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(q * kPart + c * kChunk), v);
           tmem_ld_wait();
-          if (ok && q_has_rows) {
+          if (ok) {
 #pragma unroll
             for (int j = 0; j < kChunk; ++j)
-              st_shared_cluster_f32(dst + static_cast<uint32_t>((c * kChunk + j) * 128 * 4), __uint_as_float(v[j]));
+              st_async_cluster_b32(dst + static_cast<uint32_t>((c * kChunk + j) * 128 * 4), v[j], dst_bar);
           }
         }
-        // release at cluster scope: the stores above are visible to the waiter
-        if (ok) mbar_arrive_cluster(mapa_shared(smem_u32(partial_ready), static_cast<uint32_t>(q)));
       }
-      if (ok) ok = mbar_wait_cluster(partial_ready, it & 1, abort_flag, p.status, kDevWaitOtherTimeout);
+      // After its last send a thread touches no peer again: the cluster-wide barrier that keeps every CTA alive
+      // until then is arrived at here and waited for at the very end, when it has long completed.
+      if (last) cluster_arrive_relaxed();
+      if (ok && my_rows > 0) {
+        ok = mbar_wait_cluster(partial_ready, it & 1, abort_flag, p.status, kDevWaitOtherTimeout);
 #pragma unroll
-      for (int c = 0; c < kPart / kChunk; ++c) {
-        uint32_t v[kChunk];
-        tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(my_row0 + c * kChunk), v);
-        tmem_ld_wait();
-        if (ok && my_rows > 0) {
+        for (int c = 0; c < kPart / kChunk; ++c) {
+          uint32_t v[kChunk];
+          tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(my_row0 + c * kChunk), v);
+          tmem_ld_wait();
+          if (ok) {
 #pragma unroll
-          for (int j = 0; j < kChunk; ++j) {
-            float sum = __uint_as_float(v[j]);
+            for (int j = 0; j < kChunk; ++j) {
+              float sum = __uint_as_float(v[j]);
 #pragma unroll
-            for (int sl = 0; sl < R - 1; ++sl) sum += partial[(sl * kPart + c * kChunk + j) * 128 + row];
-            partial[(c * kChunk + j) * 128 + row] = sum;  // slot 0 becomes the finished tile
+              for (int sl = 0; sl < R - 1; ++sl) sum += partial[(sl * kPart + c * kChunk + j) * 128 + row];
+              tile[(c * kChunk + j) * 128 + row] = sum;
+            }
           }
         }
       }
@@ -481,7 +501,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         // two rows (j and j + 8) per trip: two independent chains for the one warp each scheduler has
         for (int j = et >> 4; j < my_rows; j += 16) {
           const bool two = j + 8 < my_rows;
-          const float* src0 = partial + j * 128 + (et & 15) * 8;
+          const float* src0 = tile + j * 128 + (et & 15) * 8;
           const float* src1 = src0 + (two ? 8 * 128 : 0);
           if (vec) {
             const float4 a0 = *reinterpret_cast<const float4*>(src0), a1 = *reinterpret_cast<const float4*>(src0 + 4);
@@ -499,23 +519,34 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
               }
           }
         }
-        // this thread is done reading: the peers may send the next slab's sums
+        // This thread is done reading `partial`: the peers may send the next slab's sums. (Its reads have returned -
+        // their values went into `tile` - so the signal needs no release. A rank without rows signals all the same:
+        // the senders count every peer.)
+        if (!last) {
 #pragma unroll
-        for (int q = 0; q < R; ++q)
-          if (q != rank) mbar_arrive_cluster(mapa_shared(smem_u32(partial_taken), static_cast<uint32_t>(q)));
+          for (int q = 0; q < R; ++q)
+            if (q != rank) mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(partial_taken), static_cast<uint32_t>(q)));
+        }
+      }
+      if (last) {
+        epi_arrived = true;
+        break;
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
   }
 
+  // Every thread arrives at the cluster-wide barrier exactly once: the epilogue threads did after their last send
+  // (unless a wait ran out first), everybody else does here.
+  if (!epi_arrived) cluster_arrive_relaxed();
   tc_fence_before();
   __syncthreads();
-  cluster_sync_all();  // neither CTA leaves while its peer can still write to it or signal it
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+  cluster_wait();  // no CTA leaves while a peer can still write to it or signal it
 }
 
 template <bool BF16, int MX, int R>

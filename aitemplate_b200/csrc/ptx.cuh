@@ -116,6 +116,20 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
     }
   }
 }
+// One 32-bit word into the shared memory of a CTA of this cluster, asynchronously: the 4 bytes are credited to the
+// mbarrier at `cluster_bar` (same CTA as the destination) when they have landed, so the sender orders nothing.
+__device__ __forceinline__ void st_async_cluster_b32(uint32_t cluster_addr, uint32_t v, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(cluster_addr),
+               "r"(v), "r"(cluster_bar)
+               : "memory");
+}
+// arrive on a peer CTA's mbarrier without ordering this thread's earlier writes
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// the cluster-wide barrier in two halves (every thread of every CTA of the cluster executes each exactly once)
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 // one fp32 word into the shared memory of a CTA of this cluster (address from mapa_shared)
 __device__ __forceinline__ void st_shared_cluster_f32(uint32_t cluster_addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
