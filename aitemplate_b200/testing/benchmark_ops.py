@@ -209,9 +209,10 @@ def bench_concat_split(config: str, peaks: Dict) -> List[Dict]:
 
 def bench_sd_block(config: str, peaks: Dict) -> Dict:
     """The whole Stable-Diffusion UNet transformer block of benchmark configuration 3 through compile_model() and
-    Model.benchmark_with_tensors() in graph mode (22 kernels per run)."""
+    Model.benchmark_with_tensors() in graph mode; the row's label carries the kernels one run launches."""
     import tempfile
 
+    from .. import _lib
     from ..compiler import compile_model
     from . import detect_target, workloads
 
@@ -222,6 +223,9 @@ def bench_sd_block(config: str, peaks: Dict) -> Dict:
     module.set_many_constants_with_tensors({k: v.cuda() for k, v in params.items()})
     out = torch.empty((batch, 4096, 320), dtype=torch.float16, device="cuda")
     ins = {"latent": x.cuda(), "context": context.cuda()}
+    launches = _lib.kernel_launch_count()
+    module.run_with_tensors(ins, {"output_0": out}, graph_mode=False)
+    launches = _lib.kernel_launch_count() - launches
     module.run_with_tensors(ins, {"output_0": out}, graph_mode=True)
     time.sleep(0.2)
     mean_ms, _, _ = module.benchmark_with_tensors(ins, {"output_0": out}, count=20, repeat=3, graph_mode=True)
@@ -229,7 +233,7 @@ def bench_sd_block(config: str, peaks: Dict) -> Dict:
     gemm = 2.0 * batch * (tokens * dim * dim * 4 + tokens * dim * dim * 2 + 2 * ctx * cdim * dim
                           + 2 * tokens * dim * 4 * dim + tokens * 4 * dim * dim)
     attn = 4.0 * batch * 8 * tokens * (tokens + ctx) * 40
-    row = {"config": config, "op": "sd_transformer_block (22 kernels, graph mode)", "shape": "B2 4096x320, ctx 77x768",
+    row = {"config": config, "op": f"sd_transformer_block ({launches} kernels, graph mode)", "shape": "B2 4096x320, ctx 77x768",
            "us": round(mean_ms * 1e3, 2), "bound": "tensor"}
     tf = (gemm + attn) / (mean_ms * 1e-3) / 1e12
     row.update(tflops=round(tf, 1), frac_measured=round(tf / peaks["tflops_burst"], 3),
@@ -240,36 +244,54 @@ def bench_sd_block(config: str, peaks: Dict) -> Dict:
     return row
 
 
-def run_suite(peaks: Dict, quick: bool = False):
+def run_suite(peaks: Dict, quick: bool = False, only: str = ""):
     """Yields one row per op of the benchmark configurations. quick=True shrinks the CPU-side samples (not the GPU
-    problems) so that the whole sweep, CPU checks included, stays within about a minute."""
+    problems) so that the whole sweep, CPU checks included, stays within about a minute. `only` keeps the cases
+    whose label ("<config>:<op>:<shape>", e.g. "5:gemm:16x8192x8192") contains it - for a profiler capture of one
+    kernel without the rest of the sweep in front of it."""
     sf = 2.5e11 if quick else 1.2e12
-    for r in _suite_rows(peaks, sf):
-        yield r
+    for label, case in _suite_cases(peaks, sf):
+        if only and only not in label:
+            continue
+        rows = case()
+        for r in rows if isinstance(rows, list) else [rows]:
+            yield r
 
 
-def _suite_rows(peaks: Dict, sf: float):
-    yield bench_gemm("1", 256, 3072, 768, "fast_gelu", peaks)
+def _suite_cases(peaks: Dict, sf: float):
+    """(label, thunk) per case, in running order; nothing touches the GPU until a thunk is called."""
+    cases = []
+
+    def gemm(config, m, n, k, epilogue, **kw):
+        cases.append((f"{config}:gemm:{m}x{n}x{k}", lambda: bench_gemm(config, m, n, k, epilogue, peaks, **kw)))
+
+    def attention(config, b, h, sq, skv, d):
+        cases.append((f"{config}:attention:{b}x{h}x{sq}x{skv}x{d}", lambda: bench_attention(config, b, h, sq, skv, d, peaks)))
+
+    def layernorm(config, m, n, eps):
+        cases.append((f"{config}:layernorm:{m}x{n}", lambda: bench_layernorm(config, m, n, eps, peaks)))
+
+    gemm("1", 256, 3072, 768, "fast_gelu")
     m2 = 64 * 384
-    yield bench_gemm("2", m2, 2304, 768, "", peaks, permute=(384, 3, 12))
-    yield bench_attention("2", 64, 12, 384, 384, 64, peaks)
-    yield bench_gemm("2", m2, 768, 768, "add", peaks, residual=True)
-    yield bench_layernorm("2", m2, 768, 1e-12, peaks)
-    yield bench_gemm("2", m2, 3072, 768, "fast_gelu", peaks)
-    yield bench_gemm("2", m2, 768, 3072, "add", peaks, residual=True)
+    gemm("2", m2, 2304, 768, "", permute=(384, 3, 12))
+    attention("2", 64, 12, 384, 384, 64)
+    gemm("2", m2, 768, 768, "add", residual=True)
+    layernorm("2", m2, 768, 1e-12)
+    gemm("2", m2, 3072, 768, "fast_gelu")
+    gemm("2", m2, 768, 3072, "add", residual=True)
     for n in (768, 1024, 4096):
-        yield bench_layernorm("3", 65536, n, 1e-5, peaks)
-    yield bench_softmax("3", (512, 1024, 1024), peaks)
-    yield from bench_concat_split("3", peaks)
-    yield bench_attention("4", 2, 8, 4096, 4096, 40, peaks)
-    yield bench_attention("4", 2, 8, 4096, 77, 40, peaks)
-    yield bench_gemm("4", 8192, 320, 320, "", peaks)
-    yield bench_gemm("4", 8192, 2560, 320, "", peaks)
-    yield bench_gemm("4", 8192, 1280, 320, "mul", peaks, residual=True)
-    yield bench_gemm("4", 8192, 320, 1280, "add", peaks, residual=True)
-    yield bench_layernorm("4", 8192, 320, 1e-5, peaks)
-    yield bench_sd_block("4", peaks)
-    yield bench_bmm("5", 1024, 512, 512, 64, peaks)
+        layernorm("3", 65536, n, 1e-5)
+    cases.append(("3:softmax:512x1024x1024", lambda: bench_softmax("3", (512, 1024, 1024), peaks)))
+    cases.append(("3:concat_split", lambda: list(bench_concat_split("3", peaks))))
+    attention("4", 2, 8, 4096, 4096, 40)
+    attention("4", 2, 8, 4096, 77, 40)
+    gemm("4", 8192, 320, 320, "")
+    gemm("4", 8192, 2560, 320, "")
+    gemm("4", 8192, 1280, 320, "mul", residual=True)
+    gemm("4", 8192, 320, 1280, "add", residual=True)
+    layernorm("4", 8192, 320, 1e-5)
+    cases.append(("4:sd_transformer_block", lambda: bench_sd_block("4", peaks)))
+    cases.append(("5:bmm:1024x512x512x64", lambda: bench_bmm("5", 1024, 512, 512, 64, peaks)))
     for m in (1, 16, 128, 1024, 8192, 65536):  # the seconds-long cases last: they leave the GPU power-capped
-        yield bench_gemm("5", m, 8192, 8192, "relu", peaks, w_scale=0.01, sample_flops=sf)
-
+        gemm("5", m, 8192, 8192, "relu", w_scale=0.01, sample_flops=sf)
+    return cases

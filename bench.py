@@ -553,7 +553,7 @@ def _check_sample(sample):
     return cpu_ms, float(err.max()), float((err / want.abs().clamp_min(atol)).max()), ok, len(times)
 
 
-def ops_rows(peaks, quick: bool = False):
+def ops_rows(peaks, quick: bool = False, only: str = ""):
     """Per-op rows of the benchmark configurations: GPU time and roofline fractions from the package's sweep, CPU
     time (the oracle expression in fp32 on all host cores, on the row's sample, scaled to the whole op) and the
     error of the kernel's output against that oracle."""
@@ -563,7 +563,7 @@ def ops_rows(peaks, quick: bool = False):
 
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    for row in benchmark_ops.run_suite(peaks, quick=quick):
+    for row in benchmark_ops.run_suite(peaks, quick=quick, only=only):
         sample = row.pop("_sample", None)
         row["gpu_ms"] = round(row.pop("us") / 1000.0, 5)
         if sample is not None:
@@ -589,7 +589,7 @@ def run_ops_suite(args) -> None:
 
     torch.cuda.set_device(0)
     peaks = _peaks()
-    for row in ops_rows(peaks, quick=False):
+    for row in ops_rows(peaks, quick=False, only=args.only):
         print(json.dumps(row), flush=True)
 
 
@@ -698,6 +698,8 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-ops", action="store_true",
                     help="layer suite: leave the per-op digest (GPU time, CPU time, error per op) out of the line")
+    ap.add_argument("--only", default="",
+                    help="ops suite: run the cases whose label '<config>:<op>:<shape>' contains this, e.g. 5:gemm:16x8192")
     ap.add_argument("--suite", choices=["layer", "ops", "nsplit"], default="layer",
                     help="layer: the contract benchmark (default); ops: per-op sweep; nsplit: config 5 on N GPUs")
     args = ap.parse_args()
