@@ -642,7 +642,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           released = true;
           tc_fence_before();
           if (PAIR) {
-            mbar_arrive_cluster(acc_empty_leader[acc]);
+            // relaxed: the leader depends on this thread's TMEM reads (fenced above), not on its memory writes; a
+            // release at cluster scope would wait here for the staged stores of the earlier chunks
+            mbar_arrive_cluster_relaxed(acc_empty_leader[acc]);
           } else {
             mbar_arrive(&acc_empty[acc]);
           }
