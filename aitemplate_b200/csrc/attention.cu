@@ -77,6 +77,9 @@ struct AttnParams {
   int B, H, Sq, Skv, D, Dv;
   int q_blocks;
   int num_items;  // B * H * q_blocks work items of 128 query rows
+  // item -> (query tile, head, batch) runs at every item boundary on the critical path of every role: the two
+  // divisions are multiplications by constants prepared on the host (FastDiv below)
+  unsigned q_blocks_mul, q_blocks_shr, h_mul, h_shr;
   float scale_log2;  // softmax scale * log2(e)
   int causal;
   void* out;  // [B, Sq, H, Dv], or [total, H, Dv] with cu_seqlens
@@ -96,6 +99,24 @@ struct AttnOperand {
   const void* ptr;
   long long row_stride, head_stride, batch_stride;
 };
+
+// n / d for 0 <= n < 2^31 as a multiply-high and a shift: with p = 31 + ceil(log2 d), mul = ceil(2^p / d), shr = p - 32,
+// floor(n * mul / 2^p) == floor(n / d) (the rounding error n * (mul - 2^p / d) / 2^p stays below 1 / d).
+struct FastDiv {
+  unsigned mul = 0, shr = 0;
+  explicit FastDiv(int d) {
+    if (d > 1) {
+      unsigned lg = 0;
+      while ((1ull << lg) < static_cast<unsigned long long>(d)) ++lg;
+      const unsigned pw = 31 + lg;
+      mul = static_cast<unsigned>(((1ull << pw) + static_cast<unsigned>(d) - 1) / static_cast<unsigned>(d));
+      shr = pw - 32;
+    }
+  }
+};
+__device__ __forceinline__ int fast_div(int n, int d, unsigned mul, unsigned shr) {
+  return d == 1 ? n : static_cast<int>(__umulhi(static_cast<unsigned>(n), mul) >> shr);
+}
 
 constexpr int kAttnThreads = 224;  // producer, P V issuer, 4 softmax warps, S issuer
 constexpr int kBlockM = 128;
@@ -176,9 +197,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
   };
   auto decode_item = [&](int item) {
     Item w;
-    const int q_blk = item % p.q_blocks;
-    const int bh = item / p.q_blocks;
-    const int b = bh / p.H;
+    const int bh = fast_div(item, p.q_blocks, p.q_blocks_mul, p.q_blocks_shr);
+    const int q_blk = item - bh * p.q_blocks;
+    const int b = fast_div(bh, p.H, p.h_mul, p.h_shr);
     w.h = bh - b * p.H;
     w.q0 = q_blk * kBlockM;
     if (p.cu_seqlens) {
@@ -734,6 +755,9 @@ static bool operand_ok_for_tma(const AttnOperand& o) {
 static void attention_run(void* output, const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, AttnParams p,
                           long long q_rows, long long kv_rows, bool contiguous_bhsd, bool bf16, cudaStream_t stream) {
   p.q_blocks = (p.Sq + kBlockM - 1) / kBlockM;
+  const FastDiv by_q_blocks(p.q_blocks), by_heads(p.H);
+  p.q_blocks_mul = by_q_blocks.mul, p.q_blocks_shr = by_q_blocks.shr;
+  p.h_mul = by_heads.mul, p.h_shr = by_heads.shr;
   p.out = output;
   p.status = device_status_word();
   const bool tc_ok = p.D % 8 == 0 && p.Dv % 8 == 0 && p.D <= 128 && p.Dv <= 128 && operand_ok_for_tma(q) &&
