@@ -122,6 +122,32 @@ constexpr int kAttnThreads = 224;  // producer, P V issuer, 4 softmax warps, S i
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 64;     // keys per block
 constexpr float kRescaleLog2 = 8.f;  // a row's reference maximum may lag its true maximum by this much (log2 units)
+// Of every eight pairs of scores, this many get their exp2 from the FMA pipe (exp2_poly2 below) instead of the
+// special-function unit, which is the busiest unit of the kernel (64 exp2 per row and key block at 4 lanes per
+// clock and scheduler).
+#ifndef B200AIT_ATTN_POLY_OF8
+#define B200AIT_ATTN_POLY_OF8 2
+#endif
+constexpr int kPolyOf8 = B200AIT_ATTN_POLY_OF8;
+
+// exp2 of two values on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic whose relative
+// error stays below 7.5e-5 (P is rounded to 11 significant bits right after, 4.9e-4); n goes into the exponent
+// field. x is clamped at -126, where the result is ~1e-38 (exp2f would return a denormal or 0).
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& p0, float& p1) {
+  constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+  const uint64_t t = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t r = add2(t, pack2(kMagic, kMagic));
+  const uint64_t n = add2(r, pack2(-kMagic, -kMagic));          // round(x), exact
+  const uint64_t f = fma2(n, pack2(-1.f, -1.f), t);             // x - round(x), exact
+  uint64_t q = fma2(f, pack2(0.055171459913253784f, 0.055171459913253784f), pack2(0.2426108568906784f, 0.2426108568906784f));
+  q = fma2(q, f, pack2(0.6932609677314758f, 0.6932609677314758f));
+  q = fma2(q, f, pack2(0.9999281167984009f, 0.9999281167984009f));
+  float q0, q1, r0, r1;
+  unpack2(q, q0, q1);
+  unpack2(r, r0, r1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+}
 
 template <int DCH>
 struct AttnCfg {
@@ -562,8 +588,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
 #ifdef B200AIT_ATTN_EXP_SKIP  // tuning experiment: no exponentials, to expose the MMA side's own pace
               float p0 = x0, p1 = x1;
 #else
-              float p0 = exp2f(x0);
-              float p1 = exp2f(x1);
+              float p0, p1;
+              if (((i >> 1) & 7) < kPolyOf8) {  // compile-time: the loop is unrolled
+                exp2_poly2(x0, x1, p0, p1);
+              } else {
+                p0 = exp2f(x0);
+                p1 = exp2f(x1);
+              }
 #endif
               if (!kPlain) {
                 p0 = (h * 32 + i < limit) ? p0 : 0.f;
