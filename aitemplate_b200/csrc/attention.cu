@@ -100,24 +100,6 @@ struct AttnOperand {
   long long row_stride, head_stride, batch_stride;
 };
 
-// n / d for 0 <= n < 2^31 as a multiply-high and a shift: with p = 31 + ceil(log2 d), mul = ceil(2^p / d), shr = p - 32,
-// floor(n * mul / 2^p) == floor(n / d) (the rounding error n * (mul - 2^p / d) / 2^p stays below 1 / d).
-struct FastDiv {
-  unsigned mul = 0, shr = 0;
-  explicit FastDiv(int d) {
-    if (d > 1) {
-      unsigned lg = 0;
-      while ((1ull << lg) < static_cast<unsigned long long>(d)) ++lg;
-      const unsigned pw = 31 + lg;
-      mul = static_cast<unsigned>(((1ull << pw) + static_cast<unsigned>(d) - 1) / static_cast<unsigned>(d));
-      shr = pw - 32;
-    }
-  }
-};
-__device__ __forceinline__ int fast_div(int n, int d, unsigned mul, unsigned shr) {
-  return d == 1 ? n : static_cast<int>(__umulhi(static_cast<unsigned>(n), mul) >> shr);
-}
-
 constexpr int kAttnThreads = 224;  // producer, P V issuer, 4 softmax warps, S issuer
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 64;     // keys per block
