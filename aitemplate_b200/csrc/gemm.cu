@@ -483,9 +483,15 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
           if (ok) {
 #pragma unroll
             for (int j = 0; j < kChunk; ++j) {
-              float sum = __uint_as_float(v[j]);
+              // The K shares are added in the order of their ranks whichever rank does the adding, so a row's result
+              // does not depend on which rank finishes it (= on its position in X).
+              float sum = 0.f;
 #pragma unroll
-              for (int sl = 0; sl < R - 1; ++sl) sum += partial[(sl * kPart + c * kChunk + j) * 128 + row];
+              for (int q = 0; q < R; ++q) {
+                const int slot = q < rank ? q : q - 1;  // where rank q's sums sit in this rank's buffer
+                const float term = q == rank ? __uint_as_float(v[j]) : partial[(slot * kPart + c * kChunk + j) * 128 + row];
+                sum = q == 0 ? term : sum + term;
+              }
               tile[(c * kChunk + j) * 128 + row] = sum;
             }
           }

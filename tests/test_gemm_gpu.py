@@ -475,6 +475,21 @@ def test_swapped_operand_weight_streaming(m, n, kk, epilogue, dtype):
     _close(y256, want, atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("m,n,kk", [(128, 8192, 2048), (96, 3072, 2048), (40, 1024, 4096)])
+def test_swapped_operand_rows_do_not_depend_on_their_position(m, n, kk):
+    """Which rank of the cluster finishes a row of X depends on the row's index; the K shares are added in rank
+    order all the same, so X with its rows reversed gives Y with its rows reversed, bit for bit (clusters of two
+    and of four)."""
+    k = _kernels()
+    x = _rand((m, kk), 620, dist="uniform").cuda()
+    w = _rand((n, kk), 621, scale=0.02).cuda()
+    b = _rand((n,), 622, scale=0.1).cuda()
+    y = k.gemm_rcr(x, w, b, epilogue="relu")
+    y_rev = k.gemm_rcr(x.flip(0).contiguous(), w, b, epilogue="relu")
+    assert k.device_status() == 0
+    assert torch.equal(y_rev.flip(0), y)
+
+
 @pytest.mark.parametrize("m,seq", [(32, 16), (96, 32)])
 def test_swapped_operand_permuted_store(m, seq):
     """The weight-streaming path writes the permuted [3, B, H, S, D] projection layout like the tile kernels do."""
