@@ -22,3 +22,17 @@ def test_reference_arm_prints_one_contract_line():
     assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == d["value"] and "sample" in cb
     e2e = d["e2e"]
     assert e2e["value"] == d["value"] and e2e["h2d_bytes_per_step"] == 0 and e2e["d2h_bytes_per_step"] == 0
+
+
+def test_ops_suite_cases_are_labelled_and_filterable():
+    """`bench.py --suite ops --only <text>` selects cases by label `<config>:<op>:<shape>`; building the case list
+    touches no GPU, the labels are unique, and every benchmark configuration has its rows."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from aitemplate_b200.testing import benchmark_ops
+
+    labels = [label for label, _ in benchmark_ops._suite_cases({}, 1e12)]
+    assert len(labels) == len(set(labels))
+    for config in "12345":
+        assert any(label.startswith(config + ":") for label in labels)
+    assert "5:gemm:16x8192x8192" in labels and "2:attention:64x12x384x384x64" in labels
+    assert [label for label in labels if "5:gemm:16x" in label] == ["5:gemm:16x8192x8192"]
