@@ -568,3 +568,34 @@ def test_dynamic_m_reserves_split_k_workspace_for_interior_sizes(workdir):
         res = module.run_with_tensors({"input_0": x.cuda(), "input_1": w.cuda(), "input_2": b.cuda()}, [y])
         _close(res["output_0"], oracle.gemm_rcr(x, w, b, epilogue="relu"))
     module.close()
+
+
+def test_dynamic_m_walks_every_gemm_kernel_in_graph_mode(workdir):
+    """Two GEMMs with a dynamic M in one model: M = 1..4 take the row-dot kernel, 5..128 the weight-streaming
+    tensor-core kernel (N = 8192: clusters of two, N = 1024: clusters of four, every width of the X tile), above that
+    the tile kernels. Every size runs eagerly and then twice as a CUDA graph, against the oracle."""
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    k = 2048
+    m_dim = IntVar([1, 512], name="m")
+    X = Tensor(shape=[m_dim, k], dtype="float16", name="x", is_input=True)
+    R1 = Tensor(shape=[m_dim, 8192], dtype="float16", name="r1", is_input=True)
+    W1 = Tensor(shape=[8192, k], dtype="float16", name="w1", is_input=True)
+    B1 = Tensor(shape=[8192], dtype="float16", name="b1", is_input=True)
+    W2 = Tensor(shape=[1024, 8192], dtype="float16", name="w2", is_input=True)
+    B2 = Tensor(shape=[1024], dtype="float16", name="b2", is_input=True)
+    H = ops.gemm_rcr_bias_add()(X, W1, B1, R1)
+    Y = ops.gemm_rcr_bias_relu()(H, W2, B2)
+    Y._attrs["name"], Y._attrs["is_output"] = "y", True
+    module = compile_model(Y, detect_target(), workdir, "dyn_m_kernels")
+    w1, b1, w2, b2 = _rand((8192, k), 31, 0.02), _rand((8192,), 32), _rand((1024, 8192), 33, 0.02), _rand((1024,), 34)
+    fixed = {"w1": w1.cuda(), "b1": b1.cuda(), "w2": w2.cuda(), "b2": b2.cuda()}
+    for m in (1, 4, 5, 16, 17, 33, 64, 100, 128, 129, 512):
+        x, r1 = _rand((m, k), 40 + m), _rand((m, 8192), 90 + m)
+        h = oracle.gemm_rcr(x, w1, b1, r1, epilogue="add").half()
+        want = oracle.gemm_rcr(h, w2, b2, epilogue="relu")
+        for graph_mode in (False, True, True):
+            y = torch.empty((512, 1024), dtype=torch.float16, device="cuda")
+            res = module.run_with_tensors(dict(fixed, x=x.cuda(), r1=r1.cuda()), {"y": y}, graph_mode=graph_mode)
+            assert tuple(res["y"].shape) == (m, 1024)
+            _close(res["y"], want, tol=2e-2)
+    module.close()
