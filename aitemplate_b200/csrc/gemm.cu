@@ -100,35 +100,6 @@ __device__ __forceinline__ void epilogue_scalar_store(const GemmParams& p, float
   static_cast<T*>(p.out)[batch_offset(p, b) + row_offset(p, row) + col_offset(p, col)] = E::from_float(v);
 }
 
-// The fused epilogue on 8 consecutive columns of one row whose 16-byte accesses are legal; the bias is already
-// in registers. Kept small on purpose: the weight-streaming kernel runs it once, at its very end, from a cold
-// instruction cache.
-template <bool BF16>
-__device__ __forceinline__ void epilogue_row8_store(const GemmParams& p, float (&v)[8], const float (&bias_v)[8],
-                                                    int row, int col0) {
-  using T = typename Elem16<BF16>::T;
-  const int u1 = epi_u1(p.epilogue), b1 = epi_b1(p.epilogue), b2 = epi_b2(p.epilogue), u2 = epi_u2(p.epilogue);
-#pragma unroll
-  for (int e = 0; e < 8; ++e) v[e] = v[e] * p.alpha + bias_v[e];
-  apply_unary_vec(u1, v);
-  const long long d_base = static_cast<long long>(row) * p.ldd + col0;
-  if (b1 != kBinaryNone) {
-    float f[8];
-    unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.d0) + d_base)), f);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = (b1 == kBinaryAdd) ? v[e] + f[e] : v[e] * f[e];
-  }
-  if (b2 != kBinaryNone) {
-    float f[8];
-    unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.d1) + d_base)), f);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = (b2 == kBinaryAdd) ? v[e] + f[e] : v[e] * f[e];
-  }
-  apply_unary_vec(u2, v);
-  T* out = static_cast<T*>(p.out) + row_offset(p, row) + col_offset(p, col0);
-  *reinterpret_cast<uint4*>(out) = pack8<BF16>(v);
-}
-
 // ------------------------------------------------------------------------------------------------
 // CUDA-core kernel for shapes TMA cannot address. 32x32 output tile per block, K staged in smem.
 template <bool BF16>
@@ -481,19 +452,22 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
           tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(my_row0 + c * kChunk), v);
           tmem_ld_wait();
           if (ok) {
+            // The K shares are added in the order of their ranks whichever rank does the adding, so a row's result
+            // does not depend on which rank finishes it (= on its position in X). All loads of the chunk come before
+            // its first store: the compiler may not move a load of `partial` over a store to `tile` by itself.
+            float sum[kChunk];
 #pragma unroll
             for (int j = 0; j < kChunk; ++j) {
-              // The K shares are added in the order of their ranks whichever rank does the adding, so a row's result
-              // does not depend on which rank finishes it (= on its position in X).
-              float sum = 0.f;
+              sum[j] = 0.f;
 #pragma unroll
               for (int q = 0; q < R; ++q) {
                 const int slot = q < rank ? q : q - 1;  // where rank q's sums sit in this rank's buffer
                 const float term = q == rank ? __uint_as_float(v[j]) : partial[(slot * kPart + c * kChunk + j) * 128 + row];
-                sum = q == 0 ? term : sum + term;
+                sum[j] = q == 0 ? term : sum[j] + term;
               }
-              tile[(c * kChunk + j) * 128 + row] = sum;
             }
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) tile[(c * kChunk + j) * 128 + row] = sum[j];
           }
         }
       }
@@ -504,25 +478,92 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         ok = mbar_wait(tile_summed, it & 1, abort_flag, p.status, kDevWaitOtherTimeout);
       }
       if (ok) {
-        // two rows (j and j + 8) per trip: two independent chains for the one warp each scheduler has
-        for (int j = et >> 4; j < my_rows; j += 16) {
-          const bool two = j + 8 < my_rows;
-          const float* src0 = tile + j * 128 + (et & 15) * 8;
-          const float* src1 = src0 + (two ? 8 * 128 : 0);
-          if (vec) {
-            const float4 a0 = *reinterpret_cast<const float4*>(src0), a1 = *reinterpret_cast<const float4*>(src0 + 4);
-            const float4 b0 = *reinterpret_cast<const float4*>(src1), b1 = *reinterpret_cast<const float4*>(src1 + 4);
-            float oa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            float ob[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-            epilogue_row8_store<BF16>(p, oa, bias_v, my_row0 + j, col0);
-            if (two) epilogue_row8_store<BF16>(p, ob, bias_v, my_row0 + j + 8, col0);
-          } else {
+        const int code = p.epilogue;
+        const bool simple = vec && epi_b1(code) == kBinaryNone && epi_b2(code) == kBinaryNone &&
+                            epi_u2(code) == kUnaryIdentity &&
+                            (epi_u1(code) == kUnaryIdentity || epi_u1(code) == kUnaryRelu) && p.store_mode == 0;
+        if (simple) {
+          // bias (+ relu) into a row-major output: four rows (j, j + 8, j + 16, j + 24) per trip, all of a trip's
+          // shared-memory loads first; no per-row dispatch on the epilogue code
+          using T = typename Elem16<BF16>::T;
+          const bool relu = epi_u1(code) == kUnaryRelu;
+          const float lo = relu ? 0.f : -INFINITY;
+          T* out0 = static_cast<T*>(p.out) + col0;
+          for (int j = et >> 4; j < my_rows; j += 32) {
+            float o[4][8];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const int jj = j + 8 * t < my_rows ? j + 8 * t : j;
+              const float* src = tile + jj * 128 + (et & 15) * 8;
+              const float4 a0 = *reinterpret_cast<const float4*>(src), a1 = *reinterpret_cast<const float4*>(src + 4);
+              o[t][0] = a0.x, o[t][1] = a0.y, o[t][2] = a0.z, o[t][3] = a0.w;
+              o[t][4] = a1.x, o[t][5] = a1.y, o[t][6] = a1.z, o[t][7] = a1.w;
+            }
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              if (j + 8 * t < my_rows) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[t][e] = fmaxf(o[t][e] * p.alpha + bias_v[e], lo);
+                *reinterpret_cast<uint4*>(out0 + static_cast<long long>(my_row0 + j + 8 * t) * p.ldc) = pack8<BF16>(o[t]);
+              }
+            }
+          }
+        }
+        if (!simple && vec) {
+          // Any epilogue: four rows per trip again. A trip's shared-memory loads and residual loads all go out
+          // before the first is used, and each activation is dispatched once per trip, over the 32 values.
+          using T = typename Elem16<BF16>::T;
+          const int u1 = epi_u1(code), b1 = epi_b1(code), b2 = epi_b2(code), u2 = epi_u2(code);
+          T* out0 = static_cast<T*>(p.out) + col_offset(p, col0);
+          for (int j = et >> 4; j < my_rows; j += 32) {
+            float o[32];
+            uint4 r0[4], r1[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const int jj = j + 8 * t < my_rows ? j + 8 * t : j;
+              const float* src = tile + jj * 128 + (et & 15) * 8;
+              const float4 a0 = *reinterpret_cast<const float4*>(src), a1 = *reinterpret_cast<const float4*>(src + 4);
+              o[t * 8 + 0] = a0.x, o[t * 8 + 1] = a0.y, o[t * 8 + 2] = a0.z, o[t * 8 + 3] = a0.w;
+              o[t * 8 + 4] = a1.x, o[t * 8 + 5] = a1.y, o[t * 8 + 6] = a1.z, o[t * 8 + 7] = a1.w;
+              const long long d_at = static_cast<long long>(my_row0 + jj) * p.ldd + col0;
+              if (b1 != kBinaryNone) r0[t] = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.d0) + d_at));
+              if (b2 != kBinaryNone) r1[t] = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.d1) + d_at));
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = o[i] * p.alpha + bias_v[i & 7];
+            apply_unary_vec(u1, o);
+            if (b1 != kBinaryNone) {
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                float f[8];
+                unpack8<BF16>(r0[t], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[t * 8 + e] = (b1 == kBinaryAdd) ? o[t * 8 + e] + f[e] : o[t * 8 + e] * f[e];
+              }
+            }
+            if (b2 != kBinaryNone) {
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                float f[8];
+                unpack8<BF16>(r1[t], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[t * 8 + e] = (b2 == kBinaryAdd) ? o[t * 8 + e] + f[e] : o[t * 8 + e] * f[e];
+              }
+            }
+            apply_unary_vec(u2, o);
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+              if (j + 8 * t < my_rows)
+                *reinterpret_cast<uint4*>(out0 + row_offset(p, my_row0 + j + 8 * t)) = pack8<BF16>(&o[t * 8]);
+          }
+        }
+        if (!vec) {
+          // columns whose 16-byte accesses are not legal (a ragged last slab, an odd row pitch): element by element
+          for (int j = et >> 4; j < my_rows; j += 8) {
+            const float* src = tile + j * 128 + (et & 15) * 8;
 #pragma unroll 1
             for (int e = 0; e < 8; ++e)
-              if (col0 + e < p.N) {
-                epilogue_scalar_store<BF16>(p, src0[e], 0, my_row0 + j, col0 + e);
-                if (two) epilogue_scalar_store<BF16>(p, src1[e], 0, my_row0 + j + 8, col0 + e);
-              }
+              if (col0 + e < p.N) epilogue_scalar_store<BF16>(p, src[e], 0, my_row0 + j, col0 + e);
           }
         }
         // This thread is done reading `partial`: the peers may send the next slab's sums. (Its reads have returned -
