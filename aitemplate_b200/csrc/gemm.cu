@@ -291,7 +291,6 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     mbar_init(tile_summed, 128);
     *abort_flag = 0;
     fence_mbar_init();
-    fence_proxy_async_smem();  // this thread's own TMA loads, issued below, signal the barriers just initialised
     tma_prefetch_desc(&tma_w);
     tma_prefetch_desc(&tma_x);
   }
@@ -316,10 +315,9 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
     return true;
   };
-  // The first ring-full of loads needs this CTA's barriers only: it leaves before the TMEM allocation and the
-  // cluster-wide sync, which then cost nothing on top of the first trip to DRAM.
-  const int prefill = nkb < Cfg::kStages ? nkb : Cfg::kStages;
-  if (threadIdx.x == 0 && walker < my_slabs) produce(walker, 0, prefill);
+  // (Issuing the first ring-full of loads here, before the TMEM allocation and the cluster-wide sync, was measured:
+  // 0.5 - 1.5 us SLOWER on every shape. The first TMA instruction waits for its tensor map, just prefetched above, and
+  // thread 0 then holds up the CTA's set-up for that long.)
   __syncthreads();
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);  // two accumulators
@@ -336,7 +334,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     if (lane == 0) {
       bool ok = true;
       for (int slab = walker; ok && slab < my_slabs; slab += num_walkers)
-        ok = produce(slab, slab == walker ? prefill : 0, nkb);
+        ok = produce(slab, 0, nkb);
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) {
