@@ -485,7 +485,6 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
           // shared-memory loads first; no per-row dispatch on the epilogue code
           using T = typename Elem16<BF16>::T;
           const bool relu = epi_u1(code) == kUnaryRelu;
-          const float lo = relu ? 0.f : -INFINITY;
           T* out0 = static_cast<T*>(p.out) + col0;
           for (int j = et >> 4; j < my_rows; j += 32) {
             float o[4][8];
@@ -501,7 +500,10 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             for (int t = 0; t < 4; ++t) {
               if (j + 8 * t < my_rows) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[t][e] = fmaxf(o[t][e] * p.alpha + bias_v[e], lo);
+                for (int e = 0; e < 8; ++e) {
+                  const float y = o[t][e] * p.alpha + bias_v[e];
+                  o[t][e] = relu ? fmaxf(y, 0.f) : y;  // identity keeps a NaN a NaN
+                }
                 *reinterpret_cast<uint4*>(out0 + static_cast<long long>(my_row0 + j + 8 * t) * p.ldc) = pack8<BF16>(o[t]);
               }
             }
