@@ -770,7 +770,11 @@ SplitPlan plan_split_k(long long batch, long long m, long long n, long long k, i
     s = std::min<long long>(max_splits, num_kb / 2);  // the caller's choice
   } else {
     if (tiles * 2 > sms) return sp;
-    s = std::min<long long>(std::min<long long>(sms / tiles, num_kb / 2), 16);
+    // A split adds a second launch and a round trip of fp32 partial sums (4 - 5 us on a small problem): it pays only
+    // when it takes that much off the main loop, i.e. from K = 2048 on and with at least 8 k-blocks left per split
+    // (384 x 768 x 768: 8.3 us unsplit against 13.9 us in 6 splits; 256 x 768 x 3072: 16.7 us in 4 splits against 18.8).
+    if (num_kb < 32) return sp;
+    s = std::min<long long>(std::min<long long>(sms / tiles, num_kb / 8), 16);
   }
   while (s > 1 && s * batch * m * n * 4 > workspace_bytes) --s;
   if (s <= 1) return sp;
