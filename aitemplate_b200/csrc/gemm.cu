@@ -947,7 +947,8 @@ void gemm_run(const GemmArgs& g_in) {
   const bool staged_residual = b1 != kBinaryNone && b2 == kBinaryNone;
   // From K = 2048 on the pairs win even when only 3 in 5 of them get a tile: the operand traffic they save counts for
   // more than the idle SMs (768 x 4096 x 4096: 28.2 against 32.0 us with 48 tiles for 74 pairs).
-  const long long pair_tiles_min = g.k >= 2048 ? sm_count() * 3 / 10 : sm_count() / 2;
+  // (and with a residual, which only the pairs fetch by TMA: 3072 x 1280 x 320 + add: 11.3 against 12.3 us)
+  const long long pair_tiles_min = (g.k >= 2048 || staged_residual) ? sm_count() * 3 / 10 : sm_count() / 2;
   const bool pair = force_pair || (g.tile_n == 0 && bn == 256 && sp.splits == 1 &&
                                    g.k >= (staged_residual ? 256 : 512) && pair_tiles >= pair_tiles_min &&
                                    p.c_bdiv == 0);
