@@ -721,7 +721,11 @@ int choose_tile_n(long long m, long long n, long long k, long long batch) {
   // through its one staging buffer, the second waiting for the first to drain; 128-wide tiles store one box per
   // tile and overlap the drain with the next tile. Measured, 1024 x [512 x 512 x 64]: 119 us against 133 us;
   // K = 128: 131 against 159 us; from K = 256 on the wider tile wins again (89 against 105 us).
-  if (k <= 2 * kBK && n >= 128 && batch * m * n * 2 > (96ll << 20)) return 128;
+  // Measured later on wider results (us, 128- against 256-wide): K = 64 with N = 1024 .. 4096: 105 against 111 - 126;
+  // K = 128 with N = 1024 / 2048: 128 against 118 / 107; K = 40 (rows of 80 bytes, padded to one k-block) with N = 2048 /
+  // 4096: 141 against 125 (the wide tile fetches a quarter fewer operand rows, and TMA pays per row). So the narrow
+  // tile is taken for one full k-block, and for two only on a narrow result.
+  if (n >= 128 && batch * m * n * 2 > (96ll << 20) && ((k == kBK) || (k > kBK && k <= 2 * kBK && n <= 512))) return 128;
   int best = 256;
   long long best_cost = -1;
   for (int bn : {256, 128, 64}) {
