@@ -272,9 +272,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   const int my_slabs = misaligned ? 0 : num_slabs;
   // this rank's share of the k-blocks (the host sends no problem with fewer k-blocks than ranks)
   const int kb_total = (p.K + kBK - 1) / kBK;
-  const int kb_share = (kb_total + R - 1) / R;
-  const int kb0 = rank * kb_share < kb_total ? rank * kb_share : kb_total;
-  const int kb1 = kb0 + kb_share < kb_total ? kb0 + kb_share : kb_total;
+  // split evenly, so that no rank is left without a k-block (its accumulator would never be written)
+  const int kb0 = rank * kb_total / R, kb1 = (rank + 1) * kb_total / R;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -895,10 +894,11 @@ void gemm_run(const GemmArgs& g_in) {
     B200AIT_CUDA_CHECK(cudaGetLastError());
     return;
   }
-  // 5 <= M <= 128 against a big weight matrix, tile width and split-K left to the library: stream W once with the
+  // 5 <= M <= 128, tile width and split-K left to the library (measured against the tile kernels: ahead for every
+  // N >= 128 from K = 512 on, and for M <= 32 from K = 256 on; 256 x 4096 at M = 64: 9.4 against 17.5 us): stream W once with the
   // operands swapped (W rows on the MMA rows), K split across a cluster of two or four, no workspace
   if (tma_ok && g.batch == 1 && g.m <= kSwapMaxM && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0 &&
-      g.k >= 512 && g.n >= 512) {
+      g.n >= 128 && (g.k >= 512 || (g.k >= 256 && g.m <= 32))) {
     const int num_slabs = static_cast<int>((g.n + 127) / 128);
     // few slabs (N <= 128 * SMs / 4): K goes four ways, so that most SMs stream
     const bool quad = num_slabs <= sm_count() / 4;

@@ -486,6 +486,26 @@ def test_swapped_operand_weight_streaming(m, n, kk, epilogue, dtype):
     _close(y256, want, atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("m,n,kk,epilogue", [(128, 320, 1280, "add"), (64, 128, 2048, "relu"), (100, 200, 768, "fast_gelu"),
+                                              (16, 768, 320, ""), (32, 136, 264, "tanh"), (5, 128, 512, "mul"),
+                                              (48, 1024, 576, "relu"), (128, 4096, 384 + 8, "")])
+def test_swapped_operand_narrow_and_shallow_weights(m, n, kk, epilogue):
+    """The edges of what the weight-streaming kernel takes: one or two slabs (N = 128 .. 320, a ragged single slab),
+    and K down to 256 for M <= 32 (four to five k-blocks shared by a cluster of four); k-block counts that do not
+    divide by the cluster size (5, 7, 9) must still give every rank a share."""
+    k = _kernels()
+    x = _rand((m, kk), 630, dist="uniform")
+    w = _rand((n, kk), 631, scale=0.05)
+    b = _rand((n,), 632, scale=0.1)
+    nres = {"add": 1, "mul": 1}.get(epilogue, 0)
+    d = [_rand((m, n), 633 + i) for i in range(nres)]
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), *[t.cuda() for t in d], epilogue=epilogue)
+    assert k.device_status() == 0
+    _close(y, oracle.gemm_rcr(x, w, b, *d, epilogue=epilogue))
+    y256 = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), *[t.cuda() for t in d], epilogue=epilogue, tile_n=128)
+    _close(y256, oracle.gemm_rcr(x, w, b, *d, epilogue=epilogue))
+
+
 @pytest.mark.parametrize("m,n,kk", [(128, 8192, 2048), (96, 3072, 2048), (40, 1024, 4096)])
 def test_swapped_operand_rows_do_not_depend_on_their_position(m, n, kk):
     """Which rank of the cluster finishes a row of X depends on the row's index; the K shares are added in rank
