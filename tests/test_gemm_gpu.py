@@ -506,6 +506,32 @@ def test_swapped_operand_narrow_and_shallow_weights(m, n, kk, epilogue):
     _close(y256, oracle.gemm_rcr(x, w, b, *d, epilogue=epilogue))
 
 
+def test_swapped_operand_random_shapes():
+    """Seeded random problems all over what the weight-streaming kernel takes (5 <= M <= 128, N >= 128, K >= 512, or
+    K >= 256 with M <= 32): ragged slabs, k-block counts of every residue, every X-tile width, both cluster sizes."""
+    import random
+
+    k = _kernels()
+    rng = random.Random(20240611)
+    epilogues = ["", "relu", "fast_gelu", "add", "mul_add", "add_relu", "sigmoid"]
+    for case in range(48):
+        m = rng.choice([5, 8, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100, 127, 128])
+        n = rng.choice([128, 136, 200, 256, 320, 512, 1000, 2048, 3000, 4736, 4744, 6000])
+        kk = 8 * rng.randint(32 if m <= 32 else 64, 400)
+        epilogue = rng.choice(epilogues)
+        x = _rand((m, kk), 700 + case, dist="uniform")
+        w = _rand((n, kk), 800 + case, scale=0.03)
+        b = _rand((n,), 900 + case, scale=0.1)
+        nres = {"add": 1, "mul_add": 2, "add_relu": 1}.get(epilogue, 0)
+        d = [_rand((m, n), 1000 + 2 * case + i) for i in range(nres)]
+        y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), *[t.cuda() for t in d], epilogue=epilogue)
+        assert k.device_status() == 0, (m, n, kk, epilogue)
+        try:
+            _close(y, oracle.gemm_rcr(x, w, b, *d, epilogue=epilogue), atol=1.5e-2, rtol=1.5e-2)
+        except AssertionError as e:
+            raise AssertionError(f"m={m} n={n} k={kk} epilogue={epilogue!r}: {e}") from None
+
+
 @pytest.mark.parametrize("m,n,kk", [(128, 8192, 2048), (96, 3072, 2048), (40, 1024, 4096)])
 def test_swapped_operand_rows_do_not_depend_on_their_position(m, n, kk):
     """Which rank of the cluster finishes a row of X depends on the row's index; the K shares are added in rank
