@@ -138,3 +138,25 @@ def test_strided_operands_read_in_place(b, h, sq, skv, d, causal):
     out2 = kernels.mem_eff_attention_strided(qd.permute(0, 2, 1, 3), kd.permute(0, 2, 1, 3).contiguous(),
                                              vd.permute(0, 2, 1, 3).contiguous(), causal=causal)
     assert torch.equal(out2, out)
+
+
+def test_random_shapes():
+    """Seeded random problems: every head size the tensor-core kernel takes (multiples of 8 up to 128), ragged query
+    and key tails, one to a few dozen key blocks, causal or not, different value head sizes."""
+    import random
+
+    rng = random.Random(20240612)
+    for case in range(32):
+        b, h = rng.randint(1, 3), rng.randint(1, 5)
+        d = rng.choice([8, 16, 24, 32, 40, 48, 64, 72, 80, 96, 128])
+        causal = rng.random() < 0.35
+        sq = rng.choice([1, 7, 64, 100, 128, 129, 200, 384, 500, 777])
+        skv = sq if causal else rng.choice([1, 13, 63, 64, 65, 77, 128, 191, 320, 1000, 1500])
+        dv = d if rng.random() < 0.7 else rng.choice([8, 32, 64, 128])
+        q = _rand((b, h, sq, d), 2000 + case)
+        k = _rand((b, h, skv, d), 3000 + case)
+        v = _rand((b, h, skv, dv), 4000 + case)
+        try:
+            _check(q, k, v, causal=causal)
+        except AssertionError as e:
+            raise AssertionError(f"b={b} h={h} sq={sq} skv={skv} d={d} dv={dv} causal={causal}: {e}") from None

@@ -558,3 +558,35 @@ def test_swapped_operand_permuted_store(m, seq):
     y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), permute_shape=(seq, 3, h))
     assert k.device_status() == 0
     _close(y, oracle.gemm_rcr_bias_permute(x, w, b, (seq, 3, h)))
+
+
+def test_tile_kernels_random_shapes():
+    """Seeded random problems for the tile kernels (M > 128, or a tile hint): ragged M / N / K, every tile width
+    including the CTA pairs, library-chosen and capped split-K, all epilogue families, both dtypes."""
+    import random
+
+    k = _kernels()
+    rng = random.Random(20240613)
+    epilogues = ["", "relu", "gelu", "fast_gelu", "add", "add_relu", "mul", "mul_add", "sigmoid_mul", "tanh", "add_add"]
+    for case in range(40):
+        m = rng.choice([129, 200, 256, 300, 511, 640, 1000, 1536])
+        n = 8 * rng.randint(8, 160)
+        kk = 8 * rng.randint(8, 300)
+        epilogue = rng.choice(epilogues)
+        dtype = torch.bfloat16 if rng.random() < 0.25 else torch.float16
+        tile_n = rng.choice([0, 0, 0, 64, 128, 256, 512])
+        split_k = rng.choice([0, 0, 1, 3]) if tile_n != 512 else 0
+        x = _rand((m, kk), 5000 + case, dist="uniform", dtype=dtype)
+        w = _rand((n, kk), 6000 + case, scale=0.03, dtype=dtype)
+        b = _rand((n,), 7000 + case, scale=0.1, dtype=dtype)
+        nres = {"add": 1, "add_relu": 1, "mul": 1, "mul_add": 2, "sigmoid_mul": 1, "add_add": 2}.get(epilogue, 0)
+        d = [_rand((m, n), 8000 + 2 * case + i, dtype=dtype) for i in range(nres)]
+        tol = 1.5e-2 if dtype == torch.float16 else 5e-2
+        try:
+            y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), *[t.cuda() for t in d], epilogue=epilogue, tile_n=tile_n,
+                           split_k=split_k)
+            assert k.device_status() == 0
+            _close(y, oracle.gemm_rcr(x, w, b, *d, epilogue=epilogue), atol=tol, rtol=tol)
+        except AssertionError as e:
+            raise AssertionError(f"m={m} n={n} k={kk} epilogue={epilogue!r} {dtype} tile_n={tile_n} split_k={split_k}: {e}") from None
+
