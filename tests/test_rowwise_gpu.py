@@ -124,3 +124,26 @@ def test_full_size_rows_are_independent_and_normalised():
     p = kernels.softmax(s, -1)
     assert float((p.float().sum(-1) - 1).abs().max()) < 2e-2
     _close(p[3, 100:108], oracle.softmax(s[3, 100:108], -1), 1e-2)
+
+
+def test_random_shapes():
+    """Seeded random row counts and row lengths (odd lengths, lengths around the vector widths and the per-warp and
+    per-block limits of the kernels) for layernorm and for softmax over the last and over an inner dimension."""
+    import random
+
+    from aitemplate_b200 import kernels
+
+    rng = random.Random(20240614)
+    for case in range(40):
+        m = rng.choice([1, 3, 31, 64, 257, 1000])
+        n = rng.choice([1, 2, 7, 8, 9, 63, 64, 65, 255, 256, 320, 511, 777, 1024, 1025, 2048, 3000, 4097, 9000, 16384])
+        x = _rand((m, n), 9000 + case, scale=rng.choice([0.1, 1.0, 8.0]))
+        g, b = (_rand((n,), 9100 + case, dist="uniform") + 0.5).half(), _rand((n,), 9200 + case, scale=0.1)
+        try:
+            _close(kernels.layernorm(x.cuda(), g.cuda(), b.cuda(), eps=1e-5), oracle.layernorm(x, g, b, 1e-5), 4e-3)
+            _close(kernels.softmax(x.cuda(), -1), oracle.softmax(x, -1), 1e-2)
+            inner = rng.choice([2, 5, 16])
+            x3 = _rand((rng.choice([1, 4]), max(1, min(n, 300)), inner), 9300 + case)
+            _close(kernels.softmax(x3.cuda(), 1), oracle.softmax(x3, 1), 1e-2)
+        except AssertionError as e:
+            raise AssertionError(f"m={m} n={n}: {e}") from None
