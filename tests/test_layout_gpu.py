@@ -117,3 +117,35 @@ def test_elementwise_chain(shapes, steps):
     got = y.float().cpu()
     assert got.shape == want.shape
     assert bool(((got - want).abs() <= 1e-2 + 1e-2 * want.abs()).all())
+
+
+def test_random_shapes_bit_exact():
+    """Seeded random concatenate / split / permute problems (ranks 2-5, odd extents, every dim, both 16-bit types and
+    fp32): results must equal torch's bit for bit."""
+    import itertools
+    import random
+
+    from aitemplate_b200 import kernels
+
+    rng = random.Random(20240615)
+    for case in range(40):
+        rank = rng.randint(2, 5)
+        dtype = rng.choice([torch.float16, torch.bfloat16, torch.float32])
+        shape = [rng.choice([1, 2, 3, 5, 8, 17, 32, 63]) for _ in range(rank)]
+        dim = rng.randrange(rank)
+        gen = torch.Generator().manual_seed(11000 + case)
+        xs = []
+        for i in range(rng.randint(1, 4)):
+            s = list(shape)
+            s[dim] = rng.choice([1, 2, 7, 16, 40])
+            xs.append(torch.randn(s, generator=gen).to(dtype))
+        want = torch.cat(xs, dim)
+        got = kernels.concatenate([x.cuda() for x in xs], dim)
+        assert torch.equal(got.cpu(), want), f"concatenate {[tuple(x.shape) for x in xs]} dim {dim} {dtype}"
+        parts = kernels.split(got, [x.shape[dim] for x in xs], dim)
+        for p, x in zip(parts, xs):
+            assert torch.equal(p.cpu(), x), f"split {tuple(want.shape)} dim {dim} {dtype}"
+        dims = list(range(rank))
+        rng.shuffle(dims)
+        x = torch.randn(shape, generator=gen).to(dtype)
+        assert torch.equal(kernels.permute(x.cuda(), dims).cpu(), x.permute(dims).contiguous()), f"permute {shape} {dims} {dtype}"
