@@ -590,3 +590,34 @@ def test_tile_kernels_random_shapes():
         except AssertionError as e:
             raise AssertionError(f"m={m} n={n} k={kk} epilogue={epilogue!r} {dtype} tile_n={tile_n} split_k={split_k}: {e}") from None
 
+
+def test_batched_and_row_major_random_shapes():
+    """Seeded random problems for bmm_rcr, bmm_rrr (B stored [K, N]), gemm_rrr and a broadcast operand."""
+    import random
+
+    k = _kernels()
+    rng = random.Random(20240616)
+    for case in range(30):
+        bsz = rng.choice([1, 2, 5, 16])
+        m = rng.choice([1, 8, 100, 128, 200, 384])
+        n = 8 * rng.randint(1, 60)
+        kk = 8 * rng.randint(1, 80)
+        alpha = rng.choice([1.0, 0.125])
+        a = _rand((bsz, m, kk), 12000 + case, dist="uniform")
+        try:
+            if case % 3 == 0:
+                b = _rand((bsz, n, kk), 13000 + case, scale=0.1)
+                _close(k.bmm_rcr(a.cuda(), b.cuda(), alpha=alpha), oracle.bmm_rcr(a, b, alpha=alpha), atol=1.5e-2, rtol=1.5e-2)
+                b1 = b[:1]  # one B for every batch
+                _close(k.bmm_rcr(a.cuda(), b1.cuda(), alpha=alpha), oracle.bmm_rcr(a, b1.expand(bsz, n, kk), alpha=alpha),
+                       atol=1.5e-2, rtol=1.5e-2)
+            elif case % 3 == 1:
+                b = _rand((bsz, kk, n), 13000 + case, scale=0.1)
+                _close(k.bmm_rrr(a.cuda(), b.cuda(), alpha=alpha), oracle.bmm_rrr(a, b, alpha=alpha), atol=1.5e-2, rtol=1.5e-2)
+            else:
+                w = _rand((kk, n), 13000 + case, scale=0.1)
+                bias = _rand((n,), 14000 + case, scale=0.1)
+                _close(k.gemm_rrr(a[0].cuda(), w.cuda(), bias.cuda()), oracle.gemm_rrr(a[0], w, bias), atol=1.5e-2, rtol=1.5e-2)
+        except AssertionError as e:
+            raise AssertionError(f"case {case}: batch={bsz} m={m} n={n} k={kk} alpha={alpha}: {e}") from None
+
