@@ -211,24 +211,25 @@ __global__ void __launch_bounds__(kRowDotThreads, 1) gemm_rowdot_kernel(const vo
 // split-K + reduce kernel this replaces ran at 0.54 of the copy rate for these shapes).
 //   warp 0: TMA producer   warp 1: MMA issuer   warps 2-5: epilogue (TMEM lane = weight row = output column)
 constexpr int kSwapThreads = 192;
-constexpr int kSwapMaxM = 128;
-template <int MX, int R>
+constexpr int kSwapMaxM = 256;
+template <int MX, int R, int H>
 struct SwapCfg {
   static_assert(R == 2 || R == 4, "cluster size");
-  static constexpr int kPart = MX / R;              // rows of X each rank finishes
-  static_assert(kPart >= 8, "a rank finishes at least 8 rows");
+  static constexpr int kPart = MX / R;              // rows of X each rank finishes ...
+  static constexpr int kSub = kPart / H;            // ... in H passes of kSub rows (what bounds the exchange buffers)
+  static_assert(H >= 1 && kSub * H == kPart && kSub >= 8, "a rank finishes at least 8 rows per pass");
   static constexpr int kWBytes = 128 * kBK * 2;     // 16 KB: 128 weight rows x 64 k
   static constexpr int kXBytes = MX * kBK * 2;      // MX rows of X x 64 k
   static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kSlotBytes = 128 * kPart * 4;               // [128 weight rows][kPart rows of X] fp32
+  static constexpr int kSlotBytes = 128 * kSub * 4;                // [kSub rows of X][128 weight rows] fp32
   static constexpr int kPartialBytes = (R - 1) * kSlotBytes;       // one slot per peer: its sums for this rank's rows
-  static constexpr int kTileBytes = kSlotBytes;                    // the finished tile, [kPart][128]
+  static constexpr int kTileBytes = kSlotBytes;                    // the finished tile, [kSub][128]
   static constexpr int kFit = (227 * 1024 - 256 - kPartialBytes - kTileBytes) / kStageBytes;
   static constexpr int kStages = kFit < 8 ? kFit : 8;  // 144 to 192 KB in flight
   static constexpr int kAccCols = MX < 32 ? 32 : MX;  // TMEM columns of one accumulator
   static constexpr int kTmemCols = 2 * kAccCols;
   static constexpr int kSmemBytes = kStages * kStageBytes + kPartialBytes + kTileBytes + 256;
-  static_assert(kStages >= 4 && kSmemBytes <= 227 * 1024, "swapped-operand kernel: shared memory");
+  static_assert(kStages >= 3 && kSmemBytes <= 227 * 1024, "swapped-operand kernel: shared memory");
 };
 
 template <int N>
@@ -243,16 +244,16 @@ __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[N]) 
   }
 }
 
-template <bool BF16, int MX, int R>
+template <bool BF16, int MX, int R, int H>
 __global__ void __launch_bounds__(kSwapThreads, 1)
 gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
                    const GemmParams p, const int num_slabs) {
-  using Cfg = SwapCfg<MX, R>;
+  using Cfg = SwapCfg<MX, R, H>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const bool misaligned = (smem_u32(smem) & 1023u) != 0u;
   if (misaligned && threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevBadSmemAlignment);
-  float* partial = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);  // [R - 1][MX / R][128], a slot per peer
-  float* tile = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes);  // [MX / R][128]
+  float* partial = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);  // [R - 1][kSub][128], a slot per peer
+  float* tile = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes);  // [kSub][128]
   uint64_t* full_bar =
       reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes + Cfg::kTileBytes);
   uint64_t* empty_bar = full_bar + Cfg::kStages;
@@ -384,52 +385,57 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       }
     }
   } else {
-    // Every rank finishes MX / R of the slab's rows of X: rank r keeps rows [r * MX/R, (r + 1) * MX/R) of its own
-    // sums and sends the others to the rank that finishes them (slot "sender" of that rank's `partial`; a warp's
+    // The MX rows of X are cut into H x R blocks of kSub rows; in pass h rank r finishes block h * R + r: it keeps
+    // that block of its own sums and sends each peer q the block h * R + q (slot "sender" of q's `partial`; a warp's
     // store covers 128 consecutive bytes). The stores are asynchronous and credit their bytes to the receiver's
-    // `partial_ready`: nobody waits for a store to land except the thread that needs the data. Then the rank
-    // adds what its peers sent into `tile` and writes its rows out.
-    constexpr int kPart = Cfg::kPart;
-    constexpr int kChunk = kPart < 32 ? kPart : 32;  // TMEM columns per load
+    // `partial_ready`: nobody waits for a store to land except the thread that needs the data. Then the rank adds
+    // what its peers sent into `tile` and writes its rows out. (H > 1 only bounds the buffers: 256 rows of X would
+    // otherwise need 128 KB of them.)
+    constexpr int kSub = Cfg::kSub;
+    constexpr int kChunk = kSub < 32 ? kSub : 32;  // TMEM columns per load
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // weight row inside the slab == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const int my_row0 = rank * kPart;
-    const int my_rows = p.M - my_row0 < 0 ? 0 : (p.M - my_row0 < kPart ? p.M - my_row0 : kPart);
     const int et = static_cast<int>(threadIdx.x) - 64;  // 0..127 over the four epilogue warps
     int acc = 0;
     uint32_t acc_phase = 0;
-    int it = 0;
+    int seq = 0;  // passes done so far: the exchange barriers change phase once per pass
     bool ok = true;
-    for (int slab = walker; ok && slab < my_slabs; slab += num_walkers, ++it) {
-      const bool last = slab + num_walkers >= my_slabs;
-      // what the peers will send for this slab (a rank with no valid row of X is sent nothing and waits for nothing)
-      if (et == 0 && my_rows > 0) mbar_arrive_expect_tx(partial_ready, (R - 1) * Cfg::kSlotBytes);
+    for (int slab = walker; ok && slab < my_slabs; slab += num_walkers) {
+      const bool last_slab = slab + num_walkers >= my_slabs;
       // The tile goes out row by row: a thread takes 8 consecutive columns (one 16-byte store), 16 threads one
       // row of the slab. A thread keeps the same columns for every row, so it fetches their bias once, early.
       const int col0 = slab * 128 + (et & 15) * 8;
       const bool vec = p.vec_ok && col0 + 8 <= p.N;
       float bias_v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      if (vec && p.bias != nullptr && my_rows > 0)
+      if (vec && p.bias != nullptr)
         unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(static_cast<const typename Elem16<BF16>::T*>(p.bias) + col0)),
                       bias_v);
       ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, kDevWaitAccFullTimeout);
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + lane_addr + static_cast<uint32_t>(acc * Cfg::kAccCols);
-      // the peers must have read what this CTA sent for the previous slab before it is overwritten
-      if (it > 0) ok = mbar_wait_cluster(partial_taken, (it - 1) & 1, abort_flag, p.status, kDevWaitOtherTimeout);
+#pragma unroll 1
+      for (int pass = 0; ok && pass < H; ++pass, ++seq) {
+      const bool last = last_slab && pass == H - 1;
+      const int my_row0 = (pass * R + rank) * kSub;
+      const int my_rows = p.M - my_row0 < 0 ? 0 : (p.M - my_row0 < kSub ? p.M - my_row0 : kSub);
+      // what the peers will send for this pass (a rank with no valid row of X is sent nothing and waits for nothing)
+      if (et == 0 && my_rows > 0) mbar_arrive_expect_tx(partial_ready, (R - 1) * Cfg::kSlotBytes);
+      // the peers must have read what this CTA sent for the previous pass before it is overwritten
+      if (seq > 0) ok = mbar_wait_cluster(partial_taken, (seq - 1) & 1, abort_flag, p.status, kDevWaitOtherTimeout);
 #pragma unroll
       for (int q = 0; q < R; ++q) {
-        if (q == rank || p.M <= q * kPart) continue;
+        const int q_row0 = (pass * R + q) * kSub;
+        if (q == rank || p.M <= q_row0) continue;
         const int slot = rank < q ? rank : rank - 1;  // where this rank's sums go in rank q's buffer
         const uint32_t dst = mapa_shared(smem_u32(partial), static_cast<uint32_t>(q)) +
-                             static_cast<uint32_t>((slot * kPart * 128 + row) * 4);
+                             static_cast<uint32_t>((slot * kSub * 128 + row) * 4);
         const uint32_t dst_bar = mapa_shared(smem_u32(partial_ready), static_cast<uint32_t>(q));
 #pragma unroll
-        for (int c = 0; c < kPart / kChunk; ++c) {
+        for (int c = 0; c < kSub / kChunk; ++c) {
           uint32_t v[kChunk];
-          tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(q * kPart + c * kChunk), v);
+          tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(q_row0 + c * kChunk), v);
           tmem_ld_wait();
           if (ok) {
 #pragma unroll
@@ -440,11 +446,14 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       }
       // After its last send a thread touches no peer again: the cluster-wide barrier that keeps every CTA alive
       // until then is arrived at here and waited for at the very end, when it has long completed.
-      if (last) cluster_arrive_relaxed();
+      if (last) {
+        cluster_arrive_relaxed();
+        epi_arrived = true;
+      }
       if (ok && my_rows > 0) {
-        ok = mbar_wait_cluster(partial_ready, it & 1, abort_flag, p.status, kDevWaitOtherTimeout);
+        ok = mbar_wait_cluster(partial_ready, seq & 1, abort_flag, p.status, kDevWaitOtherTimeout);
 #pragma unroll
-        for (int c = 0; c < kPart / kChunk; ++c) {
+        for (int c = 0; c < kSub / kChunk; ++c) {
           uint32_t v[kChunk];
           tmem_ld_chunk<kChunk>(t_addr + static_cast<uint32_t>(my_row0 + c * kChunk), v);
           tmem_ld_wait();
@@ -459,7 +468,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
 #pragma unroll
               for (int q = 0; q < R; ++q) {
                 const int slot = q < rank ? q : q - 1;  // where rank q's sums sit in this rank's buffer
-                const float term = q == rank ? __uint_as_float(v[j]) : partial[(slot * kPart + c * kChunk + j) * 128 + row];
+                const float term = q == rank ? __uint_as_float(v[j]) : partial[(slot * kSub + c * kChunk + j) * 128 + row];
                 sum[j] = q == 0 ? term : sum[j] + term;
               }
             }
@@ -468,11 +477,13 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
           }
         }
       }
-      tc_fence_before();
-      mbar_arrive(&acc_empty[acc]);
+      if (pass == H - 1) {  // the accumulator has been read for the last time
+        tc_fence_before();
+        mbar_arrive(&acc_empty[acc]);
+      }
       if (ok) {
         mbar_arrive(tile_summed);
-        ok = mbar_wait(tile_summed, it & 1, abort_flag, p.status, kDevWaitOtherTimeout);
+        ok = mbar_wait(tile_summed, seq & 1, abort_flag, p.status, kDevWaitOtherTimeout);
       }
       if (ok) {
         const int code = p.epilogue;
@@ -565,7 +576,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
               if (col0 + e < p.N) epilogue_scalar_store<BF16>(p, src[e], 0, my_row0 + j, col0 + e);
           }
         }
-        // This thread is done reading `partial`: the peers may send the next slab's sums. (Its reads have returned -
+        // This thread is done reading `partial`: the peers may send the next pass's sums. (Its reads have returned -
         // their values went into `tile` - so the signal needs no release. A rank without rows signals all the same:
         // the senders count every peer.)
         if (!last) {
@@ -574,10 +585,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             if (q != rank) mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(partial_taken), static_cast<uint32_t>(q)));
         }
       }
-      if (last) {
-        epi_arrived = true;
-        break;
-      }
+      }  // passes
+      if (last_slab) break;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -595,12 +604,12 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   cluster_wait();  // no CTA leaves while a peer can still write to it or signal it
 }
 
-template <bool BF16, int MX, int R>
+template <bool BF16, int MX, int R, int H>
 static void launch_swapab(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int num_slabs,
                           cudaStream_t stream) {
-  using Cfg = SwapCfg<MX, R>;
+  using Cfg = SwapCfg<MX, R, H>;
   static std::atomic<uint64_t> configured{0};
-  auto* kernel = &gemm_swapab_kernel<BF16, MX, R>;
+  auto* kernel = &gemm_swapab_kernel<BF16, MX, R, H>;
   opt_in_smem_once(configured, reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(R * (sm_count() / R)));
@@ -894,28 +903,30 @@ void gemm_run(const GemmArgs& g_in) {
     B200AIT_CUDA_CHECK(cudaGetLastError());
     return;
   }
-  // 5 <= M <= 128, tile width and split-K left to the library (measured against the tile kernels: ahead for every
-  // N >= 128 from K = 512 on, and for M <= 32 from K = 256 on; 256 x 4096 at M = 64: 9.4 against 17.5 us): stream W once with the
+  // 5 <= M <= 256, tile width and split-K left to the library (measured against the tile kernels: up to M = 128 ahead
+  // for every N >= 128 from K = 512 on, and for M <= 32 from K = 256 on; 256 x 4096 at M = 64: 9.4 against 17.5 us; for
+  // 128 < M <= 256, where X is 256 rows per k-block, from K = 2048 on: 4096 x 4096 at M = 256 19.9 against 24.9 us, but
+  // 3072 x 768 11.6 against 8.8): stream W once with the
   // operands swapped (W rows on the MMA rows), K split across a cluster of two or four, no workspace
   if (tma_ok && g.batch == 1 && g.m <= kSwapMaxM && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0 &&
-      g.n >= 128 && (g.k >= 512 || (g.k >= 256 && g.m <= 32))) {
+      g.n >= 128 && (g.m <= 128 ? (g.k >= 512 || (g.k >= 256 && g.m <= 32)) : g.k >= 2048)) {
     const int num_slabs = static_cast<int>((g.n + 127) / 128);
     // few slabs (N <= 128 * SMs / 4): K goes four ways, so that most SMs stream
     const bool quad = num_slabs <= sm_count() / 4;
-    const int mx = g.m <= 16 && !quad ? 16 : g.m <= 32 ? 32 : g.m <= 64 ? 64 : 128;
+    const int mx = g.m <= 16 && !quad ? 16 : g.m <= 32 ? 32 : g.m <= 64 ? 64 : g.m <= 128 ? 128 : 256;
     CUtensorMap tw = make_tile_map(g.b, bf16, g.k, g.n, 1, g.ldb, 0, 128);
     CUtensorMap tx = make_tile_map(g.a, bf16, g.k, g.m, 1, g.lda, 0, mx);
-#define B200AIT_SWAP(MX, R)                                                \
+#define B200AIT_SWAP(MX, R, H)                                             \
   do {                                                                     \
     if (bf16)                                                              \
-      launch_swapab<true, MX, R>(tw, tx, p, num_slabs, g.stream);          \
+      launch_swapab<true, MX, R, H>(tw, tx, p, num_slabs, g.stream);       \
     else                                                                   \
-      launch_swapab<false, MX, R>(tw, tx, p, num_slabs, g.stream);         \
+      launch_swapab<false, MX, R, H>(tw, tx, p, num_slabs, g.stream);      \
   } while (0)
     if (quad) {
-      if (mx == 32) B200AIT_SWAP(32, 4); else if (mx == 64) B200AIT_SWAP(64, 4); else B200AIT_SWAP(128, 4);
+      if (mx == 32) B200AIT_SWAP(32, 4, 1); else if (mx == 64) B200AIT_SWAP(64, 4, 1); else if (mx == 128) B200AIT_SWAP(128, 4, 1); else B200AIT_SWAP(256, 4, 2);
     } else {
-      if (mx == 16) B200AIT_SWAP(16, 2); else if (mx == 32) B200AIT_SWAP(32, 2); else if (mx == 64) B200AIT_SWAP(64, 2); else B200AIT_SWAP(128, 2);
+      if (mx == 16) B200AIT_SWAP(16, 2, 1); else if (mx == 32) B200AIT_SWAP(32, 2, 1); else if (mx == 64) B200AIT_SWAP(64, 2, 1); else if (mx == 128) B200AIT_SWAP(128, 2, 1); else B200AIT_SWAP(256, 2, 2);
     }
 #undef B200AIT_SWAP
     return;

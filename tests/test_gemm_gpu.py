@@ -458,7 +458,7 @@ def test_split_k_with_permuted_store():
     _close(y, oracle.gemm_rcr_bias_permute(x, w, b, (s, 3, h)))
 
 
-@pytest.mark.parametrize("m", [5, 16, 17, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("m", [5, 16, 17, 32, 33, 64, 100, 128, 129, 200, 256])
 @pytest.mark.parametrize("n,kk,epilogue,dtype", [(8192, 8192, "relu", torch.float16), (4104, 2056, "add", torch.float16),
                                                    (2048, 4096, "mul_add", torch.float16),
                                                    (3000, 2304, "fast_gelu", torch.bfloat16),
@@ -515,7 +515,7 @@ def test_swapped_operand_random_shapes():
     rng = random.Random(20240611)
     epilogues = ["", "relu", "fast_gelu", "add", "mul_add", "add_relu", "sigmoid"]
     for case in range(48):
-        m = rng.choice([5, 8, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100, 127, 128])
+        m = rng.choice([5, 8, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100, 127, 128, 129, 160, 192, 193, 255, 256])
         n = rng.choice([128, 136, 200, 256, 320, 512, 1000, 2048, 3000, 4736, 4744, 6000])
         kk = 8 * rng.randint(32 if m <= 32 else 64, 400)
         epilogue = rng.choice(epilogues)
@@ -532,7 +532,7 @@ def test_swapped_operand_random_shapes():
             raise AssertionError(f"m={m} n={n} k={kk} epilogue={epilogue!r}: {e}") from None
 
 
-@pytest.mark.parametrize("m,n,kk", [(128, 8192, 2048), (96, 3072, 2048), (40, 1024, 4096)])
+@pytest.mark.parametrize("m,n,kk", [(128, 8192, 2048), (96, 3072, 2048), (40, 1024, 4096), (256, 8192, 2048), (200, 2048, 2048)])
 def test_swapped_operand_rows_do_not_depend_on_their_position(m, n, kk):
     """Which rank of the cluster finishes a row of X depends on the row's index; the K shares are added in rank
     order all the same, so X with its rows reversed gives Y with its rows reversed, bit for bit (clusters of two
@@ -547,7 +547,7 @@ def test_swapped_operand_rows_do_not_depend_on_their_position(m, n, kk):
     assert torch.equal(y_rev.flip(0), y)
 
 
-@pytest.mark.parametrize("m,seq", [(32, 16), (96, 32)])
+@pytest.mark.parametrize("m,seq", [(32, 16), (96, 32), (192, 64)])
 def test_swapped_operand_permuted_store(m, seq):
     """The weight-streaming path writes the permuted [3, B, H, S, D] projection layout like the tile kernels do."""
     k = _kernels()
