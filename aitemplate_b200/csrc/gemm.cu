@@ -214,7 +214,7 @@ constexpr int kSwapThreads = 192;
 constexpr int kSwapMaxM = 256;
 template <int MX, int R, int H>
 struct SwapCfg {
-  static_assert(R == 2 || R == 4, "cluster size");
+  static_assert(R == 2 || R == 4 || R == 8, "cluster size");
   static constexpr int kPart = MX / R;              // rows of X each rank finishes ...
   static constexpr int kSub = kPart / H;            // ... in H passes of kSub rows (what bounds the exchange buffers)
   static_assert(H >= 1 && kSub * H == kPart && kSub >= 8, "a rank finishes at least 8 rows per pass");
@@ -399,7 +399,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     const int et = static_cast<int>(threadIdx.x) - 64;  // 0..127 over the four epilogue warps
     int acc = 0;
     uint32_t acc_phase = 0;
-    int seq = 0;  // passes done so far: the exchange barriers change phase once per pass
+    int seq = 0;  // passes done so far: `partial_taken` and `tile_summed` change phase once per pass
+    uint32_t ready_phase = 0;  // `partial_ready` only changes phase in the passes in which this rank has rows
     bool ok = true;
     for (int slab = walker; ok && slab < my_slabs; slab += num_walkers) {
       const bool last_slab = slab + num_walkers >= my_slabs;
@@ -451,7 +452,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         epi_arrived = true;
       }
       if (ok && my_rows > 0) {
-        ok = mbar_wait_cluster(partial_ready, seq & 1, abort_flag, p.status, kDevWaitOtherTimeout);
+        ok = mbar_wait_cluster(partial_ready, ready_phase, abort_flag, p.status, kDevWaitOtherTimeout);
+        ready_phase ^= 1u;
 #pragma unroll
         for (int c = 0; c < kSub / kChunk; ++c) {
           uint32_t v[kChunk];
@@ -911,9 +913,14 @@ void gemm_run(const GemmArgs& g_in) {
   if (tma_ok && g.batch == 1 && g.m <= kSwapMaxM && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0 &&
       g.n >= 128 && (g.m <= 128 ? (g.k >= 512 || (g.k >= 256 && g.m <= 32)) : g.k >= 2048)) {
     const int num_slabs = static_cast<int>((g.n + 127) / 128);
-    // few slabs (N <= 128 * SMs / 4): K goes four ways, so that most SMs stream
-    const bool quad = num_slabs <= sm_count() / 4;
-    const int mx = g.m <= 16 && !quad ? 16 : g.m <= 32 ? 32 : g.m <= 64 ? 64 : g.m <= 128 ? 128 : 256;
+    // few slabs: K goes four ways (N <= 128 * SMs / 4) or, with at least four k-blocks left per rank, eight ways
+    // (N <= 128 * SMs / 16: measured ahead of four ways up to 8 slabs, behind at 16), so that most SMs stream
+    const long long kb_total = (g.k + kBK - 1) / kBK;
+    const bool oct = num_slabs <= sm_count() / 16 && kb_total >= 32;
+    const bool quad = !oct && num_slabs <= sm_count() / 4;
+    // the X tile is at least 8 rows per rank wide
+    const int mx_min = oct ? 64 : quad ? 32 : 16;
+    const int mx = std::max(mx_min, g.m <= 16 ? 16 : g.m <= 32 ? 32 : g.m <= 64 ? 64 : g.m <= 128 ? 128 : 256);
     CUtensorMap tw = make_tile_map(g.b, bf16, g.k, g.n, 1, g.ldb, 0, 128);
     CUtensorMap tx = make_tile_map(g.a, bf16, g.k, g.m, 1, g.lda, 0, mx);
 #define B200AIT_SWAP(MX, R, H)                                             \
@@ -923,7 +930,9 @@ void gemm_run(const GemmArgs& g_in) {
     else                                                                   \
       launch_swapab<false, MX, R, H>(tw, tx, p, num_slabs, g.stream);      \
   } while (0)
-    if (quad) {
+    if (oct) {
+      if (mx == 64) B200AIT_SWAP(64, 8, 1); else if (mx == 128) B200AIT_SWAP(128, 8, 1); else B200AIT_SWAP(256, 8, 2);
+    } else if (quad) {
       if (mx == 32) B200AIT_SWAP(32, 4, 1); else if (mx == 64) B200AIT_SWAP(64, 4, 1); else if (mx == 128) B200AIT_SWAP(128, 4, 1); else B200AIT_SWAP(256, 4, 2);
     } else {
       if (mx == 16) B200AIT_SWAP(16, 2, 1); else if (mx == 32) B200AIT_SWAP(32, 2, 1); else if (mx == 64) B200AIT_SWAP(64, 2, 1); else if (mx == 128) B200AIT_SWAP(128, 2, 1); else B200AIT_SWAP(256, 2, 2);

@@ -506,6 +506,23 @@ def test_swapped_operand_narrow_and_shallow_weights(m, n, kk, epilogue):
     _close(y256, oracle.gemm_rcr(x, w, b, *d, epilogue=epilogue))
 
 
+@pytest.mark.parametrize("m", [129, 145, 200])
+@pytest.mark.parametrize("n,kk", [(16384, 2048), (20000, 2304), (1024, 4096)])
+def test_swapped_operand_second_pass_with_idle_ranks(m, n, kk):
+    """More than 128 rows of X go through the exchange in two passes; with M just above 128 some ranks have rows in
+    the first pass only, and with more slabs than clusters they come round again: their exchange barrier must keep
+    its own phase count."""
+    k = _kernels()
+    x = _rand((m, kk), 640, dist="uniform")
+    w = _rand((n, kk), 641, scale=0.03)
+    b = _rand((n,), 642, scale=0.1)
+    want = oracle.gemm_rcr(x, w, b, epilogue="relu")
+    for _ in range(3):
+        y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), epilogue="relu")
+        assert k.device_status() == 0
+        _close(y, want, atol=1.5e-2, rtol=1.5e-2)
+
+
 def test_swapped_operand_random_shapes():
     """Seeded random problems all over what the weight-streaming kernel takes (5 <= M <= 128, N >= 128, K >= 512, or
     K >= 256 with M <= 32): ragged slabs, k-block counts of every residue, every X-tile width, both cluster sizes."""
