@@ -54,6 +54,9 @@ int b200ait_selftest_bounded_wait(int64_t* out, void* stream);
  * b [batch, n, k] (row stride ldb), c / d0 / d1 [batch, m, n] (row strides ldc / ldd). A batch stride
  * of 0 broadcasts that operand. tile_n = 0 lets the library choose; else 64, 128 or 256 (128 x tile_n tiles,
  * one CTA each) or 512 (256 x 256 tiles, each computed by a pair of CTAs with cta_group::2 MMAs).
+ * With tile_n = 0 and split_k = 0 an unbatched problem with few rows is served by the weight-streaming kernels instead
+ * of the tiles: m <= 4 by one that multiplies on the FMA pipe, m <= 256 (against n >= 128 and a deep enough k) by one
+ * that puts the weight rows on the MMA rows and splits k across a thread-block cluster; neither needs the workspace.
  * workspace / workspace_bytes / split_k: see b200ait_gemm_rcr_workspace_bytes below.
  * Replaces python/aitemplate/backend/cuda/gemm_universal/common.py:130-617 (CUTLASS instantiation). */
 int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void* d0, const void* d1, void* c,
