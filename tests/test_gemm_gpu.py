@@ -531,9 +531,9 @@ def test_swapped_operand_random_shapes():
     k = _kernels()
     rng = random.Random(20240611)
     epilogues = ["", "relu", "fast_gelu", "add", "mul_add", "add_relu", "sigmoid"]
-    for case in range(48):
+    for case in range(64):
         m = rng.choice([5, 8, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100, 127, 128, 129, 160, 192, 193, 255, 256])
-        n = rng.choice([128, 136, 200, 256, 320, 512, 1000, 2048, 3000, 4736, 4744, 6000])
+        n = rng.choice([128, 136, 200, 256, 320, 333, 512, 1000, 1001, 2048, 3000, 4736, 4744, 6000, 9601])
         kk = 8 * rng.randint(32 if m <= 32 else 64, 400)
         epilogue = rng.choice(epilogues)
         x = _rand((m, kk), 700 + case, dist="uniform")
