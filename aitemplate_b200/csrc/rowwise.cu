@@ -132,6 +132,74 @@ __global__ void __launch_bounds__(256, (VPL >= 12) ? 2 : (VPL >= 6) ? 4 : (VPL >
   }
 }
 
+// Rows wider than a warp can hold (4096 < N <= 32768, vector-aligned): one block of 512 threads per row, the packed
+// row in registers (VPT x 16 bytes per thread), so the row is read once and written once like in the warp kernel;
+// the two reductions go through shared memory.
+template <int VPT, bool BF16>
+__global__ void __launch_bounds__(512) layernorm_wide_kernel(const LayerNormParams p) {
+  using T = typename Elem16<BF16>::T;
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const int nvec = p.n >> 3;
+  const uint4* xin = reinterpret_cast<const uint4*>(static_cast<const T*>(p.x) + row * p.x_stride);
+  uint4 raw[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = static_cast<int>(threadIdx.x) + 512 * i;
+    raw[i] = (v < nvec) ? ld_stream(xin + v) : make_uint4(0, 0, 0, 0);
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    float f[8];
+    unpack8<BF16>(raw[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += f[j];
+  }
+  const float inv_n = 1.f / static_cast<float>(p.n);
+  const float mean = block_sum(s, red) * inv_n;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    if (static_cast<int>(threadIdx.x) + 512 * i < nvec) {
+      float f[8];
+      unpack8<BF16>(raw[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = f[j] - mean;
+        q += d * d;
+      }
+    }
+  }
+  const float rstd = rsqrtf(block_sum(q, red) * inv_n + p.eps);
+  uint4* yout = reinterpret_cast<uint4*>(static_cast<T*>(p.y) + row * p.y_stride);
+  const uint4* g4 = reinterpret_cast<const uint4*>(p.gamma);
+  const uint4* b4 = reinterpret_cast<const uint4*>(p.beta);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = static_cast<int>(threadIdx.x) + 512 * i;
+    if (v < nvec) {
+      float f[8], g[8], b[8], o[8];
+      unpack8<BF16>(raw[i], f);
+      if (g4) {
+        unpack8<BF16>(__ldg(g4 + v), g);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = 1.f;
+      }
+      if (b4) {
+        unpack8<BF16>(__ldg(b4 + v), b);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) b[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (f[j] - mean) * rstd * g[j] + b[j];
+      st_stream(yout + v, pack8<BF16>(o));
+    }
+  }
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(512) layernorm_block_kernel(const LayerNormParams p) {
   using E = Elem16<BF16>;
@@ -161,9 +229,20 @@ static bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) 
 
 template <bool BF16>
 void layernorm_launch(const LayerNormParams& p, cudaStream_t stream) {
-  const bool vec = (p.n % 8 == 0) && (p.x_stride % 8 == 0) && (p.y_stride % 8 == 0) && al16(p.x) && al16(p.y) &&
-                   (!p.gamma || al16(p.gamma)) && (!p.beta || al16(p.beta)) && p.n <= 4096;
-  if (vec) {
+  const bool aligned = (p.n % 8 == 0) && (p.x_stride % 8 == 0) && (p.y_stride % 8 == 0) && al16(p.x) && al16(p.y) &&
+                       (!p.gamma || al16(p.gamma)) && (!p.beta || al16(p.beta));
+  const bool vec = aligned && p.n <= 4096;
+  if (aligned && p.n > 4096 && p.n <= 32768) {
+    B200AIT_REQUIRE(p.m < (1ll << 31), "layernorm: too many rows");
+    const unsigned grid = static_cast<unsigned>(p.m);
+    const int vpt = (p.n / 8 + 511) / 512;
+    if (vpt <= 2)
+      ::b200ait::count_launch(), layernorm_wide_kernel<2, BF16><<<grid, 512, 0, stream>>>(p);
+    else if (vpt <= 4)
+      ::b200ait::count_launch(), layernorm_wide_kernel<4, BF16><<<grid, 512, 0, stream>>>(p);
+    else
+      ::b200ait::count_launch(), layernorm_wide_kernel<8, BF16><<<grid, 512, 0, stream>>>(p);
+  } else if (vec) {
     const int nvec = p.n / 8;
     const int vpl = (nvec + 31) / 32;
     const int wpb = (vpl <= 4) ? 8 : 4;  // warps per block
@@ -259,6 +338,59 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SoftmaxParams p
 
 // one block per (outer, inner-chunk); blockDim.x threads walk the reduction dim when inner == 1,
 // otherwise each thread owns one inner index and loops over k (coalesced along inner)
+// softmax over the last dim of rows wider than a warp can hold (4096 < K <= 32768, vector-aligned): see
+// layernorm_wide_kernel
+template <int VPT, bool BF16>
+__global__ void __launch_bounds__(512) softmax_wide_kernel(const SoftmaxParams p) {
+  using T = typename Elem16<BF16>::T;
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const int nvec = p.k >> 3;
+  const uint4* xin = reinterpret_cast<const uint4*>(static_cast<const T*>(p.x) + row * p.k);
+  uint4 raw[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = static_cast<int>(threadIdx.x) + 512 * i;
+    raw[i] = (v < nvec) ? ld_stream(xin + v) : make_uint4(0, 0, 0, 0);
+  }
+  constexpr float kLog2e = 1.4426950408889634f;
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    if (static_cast<int>(threadIdx.x) + 512 * i < nvec) {
+      float f[8];
+      unpack8<BF16>(raw[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);
+    }
+  }
+  mx = block_max(mx, red);
+  const float mb = (mx == -INFINITY) ? 0.f : mx * kLog2e;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    if (static_cast<int>(threadIdx.x) + 512 * i < nvec) {
+      float f[8];
+      unpack8<BF16>(raw[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += exp2f(f[j] * kLog2e - mb);
+    }
+  }
+  const float inv = 1.f / block_sum(s, red);
+  uint4* yout = reinterpret_cast<uint4*>(static_cast<T*>(p.y) + row * p.k);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = static_cast<int>(threadIdx.x) + 512 * i;
+    if (v < nvec) {
+      float f[8], o[8];
+      unpack8<BF16>(raw[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = exp2f(f[j] * kLog2e - mb) * inv;
+      st_stream(yout + v, pack8<BF16>(o));
+    }
+  }
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(512) softmax_block_kernel(const SoftmaxParams p) {
   using E = Elem16<BF16>;
@@ -300,6 +432,16 @@ void softmax_launch(const SoftmaxParams& p, cudaStream_t stream) {
   if (p.inner > 1) {
     const long long total = p.outer * p.inner;
     ::b200ait::count_launch(), softmax_strided_kernel<BF16><<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(p);
+  } else if (p.k % 8 == 0 && p.k > 4096 && p.k <= 32768 && al16(p.x) && al16(p.y)) {
+    B200AIT_REQUIRE(p.outer < (1ll << 31), "softmax: too many rows");
+    const unsigned grid = static_cast<unsigned>(p.outer);
+    const int vpt = (p.k / 8 + 511) / 512;
+    if (vpt <= 2)
+      ::b200ait::count_launch(), softmax_wide_kernel<2, BF16><<<grid, 512, 0, stream>>>(p);
+    else if (vpt <= 4)
+      ::b200ait::count_launch(), softmax_wide_kernel<4, BF16><<<grid, 512, 0, stream>>>(p);
+    else
+      ::b200ait::count_launch(), softmax_wide_kernel<8, BF16><<<grid, 512, 0, stream>>>(p);
   } else if (p.k % 8 == 0 && p.k <= 4096 && al16(p.x) && al16(p.y)) {
     const int vpl = (p.k / 8 + 31) / 32;
     const int wpb = (vpl <= 4) ? 8 : 4;
