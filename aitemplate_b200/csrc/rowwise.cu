@@ -427,9 +427,52 @@ __global__ void __launch_bounds__(256) softmax_strided_kernel(const SoftmaxParam
   for (int i = 0; i < p.k; ++i) y[i * p.inner] = E::from_float(__expf(E::to_float(x[i * p.inner]) - mx) * inv);
 }
 
+// softmax over a non-innermost dim with a long reduction: a block (256 threads, 1024 when there are few blocks) takes
+// one outer index and `ti` consecutive inner indices (coalesced), and splits the reduction dim over its thread rows, which meet in
+// shared memory for the maximum and for the sum. (One thread per (outer, inner) pair, as in softmax_strided_kernel,
+// leaves a [16, 16384, 8] problem with 128 threads.)
+template <bool BF16>
+__global__ void __launch_bounds__(1024) softmax_inner_kernel(const SoftmaxParams p, const int ti) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  __shared__ float red[1024];
+  const int tks = static_cast<int>(blockDim.x) / ti;
+  const int tx = static_cast<int>(threadIdx.x) % ti, ty = static_cast<int>(threadIdx.x) / ti;
+  const long long tiles = (p.inner + ti - 1) / ti;
+  const long long o = blockIdx.x / tiles;
+  const long long in = (blockIdx.x - o * tiles) * ti + tx;
+  const bool valid = in < p.inner;
+  const T* x = static_cast<const T*>(p.x) + o * p.k * p.inner + (valid ? in : 0);
+  T* y = static_cast<T*>(p.y) + o * p.k * p.inner + (valid ? in : 0);
+  constexpr float kLog2e = 1.4426950408889634f;
+  float mx = -INFINITY;
+  for (long long i = ty; i < p.k; i += tks) mx = fmaxf(mx, E::to_float(x[i * p.inner]));
+  red[threadIdx.x] = mx;
+  __syncthreads();
+  for (int j = 0; j < tks; ++j) mx = fmaxf(mx, red[j * ti + tx]);
+  __syncthreads();
+  const float mb = (mx == -INFINITY) ? 0.f : mx * kLog2e;
+  float sum = 0.f;
+  for (long long i = ty; i < p.k; i += tks) sum += exp2f(E::to_float(x[i * p.inner]) * kLog2e - mb);
+  red[threadIdx.x] = sum;
+  __syncthreads();
+  sum = 0.f;
+  for (int j = 0; j < tks; ++j) sum += red[j * ti + tx];
+  const float inv = 1.f / sum;
+  if (!valid) return;
+  for (long long i = ty; i < p.k; i += tks) y[i * p.inner] = E::from_float(exp2f(E::to_float(x[i * p.inner]) * kLog2e - mb) * inv);
+}
+
 template <bool BF16>
 void softmax_launch(const SoftmaxParams& p, cudaStream_t stream) {
-  if (p.inner > 1) {
+  if (p.inner > 1 && p.k >= 128) {
+    int ti = 32;
+    while (ti > 1 && ti / 2 >= p.inner) ti /= 2;  // the smallest power of two covering a narrow inner extent
+    const long long blocks = p.outer * ((p.inner + ti - 1) / ti);
+    B200AIT_REQUIRE(blocks < (1ll << 31), "softmax: too many blocks");
+    const int threads = blocks < 2 * sm_count() ? 1024 : 256;
+    ::b200ait::count_launch(), softmax_inner_kernel<BF16><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p, ti);
+  } else if (p.inner > 1) {
     const long long total = p.outer * p.inner;
     ::b200ait::count_launch(), softmax_strided_kernel<BF16><<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(p);
   } else if (p.k % 8 == 0 && p.k > 4096 && p.k <= 32768 && al16(p.x) && al16(p.y)) {
