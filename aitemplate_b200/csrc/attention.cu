@@ -206,7 +206,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
   auto decode_item = [&](int item) {
     Item w;
     const int bh = fast_div(item, p.q_blocks, p.q_blocks_mul, p.q_blocks_shr);
-    const int q_blk = item - bh * p.q_blocks;
+    int q_blk = item - bh * p.q_blocks;
+    // causal: a tile's work grows with its position, so the items are handed out longest first (every CTA's last item
+    // is then a short one, which evens out the end of the kernel)
+    if (!NOMASK && p.causal) q_blk = p.q_blocks - 1 - q_blk;
     const int b = fast_div(bh, p.H, p.h_mul, p.h_shr);
     w.h = bh - b * p.H;
     w.q0 = q_blk * kBlockM;
