@@ -132,6 +132,47 @@ __global__ void __launch_bounds__(256, (VPL >= 12) ? 2 : (VPL >= 6) ? 4 : (VPL >
   }
 }
 
+// Short rows that the vector kernel cannot take (N or a stride not a multiple of 8, an unaligned pointer; N <= 1024):
+// still one warp per row and one read of the row, element by element (a warp's load covers 64 consecutive bytes),
+// instead of a block per row with shared-memory reductions.
+template <int EPL, bool BF16>
+__global__ void __launch_bounds__(256) layernorm_warp_scalar_kernel(const LayerNormParams p) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= p.m) return;
+  const T* x = static_cast<const T*>(p.x) + row * p.x_stride;
+  float f[EPL];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int c = lane + 32 * i;
+    f[i] = (c < p.n) ? E::to_float(x[c]) : 0.f;
+    s += f[i];
+  }
+  const float inv_n = 1.f / static_cast<float>(p.n);
+  const float mean = warp_sum(s) * inv_n;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const float d = (lane + 32 * i < p.n) ? f[i] - mean : 0.f;
+    q += d * d;
+  }
+  const float rstd = rsqrtf(warp_sum(q) * inv_n + p.eps);
+  T* y = static_cast<T*>(p.y) + row * p.y_stride;
+  const T* g = static_cast<const T*>(p.gamma);
+  const T* b = static_cast<const T*>(p.beta);
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int c = lane + 32 * i;
+    if (c < p.n) {
+      const float gv = g ? E::to_float(g[c]) : 1.f, bv = b ? E::to_float(b[c]) : 0.f;
+      y[c] = E::from_float((f[i] - mean) * rstd * gv + bv);
+    }
+  }
+}
+
 // Rows wider than a warp can hold (4096 < N <= 32768, vector-aligned): one block of 512 threads per row, the packed
 // row in registers (VPT x 16 bytes per thread), so the row is read once and written once like in the warp kernel;
 // the two reductions go through shared memory.
@@ -266,6 +307,13 @@ void layernorm_launch(const LayerNormParams& p, cudaStream_t stream) {
     else
       B200AIT_LN(16);
 #undef B200AIT_LN
+  } else if (p.n <= 1024) {
+    const unsigned grid = static_cast<unsigned>((p.m + 7) / 8);
+    const int epl = (p.n + 31) / 32;
+#define B200AIT_LNS(V) ::b200ait::count_launch(), layernorm_warp_scalar_kernel<V, BF16><<<grid, 256, 0, stream>>>(p)
+    if (epl <= 1) B200AIT_LNS(1); else if (epl <= 2) B200AIT_LNS(2); else if (epl <= 4) B200AIT_LNS(4);
+    else if (epl <= 8) B200AIT_LNS(8); else if (epl <= 16) B200AIT_LNS(16); else B200AIT_LNS(32);
+#undef B200AIT_LNS
   } else {
     B200AIT_REQUIRE(p.m < (1ll << 31), "layernorm: too many rows");
     const int threads = p.n >= 2048 ? 512 : (p.n >= 512 ? 256 : 128);
@@ -338,6 +386,42 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SoftmaxParams p
 
 // one block per (outer, inner-chunk); blockDim.x threads walk the reduction dim when inner == 1,
 // otherwise each thread owns one inner index and loops over k (coalesced along inner)
+// short rows the vector kernel cannot take (K not a multiple of 8, e.g. the 77 keys of a text encoder; K <= 1024):
+// see layernorm_warp_scalar_kernel
+template <int EPL, bool BF16>
+__global__ void __launch_bounds__(256) softmax_warp_scalar_kernel(const SoftmaxParams p) {
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= p.outer) return;
+  const T* x = static_cast<const T*>(p.x) + row * p.k;
+  constexpr float kLog2e = 1.4426950408889634f;
+  float f[EPL];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int c = lane + 32 * i;
+    f[i] = (c < p.k) ? E::to_float(x[c]) : -INFINITY;
+    mx = fmaxf(mx, f[i]);
+  }
+  mx = warp_max(mx);
+  const float mb = (mx == -INFINITY) ? 0.f : mx * kLog2e;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    f[i] = (lane + 32 * i < p.k) ? exp2f(f[i] * kLog2e - mb) : 0.f;
+    s += f[i];
+  }
+  const float inv = 1.f / warp_sum(s);
+  T* y = static_cast<T*>(p.y) + row * p.k;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int c = lane + 32 * i;
+    if (c < p.k) y[c] = E::from_float(f[i] * inv);
+  }
+}
+
 // softmax over the last dim of rows wider than a warp can hold (4096 < K <= 32768, vector-aligned): see
 // layernorm_wide_kernel
 template <int VPT, bool BF16>
@@ -502,6 +586,13 @@ void softmax_launch(const SoftmaxParams& p, cudaStream_t stream) {
     else
       B200AIT_SM(16);
 #undef B200AIT_SM
+  } else if (p.k <= 1024) {
+    const unsigned grid = static_cast<unsigned>((p.outer + 7) / 8);
+    const int epl = (p.k + 31) / 32;
+#define B200AIT_SMS(V) ::b200ait::count_launch(), softmax_warp_scalar_kernel<V, BF16><<<grid, 256, 0, stream>>>(p)
+    if (epl <= 1) B200AIT_SMS(1); else if (epl <= 2) B200AIT_SMS(2); else if (epl <= 4) B200AIT_SMS(4);
+    else if (epl <= 8) B200AIT_SMS(8); else if (epl <= 16) B200AIT_SMS(16); else B200AIT_SMS(32);
+#undef B200AIT_SMS
   } else {
     B200AIT_REQUIRE(p.outer < (1ll << 31), "softmax: too many rows");
     const int threads = p.k >= 2048 ? 512 : (p.k >= 256 ? 256 : (p.k >= 64 ? 64 : 32));
