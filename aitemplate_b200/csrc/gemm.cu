@@ -202,13 +202,14 @@ __global__ void __launch_bounds__(kRowDotThreads, 1) gemm_rowdot_kernel(const vo
 }
 
 // ------------------------------------------------------------------------------------------------
-// Weight-streaming tensor-core kernel for 5 <= M <= 32 with the operands swapped: Y^T = W X^T.
-// The run time of such a GEMM is the time to read W once. Here the rows of W sit on the 128 MMA rows and the few
-// rows of X are the MMA's N (16 or 32), so a CTA consumes 16 KB of weights per four short MMAs, and W is
-// partitioned so that every byte is read by exactly one CTA: a cluster of two CTAs owns a slab of 128 weight rows,
-// rank r streams half r of K through an 8-stage TMA ring, and rank 1 hands its 128 x MX fp32 partial sums to
-// rank 0 through the cluster's shared-memory window. No global workspace, no second pass (the 128 x 256 tiles +
-// split-K + reduce kernel this replaces ran at 0.54 of the copy rate for these shapes).
+// Weight-streaming tensor-core kernel with the operands swapped: Y^T = W X^T.
+// The run time of a GEMM with few rows of X is the time to read W once. Here the rows of W sit on the 128 MMA rows
+// and the rows of X are the MMA's N (MX = 16 .. 256), so a CTA consumes 16 KB of weights per four MMAs, and W is
+// partitioned so that every byte is read by exactly one CTA per group of MX rows of X: a cluster of R = 2, 4 or 8 CTAs
+// owns a slab of 128 weight rows, rank r streams share r of K through a TMA ring, and the ranks hand each other
+// their 128 x MX fp32 partial sums through the cluster's shared-memory window (a reduce-scatter: every rank finishes
+// MX / R rows of X). No global workspace, no second pass (the 128 x 256 tiles + split-K + reduce kernel this
+// replaces ran at 0.54 of the copy rate for M <= 32). More than 256 rows of X are taken in groups of 256.
 //   warp 0: TMA producer   warp 1: MMA issuer   warps 2-5: epilogue (TMEM lane = weight row = output column)
 constexpr int kSwapThreads = 192;
 constexpr int kSwapMaxM = 256;
@@ -247,7 +248,7 @@ __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[N]) 
 template <bool BF16, int MX, int R, int H>
 __global__ void __launch_bounds__(kSwapThreads, 1)
 gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
-                   const GemmParams p, const int num_slabs) {
+                   const GemmParams p, const int num_slabs, const int num_groups) {
   using Cfg = SwapCfg<MX, R, H>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const bool misaligned = (smem_u32(smem) & 1023u) != 0u;
@@ -260,17 +261,19 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   uint64_t* acc_full = empty_bar + Cfg::kStages;   // [2]
   uint64_t* acc_empty = acc_full + 2;             // [2]
   uint64_t* partial_ready = acc_empty + 2;        // every peer's partial sums are in `partial` (counts their bytes)
-  uint64_t* partial_taken = partial_ready + 1;    // every peer has read the sums it was sent
-  uint64_t* drain_bar = partial_taken + 1;
+  uint64_t* partial_taken = partial_ready + 1;    // [2] every peer has read the sums it was sent (even / odd passes)
+  uint64_t* drain_bar = partial_taken + 2;
   uint64_t* tile_summed = drain_bar + 1;          // every thread has put its sums into `tile`
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_summed + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  static_assert((2 * Cfg::kStages + 8) * 8 + 8 <= 256, "barrier area too small");
+  static_assert((2 * Cfg::kStages + 9) * 8 + 8 <= 256, "barrier area too small");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(cluster_ctarank());
   const int walker = blockIdx.x / R, num_walkers = gridDim.x / R;
-  const int my_slabs = misaligned ? 0 : num_slabs;
+  // a unit of work: one slab of 128 weight rows against one group of MX rows of X (consecutive units share the slab,
+  // so the clusters that run them side by side fetch its weights from HBM once)
+  const int my_units = misaligned ? 0 : num_slabs * num_groups;
   // this rank's share of the k-blocks (the host sends no problem with fewer k-blocks than ranks)
   const int kb_total = (p.K + kBK - 1) / kBK;
   // split evenly, so that no rank is left without a k-block (its accumulator would never be written)
@@ -286,7 +289,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       mbar_init(&acc_empty[i], 128);
     }
     mbar_init(partial_ready, 1);
-    mbar_init(partial_taken, 128 * (R - 1));
+    mbar_init(&partial_taken[0], 128 * (R - 1));
+    mbar_init(&partial_taken[1], 128 * (R - 1));
     mbar_init(drain_bar, 1);
     mbar_init(tile_summed, 128);
     *abort_flag = 0;
@@ -299,15 +303,16 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   const int nkb = kb1 - kb0;
   int prod_stage = 0;
   uint32_t prod_phase = 0;
-  auto produce = [&](int slab, int i0, int i1) -> bool {
-    const int rot = nkb > 0 ? static_cast<int>((static_cast<unsigned>(slab) * 11u) % static_cast<unsigned>(nkb)) : 0;
+  auto produce = [&](int unit, int i0, int i1) -> bool {
+    const int slab = unit / num_groups, grp = unit - slab * num_groups;
+    const int rot = nkb > 0 ? static_cast<int>((static_cast<unsigned>(unit) * 11u) % static_cast<unsigned>(nkb)) : 0;
     for (int i = i0; i < i1; ++i) {
       const int kb = kb0 + (i + rot >= nkb ? i + rot - nkb : i + rot);
       if (!mbar_wait(&empty_bar[prod_stage], prod_phase ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout)) return false;
       uint8_t* sw = smem + prod_stage * Cfg::kStageBytes;
       mbar_arrive_expect_tx(&full_bar[prod_stage], Cfg::kStageBytes);
       tma_load_3d(sw, &tma_w, &full_bar[prod_stage], kb * kBK, slab * 128, 0);
-      tma_load_3d(sw + Cfg::kWBytes, &tma_x, &full_bar[prod_stage], kb * kBK, 0, 0);
+      tma_load_3d(sw + Cfg::kWBytes, &tma_x, &full_bar[prod_stage], kb * kBK, grp * MX, 0);
       if (++prod_stage == Cfg::kStages) {
         prod_stage = 0;
         prod_phase ^= 1u;
@@ -333,8 +338,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   if (warp == 0) {
     if (lane == 0) {
       bool ok = true;
-      for (int slab = walker; ok && slab < my_slabs; slab += num_walkers)
-        ok = produce(slab, 0, nkb);
+      for (int unit = walker; ok && unit < my_units; unit += num_walkers)
+        ok = produce(unit, 0, nkb);
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) {
@@ -349,7 +354,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int slab = walker; ok && slab < my_slabs; slab += num_walkers) {
+      for (int unit = walker; ok && unit < my_units; unit += num_walkers) {
         ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, kDevWaitAccEmptyTimeout);
         if (!ok) break;
         tc_fence_after();
@@ -399,11 +404,19 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     const int et = static_cast<int>(threadIdx.x) - 64;  // 0..127 over the four epilogue warps
     int acc = 0;
     uint32_t acc_phase = 0;
-    int seq = 0;  // passes done so far: `partial_taken` and `tile_summed` change phase once per pass
+    // Passes done so far: `tile_summed` changes phase once per pass. The peers' "taken" signals of pass s go to
+    // partial_taken[s & 1]: a rank that has no rows in a pass runs through it without waiting for anybody's sums, so
+    // its signals of pass s + 1 can be complete before a slow thread here has looked at those of pass s. With one
+    // barrier that thread would then wait on a parity that has come round again; with two, a barrier is reused only
+    // for pass s + 2, which no peer can finish before every thread here has signalled pass s + 1.
+    int seq = 0;
     uint32_t ready_phase = 0;  // `partial_ready` only changes phase in the passes in which this rank has rows
     bool ok = true;
-    for (int slab = walker; ok && slab < my_slabs; slab += num_walkers) {
-      const bool last_slab = slab + num_walkers >= my_slabs;
+    for (int unit = walker; ok && unit < my_units; unit += num_walkers) {
+      const bool last_slab = unit + num_walkers >= my_units;
+      const int slab = unit / num_groups;
+      const int row_base = (unit - slab * num_groups) * MX;  // first row of X of this unit's group
+      const int m_here = p.M - row_base < MX ? p.M - row_base : MX;
       // The tile goes out row by row: a thread takes 8 consecutive columns (one 16-byte store), 16 threads one
       // row of the slab. A thread keeps the same columns for every row, so it fetches their bias once, early.
       const int col0 = slab * 128 + (et & 15) * 8;
@@ -420,15 +433,18 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       for (int pass = 0; ok && pass < H; ++pass, ++seq) {
       const bool last = last_slab && pass == H - 1;
       const int my_row0 = (pass * R + rank) * kSub;
-      const int my_rows = p.M - my_row0 < 0 ? 0 : (p.M - my_row0 < kSub ? p.M - my_row0 : kSub);
+      const int my_rows = m_here - my_row0 < 0 ? 0 : (m_here - my_row0 < kSub ? m_here - my_row0 : kSub);
+      const int out_row0 = row_base + my_row0;  // where this rank's block starts in the output
       // what the peers will send for this pass (a rank with no valid row of X is sent nothing and waits for nothing)
       if (et == 0 && my_rows > 0) mbar_arrive_expect_tx(partial_ready, (R - 1) * Cfg::kSlotBytes);
       // the peers must have read what this CTA sent for the previous pass before it is overwritten
-      if (seq > 0) ok = mbar_wait_cluster(partial_taken, (seq - 1) & 1, abort_flag, p.status, kDevWaitOtherTimeout);
+      if (seq > 0)
+        ok = mbar_wait_cluster(&partial_taken[(seq - 1) & 1], ((seq - 1) >> 1) & 1, abort_flag, p.status,
+                               kDevWaitOtherTimeout);
 #pragma unroll
       for (int q = 0; q < R; ++q) {
         const int q_row0 = (pass * R + q) * kSub;
-        if (q == rank || p.M <= q_row0) continue;
+        if (q == rank || m_here <= q_row0) continue;
         const int slot = rank < q ? rank : rank - 1;  // where this rank's sums go in rank q's buffer
         const uint32_t dst = mapa_shared(smem_u32(partial), static_cast<uint32_t>(q)) +
                              static_cast<uint32_t>((slot * kSub * 128 + row) * 4);
@@ -516,7 +532,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                   const float y = o[t][e] * p.alpha + bias_v[e];
                   o[t][e] = relu ? fmaxf(y, 0.f) : y;  // identity keeps a NaN a NaN
                 }
-                *reinterpret_cast<uint4*>(out0 + static_cast<long long>(my_row0 + j + 8 * t) * p.ldc) = pack8<BF16>(o[t]);
+                *reinterpret_cast<uint4*>(out0 + static_cast<long long>(out_row0 + j + 8 * t) * p.ldc) = pack8<BF16>(o[t]);
               }
             }
           }
@@ -537,7 +553,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
               const float4 a0 = *reinterpret_cast<const float4*>(src), a1 = *reinterpret_cast<const float4*>(src + 4);
               o[t * 8 + 0] = a0.x, o[t * 8 + 1] = a0.y, o[t * 8 + 2] = a0.z, o[t * 8 + 3] = a0.w;
               o[t * 8 + 4] = a1.x, o[t * 8 + 5] = a1.y, o[t * 8 + 6] = a1.z, o[t * 8 + 7] = a1.w;
-              const long long d_at = static_cast<long long>(my_row0 + jj) * p.ldd + col0;
+              const long long d_at = static_cast<long long>(out_row0 + jj) * p.ldd + col0;
               if (b1 != kBinaryNone) r0[t] = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.d0) + d_at));
               if (b2 != kBinaryNone) r1[t] = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.d1) + d_at));
             }
@@ -566,7 +582,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
 #pragma unroll
             for (int t = 0; t < 4; ++t)
               if (j + 8 * t < my_rows)
-                *reinterpret_cast<uint4*>(out0 + row_offset(p, my_row0 + j + 8 * t)) = pack8<BF16>(&o[t * 8]);
+                *reinterpret_cast<uint4*>(out0 + row_offset(p, out_row0 + j + 8 * t)) = pack8<BF16>(&o[t * 8]);
           }
         }
         if (!vec) {
@@ -575,7 +591,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             const float* src = tile + j * 128 + (et & 15) * 8;
 #pragma unroll 1
             for (int e = 0; e < 8; ++e)
-              if (col0 + e < p.N) epilogue_scalar_store<BF16>(p, src[e], 0, my_row0 + j, col0 + e);
+              if (col0 + e < p.N) epilogue_scalar_store<BF16>(p, src[e], 0, out_row0 + j, col0 + e);
           }
         }
         // This thread is done reading `partial`: the peers may send the next pass's sums. (Its reads have returned -
@@ -584,7 +600,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         if (!last) {
 #pragma unroll
           for (int q = 0; q < R; ++q)
-            if (q != rank) mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(partial_taken), static_cast<uint32_t>(q)));
+            if (q != rank)
+              mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(&partial_taken[seq & 1]), static_cast<uint32_t>(q)));
         }
       }
       }  // passes
@@ -608,7 +625,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
 
 template <bool BF16, int MX, int R, int H>
 static void launch_swapab(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int num_slabs,
-                          cudaStream_t stream) {
+                          int num_groups, cudaStream_t stream) {
   using Cfg = SwapCfg<MX, R, H>;
   static std::atomic<uint64_t> configured{0};
   auto* kernel = &gemm_swapab_kernel<BF16, MX, R, H>;
@@ -634,9 +651,9 @@ static void launch_swapab(const CUtensorMap& tw, const CUtensorMap& tx, const Ge
     B200AIT_REQUIRE(walkers > 0, "gemm: the weight-streaming kernel's cluster does not fit this GPU");
     resident.store(walkers, std::memory_order_relaxed);
   }
-  cfg.gridDim = dim3(static_cast<unsigned>(R * std::min(num_slabs, walkers)));
+  cfg.gridDim = dim3(static_cast<unsigned>(R * std::min(num_slabs * num_groups, walkers)));
   ::b200ait::count_launch();
-  B200AIT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, tw, tx, p, num_slabs));
+  B200AIT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, tw, tx, p, num_slabs, num_groups));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -910,14 +927,23 @@ void gemm_run(const GemmArgs& g_in) {
   // 128 < M <= 256, where X is 256 rows per k-block, from K = 2048 on: 4096 x 4096 at M = 256 19.9 against 24.9 us, but
   // 3072 x 768 11.6 against 8.8): stream W once with the
   // operands swapped (W rows on the MMA rows), K split across a cluster of two or four, no workspace
-  if (tma_ok && g.batch == 1 && g.m <= kSwapMaxM && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0 &&
-      g.n >= 128 && (g.m <= 128 ? (g.k >= 512 || (g.k >= 256 && g.m <= 32)) : g.k >= 2048)) {
-    const int num_slabs = static_cast<int>((g.n + 127) / 128);
-    // few slabs: K goes four ways (N <= 128 * SMs / 4) or, with at least four k-blocks left per rank, eight ways
-    // (N <= 128 * SMs / 16: measured ahead of four ways up to 8 slabs, behind at 16), so that most SMs stream
+  // M > 256 with few output tiles and a deep K (768 x 3072 at M = 512: 12 tiles of 128 x 256, which the tile kernels
+  // cut into 6 K shares with a second kernel to add them up): the same kernel, X taken in groups of 256 rows, so that a
+  // unit of work is a slab of W against a group of X. Measured ahead of the tile kernels while there are at most 32
+  // units (1024 x 768 x 3072 16.3 against 19.5 us, 768 x 1280 x 5120 21 against 29), behind from 36 on.
+  const long long swap_groups = (g.m + kSwapMaxM - 1) / kSwapMaxM, swap_slabs = (g.n + 127) / 128;
+  if (tma_ok && g.batch == 1 && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0 && g.n >= 128 &&
+      (g.m <= 128   ? (g.k >= 512 || (g.k >= 256 && g.m <= 32))
+       : g.m <= 256 ? g.k >= 2048
+                    : (g.k >= 2048 && swap_groups * swap_slabs <= 32))) {
+    const int num_groups = static_cast<int>(swap_groups);
+    const int num_slabs = static_cast<int>(swap_slabs);
+    const int num_units = num_slabs * num_groups;
+    // few units: K goes four ways (at most SMs / 4 units) or, with at least four k-blocks left per rank, eight ways
+    // (at most SMs / 16 units: measured ahead of four ways up to 8 slabs, behind at 16), so that most SMs stream
     const long long kb_total = (g.k + kBK - 1) / kBK;
-    const bool oct = num_slabs <= sm_count() / 16 && kb_total >= 32;
-    const bool quad = !oct && num_slabs <= sm_count() / 4;
+    const bool oct = num_units <= sm_count() / 16 && kb_total >= 32;
+    const bool quad = !oct && num_units <= sm_count() / 4;
     // the X tile is at least 8 rows per rank wide
     const int mx_min = oct ? 64 : quad ? 32 : 16;
     const int mx = std::max(mx_min, g.m <= 16 ? 16 : g.m <= 32 ? 32 : g.m <= 64 ? 64 : g.m <= 128 ? 128 : 256);
@@ -926,9 +952,9 @@ void gemm_run(const GemmArgs& g_in) {
 #define B200AIT_SWAP(MX, R, H)                                             \
   do {                                                                     \
     if (bf16)                                                              \
-      launch_swapab<true, MX, R, H>(tw, tx, p, num_slabs, g.stream);       \
+      launch_swapab<true, MX, R, H>(tw, tx, p, num_slabs, num_groups, g.stream); \
     else                                                                   \
-      launch_swapab<false, MX, R, H>(tw, tx, p, num_slabs, g.stream);      \
+      launch_swapab<false, MX, R, H>(tw, tx, p, num_slabs, num_groups, g.stream); \
   } while (0)
     if (oct) {
       if (mx == 64) B200AIT_SWAP(64, 8, 1); else if (mx == 128) B200AIT_SWAP(128, 8, 1); else B200AIT_SWAP(256, 8, 2);

@@ -517,10 +517,45 @@ def test_swapped_operand_second_pass_with_idle_ranks(m, n, kk):
     w = _rand((n, kk), 641, scale=0.03)
     b = _rand((n,), 642, scale=0.1)
     want = oracle.gemm_rcr(x, w, b, epilogue="relu")
-    for _ in range(3):
+    for _ in range(10):
         y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), epilogue="relu")
         assert k.device_status() == 0
         _close(y, want, atol=1.5e-2, rtol=1.5e-2)
+
+
+@pytest.mark.parametrize("m,n,kk", [(257, 768, 3072), (300, 1024, 2048), (512, 768, 3072), (700, 520, 2056),
+                                    (1000, 1000, 2304), (1024, 1024, 4096), (2048, 256, 2048), (4000, 250, 2048),
+                                    (8192, 128, 2048)])
+@pytest.mark.parametrize("epilogue", ["relu", "add", "mul_add"])
+def test_swapped_operand_row_groups(m, n, kk, epilogue):
+    """More than 256 rows of X against few, deep weight slabs: the weight-streaming kernel takes X in groups of 256
+    rows (a ragged last group, a last group with a single row, ragged slabs, up to 32 groups)."""
+    k = _kernels()
+    x = _rand((m, kk), 650, dist="uniform")
+    w = _rand((n, kk), 651, scale=0.03)
+    b = _rand((n,), 652, scale=0.1)
+    nres = {"add": 1, "mul_add": 2}.get(epilogue, 0)
+    d = [_rand((m, n), 653 + i) for i in range(nres)]
+    from aitemplate_b200 import _lib
+
+    xd, wd, bd, dd = x.cuda(), w.cuda(), b.cuda(), [t.cuda() for t in d]
+    launches = _lib.kernel_launch_count()
+    y = k.gemm_rcr(xd, wd, bd, *dd, epilogue=epilogue)
+    assert k.device_status() == 0
+    assert _lib.kernel_launch_count() - launches == 1  # one kernel: no split-K reduction pass
+    _close(y, oracle.gemm_rcr(x, w, b, *d, epilogue=epilogue), atol=1.5e-2, rtol=1.5e-2)
+
+
+def test_swapped_operand_row_groups_permuted_store():
+    """The grouped rows land where a fused output permutation sends them (row index = group base + row in group)."""
+    k = _kernels()
+    m, seq, h, hid = 768, 384, 4, 256  # [B * S, 3 * H * D] -> [3, B, H, S, D]
+    x = _rand((m, 2048), 660, scale=0.5)
+    w = _rand((3 * hid, 2048), 661, scale=0.05)
+    b = _rand((3 * hid,), 662, scale=0.1)
+    y = k.gemm_rcr(x.cuda(), w.cuda(), b.cuda(), permute_shape=(seq, 3, h))
+    assert k.device_status() == 0
+    _close(y, oracle.gemm_rcr_bias_permute(x, w, b, (seq, 3, h)))
 
 
 def test_swapped_operand_random_shapes():
