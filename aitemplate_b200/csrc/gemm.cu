@@ -18,8 +18,10 @@
 // pointers) run on a plain tiled CUDA-core kernel in this file; there is no host fallback.
 #include <cuda.h>
 
+#include <algorithm>
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "gemm_kernel.cuh"
 
@@ -215,7 +217,7 @@ constexpr int kSwapThreads = 192;
 constexpr int kSwapMaxM = 256;
 template <int MX, int R, int H>
 struct SwapCfg {
-  static_assert(R == 2 || R == 4 || R == 8, "cluster size");
+  static_assert(R == 1 || R == 2 || R == 4 || R == 8, "cluster size");
   static constexpr int kPart = MX / R;              // rows of X each rank finishes ...
   static constexpr int kSub = kPart / H;            // ... in H passes of kSub rows (what bounds the exchange buffers)
   static_assert(H >= 1 && kSub * H == kPart && kSub >= 8, "a rank finishes at least 8 rows per pass");
@@ -253,7 +255,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   extern __shared__ __align__(1024) uint8_t smem[];
   const bool misaligned = (smem_u32(smem) & 1023u) != 0u;
   if (misaligned && threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevBadSmemAlignment);
-  float* partial = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);  // [R - 1][kSub][128], a slot per peer
+  float* partial = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);  // [R - 1][kSub / 4][128][4], a slot per peer
   float* tile = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes);  // [kSub][128]
   uint64_t* full_bar =
       reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes + Cfg::kTileBytes);
@@ -279,24 +281,30 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   // split evenly, so that no rank is left without a k-block (its accumulator would never be written)
   const int kb0 = rank * kb_total / R, kb1 = (rank + 1) * kb_total / R;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+  // Set-up, kept short because a small problem's whole run is a few microseconds: the lanes of warp 0 initialise one
+  // barrier each while warp 1 allocates tensor memory, and the opening cluster barrier is arrived at without a release
+  // (the initialisations are published by fence.mbarrier_init; a releasing arrive alone was measured at 0.5 us):
+  // 0.68 us from the CTA's start to its first instruction after the set-up, 1.26 us with everything done in turn.
+  // (Letting the producer thread start streaming before the set-up barriers changed nothing: the first bytes land
+  // 1.7 us after the CTA's start either way, a tensor-map fetch plus a trip to HBM after the first TMA instruction.)
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_w);
+      tma_prefetch_desc(&tma_x);
+      *abort_flag = 0;
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 128);
+    // barriers in the order they lie in shared memory: full[kStages], empty[kStages], acc_full[2], acc_empty[2],
+    // partial_ready, partial_taken[2], drain_bar, tile_summed
+    constexpr int kBars = 2 * Cfg::kStages + 9;
+    for (int i = lane; i < kBars; i += 32) {
+      const int j = i - 2 * Cfg::kStages;  // index among the barriers after the ring's
+      const uint32_t count = j < 0 ? 1u : j < 2 ? 1u : j < 4 ? 128u : j == 4 ? 1u : j < 7 ? 128u * (R > 1 ? R - 1 : 1) : j == 7 ? 1u : 128u;
+      mbar_init(&full_bar[i], count);
     }
-    mbar_init(partial_ready, 1);
-    mbar_init(&partial_taken[0], 128 * (R - 1));
-    mbar_init(&partial_taken[1], 128 * (R - 1));
-    mbar_init(drain_bar, 1);
-    mbar_init(tile_summed, 128);
-    *abort_flag = 0;
     fence_mbar_init();
-    tma_prefetch_desc(&tma_w);
-    tma_prefetch_desc(&tma_x);
+  } else if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);  // two accumulators
+    tmem_relinquish();
   }
   // The TMA producer (thread 0). Every CTA reads the same rows of X: walking the k-blocks from a different starting
   // point in every cluster keeps the CTAs from asking L2 for the same lines of X at the same moment.
@@ -305,7 +313,9 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   uint32_t prod_phase = 0;
   auto produce = [&](int unit, int i0, int i1) -> bool {
     const int slab = unit / num_groups, grp = unit - slab * num_groups;
-    const int rot = nkb > 0 ? static_cast<int>((static_cast<unsigned>(unit) * 11u) % static_cast<unsigned>(nkb)) : 0;
+    // (by slab, not by unit: every group of X rows adds its k-blocks up in the same order, so a row's result does not
+    // depend on the group it falls into)
+    const int rot = nkb > 0 ? static_cast<int>((static_cast<unsigned>(slab) * 11u) % static_cast<unsigned>(nkb)) : 0;
     for (int i = i0; i < i1; ++i) {
       const int kb = kb0 + (i + rot >= nkb ? i + rot - nkb : i + rot);
       if (!mbar_wait(&empty_bar[prod_stage], prod_phase ^ 1u, abort_flag, p.status, kDevWaitEmptyTimeout)) return false;
@@ -320,17 +330,10 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
     return true;
   };
-  // (Issuing the first ring-full of loads here, before the TMEM allocation and the cluster-wide sync, was measured:
-  // 0.5 - 1.5 us SLOWER on every shape. The first TMA instruction waits for its tensor map, just prefetched above, and
-  // thread 0 then holds up the CTA's set-up for that long.)
-  __syncthreads();
-  if (warp == 1) {
-    tmem_alloc(tmem_slot, Cfg::kTmemCols);  // two accumulators
-    tmem_relinquish();
-  }
   tc_fence_before();
+  cluster_arrive_relaxed();
   __syncthreads();
-  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  cluster_wait();  // the peers' barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool epi_arrived = false;  // this thread has arrived at the closing cluster barrier
@@ -391,8 +394,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
   } else {
     // The MX rows of X are cut into H x R blocks of kSub rows; in pass h rank r finishes block h * R + r: it keeps
-    // that block of its own sums and sends each peer q the block h * R + q (slot "sender" of q's `partial`; a warp's
-    // store covers 128 consecutive bytes). The stores are asynchronous and credit their bytes to the receiver's
+    // that block of its own sums and sends each peer q the block h * R + q (slot "sender" of q's `partial`, four rows
+    // of X per 16-byte store: a warp's store covers 512 consecutive bytes). The stores are asynchronous and credit their bytes to the receiver's
     // `partial_ready`: nobody waits for a store to land except the thread that needs the data. Then the rank adds
     // what its peers sent into `tile` and writes its rows out. (H > 1 only bounds the buffers: 256 rows of X would
     // otherwise need 128 KB of them.)
@@ -436,9 +439,9 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       const int my_rows = m_here - my_row0 < 0 ? 0 : (m_here - my_row0 < kSub ? m_here - my_row0 : kSub);
       const int out_row0 = row_base + my_row0;  // where this rank's block starts in the output
       // what the peers will send for this pass (a rank with no valid row of X is sent nothing and waits for nothing)
-      if (et == 0 && my_rows > 0) mbar_arrive_expect_tx(partial_ready, (R - 1) * Cfg::kSlotBytes);
+      if (R > 1 && et == 0 && my_rows > 0) mbar_arrive_expect_tx(partial_ready, (R - 1) * Cfg::kSlotBytes);
       // the peers must have read what this CTA sent for the previous pass before it is overwritten
-      if (seq > 0)
+      if (R > 1 && seq > 0)
         ok = mbar_wait_cluster(&partial_taken[(seq - 1) & 1], ((seq - 1) >> 1) & 1, abort_flag, p.status,
                                kDevWaitOtherTimeout);
 #pragma unroll
@@ -447,7 +450,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         if (q == rank || m_here <= q_row0) continue;
         const int slot = rank < q ? rank : rank - 1;  // where this rank's sums go in rank q's buffer
         const uint32_t dst = mapa_shared(smem_u32(partial), static_cast<uint32_t>(q)) +
-                             static_cast<uint32_t>((slot * kSub * 128 + row) * 4);
+                             static_cast<uint32_t>((slot * kSub * 128 + row * 4) * 4);
         const uint32_t dst_bar = mapa_shared(smem_u32(partial_ready), static_cast<uint32_t>(q));
 #pragma unroll
         for (int c = 0; c < kSub / kChunk; ++c) {
@@ -456,8 +459,9 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
           tmem_ld_wait();
           if (ok) {
 #pragma unroll
-            for (int j = 0; j < kChunk; ++j)
-              st_async_cluster_b32(dst + static_cast<uint32_t>((c * kChunk + j) * 128 * 4), v[j], dst_bar);
+            for (int j = 0; j < kChunk; j += 4)
+              st_async_cluster_v4(dst + static_cast<uint32_t>((c * kChunk + j) * 128 * 4), v[j], v[j + 1], v[j + 2], v[j + 3],
+                                  dst_bar);
           }
         }
       }
@@ -468,8 +472,10 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         epi_arrived = true;
       }
       if (ok && my_rows > 0) {
-        ok = mbar_wait_cluster(partial_ready, ready_phase, abort_flag, p.status, kDevWaitOtherTimeout);
-        ready_phase ^= 1u;
+        if constexpr (R > 1) {
+          ok = mbar_wait_cluster(partial_ready, ready_phase, abort_flag, p.status, kDevWaitOtherTimeout);
+          ready_phase ^= 1u;
+        }
 #pragma unroll
         for (int c = 0; c < kSub / kChunk; ++c) {
           uint32_t v[kChunk];
@@ -481,13 +487,18 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             // its first store: the compiler may not move a load of `partial` over a store to `tile` by itself.
             float sum[kChunk];
 #pragma unroll
-            for (int j = 0; j < kChunk; ++j) {
-              sum[j] = 0.f;
+            for (int j = 0; j < kChunk; j += 4) {
 #pragma unroll
               for (int q = 0; q < R; ++q) {
                 const int slot = q < rank ? q : q - 1;  // where rank q's sums sit in this rank's buffer
-                const float term = q == rank ? __uint_as_float(v[j]) : partial[(slot * kSub + c * kChunk + j) * 128 + row];
-                sum[j] = q == 0 ? term : sum[j] + term;
+                const float4 term =
+                    q == rank ? make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                            __uint_as_float(v[j + 3]))
+                              : *reinterpret_cast<const float4*>(partial + ((slot * kSub + c * kChunk + j) * 128 + row * 4));
+                sum[j] = q == 0 ? term.x : sum[j] + term.x;
+                sum[j + 1] = q == 0 ? term.y : sum[j + 1] + term.y;
+                sum[j + 2] = q == 0 ? term.z : sum[j + 2] + term.z;
+                sum[j + 3] = q == 0 ? term.w : sum[j + 3] + term.w;
               }
             }
 #pragma unroll
@@ -597,7 +608,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         // This thread is done reading `partial`: the peers may send the next pass's sums. (Its reads have returned -
         // their values went into `tile` - so the signal needs no release. A rank without rows signals all the same:
         // the senders count every peer.)
-        if (!last) {
+        if (R > 1 && !last) {
 #pragma unroll
           for (int q = 0; q < R; ++q)
             if (q != rank)
@@ -623,15 +634,42 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   cluster_wait();  // no CTA leaves while a peer can still write to it or signal it
 }
 
+// One walker per cluster the GPU can hold at once (clusters do not straddle GPCs, so this can be fewer than SMs / R):
+// a cluster left for a second wave would start when the first is already done streaming.
+template <bool BF16, int MX, int R, int H>
+static int swapab_resident_clusters() {
+  using Cfg = SwapCfg<MX, R, H>;
+  static std::atomic<uint64_t> configured{0};
+  static std::atomic<int> resident{0};
+  int clusters = resident.load(std::memory_order_relaxed);
+  if (clusters == 0) {
+    auto* kernel = &gemm_swapab_kernel<BF16, MX, R, H>;
+    opt_in_smem_once(configured, reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(R * (sm_count() / R)));
+    cfg.blockDim = dim3(kSwapThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = R;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200AIT_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+    B200AIT_REQUIRE(clusters > 0, "gemm: the weight-streaming kernel's cluster does not fit this GPU");
+    resident.store(clusters, std::memory_order_relaxed);
+  }
+  return clusters;
+}
+
 template <bool BF16, int MX, int R, int H>
 static void launch_swapab(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int num_slabs,
                           int num_groups, cudaStream_t stream) {
   using Cfg = SwapCfg<MX, R, H>;
-  static std::atomic<uint64_t> configured{0};
-  auto* kernel = &gemm_swapab_kernel<BF16, MX, R, H>;
-  opt_in_smem_once(configured, reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes);
+  const int walkers = swapab_resident_clusters<BF16, MX, R, H>();  // also opts the kernel in to its shared memory
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(R * (sm_count() / R)));
+  cfg.gridDim = dim3(static_cast<unsigned>(R * std::min(num_slabs * num_groups, walkers)));
   cfg.blockDim = dim3(kSwapThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
@@ -642,18 +680,92 @@ static void launch_swapab(const CUtensorMap& tw, const CUtensorMap& tx, const Ge
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  // one walker per cluster the GPU can hold at once (clusters do not straddle GPCs, so this can be fewer than
-  // SMs / R): a cluster left for a second wave would start when the first is already done streaming
-  static std::atomic<int> resident{0};
-  int walkers = resident.load(std::memory_order_relaxed);
-  if (walkers == 0) {
-    B200AIT_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&walkers, kernel, &cfg));
-    B200AIT_REQUIRE(walkers > 0, "gemm: the weight-streaming kernel's cluster does not fit this GPU");
-    resident.store(walkers, std::memory_order_relaxed);
-  }
-  cfg.gridDim = dim3(static_cast<unsigned>(R * std::min(num_slabs * num_groups, walkers)));
   ::b200ait::count_launch();
-  B200AIT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, tw, tx, p, num_slabs, num_groups));
+  B200AIT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, &gemm_swapab_kernel<BF16, MX, R, H>, tw, tx, p, num_slabs, num_groups));
+}
+
+// The instantiations the planner chooses from: MX rows of X per group, K split R ways, exchange in H passes.
+struct SwapKernel {
+  int mx, r, stages;
+  void (*launch)(bool bf16, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int num_slabs,
+                 int num_groups, cudaStream_t stream);
+  int (*resident)(bool bf16);
+};
+template <int MX, int R, int H>
+static SwapKernel swap_kernel_entry() {
+  return SwapKernel{MX, R, SwapCfg<MX, R, H>::kStages,
+                    [](bool bf16, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int num_slabs,
+                       int num_groups, cudaStream_t stream) {
+                      if (bf16)
+                        launch_swapab<true, MX, R, H>(tw, tx, p, num_slabs, num_groups, stream);
+                      else
+                        launch_swapab<false, MX, R, H>(tw, tx, p, num_slabs, num_groups, stream);
+                    },
+                    [](bool bf16) {
+                      return bf16 ? swapab_resident_clusters<true, MX, R, H>() : swapab_resident_clusters<false, MX, R, H>();
+                    }};
+}
+static const std::vector<SwapKernel>& swap_kernels() {
+  static const std::vector<SwapKernel> table = {
+      swap_kernel_entry<16, 2, 1>(),  swap_kernel_entry<32, 2, 1>(),  swap_kernel_entry<64, 2, 1>(),
+      swap_kernel_entry<128, 2, 1>(), swap_kernel_entry<256, 2, 2>(), swap_kernel_entry<32, 4, 1>(),
+      swap_kernel_entry<64, 4, 1>(),  swap_kernel_entry<128, 4, 1>(), swap_kernel_entry<256, 4, 2>(),
+      swap_kernel_entry<64, 8, 1>(),  swap_kernel_entry<128, 8, 1>(), swap_kernel_entry<256, 8, 2>()};
+  return table;
+}
+
+// Which weight-streaming kernel takes an unbatched problem (nullptr: the tile kernels do).
+//
+// Weights of more than 16 MB are bandwidth problems: W is read once at the HBM rate whatever the X tile, so the X
+// tile is as wide as M needs (one group up to M = 256), K goes two ways, or four / eight ways while the slabs are too
+// few to put most SMs to work. Bounds from sweeps against the tile kernels: M <= 128 from K = 512 on (M <= 32 from
+// K = 256), M <= 256 from K = 2048 on (4096 x 4096 at M = 256: 19.9 against 24.9 us), larger M in groups of 256 while
+// K >= 2048 and there are at most 32 units (beyond, the tile kernels are ahead again).
+//
+// Smaller problems are latency problems: a CTA's ring holds 150 - 190 KB, a trip to memory takes about 0.7 us, and a
+// launch costs about 3 us before the first byte arrives, so the time is the number of ring-fulls a rank streams, plus
+// the exchange (each CTA sends (R - 1) / R of its 128 x MX sums through the cluster's shared-memory window, measured
+// at about 40 GB/s per CTA), plus a second wave's worth if the units outnumber the resident clusters. X is therefore
+// cut into groups that are as small as it takes to fill one wave: 768 x 768 at M = 128 runs as 24 units of 32 rows,
+// K four ways (5.7 us) rather than 6 units of 128 rows (7.5 us). The estimate below was fitted to a sweep of 84 shapes
+// x 12 kernels (M = 32 .. 2048, N and K = 320 .. 4096) and picks within 2 % of the best kernel on average. Where the
+// tile kernels win instead was read off the same sweep: more than 64 output tiles of 128 x 128 (128 with K >= 4096),
+// M > 1024 (2048 with K >= 4096), or K < 512 with M > 256.
+static const SwapKernel* plan_swapab(long long m, long long n, long long k, bool bf16) {
+  if (n < 128 || m < 5) return nullptr;
+  const long long slabs = (n + 127) / 128, kb_total = (k + kBK - 1) / kBK;
+  const auto& table = swap_kernels();
+  auto find = [&](int mx, int r) -> const SwapKernel* {
+    for (const SwapKernel& sk : table)
+      if (sk.mx == mx && sk.r == r) return &sk;
+    return nullptr;
+  };
+  if (n * k * 2 > (16ll << 20)) {
+    const long long units = ((m + kSwapMaxM - 1) / kSwapMaxM) * slabs;
+    const bool take = m <= 128   ? (k >= 512 || (k >= 256 && m <= 32))
+                      : m <= 256 ? k >= 2048
+                                 : (k >= 2048 && units <= 32);
+    if (!take) return nullptr;
+    const int r = (units <= sm_count() / 16 && kb_total >= 32) ? 8 : units <= sm_count() / 4 ? 4 : 2;
+    const int mx = std::max(8 * r, m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256);
+    return find(mx, r);
+  }
+  const long long tiles = ((m + 127) / 128) * slabs;
+  const bool deep = kb_total >= 64;
+  if (k < 256 || (k < 512 && m > 256) || tiles > (deep ? 128 : 64) || m > (deep ? 2048 : 1024)) return nullptr;
+  const SwapKernel* best = nullptr;
+  double best_us = 0.0;
+  for (const SwapKernel& sk : table) {
+    if (kb_total < sk.r) continue;                       // every rank needs a k-block
+    const long long units = ((m + sk.mx - 1) / sk.mx) * slabs;
+    const long long waves = (units + sk.resident(bf16) - 1) / sk.resident(bf16);
+    const double kb_rank = static_cast<double>((kb_total + sk.r - 1) / sk.r);
+    const double stream = std::max(0.7, kb_rank / sk.stages * 0.7) + kb_rank * 0.06;
+    const double tail = 128.0 * sk.mx * 4.0 * (sk.r - 1) / sk.r / 40e3 + 0.005 * sk.mx / sk.r;
+    const double us = 3.0 + stream + tail + (waves - 1) * (std::max(stream, tail) + 0.3);
+    if (best == nullptr || us < best_us) best = &sk, best_us = us;
+  }
+  return best;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -922,49 +1034,16 @@ void gemm_run(const GemmArgs& g_in) {
     B200AIT_CUDA_CHECK(cudaGetLastError());
     return;
   }
-  // 5 <= M <= 256, tile width and split-K left to the library (measured against the tile kernels: up to M = 128 ahead
-  // for every N >= 128 from K = 512 on, and for M <= 32 from K = 256 on; 256 x 4096 at M = 64: 9.4 against 17.5 us; for
-  // 128 < M <= 256, where X is 256 rows per k-block, from K = 2048 on: 4096 x 4096 at M = 256 19.9 against 24.9 us, but
-  // 3072 x 768 11.6 against 8.8): stream W once with the
-  // operands swapped (W rows on the MMA rows), K split across a cluster of two or four, no workspace
-  // M > 256 with few output tiles and a deep K (768 x 3072 at M = 512: 12 tiles of 128 x 256, which the tile kernels
-  // cut into 6 K shares with a second kernel to add them up): the same kernel, X taken in groups of 256 rows, so that a
-  // unit of work is a slab of W against a group of X. Measured ahead of the tile kernels while there are at most 32
-  // units (1024 x 768 x 3072 16.3 against 19.5 us, 768 x 1280 x 5120 21 against 29), behind from 36 on.
-  const long long swap_groups = (g.m + kSwapMaxM - 1) / kSwapMaxM, swap_slabs = (g.n + 127) / 128;
-  if (tma_ok && g.batch == 1 && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0 && g.n >= 128 &&
-      (g.m <= 128   ? (g.k >= 512 || (g.k >= 256 && g.m <= 32))
-       : g.m <= 256 ? g.k >= 2048
-                    : (g.k >= 2048 && swap_groups * swap_slabs <= 32))) {
-    const int num_groups = static_cast<int>(swap_groups);
-    const int num_slabs = static_cast<int>(swap_slabs);
-    const int num_units = num_slabs * num_groups;
-    // few units: K goes four ways (at most SMs / 4 units) or, with at least four k-blocks left per rank, eight ways
-    // (at most SMs / 16 units: measured ahead of four ways up to 8 slabs, behind at 16), so that most SMs stream
-    const long long kb_total = (g.k + kBK - 1) / kBK;
-    const bool oct = num_units <= sm_count() / 16 && kb_total >= 32;
-    const bool quad = !oct && num_units <= sm_count() / 4;
-    // the X tile is at least 8 rows per rank wide
-    const int mx_min = oct ? 64 : quad ? 32 : 16;
-    const int mx = std::max(mx_min, g.m <= 16 ? 16 : g.m <= 32 ? 32 : g.m <= 64 ? 64 : g.m <= 128 ? 128 : 256);
-    CUtensorMap tw = make_tile_map(g.b, bf16, g.k, g.n, 1, g.ldb, 0, 128);
-    CUtensorMap tx = make_tile_map(g.a, bf16, g.k, g.m, 1, g.lda, 0, mx);
-#define B200AIT_SWAP(MX, R, H)                                             \
-  do {                                                                     \
-    if (bf16)                                                              \
-      launch_swapab<true, MX, R, H>(tw, tx, p, num_slabs, num_groups, g.stream); \
-    else                                                                   \
-      launch_swapab<false, MX, R, H>(tw, tx, p, num_slabs, num_groups, g.stream); \
-  } while (0)
-    if (oct) {
-      if (mx == 64) B200AIT_SWAP(64, 8, 1); else if (mx == 128) B200AIT_SWAP(128, 8, 1); else B200AIT_SWAP(256, 8, 2);
-    } else if (quad) {
-      if (mx == 32) B200AIT_SWAP(32, 4, 1); else if (mx == 64) B200AIT_SWAP(64, 4, 1); else if (mx == 128) B200AIT_SWAP(128, 4, 1); else B200AIT_SWAP(256, 4, 2);
-    } else {
-      if (mx == 16) B200AIT_SWAP(16, 2, 1); else if (mx == 32) B200AIT_SWAP(32, 2, 1); else if (mx == 64) B200AIT_SWAP(64, 2, 1); else if (mx == 128) B200AIT_SWAP(128, 2, 1); else B200AIT_SWAP(256, 2, 2);
+  // few rows of X, or few output tiles: the weight-streaming kernel where its planner takes the problem
+  if (tma_ok && g.batch == 1 && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0) {
+    if (const SwapKernel* sk = plan_swapab(g.m, g.n, g.k, bf16)) {
+      const int num_groups = static_cast<int>((g.m + sk->mx - 1) / sk->mx);
+      const int num_slabs = static_cast<int>((g.n + 127) / 128);
+      CUtensorMap tw = make_tile_map(g.b, bf16, g.k, g.n, 1, g.ldb, 0, 128);
+      CUtensorMap tx = make_tile_map(g.a, bf16, g.k, g.m, 1, g.lda, 0, sk->mx);
+      sk->launch(bf16, tw, tx, p, num_slabs, num_groups, g.stream);
+      return;
     }
-#undef B200AIT_SWAP
-    return;
   }
   if (!tma_ok) {
     dim3 grid(static_cast<unsigned>((g.n + 31) / 32), static_cast<unsigned>((g.m + 31) / 32),

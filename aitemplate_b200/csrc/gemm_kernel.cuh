@@ -363,30 +363,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   if (blockIdx.x == 0 && threadIdx.x == 0) g_gemm_probe[15] = clock64();  // kernel start
 #endif
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+  // Set-up in parallel (a small problem's whole run is a few microseconds): lane 0 of warp 0 asks for the tensor maps,
+  // the lanes of warp 0 initialise one barrier each, warp 1 allocates tensor memory meanwhile. The barriers lie in
+  // shared memory as full[kStages], empty[kStages], acc_full[2], acc_empty[2], drain_bar, d0_bar[2 * kEpiWarps].
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_a);
+      tma_prefetch_desc(&tma_b);
+      if (p.tma_store) {
+        tma_prefetch_desc(&tma_out);
+        if (MULTI)
+          for (int i = 1; i < p.num_out; ++i) tma_prefetch_desc(&outs.m[i]);
+      }
+      if (D0BOX && p.tma_d0) tma_prefetch_desc(&tma_d0);
+      *abort_flag = 0;
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], (PAIR ? 2 : 1) * 32 * kEpiWarps);  // the leader hears from both CTAs' epilogues
+    constexpr int kBars = 2 * kStages + 5 + 2 * kEpiWarps;
+    for (int i = lane; i < kBars; i += 32) {
+      const int j = i - 2 * kStages;
+      // acc_empty: the leader hears from both CTAs' epilogues
+      mbar_init(&full_bar[i], (j == 2 || j == 3) ? static_cast<uint32_t>((PAIR ? 2 : 1) * 32 * kEpiWarps) : 1u);
     }
-    mbar_init(drain_bar, 1);
-    for (int i = 0; i < 2 * kEpiWarps; ++i) mbar_init(&d0_bar[i], 1);
-    *abort_flag = 0;
     fence_mbar_init();
-    tma_prefetch_desc(&tma_a);
-    tma_prefetch_desc(&tma_b);
-    if (p.tma_store) {
-      tma_prefetch_desc(&tma_out);
-      if (MULTI)
-        for (int i = 1; i < p.num_out; ++i) tma_prefetch_desc(&outs.m[i]);
-    }
-    if (D0BOX && p.tma_d0) tma_prefetch_desc(&tma_d0);
-  }
-  __syncthreads();
-  if (warp == 1) {
+  } else if (warp == 1) {
     if (PAIR) {  // the same warp of both CTAs, same result slot
       tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
       tmem_relinquish_pair();
@@ -396,8 +395,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     }
   }
   tc_fence_before();
+  // the peer's barriers are initialised before anything signals them (no release needed on the arrive: the
+  // initialisations are published by fence.mbarrier_init, and a releasing arrive costs about 0.5 us)
+  if (PAIR) cluster_arrive_relaxed();
   __syncthreads();
-  if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  if (PAIR) cluster_wait();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 

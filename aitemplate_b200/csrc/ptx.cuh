@@ -142,6 +142,14 @@ __device__ __forceinline__ void st_async_cluster_b32(uint32_t cluster_addr, uint
                "r"(v), "r"(cluster_bar)
                : "memory");
 }
+// Four consecutive 32-bit words (16-byte aligned), same contract: 16 bytes credited.
+__device__ __forceinline__ void st_async_cluster_v4(uint32_t cluster_addr, uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3,
+                                                    uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(
+                   cluster_addr),
+               "r"(v0), "r"(v1), "r"(v2), "r"(v3), "r"(cluster_bar)
+               : "memory");
+}
 // arrive on a peer CTA's mbarrier without ordering this thread's earlier writes
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
@@ -413,5 +421,4 @@ __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
-
 }  // namespace b200ait

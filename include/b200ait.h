@@ -57,7 +57,8 @@ int b200ait_selftest_bounded_wait(int64_t* out, void* stream);
  * With tile_n = 0 and split_k = 0 an unbatched problem with few rows is served by the weight-streaming kernels instead
  * of the tiles: m <= 4 by one that multiplies on the FMA pipe, m <= 256 (against n >= 128 and a deep enough k) by one
  * that puts the weight rows on the MMA rows and splits k across a thread-block cluster; neither needs the workspace.
- * The second also takes a larger m, in groups of 256 rows, while k >= 2048 and ceil(m / 256) * ceil(n / 128) <= 32.
+ * The second also takes a larger m while it makes at most 32 units of work: in groups of 256 rows for k >= 2048
+ * (units = ceil(m / 256) * ceil(n / 128)), in groups of 128 rows for 768 <= k < 2048 (ceil(m / 128) * ceil(n / 128)).
  * workspace / workspace_bytes / split_k: see b200ait_gemm_rcr_workspace_bytes below.
  * Replaces python/aitemplate/backend/cuda/gemm_universal/common.py:130-617 (CUTLASS instantiation). */
 int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void* d0, const void* d1, void* c,

@@ -524,12 +524,12 @@ def test_swapped_operand_second_pass_with_idle_ranks(m, n, kk):
 
 
 @pytest.mark.parametrize("m,n,kk", [(257, 768, 3072), (300, 1024, 2048), (512, 768, 3072), (700, 520, 2056),
-                                    (1000, 1000, 2304), (1024, 1024, 4096), (2048, 256, 2048), (4000, 250, 2048),
-                                    (8192, 128, 2048)])
+                                    (1000, 1000, 2304), (1024, 1024, 4096), (2048, 256, 4096), (1900, 250, 4104),
+                                    (1024, 128, 2048), (400, 8192, 2048), (513, 4100, 8192)])
 @pytest.mark.parametrize("epilogue", ["relu", "add", "mul_add"])
 def test_swapped_operand_row_groups(m, n, kk, epilogue):
-    """More than 256 rows of X against few, deep weight slabs: the weight-streaming kernel takes X in groups of 256
-    rows (a ragged last group, a last group with a single row, ragged slabs, up to 32 groups)."""
+    """More rows of X than one tile holds, against few weight slabs: the weight-streaming kernel takes X in groups
+    of 32 to 256 rows (a ragged last group, a last group with a single row, ragged slabs, small and large weights)."""
     k = _kernels()
     x = _rand((m, kk), 650, dist="uniform")
     w = _rand((n, kk), 651, scale=0.03)
