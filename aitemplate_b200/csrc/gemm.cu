@@ -729,9 +729,9 @@ static const std::vector<SwapKernel>& swap_kernels() {
 // cut into groups that are as small as it takes to fill one wave: 768 x 768 at M = 128 runs as 24 units of 32 rows,
 // K four ways (5.7 us) rather than 6 units of 128 rows (7.5 us). The estimate below was fitted to a sweep of 84 shapes
 // x 12 kernels (M = 32 .. 2048, N and K = 320 .. 4096) and picks within 2 % of the best kernel on average. Where the
-// tile kernels win instead was read off the same sweep: more than 64 output tiles of 128 x 128 (128 with K >= 4096),
-// M > 1024 (2048 with K >= 4096), or K < 512 with M > 256.
-static const SwapKernel* plan_swapab(long long m, long long n, long long k, bool bf16) {
+// tile kernels win instead was read off the same sweep: more than 64 output tiles of 128 x 128 (128 with K >= 4096; 32
+// when the epilogue is more than bias + relu), M > 1024 (2048 with K >= 4096), or K < 512 with M > 256.
+static const SwapKernel* plan_swapab(long long m, long long n, long long k, bool bf16, bool plain_epilogue) {
   if (n < 128 || m < 5) return nullptr;
   const long long slabs = (n + 127) / 128, kb_total = (k + kBK - 1) / kBK;
   const auto& table = swap_kernels();
@@ -752,7 +752,10 @@ static const SwapKernel* plan_swapab(long long m, long long n, long long k, bool
   }
   const long long tiles = ((m + 127) / 128) * slabs;
   const bool deep = kb_total >= 64;
-  if (k < 256 || (k < 512 && m > 256) || tiles > (deep ? 128 : 64) || m > (deep ? 2048 : 1024)) return nullptr;
+  // (an activation other than relu, a residual or a permuted store goes through this kernel's run-time dispatch, which
+  // the tile kernels compile away: 3072 x 768 + fast_gelu at M = 256, 48 tiles, is 9.0 us here against 8.4)
+  const long long max_tiles = !plain_epilogue ? 32 : deep ? 128 : 64;
+  if (k < 256 || (k < 512 && m > 256) || tiles > max_tiles || m > (deep ? 2048 : 1024)) return nullptr;
   const SwapKernel* best = nullptr;
   double best_us = 0.0;
   for (const SwapKernel& sk : table) {
@@ -1036,7 +1039,10 @@ void gemm_run(const GemmArgs& g_in) {
   }
   // few rows of X, or few output tiles: the weight-streaming kernel where its planner takes the problem
   if (tma_ok && g.batch == 1 && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0) {
-    if (const SwapKernel* sk = plan_swapab(g.m, g.n, g.k, bf16)) {
+    const int code = p.epilogue;
+    const bool plain = epi_b1(code) == kBinaryNone && epi_b2(code) == kBinaryNone && epi_u2(code) == kUnaryIdentity &&
+                       (epi_u1(code) == kUnaryIdentity || epi_u1(code) == kUnaryRelu) && p.store_mode == 0;
+    if (const SwapKernel* sk = plan_swapab(g.m, g.n, g.k, bf16, plain)) {
       const int num_groups = static_cast<int>((g.m + sk->mx - 1) / sk->mx);
       const int num_slabs = static_cast<int>((g.n + 127) / 128);
       CUtensorMap tw = make_tile_map(g.b, bf16, g.k, g.n, 1, g.ldb, 0, 128);
