@@ -93,13 +93,18 @@ __device__ __forceinline__ void apply_unary_vec(int u, float (&v)[N]) {
       }
       break;
     }
-    case kUnaryGelu:
-#pragma unroll
-      for (int i = 0; i < N; ++i) v[i] = apply_unary(kUnaryGelu, v[i]);
-      break;
+#define B200AIT_UNARY_CASE(U)                                      \
+  case U:                                                          \
+    _Pragma("unroll") for (int i = 0; i < N; ++i) v[i] = apply_unary(U, v[i]); \
+    break;
+      // one straight loop per activation: with the code as a constant the per-element switch folds away
+      B200AIT_UNARY_CASE(kUnaryGelu)
+      B200AIT_UNARY_CASE(kUnarySigmoid)
+      B200AIT_UNARY_CASE(kUnaryTanh)
+      B200AIT_UNARY_CASE(kUnarySwish)
+      B200AIT_UNARY_CASE(kUnaryHardswish)
+#undef B200AIT_UNARY_CASE
     default:
-#pragma unroll
-      for (int i = 0; i < N; ++i) v[i] = apply_unary(u, v[i]);
       break;
   }
 }
