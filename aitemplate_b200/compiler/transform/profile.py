@@ -18,7 +18,7 @@ from .toposort import sorted_ops
 _LOGGER = logging.getLogger(__name__)
 
 # (tile_n, split_k); split_k 1 = never split, n = at most n splits
-# (tile_n, split_k); (0, 0) is the library's own plan, which also reaches the weight-streaming kernels for M <= 128
+# (tile_n, split_k); (0, 0) is the library's own plan, which also reaches the weight-streaming kernels (few rows or few tiles)
 CANDIDATES: Sequence[Tuple[int, int]] = ((0, 0), (64, 1), (128, 1), (256, 1), (512, 1), (128, 2), (256, 2),
                                          (256, 4), (128, 4), (256, 8))
 

@@ -54,11 +54,12 @@ int b200ait_selftest_bounded_wait(int64_t* out, void* stream);
  * b [batch, n, k] (row stride ldb), c / d0 / d1 [batch, m, n] (row strides ldc / ldd). A batch stride
  * of 0 broadcasts that operand. tile_n = 0 lets the library choose; else 64, 128 or 256 (128 x tile_n tiles,
  * one CTA each) or 512 (256 x 256 tiles, each computed by a pair of CTAs with cta_group::2 MMAs).
- * With tile_n = 0 and split_k = 0 an unbatched problem with few rows is served by the weight-streaming kernels instead
- * of the tiles: m <= 4 by one that multiplies on the FMA pipe, m <= 256 (against n >= 128 and a deep enough k) by one
- * that puts the weight rows on the MMA rows and splits k across a thread-block cluster; neither needs the workspace.
- * The second also takes a larger m while it makes at most 32 units of work: in groups of 256 rows for k >= 2048
- * (units = ceil(m / 256) * ceil(n / 128)), in groups of 128 rows for 768 <= k < 2048 (ceil(m / 128) * ceil(n / 128)).
+ * With tile_n = 0 and split_k = 0 an unbatched problem with few rows or few output tiles is served by the
+ * weight-streaming kernels instead of the tiles: m <= 4 by one that multiplies on the FMA pipe; otherwise, against
+ * n >= 128 and k >= 256, by one that puts the weight rows on the MMA rows, takes the rows of x in groups of 16 to 256
+ * and splits k across a thread-block cluster. Which problems it takes is planned from their size: weights above 16 MB
+ * up to m = 256 (larger m while k >= 2048 and ceil(m / 256) * ceil(n / 128) <= 32); smaller weights up to m = 1024
+ * and 64 output tiles of 128 x 128 (32 when the epilogue is more than bias + relu). Neither needs the workspace.
  * workspace / workspace_bytes / split_k: see b200ait_gemm_rcr_workspace_bytes below.
  * Replaces python/aitemplate/backend/cuda/gemm_universal/common.py:130-617 (CUTLASS instantiation). */
 int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void* d0, const void* d1, void* c,
