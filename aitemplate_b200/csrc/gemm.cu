@@ -516,9 +516,11 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       }
       if (ok) {
         const int code = p.epilogue;
-        // bias + one activation into a row-major output
-        const bool simple = vec && epi_b1(code) == kBinaryNone && epi_b2(code) == kBinaryNone &&
-                            epi_u2(code) == kUnaryIdentity && p.store_mode == 0;
+        // bias + one activation [+ one added residual [+ relu]] into a row-major output: the short store loop
+        const bool add_d0 = epi_b1(code) == kBinaryAdd;
+        const bool simple = vec && (epi_b1(code) == kBinaryNone || add_d0) && epi_b2(code) == kBinaryNone &&
+                            (epi_u2(code) == kUnaryIdentity || (add_d0 && epi_u2(code) == kUnaryRelu)) &&
+                            p.store_mode == 0;
         // An activation that is more than a max runs first, in place on this thread's own elements of the tile, a row
         // per trip of a rolled loop, so that the store loops below carry no activation code but relu. (This code runs
         // once or twice per launch, from a cold instruction cache: with the activations dispatched inside the 32-wide
@@ -542,13 +544,16 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
           // four rows (j, j + 8, j + 16, j + 24) per trip, all of a trip's shared-memory loads first; no per-row
           // dispatch on the epilogue code
           using T = typename Elem16<BF16>::T;
-          const bool relu = epi_u1(code) == kUnaryRelu;
+          const bool relu = epi_u1(code) == kUnaryRelu, relu_after = epi_u2(code) == kUnaryRelu;
           T* out0 = static_cast<T*>(p.out) + col0;
+          const T* res0 = static_cast<const T*>(p.d0) + col0;
           for (int j = et >> 4; j < my_rows; j += 32) {
             float o[4][8];
+            uint4 r0[4];
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
               const int jj = j + 8 * t < my_rows ? j + 8 * t : j;
+              if (add_d0) r0[t] = __ldg(reinterpret_cast<const uint4*>(res0 + static_cast<long long>(out_row0 + jj) * p.ldd));
               const float* src = tile + jj * 128 + (et & 15) * 8;
               const float4 a0 = *reinterpret_cast<const float4*>(src), a1 = *reinterpret_cast<const float4*>(src + 4);
               o[t][0] = a0.x, o[t][1] = a0.y, o[t][2] = a0.z, o[t][3] = a0.w;
@@ -561,6 +566,12 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                 for (int e = 0; e < 8; ++e) {
                   const float y = pre ? o[t][e] : o[t][e] * p.alpha + bias_v[e];
                   o[t][e] = relu ? fmaxf(y, 0.f) : y;  // identity keeps a NaN a NaN
+                }
+                if (add_d0) {
+                  float f[8];
+                  unpack8<BF16>(r0[t], f);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) o[t][e] = relu_after ? fmaxf(o[t][e] + f[e], 0.f) : o[t][e] + f[e];
                 }
                 *reinterpret_cast<uint4*>(out0 + static_cast<long long>(out_row0 + j + 8 * t) * p.ldc) = pack8<BF16>(o[t]);
               }
@@ -752,9 +763,10 @@ static const std::vector<SwapKernel>& swap_kernels() {
 // cut into groups that are as small as it takes to fill one wave: 768 x 768 at M = 128 runs as 24 units of 32 rows,
 // K four ways (5.7 us) rather than 6 units of 128 rows (7.5 us). The estimate below was fitted to a sweep of 84 shapes
 // x 12 kernels (M = 32 .. 2048, N and K = 320 .. 4096) and picks within 2 % of the best kernel on average. Where the
-// tile kernels win instead was read off the same sweep: more than 64 output tiles of 128 x 128 (128 with K >= 4096; 32
-// when the epilogue is more than bias + relu), M > 1024 (2048 with K >= 4096), or K < 512 with M > 256.
-static const SwapKernel* plan_swapab(long long m, long long n, long long k, bool bf16, bool plain_epilogue) {
+// tile kernels win instead was read off the same sweep: more than 64 output tiles of 128 x 128 (128 with K >= 4096; 48
+// with an added residual, 32 with any other epilogue beyond bias + relu), M > 1024 (2048 with K >= 4096), or K < 512
+// with M > 256.
+static const SwapKernel* plan_swapab(long long m, long long n, long long k, bool bf16, int epilogue_cost) {
   if (n < 128 || m < 5) return nullptr;
   const long long slabs = (n + 127) / 128, kb_total = (k + kBK - 1) / kBK;
   const auto& table = swap_kernels();
@@ -775,9 +787,11 @@ static const SwapKernel* plan_swapab(long long m, long long n, long long k, bool
   }
   const long long tiles = ((m + 127) / 128) * slabs;
   const bool deep = kb_total >= 64;
-  // (an activation other than relu, a residual or a permuted store goes through this kernel's run-time dispatch, which
-  // the tile kernels compile away: 3072 x 768 + fast_gelu at M = 256, 48 tiles, is 9.0 us here against 8.4)
-  const long long max_tiles = !plain_epilogue ? 32 : deep ? 128 : 64;
+  // (an activation other than relu costs this kernel a pre-pass over its tile, a second residual, a multiplied one or
+  // a permuted store its long store loop, all of which the tile kernels compile away: 3072 x 768 + fast_gelu at
+  // M = 256, 48 tiles, is 9.0 us here against 8.4)
+  // (with an added residual, 1024 x 1024 at M = 1024, 64 tiles: 10.3 us here against 9.6; 768 x 768, 48 tiles: level)
+  const long long max_tiles = epilogue_cost >= 2 ? 32 : epilogue_cost == 1 ? 48 : deep ? 128 : 64;
   if (k < 256 || (k < 512 && m > 256) || tiles > max_tiles || m > (deep ? 2048 : 1024)) return nullptr;
   const SwapKernel* best = nullptr;
   double best_us = 0.0;
@@ -1063,9 +1077,13 @@ void gemm_run(const GemmArgs& g_in) {
   // few rows of X, or few output tiles: the weight-streaming kernel where its planner takes the problem
   if (tma_ok && g.batch == 1 && !g.b_mn && g.num_out == 1 && g.tile_n == 0 && g.split_k == 0) {
     const int code = p.epilogue;
-    const bool plain = epi_b1(code) == kBinaryNone && epi_b2(code) == kBinaryNone && epi_u2(code) == kUnaryIdentity &&
+    // what the weight-streaming kernel's short store loop does without an activation pre-pass: bias [+ relu]
+    // [+ one added residual [+ relu]] into a row-major output
+    const bool added = epi_b1(code) == kBinaryAdd;
+    const bool plain = (epi_b1(code) == kBinaryNone || added) && epi_b2(code) == kBinaryNone &&
+                       (epi_u2(code) == kUnaryIdentity || (added && epi_u2(code) == kUnaryRelu)) &&
                        (epi_u1(code) == kUnaryIdentity || epi_u1(code) == kUnaryRelu) && p.store_mode == 0;
-    if (const SwapKernel* sk = plan_swapab(g.m, g.n, g.k, bf16, plain)) {
+    if (const SwapKernel* sk = plan_swapab(g.m, g.n, g.k, bf16, !plain ? 2 : added ? 1 : 0)) {
       const int num_groups = static_cast<int>((g.m + sk->mx - 1) / sk->mx);
       const int num_slabs = static_cast<int>((g.n + 127) / 128);
       CUtensorMap tw = make_tile_map(g.b, bf16, g.k, g.n, 1, g.ldb, 0, 128);

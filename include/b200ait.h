@@ -59,7 +59,7 @@ int b200ait_selftest_bounded_wait(int64_t* out, void* stream);
  * n >= 128 and k >= 256, by one that puts the weight rows on the MMA rows, takes the rows of x in groups of 16 to 256
  * and splits k across a thread-block cluster. Which problems it takes is planned from their size: weights above 16 MB
  * up to m = 256 (larger m while k >= 2048 and ceil(m / 256) * ceil(n / 128) <= 32); smaller weights up to m = 1024
- * and 64 output tiles of 128 x 128 (32 when the epilogue is more than bias + relu). Neither needs the workspace.
+ * and 64 output tiles of 128 x 128 (48 with an added residual, 32 with any other epilogue beyond bias + relu). Neither needs the workspace.
  * workspace / workspace_bytes / split_k: see b200ait_gemm_rcr_workspace_bytes below.
  * Replaces python/aitemplate/backend/cuda/gemm_universal/common.py:130-617 (CUTLASS instantiation). */
 int b200ait_gemm_rcr(const void* a, const void* b, const void* bias, const void* d0, const void* d1, void* c,
