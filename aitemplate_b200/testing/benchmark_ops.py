@@ -244,6 +244,40 @@ def bench_sd_block(config: str, peaks: Dict) -> Dict:
     return row
 
 
+def bench_bert_layer(config: str, batch: int, peaks: Dict) -> Dict:
+    """One BERT-base encoder layer at a small batch (the reference's benchmark walks batch sizes from 1 up,
+    examples/03_bert/benchmark_ait.py:263-300) through compile_model() and graph mode: the latency side of the
+    benchmark configuration whose throughput the layer suite measures at batch 64."""
+    import tempfile
+
+    from .. import _lib
+    from ..compiler import compile_model
+    from . import detect_target, workloads
+
+    seq, hidden, heads, ffn = 384, 768, 12, 3072
+    x, params = workloads.bert_layer_inputs(batch, seq, hidden, ffn)
+    _, y = workloads.build_bert_layer(batch, seq, hidden, heads, ffn)
+    module = compile_model(y, detect_target(), tempfile.mkdtemp(prefix="b200ait_bert_"), f"bert_layer_b{batch}")
+    module.set_many_constants_with_tensors({name: params[key].cuda() for name, key in workloads.BERT_PARAM_NAMES.items()})
+    out = torch.empty((batch, seq, hidden), dtype=torch.float16, device="cuda")
+    ins = {"hidden_states": x.cuda()}
+    launches = _lib.kernel_launch_count()
+    module.run_with_tensors(ins, {"output_0": out}, graph_mode=False)
+    launches = _lib.kernel_launch_count() - launches
+    module.run_with_tensors(ins, {"output_0": out}, graph_mode=True)
+    time.sleep(0.2)
+    mean_ms, _, _ = module.benchmark_with_tensors(ins, {"output_0": out}, count=50, repeat=3, graph_mode=True)
+    row = {"config": config, "op": f"bert_layer ({launches} kernels, graph mode)", "shape": f"B{batch} S{seq} H{hidden}",
+           "us": round(mean_ms * 1e3, 2), "bound": "tensor"}
+    tf = workloads.bert_layer_flops(batch, seq, hidden, heads, ffn) / (mean_ms * 1e-3) / 1e12
+    row.update(tflops=round(tf, 1), frac_measured=round(tf / peaks["tflops_burst"], 3),
+               frac_nominal=round(tf / NOMINAL_TFLOPS, 3))
+    res = module.run_with_tensors(ins, {"output_0": out}, graph_mode=True)
+    row["_sample"] = {"kind": "bert_layer", "x": x, "params": params, "heads": heads, "got": res["output_0"],
+                      "scale": 1.0, "note": "whole layer"}
+    return row
+
+
 def run_suite(peaks: Dict, quick: bool = False, only: str = ""):
     """Yields one row per op of the benchmark configurations. quick=True shrinks the CPU-side samples (not the GPU
     problems) so that the whole sweep, CPU checks included, stays within about a minute. `only` keeps the cases
@@ -279,6 +313,8 @@ def _suite_cases(peaks: Dict, sf: float):
     layernorm("2", m2, 768, 1e-12)
     gemm("2", m2, 3072, 768, "fast_gelu")
     gemm("2", m2, 768, 3072, "add", residual=True)
+    for batch in (1, 4, 16):
+        cases.append((f"2:bert_layer:B{batch}", lambda batch=batch: bench_bert_layer("2", batch, peaks)))
     for n in (768, 1024, 4096):
         layernorm("3", 65536, n, 1e-5)
     cases.append(("3:softmax:512x1024x1024", lambda: bench_softmax("3", (512, 1024, 1024), peaks)))

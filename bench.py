@@ -526,6 +526,9 @@ def _check_sample(sample):
         x = sample["x"].cpu()
         fn = lambda: R.split(x, sample["sections"], sample["dim"])  # noqa: E731
         exact = True
+    elif kind == "bert_layer":
+        fn = lambda: R.bert_layer(sample["x"], sample["params"], sample["heads"])  # noqa: E731
+        atol = rtol = 3e-2
     elif kind == "sd_block":
         fn = lambda: R.sd_transformer_block(sample["x"], sample["context"], sample["params"])  # noqa: E731
         atol = rtol = 3e-2
