@@ -644,6 +644,39 @@ def test_tile_kernels_random_shapes():
             raise AssertionError(f"m={m} n={n} k={kk} epilogue={epilogue!r} {dtype} tile_n={tile_n} split_k={split_k}: {e}") from None
 
 
+def test_planned_weight_streaming_random_shapes():
+    """Seeded random problems where the library's planner chooses among the weight-streaming kernels (weights of at
+    most 16 MB, up to 64 output tiles): every group width and cluster size it can pick, ragged groups and slabs,
+    k-block counts of every residue, every epilogue family (short store loop, activation pre-pass, long store loop),
+    both dtypes. Each result must also be what the tile kernels give for the same problem, within rounding."""
+    import random
+
+    k = _kernels()
+    rng = random.Random(20240701)
+    epilogues = ["", "relu", "gelu", "fast_gelu", "tanh", "sigmoid", "add", "add_relu", "mul", "mul_add", "add_add", "sigmoid_mul"]
+    for case in range(48):
+        m = rng.choice([33, 64, 100, 129, 200, 256, 257, 384, 500, 512, 700, 1000, 1024])
+        n = 8 * rng.randint(16, max(16, min(160, 8192 // max(m, 128) * 16)))
+        kk = 8 * rng.randint(32, 520)
+        epilogue = rng.choice(epilogues)
+        dtype = torch.bfloat16 if rng.random() < 0.25 else torch.float16
+        x = _rand((m, kk), 21000 + case, dist="uniform", dtype=dtype)
+        w = _rand((n, kk), 22000 + case, scale=0.03, dtype=dtype)
+        b = _rand((n,), 23000 + case, scale=0.1, dtype=dtype)
+        nres = {"add": 1, "add_relu": 1, "mul": 1, "mul_add": 2, "sigmoid_mul": 1, "add_add": 2}.get(epilogue, 0)
+        d = [_rand((m, n), 24000 + 2 * case + i, dtype=dtype) for i in range(nres)]
+        tol = 1.5e-2 if dtype == torch.float16 else 5e-2
+        dev = [t.cuda() for t in (x, w, b, *d)]
+        try:
+            y = k.gemm_rcr(*dev, epilogue=epilogue)
+            assert k.device_status() == 0
+            _close(y, oracle.gemm_rcr(x, w, b, *d, epilogue=epilogue), atol=tol, rtol=tol)
+            y_tile = k.gemm_rcr(*dev, epilogue=epilogue, tile_n=128, split_k=1)
+            _close(y, y_tile.float().cpu(), atol=tol, rtol=tol)
+        except AssertionError as e:
+            raise AssertionError(f"m={m} n={n} k={kk} epilogue={epilogue!r} {dtype}: {e}") from None
+
+
 def test_batched_and_row_major_random_shapes():
     """Seeded random problems for bmm_rcr, bmm_rrr (B stored [K, N]), gemm_rrr and a broadcast operand."""
     import random
