@@ -298,7 +298,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     constexpr int kBars = 2 * Cfg::kStages + 9;
     for (int i = lane; i < kBars; i += 32) {
       const int j = i - 2 * Cfg::kStages;  // index among the barriers after the ring's
-      const uint32_t count = j < 0 ? 1u : j < 2 ? 1u : j < 4 ? 128u : j == 4 ? 1u : j < 7 ? 128u * (R > 1 ? R - 1 : 1) : j == 7 ? 1u : 128u;
+      // every epilogue thread arrives at acc_empty and tile_summed, every peer's at partial_taken, one thread elsewhere
+      const uint32_t count = (j == 2 || j == 3 || j == 8) ? 128u : (j == 5 || j == 6) ? 128u * (R > 1 ? R - 1 : 1) : 1u;
       mbar_init(&full_bar[i], count);
     }
     fence_mbar_init();
