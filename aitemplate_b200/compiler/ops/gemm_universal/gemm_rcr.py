@@ -94,6 +94,8 @@ class gemm(Operator):
         # alias that starts at the block, so only the row stride is needed; 0 = contiguous rows of K
         a_acc = self._attrs["input_accessors"][0]
         a_stride = a_acc.row_stride() if a_acc.stride_dim is not None else 0
+        b_acc = self._attrs["input_accessors"][1]  # the same for operand B ([N, K] only: a block of K columns)
+        b_stride = b_acc.row_stride() if b_acc.stride_dim is not None else 0
         return {
             "kernel": "gemm_rcr",
             "operands": [a, b, bias, d0, d1],
@@ -102,7 +104,7 @@ class gemm(Operator):
             # profiled yet" (gemm_common.py:579-594), not a request to never split.
             "ints": [epilogue_code(*self._epi), store_mode, t[0], t[1], t[2], acc.offset, out_stride,
                      int(self._attrs.get("tile_n", 0)) if self._attrs.get("profiled") else 0,
-                     int(self._attrs.get("split_k", 0)) if self._attrs.get("profiled") else 0, a_stride],
+                     int(self._attrs.get("split_k", 0)) if self._attrs.get("profiled") else 0, a_stride, b_stride],
             "floats": [float(self._attrs["alpha"])],
         }
 

@@ -72,8 +72,9 @@ def fuse_strided_cat(sorted_graph: List[Tensor]) -> int:
 
 def _strided_reader_slot(op, x):
     """Index of the input accessor through which `op` can read `x` with a row stride, or None: x is operand A of
-    a 2-D GEMM, either operand of a bmm without a permuted store, or the input of a layernorm, and appears
-    nowhere else among the op's inputs."""
+    a 2-D GEMM, operand B of a gemm_rcr (python/aitemplate/backend/cuda/gemm_universal/gemm_rcr.py:203-232 gives both
+    operands an accessor), either operand of a bmm without a permuted store, or the input of a layernorm, and
+    appears nowhere else among the op's inputs."""
     from ..ops.gemm_universal.bmm import bmm
     from ..ops.gemm_universal.gemm_rcr import gemm
     from ..ops.layernorm import layernorm
@@ -87,14 +88,15 @@ def _strided_reader_slot(op, x):
     elif isinstance(op, layernorm):
         ok = idx == 0 and len(op._attrs["normalized_shape"]) == 1
     else:
-        ok = idx == 0 and isinstance(op, gemm)
+        # operand A of any 2-D GEMM; operand B ([N, K]: a block of K columns) of the gemm_rcr family
+        ok = isinstance(op, gemm) and (idx == 0 or (idx == 1 and op._attrs["op"].startswith("gemm_rcr")))
     return idx if ok and op._attrs["input_accessors"][idx].stride_dim is None else None
 
 
 def fuse_split_strided(sorted_graph: List[Tensor]) -> int:
     """The split side of the reference's strided-op pass (python/aitemplate/compiler/transform/
     transform_strided_ops.py:94-333 together with fuse_split.py): when every consumer of an output of a
-    last-dim split is a GEMM (as operand A), a bmm (either operand) or a layernorm, those kernels read their column block of the
+    last-dim split is a GEMM (as operand A, or B of a gemm_rcr), a bmm (either operand) or a layernorm, those kernels read their column block of the
     split's input in place: the consumer's input TensorAccessor is re-based onto that input (element
     offset + the wider row stride), the split output becomes an alias of it at the block's byte offset, and
     the split's output mask for it is cleared. A split whose outputs are all fused launches nothing.

@@ -473,7 +473,8 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     uint8_t* c = static_cast<uint8_t*>(ptr_of(out0)) + out_off * dtype_size(T[out0].dtype);
     // ints[9]: row stride of A when it is a column block of a wider buffer (a split read in place); 0 = K
     const int64_t lda = op.ints.size() > 9 && op.ints[9] > 0 ? op.ints[9] : k;
-    check(b200ait_gemm_rcr(ptr_of(a), ptr_of(b), ptr_of(bias), ptr_of(d0), ptr_of(d1), c, 1, m, n, k, lda, k,
+    const int64_t ldb = op.ints.size() > 10 && op.ints[10] > 0 ? op.ints[10] : k;  // ints[10]: the same for B
+    check(b200ait_gemm_rcr(ptr_of(a), ptr_of(b), ptr_of(bias), ptr_of(d0), ptr_of(d1), c, 1, m, n, k, lda, ldb,
                            out_stride, n, 0, 0, 0, 0, static_cast<int>(op.ints[0]), T[a].dtype,
                            static_cast<float>(op.floats[0]), static_cast<int>(op.ints[1]), op.ints[2], op.ints[3],
                            op.ints[4], tile_hint, workspace_, workspace_bytes_, split_hint, stream),

@@ -370,6 +370,25 @@ def test_split_strided_input_fusion_plan():
     assert views == [0, 256, 2 * (128 + 64 + 32)]                              # byte offsets of the aliased blocks
 
 
+def test_split_strided_operand_b_of_gemm_rcr():
+    # operand B of a gemm_rcr ([N, K]) read in place from a block of K columns of a wider [N, K0 + K1] tensor: the
+    # reference gives both GEMM operands an input accessor (backend/cuda/gemm_universal/gemm_rcr.py:203-232)
+    wide = Tensor([48, 64 + 32], name="wide", is_input=True)
+    x0, x1 = Tensor([8, 64], name="x0", is_input=True), Tensor([8, 32], name="x1", is_input=True)
+    w0, w1 = ops.split()(wide, [64, 32], dim=-1)
+    y0 = _out(ops.gemm_rcr()(x0, w0), "y0")
+    y1 = _out(ops.gemm_rcr()(x1, w1), "y1")
+    _, plan, _, _ = _lower([y0, y1])
+    lines = plan.splitlines()
+    assert not any(l.startswith("op split") for l in lines) or \
+        _parse_op(next(l for l in lines if l.startswith("op split")))["ints"][-2:] == [0, 0]
+    gemms = [_parse_op(l) for l in lines if l.startswith("op gemm_rcr")]
+    assert [g_["ints"][9:11] for g_ in gemms] == [[0, 96], [0, 96]]              # A contiguous, B rows 96 elements apart
+    tl = [l.split() for l in lines if l.startswith("tensor ")]
+    idx_w = next(i for i, t in enumerate(tl) if t[1] == "wide")
+    assert sorted(int(t[5]) for t in tl if t[3] == "4" and int(t[6]) == idx_w) == [0, 128]
+
+
 def test_split_strided_input_fusion_is_skipped_when_illegal():
     x = Tensor([8, 100], name="x", is_input=True)
     w = Tensor([16, 50], name="w")

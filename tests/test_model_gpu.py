@@ -351,6 +351,31 @@ def test_strided_input_fusion_from_split(workdir, m):
     _close(res["ln3"], oracle.layernorm(c3, None, None), 1e-2)
 
 
+def test_strided_operand_b_from_split(workdir):
+    # gemm_rcr reads operand B ([N, K]) in place from a block of K columns of a wider tensor: no split kernel runs
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    from aitemplate_b200 import _lib
+
+    n, k0, k1, m = 136, 256, 64, 40
+    wide = Tensor([n, k0 + k1], name="wide", is_input=True)
+    x0, x1 = Tensor([m, k0], name="x0", is_input=True), Tensor([m, k1], name="x1", is_input=True)
+    bias = Tensor([n], name="bias")
+    w0, w1 = ops.split()(wide, [k0, k1], dim=-1)
+    outs = {"y0": ops.gemm_rcr_bias_relu()(x0, w0, bias), "y1": ops.gemm_rcr()(x1, w1)}
+    for name, t in outs.items():
+        t._attrs["name"], t._attrs["is_output"] = name, True
+    module = compile_model(list(outs.values()), detect_target(), workdir, "strided_b")
+    wd, x0d, x1d, bd = _rand((n, k0 + k1), 1, 0.05), _rand((m, k0), 2), _rand((m, k1), 3), _rand((n,), 4, 0.1)
+    module.set_many_constants_with_tensors({"bias": bd.cuda()})
+    ins = {"wide": wd.cuda(), "x0": x0d.cuda(), "x1": x1d.cuda()}
+    bufs = {name: torch.full((m, n), 9.0, dtype=torch.float16, device="cuda") for name in outs}
+    launches = _lib.kernel_launch_count()
+    res = module.run_with_tensors(ins, bufs)
+    assert _lib.kernel_launch_count() - launches == 2  # the two GEMMs: the split launches nothing
+    _close(res["y0"], oracle.gemm_rcr(x0d, wd[:, :k0], bd, epilogue="relu"), 1e-2)
+    _close(res["y1"], oracle.gemm_rcr(x1d, wd[:, k0:]), 1e-2)
+
+
 def test_bmm_permute_ops_in_a_graph(workdir):
     # bmm_rcr_permute / bmm_rrr_permute (tests/unittest/ops/test_bmm_permute.py): the 0213 permutation is fused into
     # the batched GEMM's store and the node returns the [B / d1, M, d1, N] view
