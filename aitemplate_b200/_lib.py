@@ -72,7 +72,7 @@ def _signatures():
         "b200ait_bmm_rcr": (c_int, [c_void_p] * 3 + [c_void_p] + [I64P] * 9 + [c_void_p]),
         "b200ait_mem_eff_attention": (
             c_int,
-            [c_void_p] * 4 + [c_int64] * 3 + [c_int] * 3 + [c_float, c_int, POINTER(c_int32), POINTER(c_int32), c_int, c_void_p],
+            [c_void_p] * 4 + [c_int64] * 3 + [c_int] * 3 + [c_float, c_int, c_void_p, c_void_p, c_int, c_void_p],
         ),
         "b200ait_mem_eff_attention_strided": (
             c_int,

@@ -1,6 +1,9 @@
 """mem_eff_attention graph node: softmax(Q K^T / sqrt(d)) V with q, k, v [B, H, S, D] and output
 [B, Sq, H, Dv] (python/aitemplate/compiler/ops/attention/mem_eff_attention.py:50-263). The softmax
-scale is always 1/sqrt(head_size), as in the reference kernel (kernel_forward.h:655)."""
+scale is always 1/sqrt(head_size), as in the reference kernel (kernel_forward.h:655). With
+variable_seq_length_kv / variable_seq_length_q the op takes int32 tensors of batch_size lengths: batch b attends to
+its first lengths_kv[b] keys, and only its first lengths_q[b] query rows are computed and written
+(kernel_forward.h:183-197; tests/unittest/ops/test_attention.py:504-530)."""
 from __future__ import annotations
 
 import math
@@ -15,8 +18,8 @@ class mem_eff_attention(Operator):
                  use_grouped_fmha=False) -> None:
         super().__init__()
         assert dropout == 0
-        if variable_seq_length_kv or variable_seq_length_q or use_grouped_fmha:
-            raise NotImplementedError("variable sequence lengths / grouped FMHA are outside this path")
+        if use_grouped_fmha:
+            raise NotImplementedError("grouped FMHA is outside this path")
         self._attrs["op"] = "mem_eff_attention"
         self._attrs["has_profiler"] = False
         self._attrs["dropout"] = dropout
@@ -28,7 +31,9 @@ class mem_eff_attention(Operator):
         self._attrs["use_grouped_fmha"] = use_grouped_fmha
 
     def _get_op_attributes(self):
-        return {"causal": self._attrs["causal"], "dropout": self._attrs["dropout"]}
+        return {"causal": self._attrs["causal"], "dropout": self._attrs["dropout"],
+                "variable_seq_length_kv": self._attrs["variable_seq_length_kv"],
+                "variable_seq_length_q": self._attrs["variable_seq_length_q"]}
 
     def _infer_shapes(self, q: Tensor, v: Tensor) -> List[IntVar]:
         qs = q._attrs["shape"]
@@ -36,8 +41,12 @@ class mem_eff_attention(Operator):
 
     def __call__(self, q: Tensor, k: Tensor, v: Tensor, lengths_kv: Optional[Tensor] = None,
                  lengths_q: Optional[Tensor] = None) -> Tensor:
-        if lengths_kv is not None or lengths_q is not None:
-            raise NotImplementedError("lengths_kv / lengths_q are outside this path")
+        for flag, t, name in ((self._attrs["variable_seq_length_kv"], lengths_kv, "lengths_kv"),
+                              (self._attrs["variable_seq_length_q"], lengths_q, "lengths_q")):
+            if flag and t is None:
+                raise RuntimeError(f"mem_eff_attention: {name} is required by the variable_seq_length flag")
+            if flag and t.dtype() not in ("int", "int32"):
+                raise RuntimeError(f"mem_eff_attention: {name} must be an int32 tensor")
         for name, t in (("q", q), ("k", k), ("v", v)):
             if t._rank() != 4:
                 raise RuntimeError(f"mem_eff_attention: {name} must be [batch, heads, seq, head_size]")
@@ -50,6 +59,11 @@ class mem_eff_attention(Operator):
             raise RuntimeError("mem_eff_attention: k and v sequence lengths differ")
         self._attrs["head_size"] = head.value()
         self._attrs["inputs"] = [q, k, v]
+        # as in the reference, a lengths tensor is only an input when its flag is set (a stray argument is ignored)
+        if self._attrs["variable_seq_length_kv"]:
+            self._attrs["inputs"].append(lengths_kv)
+        if self._attrs["variable_seq_length_q"]:
+            self._attrs["inputs"].append(lengths_q)
         self._attrs["input_accessors"] = [TensorAccessor(t) for t in self._attrs["inputs"]]
         self._set_depth()
         out = Tensor(self._infer_shapes(q, v), src_ops={self}, dtype=q.dtype())
@@ -62,5 +76,7 @@ class mem_eff_attention(Operator):
         # input_layouts: set by fuse_permute_into_attention; "bshd" = the operand is stored [B, S, H, D] and read in place
         layouts = self._attrs.get("input_layouts", ["bhsd"] * 3)
         return {"kernel": "mem_eff_attention", "operands": list(self._attrs["inputs"]),
-                "ints": [1 if self._attrs["causal"] else 0] + [1 if l == "bshd" else 0 for l in layouts],
+                # causal, three storage flags, then whether a lengths_kv / a lengths_q operand follows q, k, v
+                "ints": [1 if self._attrs["causal"] else 0] + [1 if l == "bshd" else 0 for l in layouts[:3]]
+                + [1 if self._attrs["variable_seq_length_kv"] else 0, 1 if self._attrs["variable_seq_length_q"] else 0],
                 "floats": [1.0 / math.sqrt(d) if d else 1.0]}

@@ -224,8 +224,8 @@ def fuse_permute_into_attention(sorted_graph: List[Tensor], outputs: List[Tensor
 
     changed = False
     for op in sorted_ops(sorted_graph):
-        if not isinstance(op, mem_eff_attention):
-            continue
+        if not isinstance(op, mem_eff_attention) or len(op._attrs["inputs"]) != 3:
+            continue  # (with lengths operands the op keeps its contiguous [B, H, S, D] inputs)
         layouts = list(op._attrs.get("input_layouts", ["bhsd"] * 3))
         for i, t in enumerate(list(op._attrs["inputs"][:3])):
             if layouts[i] != "bhsd":

@@ -87,6 +87,11 @@ struct AttnParams {
   // Variable-length ("packed") mode: sequence b owns rows cu_seqlens[b] .. cu_seqlens[b+1] of q, k, v and out, and
   // Sq = Skv = the longest sequence. Null: every sequence has Sq query and Skv key rows and its own batch coordinate.
   const int* cu_seqlens;
+  // Padded variable-length mode (kernel_forward.h:183-197 in the reference): with lengths_kv, batch b attends to its
+  // first lengths_kv[b] keys only; with lengths_q, only its first lengths_q[b] query rows are computed and written.
+  // A row that sees no key comes out as NaN, as it does there (0 / 0).
+  const int* lengths_kv;
+  const int* lengths_q;
   // coordinate order of each tensor map: 0 = (channel, row, head, batch), 1 = (channel, head, row, batch); the host
   // picks whichever keeps the map's strides ascending
   int q_order, k_order, v_order;
@@ -222,8 +227,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
     } else {
       w.b4 = b;
       w.row0 = 0;
-      w.q_len = p.Sq;
-      w.kv_len = p.Skv;
+      w.q_len = p.lengths_q ? min(max(__ldg(p.lengths_q + b), 0), p.Sq) : p.Sq;
+      w.kv_len = p.lengths_kv ? min(max(__ldg(p.lengths_kv + b), 0), p.Skv) : p.Skv;
       w.out_row0 = static_cast<long long>(b) * p.Sq;
     }
     if (!NOMASK && p.causal) w.kv_len = min(w.kv_len, w.q0 + kBlockM);
@@ -472,7 +477,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
       const Item w = decode_item(item);
       const int n_blocks = w.n_blocks, kv_len = w.kv_len;
-      if (n_blocks == 0) continue;
+      if (n_blocks == 0) {
+        // no key for this tile's rows (lengths_kv[b] == 0): softmax over nothing, NaN like the reference's 0 / 0
+        if (p.lengths_kv != nullptr && w.q0 + r < w.q_len) {
+          T* row_out = static_cast<T*>(p.out) + ((w.out_row0 + w.q0 + r) * p.H + w.h) * p.Dv;
+          const uint32_t nan2 = E::from_float2(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
+          for (int c = 0; c < p.Dv; c += 8) *reinterpret_cast<uint4*>(row_out + c) = make_uint4(nan2, nan2, nan2, nan2);
+        }
+        continue;
+      }
       const int q_idx = w.q0 + r;
       const uint32_t o_addr = tmem_o + lane_addr + static_cast<uint32_t>((it & 1) * Cfg::kTWidth);
       float m_ref = -INFINITY, l_run = 0.f;
@@ -651,7 +664,10 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(const void* q_, con
   float* sq = sh + warp * p.D;
   for (int i = lane; i < p.D; i += 32) sq[i] = E::to_float(q[i]);
   __syncwarp();
-  int kv_len = p.Skv;
+  const int batch = static_cast<int>(bh / p.H);
+  if (p.lengths_q != nullptr && qi >= __ldg(p.lengths_q + batch)) return;  // (the whole warp: it owns one row)
+  int kv_len = p.lengths_kv != nullptr ? min(max(__ldg(p.lengths_kv + batch), 0), p.Skv) : p.Skv;
+  const bool no_keys = kv_len == 0;
   if (p.causal) kv_len = min(kv_len, qi + 1);
   constexpr int kMaxPerLane = 8;  // Dv <= 256
   float o[kMaxPerLane];
@@ -691,7 +707,7 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(const void* q_, con
       }
     }
   }
-  const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
+  const float inv = (l_run > 0.f) ? 1.f / l_run : no_keys ? __int_as_float(0x7fc00000) : 0.f;  // no key at all: NaN
   const long long b = bh / p.H, h = bh - b * p.H;
   T* out = static_cast<T*>(p.out) + ((b * p.Sq + qi) * p.H + h) * p.Dv;
 #pragma unroll
@@ -754,7 +770,7 @@ void launch_attn_variant(const AttnOperand& q, const AttnOperand& k, const AttnO
 template <int DCH, bool BF16>
 void launch_attn(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, const AttnParams& p,
                  long long q_rows, long long kv_rows, cudaStream_t stream) {
-  if (!p.causal && !p.cu_seqlens && p.Skv % kBlockN == 0)
+  if (!p.causal && !p.cu_seqlens && !p.lengths_kv && !p.lengths_q && p.Skv % kBlockN == 0)
     launch_attn_variant<DCH, BF16, true>(q, k, v, p, q_rows, kv_rows, stream);
   else
     launch_attn_variant<DCH, BF16, false>(q, k, v, p, q_rows, kv_rows, stream);
@@ -813,8 +829,8 @@ static void attention_run(void* output, const AttnOperand& q, const AttnOperand&
 using namespace b200ait;
 
 // Argument order follows the reference's generated function
-// (python/aitemplate/backend/cuda/attention/mem_eff_attention.py:632-654); variable-length inputs
-// (lengths_kv / lengths_q) are not part of this path and must be null.
+// (python/aitemplate/backend/cuda/attention/mem_eff_attention.py:632-654). lengths_kv / lengths_q: null, or
+// batch_size int32 values on the device (the op's variable_seq_length_kv / variable_seq_length_q inputs).
 B200AIT_EXPORT int b200ait_mem_eff_attention(void* output, const void* query, const void* key, const void* value,
                                              int64_t batch_size, int64_t seq_len_kv, int64_t seq_len_q,
                                              int num_heads, int head_size, int head_size_v, float softmax_scale,
@@ -822,7 +838,6 @@ B200AIT_EXPORT int b200ait_mem_eff_attention(void* output, const void* query, co
                                              int dtype, cudaStream_t stream) {
   return guarded("b200ait_mem_eff_attention", [&] {
     B200AIT_REQUIRE(dtype == kDTypeHalf || dtype == kDTypeBFloat16, "attention: dtype must be float16 or bfloat16");
-    B200AIT_REQUIRE(!lengths_kv && !lengths_q, "attention: variable sequence lengths are not supported");
     B200AIT_REQUIRE(batch_size >= 0 && seq_len_kv >= 0 && seq_len_q >= 0 && num_heads >= 0 && head_size >= 0 &&
                         head_size_v >= 0,
                     "attention: negative dimension");
@@ -838,6 +853,7 @@ B200AIT_EXPORT int b200ait_mem_eff_attention(void* output, const void* query, co
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.causal = is_causal ? 1 : 0;
     p.cu_seqlens = nullptr;
+    p.lengths_kv = lengths_kv, p.lengths_q = lengths_q;
     const long long h = num_heads;
     const AttnOperand q{query, head_size, seq_len_q * head_size, h * seq_len_q * head_size};
     const AttnOperand k{key, head_size, seq_len_kv * head_size, h * seq_len_kv * head_size};

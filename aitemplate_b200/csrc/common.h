@@ -62,6 +62,6 @@ int guarded(const char* where, F&& fn) {
   }
 }
 
-enum DType : int { kDTypeHalf = 1, kDTypeFloat = 2, kDTypeBFloat16 = 6 };  // values of AITemplateDtype
+enum DType : int { kDTypeHalf = 1, kDTypeFloat = 2, kDTypeInt = 3, kDTypeBFloat16 = 6 };  // values of AITemplateDtype
 
 }  // namespace b200ait

@@ -576,15 +576,28 @@ void Executor::run_one(const OpInfo& op, cudaStream_t stream, bool launch) {
     };
     const auto qs = bhsd(q, qt), ks = bhsd(k, kt), vs = bhsd(v, vt);
     bind_shape(out0, {qs[0], qs[2], qs[1], vs[3]}, "attention output");
+    // ints[4], ints[5]: an int32 lengths_kv / lengths_q operand (one value per batch) follows q, k, v
+    int next = 3;
+    const int lkv = op.ints.size() > 4 && op.ints[4] ? in(next++) : -1;
+    const int lq = op.ints.size() > 5 && op.ints[5] ? in(next++) : -1;
+    for (int t : {lkv, lq}) {
+      if (t < 0) continue;
+      int64_t count = 1;
+      for (int64_t d : shape_of(t)) count *= d;
+      if (T[t].dtype != kDTypeInt || count != qs[0])
+        throw Error("attention '" + op.name + "': a lengths operand must hold one int32 per batch");
+    }
     if (!launch) return;
     if (!qt && !kt && !vt) {
       check(b200ait_mem_eff_attention(ptr_of(out0), ptr_of(q), ptr_of(k), ptr_of(v), qs[0], ks[2], qs[2],
                                       static_cast<int>(qs[1]), static_cast<int>(qs[3]), static_cast<int>(vs[3]),
-                                      static_cast<float>(op.floats[0]), static_cast<int>(op.ints[0]), nullptr, nullptr,
-                                      T[q].dtype, stream),
+                                      static_cast<float>(op.floats[0]), static_cast<int>(op.ints[0]),
+                                      lkv >= 0 ? static_cast<const int32_t*>(ptr_of(lkv)) : nullptr,
+                                      lq >= 0 ? static_cast<const int32_t*>(ptr_of(lq)) : nullptr, T[q].dtype, stream),
             op);
       return;
     }
+    if (lkv >= 0 || lq >= 0) throw Error("attention '" + op.name + "': lengths with operands read through strides");
     auto strides = [](const std::vector<int64_t>& s, bool stored_bshd, int64_t* out) {
       const int64_t h = s[1], rows = s[2], d = s[3];
       if (stored_bshd) {

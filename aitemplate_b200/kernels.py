@@ -271,16 +271,26 @@ def bmm_rcr(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, tile_n: int = 
 
 
 def mem_eff_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
-                      scale: Optional[float] = None) -> torch.Tensor:
-    """q [B,H,Sq,D], k [B,H,Skv,D], v [B,H,Skv,Dv] -> [B,Sq,H,Dv]; scale defaults to 1/sqrt(D)."""
+                      scale: Optional[float] = None, lengths_kv: Optional[torch.Tensor] = None,
+                      lengths_q: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [B,H,Sq,D], k [B,H,Skv,D], v [B,H,Skv,Dv] -> [B,Sq,H,Dv]; scale defaults to 1/sqrt(D).
+    lengths_kv / lengths_q: int32 device tensors of B values (batch b sees its first lengths_kv[b] keys; only its
+    first lengths_q[b] rows are written - pass `out` to choose what the other rows hold)."""
     _check_cuda(q, k, v)
     bsz, h, sq, d = q.shape
     skv, dv = k.shape[2], v.shape[3]
-    out = torch.empty((bsz, sq, h, dv), dtype=q.dtype, device=q.device)
+    for name, t in (("lengths_kv", lengths_kv), ("lengths_q", lengths_q)):
+        if t is not None and (not t.is_cuda or t.dtype != torch.int32 or t.numel() != bsz or not t.is_contiguous()):
+            raise ValueError(f"{name} must be a contiguous int32 GPU tensor with one value per batch")
+    if out is None:
+        out = torch.empty((bsz, sq, h, dv), dtype=q.dtype, device=q.device)
+    elif tuple(out.shape) != (bsz, sq, h, dv) or out.dtype != q.dtype or not out.is_cuda or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [B, Sq, H, Dv] GPU tensor of the inputs' dtype")
     if scale is None:
         scale = 1.0 / math.sqrt(d) if d else 1.0
     code = _lib.load().b200ait_mem_eff_attention(
-        _ptr(out), _ptr(q), _ptr(k), _ptr(v), bsz, skv, sq, h, d, dv, c_float(scale), int(causal), None, None,
+        _ptr(out), _ptr(q), _ptr(k), _ptr(v), bsz, skv, sq, h, d, dv, c_float(scale), int(causal),
+        _ptr(lengths_kv) if lengths_kv is not None else None, _ptr(lengths_q) if lengths_q is not None else None,
         _dtype_code(q), _stream(),
     )
     _lib.check(code, "b200ait_mem_eff_attention")

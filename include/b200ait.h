@@ -174,7 +174,10 @@ int b200ait_bmm_rcr(void* a, void* b, void* c, uint8_t* workspace, int64_t* a_di
                     int64_t* c_dim1, int64_t* c_dim2, b200ait_stream_t stream);
 
 /* mem_eff_attention: q [B,H,Sq,D], k [B,H,Skv,D], v [B,H,Skv,Dv] -> output [B,Sq,H,Dv]
- * (python/aitemplate/backend/cuda/attention/mem_eff_attention.py:632-654). lengths_* must be NULL. */
+ * (python/aitemplate/backend/cuda/attention/mem_eff_attention.py:632-654). lengths_kv / lengths_q: NULL, or
+ * batch_size int32 values on the device: batch b attends to its first lengths_kv[b] keys, and only its first
+ * lengths_q[b] query rows are computed and written (static/include/kernels/mem_eff_attention/kernel_forward.h:183-197);
+ * a batch with lengths_kv[b] = 0 comes out NaN, as it does there. */
 int b200ait_mem_eff_attention(void* output, const void* query, const void* key, const void* value,
                               int64_t batch_size, int64_t seq_len_kv, int64_t seq_len_q, int num_heads,
                               int head_size, int head_size_v, float softmax_scale, int is_causal,

@@ -150,21 +150,34 @@ def bmm_rcr(a, b, alpha: float = 1.0) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------------- attention
-def mem_eff_attention(q, k, v, causal: bool = False, scale: Optional[float] = None) -> torch.Tensor:
+def mem_eff_attention(q, k, v, causal: bool = False, scale: Optional[float] = None, lengths_kv=None,
+                      lengths_q=None) -> torch.Tensor:
     """tests/unittest/ops/test_attention.py:111-139 (attention_ref_math) and :167-193
-    (ref_cross_attention): softmax(q (k/sqrt d)^T) v with q, k, v [B,H,S,D]; output [B,Sq,H,Dv]."""
+    (ref_cross_attention): softmax(q (k/sqrt d)^T) v with q, k, v [B,H,S,D]; output [B,Sq,H,Dv].
+    lengths_kv [B]: batch b sees its first lengths_kv[b] keys (test_attention.py:504-530 builds the same key mask
+    for attention_ref); a batch without keys comes out NaN, which that test accepts (equal_nan) and the reference
+    kernel produces (0 / 0, kernel_forward.h:833). lengths_q [B]: rows from lengths_q[b] on are not computed by the
+    reference (kernel_forward.h:187-192; the test zeroes them on both sides): they are returned as NaN here so that a
+    comparison has to leave them out."""
     q, k, v = _f32(q), _f32(k), _f32(v)
     d = q.shape[-1]
     if scale is None:
         scale = 1.0 / math.sqrt(d)
     s = torch.matmul(q, k.transpose(-1, -2)) * scale
+    sq, skv = s.shape[-2], s.shape[-1]
     if causal:
-        sq, skv = s.shape[-2], s.shape[-1]
         mask = torch.ones(sq, skv, dtype=torch.bool).tril()
         s = s.masked_fill(~mask, float("-inf"))
-    p = torch.softmax(s, dim=-1)
+    if lengths_kv is not None:
+        seen = torch.arange(skv)[None, :] < torch.as_tensor(lengths_kv).reshape(-1, 1).cpu()  # [B, Skv]
+        s = s.masked_fill(~seen[:, None, None, :], float("-inf"))
+    p = torch.softmax(s, dim=-1)  # a row of -inf only: NaN
     o = torch.matmul(p, v)
-    return o.permute(0, 2, 1, 3).contiguous()
+    o = o.permute(0, 2, 1, 3).contiguous()
+    if lengths_q is not None:
+        rows = torch.arange(sq)[None, :] < torch.as_tensor(lengths_q).reshape(-1, 1).cpu()      # [B, Sq]
+        o = o.masked_fill(~rows[:, :, None, None], float("nan"))
+    return o
 
 
 # ------------------------------------------------------------------------ layernorm / softmax

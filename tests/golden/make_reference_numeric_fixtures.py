@@ -179,6 +179,15 @@ def main():
     for causal in (False, True):
         y = ta.attention_ref_math(qkv.float(), mask, 0.0, upcast=True, causal=causal)  # test_attention.py:111-139
         put(f"attention_ref_math_causal{int(causal)}", {"qkv": qkv}, {"y": y})
+    # padded variable key lengths: the key mask of test_attention.py:519-523 (seq_range < lengths_kv) handed to the
+    # same function, as the variable_seq_length_kv cases of that test do through attention_ref; a batch whose length
+    # is 0 comes out NaN
+    qkv3 = rnd((3, seq, 3, heads, d), 24)
+    lengths_kv = torch.tensor([[seq], [17], [0]])
+    key_mask = torch.arange(seq).unsqueeze(0).expand((3, seq)) < lengths_kv
+    for causal in (False, True):
+        y = ta.attention_ref_math(qkv3.float(), key_mask, 0.0, upcast=True, causal=causal)
+        put(f"attention_ref_math_lengths_kv_causal{int(causal)}", {"qkv": qkv3, "lengths_kv": lengths_kv.reshape(-1)}, {"y": y})
     # attention_pt (test_attention.py:142-165): QKV projection, 20314 permute, attention; its scale is 64**-0.5
     nh, dd, sl = 2, 64, 40
     xq, wq, bq = rnd((sl, 32), 15), rnd((3 * nh * dd, 32), 16, 0.2), rnd((3 * nh * dd,), 17, 0.2)

@@ -4,7 +4,8 @@ Shapes follow tests/unittest/ops/test_attention.py:456-742 ((B16,H4,S8,d=20) and
 scaled to what the host oracle finishes in seconds), :847-1010 (cross attention, Sq != Skv), and the
 benchmark configurations (BERT S=384 D=64; UNet D=40 with Skv=4096 and Skv=77).
 The reference's tolerance is 1e-3 against an fp16 torch result; against the fp32 oracle the bound
-is atol = rtol = 1e-2 with a tighter 4e-3 absolute check on top.
+is atol = rtol = 1e-2 with a tighter 4e-3 absolute check on top. Padded variable lengths (lengths_kv / lengths_q)
+follow test_attention.py:456-742 with variable_seq_length_kv / variable_seq_length_q.
 """
 import pytest
 import torch
@@ -191,3 +192,65 @@ def test_flash_attention_random_lengths():
             err = (got[lo:lo + n] - want).abs()
             assert bool((err <= 1e-2 + 1e-2 * want.abs()).all()) and float(err.max()) < 4e-3, \
                 f"lengths={lengths} h={h} d={d} causal={causal} sequence {b}: max abs err {float(err.max()):.4g}"
+
+
+def _check_lengths(b, h, sq, skv, d, lengths_kv, lengths_q, causal=False, seed=50):
+    from aitemplate_b200 import kernels
+
+    q, k, v = _rand((b, h, sq, d), seed), _rand((b, h, skv, d), seed + 1), _rand((b, h, skv, d), seed + 2)
+    lkv = None if lengths_kv is None else torch.tensor(lengths_kv, dtype=torch.int32)
+    lq = None if lengths_q is None else torch.tensor(lengths_q, dtype=torch.int32)
+    sentinel = 7.0
+    out = torch.full((b, sq, h, d), sentinel, dtype=torch.float16, device="cuda")
+    kernels.mem_eff_attention(q.cuda(), k.cuda(), v.cuda(), causal=causal, out=out,
+                              lengths_kv=None if lkv is None else lkv.reshape(b, 1).cuda(),
+                              lengths_q=None if lq is None else lq.cuda())
+    assert kernels.device_status() == 0
+    got = out.float().cpu()
+    want = oracle.mem_eff_attention(q, k, v, causal=causal, lengths_kv=lkv, lengths_q=lq)
+    for i in range(b):
+        rows = sq if lq is None else min(int(lq[i]), sq)
+        assert bool((got[i, rows:] == sentinel).all()), f"batch {i}: rows past lengths_q were written"
+        g, w = got[i, :rows], want[i, :rows]
+        if lkv is not None and int(lkv[i]) == 0:
+            assert bool(torch.isnan(g).all()) and bool(torch.isnan(w).all()), f"batch {i}: no keys must give NaN"
+            continue
+        assert bool(torch.isfinite(g).all()), f"batch {i}"
+        err = (g - w).abs()
+        assert bool((err <= 1e-2 + 1e-2 * w.abs()).all()) and (rows == 0 or float(err.max()) < 4e-3), \
+            f"batch {i}: max abs err {float(err.max()) if rows else 0:.4g}"
+
+
+@pytest.mark.parametrize("d", [64, 40, 128, 20])  # 20: the CUDA-core kernel
+@pytest.mark.parametrize("var_kv,var_q", [(True, False), (False, True), (True, True)])
+def test_padded_variable_lengths(d, var_kv, var_q):
+    b, h, s = 6, 3, 200
+    lengths_kv = [200, 0, 1, 64, 65, 137] if var_kv else None
+    lengths_q = [0, 200, 128, 129, 5, 77] if var_q else None
+    _check_lengths(b, h, s, s, d, lengths_kv, lengths_q)
+
+
+def test_padded_variable_lengths_causal_and_cross():
+    _check_lengths(4, 2, 256, 256, 64, [256, 100, 0, 31], [256, 256, 10, 200], causal=True)
+    _check_lengths(3, 4, 384, 128, 64, [128, 64, 7], None)           # Skv a multiple of the key block: masks still apply
+    _check_lengths(2, 2, 64, 300, 32, [300, 150], [64, 1])
+    _check_lengths(2, 2, 130, 70, 20, [70, 0], [130, 129], causal=False)
+
+
+def test_padded_variable_lengths_random():
+    import random
+
+    rng = random.Random(20240702)
+    for case in range(16):
+        b, h = rng.randint(1, 5), rng.randint(1, 4)
+        d = rng.choice([16, 32, 64, 80, 128, 20])
+        sq, skv = rng.choice([1, 64, 129, 300, 512]), rng.choice([1, 63, 64, 200, 384])
+        causal = rng.random() < 0.3
+        if causal:
+            skv = sq
+        lkv = [rng.choice([0, 1, skv // 2, skv, skv + 5]) for _ in range(b)] if rng.random() < 0.8 else None
+        lq = [rng.choice([0, 1, sq // 2, sq, sq + 3]) for _ in range(b)] if rng.random() < 0.6 else None
+        try:
+            _check_lengths(b, h, sq, skv, d, lkv, lq, causal=causal, seed=100 + 3 * case)
+        except AssertionError as e:
+            raise AssertionError(f"b={b} h={h} sq={sq} skv={skv} d={d} causal={causal} lkv={lkv} lq={lq}: {e}") from None

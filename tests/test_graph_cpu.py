@@ -199,7 +199,7 @@ def test_sd_transformer_block_plan():
     attn = ["gemm_rcr"] * 3 + ["mem_eff_attention", "gemm_rcr"]
     assert kernels == ["layernorm"] + attn + ["layernorm"] + attn + ["layernorm", "gemm_rcr", "gemm_rcr", "gemm_rcr"]
     attn_ops = [_parse_op(l) for l in plan.splitlines() if l.startswith("op mem_eff_attention")]
-    assert [o["ints"] for o in attn_ops] == [[0, 1, 1, 1], [0, 1, 1, 1]]
+    assert [o["ints"] for o in attn_ops] == [[0, 1, 1, 1, 0, 0], [0, 1, 1, 1, 0, 0]]  # causal, 3 x stored [B,S,H,D], no lengths
     assert consts >= 2 * (4 * 320 * 320 + 2 * 320 * 768 + 2 * 320 * 320 + 3 * 1280 * 320)
     assert blob >= 2 * 4096 * 1280 * 2
 
@@ -368,6 +368,31 @@ def test_split_strided_input_fusion_plan():
     idx_x = next(i for i, t in enumerate(tl) if t[1] == "x")
     views = sorted(int(t[5]) for t in tl if t[3] == "4" and int(t[6]) == idx_x)
     assert views == [0, 256, 2 * (128 + 64 + 32)]                              # byte offsets of the aliased blocks
+
+
+def test_mem_eff_attention_with_lengths_plan():
+    # variable_seq_length_kv / variable_seq_length_q (python/aitemplate/compiler/ops/attention/mem_eff_attention.py:
+    # 133-158): the int32 lengths tensors become inputs of the op, in that order, only when their flag is set
+    q = Tensor([4, 2, 64, 32], name="q", is_input=True)
+    k = Tensor([4, 2, 96, 32], name="k", is_input=True)
+    v = Tensor([4, 2, 96, 32], name="v", is_input=True)
+    lkv = Tensor([4, 1], name="lengths_kv", dtype="int", is_input=True)
+    lq = Tensor([4, 1], name="lengths_q", dtype="int", is_input=True)
+    op = ops.mem_eff_attention(causal=False, variable_seq_length_kv=True, variable_seq_length_q=True)
+    y = _out(op(q, k, v, lkv, lq), "y")
+    assert [t._attrs["name"] for t in op._attrs["inputs"]] == ["q", "k", "v", "lengths_kv", "lengths_q"]
+    assert op._get_op_attributes()["variable_seq_length_kv"] is True
+    _, plan, _, _ = _lower([y])
+    assert _parse_op(next(l for l in plan.splitlines() if l.startswith("op mem_eff_attention")))["ints"] == [0, 0, 0, 0, 1, 1]
+    only_q = ops.mem_eff_attention(causal=True, variable_seq_length_q=True)
+    y2 = _out(only_q(q, q, q, None, lq), "y2")
+    assert len(only_q._attrs["inputs"]) == 4 and only_q._attrs["inputs"][3] is lq
+    _, plan2, _, _ = _lower([y2])
+    assert _parse_op(next(l for l in plan2.splitlines() if l.startswith("op mem_eff_attention")))["ints"] == [1, 0, 0, 0, 0, 1]
+    with pytest.raises(RuntimeError):
+        ops.mem_eff_attention(causal=False, variable_seq_length_kv=True)(q, k, v)          # the tensor is missing
+    with pytest.raises(RuntimeError):
+        ops.mem_eff_attention(causal=False, variable_seq_length_kv=True)(q, k, v, Tensor([4, 1], name="f", is_input=True))
 
 
 def test_split_strided_operand_b_of_gemm_rcr():

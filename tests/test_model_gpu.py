@@ -351,6 +351,37 @@ def test_strided_input_fusion_from_split(workdir, m):
     _close(res["ln3"], oracle.layernorm(c3, None, None), 1e-2)
 
 
+def test_mem_eff_attention_with_lengths_in_a_graph(workdir):
+    # tests/unittest/ops/test_attention.py:456-742 with variable_seq_length_kv / variable_seq_length_q: int32 lengths
+    # tensors as graph inputs
+    Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()
+    b, h, s, d = 5, 4, 192, 64
+    q = Tensor([b, h, s, d], name="q", is_input=True)
+    k = Tensor([b, h, s, d], name="k", is_input=True)
+    v = Tensor([b, h, s, d], name="v", is_input=True)
+    lkv = Tensor([b, 1], name="lengths_kv", dtype="int", is_input=True)
+    lq = Tensor([b, 1], name="lengths_q", dtype="int", is_input=True)
+    y = ops.mem_eff_attention(causal=False, variable_seq_length_kv=True, variable_seq_length_q=True)(q, k, v, lkv, lq)
+    y._attrs["name"], y._attrs["is_output"] = "output", True
+    module = compile_model(y, detect_target(), workdir, "attention_lengths")
+    qd, kd, vd = _rand((b, h, s, d), 1), _rand((b, h, s, d), 2), _rand((b, h, s, d), 3)
+    lengths_kv = torch.tensor([192, 7, 0, 64, 100], dtype=torch.int32)
+    lengths_q = torch.tensor([192, 192, 50, 0, 129], dtype=torch.int32)
+    out = torch.full((b, s, h, d), 5.0, dtype=torch.float16, device="cuda")
+    res = module.run_with_tensors({"q": qd.cuda(), "k": kd.cuda(), "v": vd.cuda(),
+                                   "lengths_kv": lengths_kv.reshape(b, 1).cuda(),
+                                   "lengths_q": lengths_q.reshape(b, 1).cuda()}, {"output": out})
+    got = res["output"].float().cpu()
+    want = oracle.mem_eff_attention(qd, kd, vd, lengths_kv=lengths_kv, lengths_q=lengths_q)
+    for i in range(b):
+        rows = int(lengths_q[i])
+        assert bool((got[i, rows:] == 5.0).all())
+        if int(lengths_kv[i]) == 0:
+            assert bool(torch.isnan(got[i, :rows]).all())
+        else:
+            _close(got[i, :rows], want[i, :rows], 1e-2)
+
+
 def test_strided_operand_b_from_split(workdir):
     # gemm_rcr reads operand B ([N, K]) in place from a block of K columns of a wider tensor: no split kernel runs
     Model, compile_model, ops, IntVar, Tensor, nn, detect_target = _imports()

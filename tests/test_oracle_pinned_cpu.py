@@ -55,7 +55,7 @@ def test_fixture_covers_every_pinned_case():
     for c in ("gemm_rrr", "gemm_rcr_bias_permute", "bmm_rcr", "bmm_rrr", "bmm_rrr_permute", "bmm_rcr_permute",
               "layernorm", "layernorm_2d_no_affine", "softmax_dim-1", "softmax_dim1",
               "attention_ref_math_causal0", "attention_ref_math_causal1", "attention_pt", "ref_cross_attention",
-              "ref_attention_bmhk"):
+              "ref_attention_bmhk", "attention_ref_math_lengths_kv_causal0", "attention_ref_math_lengths_kv_causal1"):
         assert c in cases, c
 
 
@@ -102,6 +102,17 @@ def test_attention_reproduces_attention_ref_math(causal):
     qkv = _in(c, "qkv")  # [B, S, 3, H, D]
     q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))  # -> [B, H, S, D]
     _close(oracle.mem_eff_attention(q, k, v, causal=causal), c, tol=2e-6)  # output [B, S, H, D]
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_with_key_lengths_reproduces_attention_ref_math(causal):
+    c = f"attention_ref_math_lengths_kv_causal{int(causal)}"
+    qkv, lengths = _in(c, "qkv"), _in(c, "lengths_kv")
+    q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    got = oracle.mem_eff_attention(q, k, v, causal=causal, lengths_kv=lengths)
+    want = torch.from_numpy(FIX[c + "/out/y"])
+    assert torch.equal(torch.isnan(got), torch.isnan(want)) and bool(torch.isnan(want[2]).all())  # the batch without keys
+    assert float((got[:2] - want[:2]).abs().max()) <= 2e-6
 
 
 def test_qkv_permute_plus_attention_reproduces_attention_pt():
