@@ -227,8 +227,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
     } else {
       w.b4 = b;
       w.row0 = 0;
-      w.q_len = p.lengths_q ? min(max(__ldg(p.lengths_q + b), 0), p.Sq) : p.Sq;
-      w.kv_len = p.lengths_kv ? min(max(__ldg(p.lengths_kv + b), 0), p.Skv) : p.Skv;
+      w.q_len = p.Sq;
+      w.kv_len = p.Skv;
+      if constexpr (!NOMASK) {  // (the host sends problems with lengths to the masking variant)
+        if (p.lengths_q) w.q_len = min(max(__ldg(p.lengths_q + b), 0), p.Sq);
+        if (p.lengths_kv) w.kv_len = min(max(__ldg(p.lengths_kv + b), 0), p.Skv);
+      }
       w.out_row0 = static_cast<long long>(b) * p.Sq;
     }
     if (!NOMASK && p.causal) w.kv_len = min(w.kv_len, w.q0 + kBlockM);
@@ -479,7 +483,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_cons
       const int n_blocks = w.n_blocks, kv_len = w.kv_len;
       if (n_blocks == 0) {
         // no key for this tile's rows (lengths_kv[b] == 0): softmax over nothing, NaN like the reference's 0 / 0
-        if (p.lengths_kv != nullptr && w.q0 + r < w.q_len) {
+        if (!NOMASK && p.lengths_kv != nullptr && w.q0 + r < w.q_len) {
           T* row_out = static_cast<T*>(p.out) + ((w.out_row0 + w.q0 + r) * p.H + w.h) * p.Dv;
           const uint32_t nan2 = E::from_float2(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
           for (int c = 0; c < p.Dv; c += 8) *reinterpret_cast<uint4*>(row_out + c) = make_uint4(nan2, nan2, nan2, nan2);
