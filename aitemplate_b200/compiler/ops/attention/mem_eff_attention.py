@@ -18,8 +18,9 @@ class mem_eff_attention(Operator):
                  use_grouped_fmha=False) -> None:
         super().__init__()
         assert dropout == 0
-        if use_grouped_fmha:
-            raise NotImplementedError("grouped FMHA is outside this path")
+        # use_grouped_fmha selects another kernel template with the same signature and results in the reference
+        # (backend/cuda/attention/mem_eff_attention.py:694-697); here one kernel already schedules (batch, head,
+        # query tile) items with per-item sizes, so the flag is kept as an attribute and changes nothing
         self._attrs["op"] = "mem_eff_attention"
         self._attrs["has_profiler"] = False
         self._attrs["dropout"] = dropout
@@ -33,7 +34,8 @@ class mem_eff_attention(Operator):
     def _get_op_attributes(self):
         return {"causal": self._attrs["causal"], "dropout": self._attrs["dropout"],
                 "variable_seq_length_kv": self._attrs["variable_seq_length_kv"],
-                "variable_seq_length_q": self._attrs["variable_seq_length_q"]}
+                "variable_seq_length_q": self._attrs["variable_seq_length_q"],
+                "use_grouped_fmha": self._attrs["use_grouped_fmha"]}
 
     def _infer_shapes(self, q: Tensor, v: Tensor) -> List[IntVar]:
         qs = q._attrs["shape"]

@@ -384,6 +384,8 @@ def test_mem_eff_attention_with_lengths_plan():
     assert op._get_op_attributes()["variable_seq_length_kv"] is True
     _, plan, _, _ = _lower([y])
     assert _parse_op(next(l for l in plan.splitlines() if l.startswith("op mem_eff_attention")))["ints"] == [0, 0, 0, 0, 1, 1]
+    grouped = ops.mem_eff_attention(causal=False, variable_seq_length_kv=True, use_grouped_fmha=True)
+    assert grouped._get_op_attributes()["use_grouped_fmha"] is True          # accepted: same kernel, same results
     only_q = ops.mem_eff_attention(causal=True, variable_seq_length_q=True)
     y2 = _out(only_q(q, q, q, None, lq), "y2")
     assert len(only_q._attrs["inputs"]) == 4 and only_q._attrs["inputs"][3] is lq
