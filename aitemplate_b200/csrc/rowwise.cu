@@ -266,7 +266,102 @@ __global__ void __launch_bounds__(512) layernorm_block_kernel(const LayerNormPar
   }
 }
 
+// Rows the vector kernels cannot take (a length or a pitch that is not a multiple of 8 elements, or more than
+// 32768 elements) but that fit in shared memory: a block stages its row there as it reads it, so the row crosses HBM
+// once in and once out instead of three times in. W = elements per access: 8 when rows, gamma and beta are whole
+// numbers of aligned 16-byte vectors (rows above 32768 elements), 2 for aligned 4-byte words, else 1.
+constexpr int kStagedMaxElems = 100 * 1024;  // 200 KB of 16-bit elements
+template <bool BF16, int W>
+__global__ void __launch_bounds__(512) layernorm_block_staged_kernel(const LayerNormParams p) {
+  constexpr bool W2 = W == 2;
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  extern __shared__ __align__(16) unsigned char staged_row[];
+  __shared__ float red[33];
+  T* xs = reinterpret_cast<T*>(staged_row);
+  const long long row = blockIdx.x;
+  const T* x = static_cast<const T*>(p.x) + row * p.x_stride;
+  T* y = static_cast<T*>(p.y) + row * p.y_stride;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  float s = 0.f;
+  if (W == 8) {
+    const uint4* x8 = reinterpret_cast<const uint4*>(x);
+    uint4* xs8 = reinterpret_cast<uint4*>(xs);
+    for (int i = tid; i < (p.n >> 3); i += nt) {
+      const uint4 w = ld_stream(x8 + i);
+      xs8[i] = w;
+      float f[8];
+      unpack8<BF16>(w, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += f[j];
+    }
+  } else if (W2) {
+    const uint32_t* x2 = reinterpret_cast<const uint32_t*>(x);
+    uint32_t* xs2 = reinterpret_cast<uint32_t*>(xs);
+    for (int i = tid; i < (p.n >> 1); i += nt) {
+      const uint32_t w = __ldcs(x2 + i);
+      xs2[i] = w;
+      const float2 f = E::to_float2(w);
+      s += f.x + f.y;
+    }
+  } else {
+    for (int i = tid; i < p.n; i += nt) {
+      const T v = x[i];
+      xs[i] = v;
+      s += E::to_float(v);
+    }
+  }
+  const float inv_n = 1.f / static_cast<float>(p.n);
+  const float mean = block_sum(s, red) * inv_n;  // (its barriers also publish the staged row)
+  float q = 0.f;
+  for (int i = tid; i < p.n; i += nt) {
+    const float d = E::to_float(xs[i]) - mean;
+    q += d * d;
+  }
+  const float rstd = rsqrtf(block_sum(q, red) * inv_n + p.eps);
+  const T* g = static_cast<const T*>(p.gamma);
+  const T* b = static_cast<const T*>(p.beta);
+  if (W == 8) {
+    uint4* y8 = reinterpret_cast<uint4*>(y);
+    const uint4* g8 = reinterpret_cast<const uint4*>(g);
+    const uint4* b8 = reinterpret_cast<const uint4*>(b);
+    for (int i = tid; i < (p.n >> 3); i += nt) {
+      float f[8], gv[8], bv[8], o[8];
+      unpack8<BF16>(reinterpret_cast<const uint4*>(xs)[i], f);
+      if (g) {
+        unpack8<BF16>(__ldg(g8 + i), gv);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) gv[j] = 1.f;
+      }
+      if (b) {
+        unpack8<BF16>(__ldg(b8 + i), bv);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) bv[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (f[j] - mean) * rstd * gv[j] + bv[j];
+      st_stream(y8 + i, pack8<BF16>(o));
+    }
+  } else if (W2) {
+    uint32_t* y2 = reinterpret_cast<uint32_t*>(y);
+    for (int i = tid; i < (p.n >> 1); i += nt) {
+      const float2 f = E::to_float2(reinterpret_cast<const uint32_t*>(xs)[i]);
+      const float g0 = g ? E::to_float(g[2 * i]) : 1.f, g1 = g ? E::to_float(g[2 * i + 1]) : 1.f;
+      const float b0 = b ? E::to_float(b[2 * i]) : 0.f, b1 = b ? E::to_float(b[2 * i + 1]) : 0.f;
+      __stcs(y2 + i, E::from_float2((f.x - mean) * rstd * g0 + b0, (f.y - mean) * rstd * g1 + b1));
+    }
+  } else {
+    for (int i = tid; i < p.n; i += nt) {
+      const float gv = g ? E::to_float(g[i]) : 1.f, bv = b ? E::to_float(b[i]) : 0.f;
+      y[i] = E::from_float((E::to_float(xs[i]) - mean) * rstd * gv + bv);
+    }
+  }
+}
+
 static bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static bool al4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
 
 template <bool BF16>
 void layernorm_launch(const LayerNormParams& p, cudaStream_t stream) {
@@ -314,6 +409,23 @@ void layernorm_launch(const LayerNormParams& p, cudaStream_t stream) {
     if (epl <= 1) B200AIT_LNS(1); else if (epl <= 2) B200AIT_LNS(2); else if (epl <= 4) B200AIT_LNS(4);
     else if (epl <= 8) B200AIT_LNS(8); else if (epl <= 16) B200AIT_LNS(16); else B200AIT_LNS(32);
 #undef B200AIT_LNS
+  } else if (p.n <= kStagedMaxElems) {
+    B200AIT_REQUIRE(p.m < (1ll << 31), "layernorm: too many rows");
+    const bool w2 = p.n % 2 == 0 && p.x_stride % 2 == 0 && p.y_stride % 2 == 0 && al4(p.x) && al4(p.y);
+    const int bytes = ((p.n * 2 + 15) / 16) * 16;
+    const unsigned grid = static_cast<unsigned>(p.m);
+    const int threads = p.n >= 8192 ? 512 : p.n >= 2048 ? 256 : 128;  // short rows: more blocks per SM instead
+    static std::atomic<uint64_t> configured[3] = {{0}, {0}, {0}};
+    if (aligned) {
+      opt_in_smem_once(configured[2], reinterpret_cast<const void*>(&layernorm_block_staged_kernel<BF16, 8>), 2 * kStagedMaxElems);
+      ::b200ait::count_launch(), layernorm_block_staged_kernel<BF16, 8><<<grid, threads, bytes, stream>>>(p);
+    } else if (w2) {
+      opt_in_smem_once(configured[0], reinterpret_cast<const void*>(&layernorm_block_staged_kernel<BF16, 2>), 2 * kStagedMaxElems);
+      ::b200ait::count_launch(), layernorm_block_staged_kernel<BF16, 2><<<grid, threads, bytes, stream>>>(p);
+    } else {
+      opt_in_smem_once(configured[1], reinterpret_cast<const void*>(&layernorm_block_staged_kernel<BF16, 1>), 2 * kStagedMaxElems);
+      ::b200ait::count_launch(), layernorm_block_staged_kernel<BF16, 1><<<grid, threads, bytes, stream>>>(p);
+    }
   } else {
     B200AIT_REQUIRE(p.m < (1ll << 31), "layernorm: too many rows");
     const int threads = p.n >= 2048 ? 512 : (p.n >= 512 ? 256 : 128);
@@ -493,6 +605,72 @@ __global__ void __launch_bounds__(512) softmax_block_kernel(const SoftmaxParams 
   for (int i = threadIdx.x; i < p.k; i += blockDim.x) y[i] = E::from_float(__expf(E::to_float(x[i]) - mx) * inv);
 }
 
+// The same for softmax rows (see layernorm_block_staged_kernel): one read, one write.
+template <bool BF16, int W>
+__global__ void __launch_bounds__(512) softmax_block_staged_kernel(const SoftmaxParams p) {
+  constexpr bool W2 = W == 2;
+  using E = Elem16<BF16>;
+  using T = typename E::T;
+  extern __shared__ __align__(16) unsigned char staged_row[];
+  __shared__ float red[33];
+  T* xs = reinterpret_cast<T*>(staged_row);
+  const long long row = blockIdx.x;
+  const T* x = static_cast<const T*>(p.x) + row * p.k;
+  T* y = static_cast<T*>(p.y) + row * p.k;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  float mx = -INFINITY;
+  if (W == 8) {
+    const uint4* x8 = reinterpret_cast<const uint4*>(x);
+    uint4* xs8 = reinterpret_cast<uint4*>(xs);
+    for (int i = tid; i < (p.k >> 3); i += nt) {
+      const uint4 w = ld_stream(x8 + i);
+      xs8[i] = w;
+      float f[8];
+      unpack8<BF16>(w, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);
+    }
+  } else if (W2) {
+    const uint32_t* x2 = reinterpret_cast<const uint32_t*>(x);
+    uint32_t* xs2 = reinterpret_cast<uint32_t*>(xs);
+    for (int i = tid; i < (p.k >> 1); i += nt) {
+      const uint32_t w = __ldcs(x2 + i);
+      xs2[i] = w;
+      const float2 f = E::to_float2(w);
+      mx = fmaxf(mx, fmaxf(f.x, f.y));
+    }
+  } else {
+    for (int i = tid; i < p.k; i += nt) {
+      const T v = x[i];
+      xs[i] = v;
+      mx = fmaxf(mx, E::to_float(v));
+    }
+  }
+  mx = block_max(mx, red);  // (its barriers also publish the staged row)
+  if (mx == -INFINITY) mx = 0.f;
+  float s = 0.f;
+  for (int i = tid; i < p.k; i += nt) s += __expf(E::to_float(xs[i]) - mx);
+  const float inv = 1.f / block_sum(s, red);
+  if (W == 8) {
+    uint4* y8 = reinterpret_cast<uint4*>(y);
+    for (int i = tid; i < (p.k >> 3); i += nt) {
+      float f[8];
+      unpack8<BF16>(reinterpret_cast<const uint4*>(xs)[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = __expf(f[j] - mx) * inv;
+      st_stream(y8 + i, pack8<BF16>(f));
+    }
+  } else if (W2) {
+    uint32_t* y2 = reinterpret_cast<uint32_t*>(y);
+    for (int i = tid; i < (p.k >> 1); i += nt) {
+      const float2 f = E::to_float2(reinterpret_cast<const uint32_t*>(xs)[i]);
+      __stcs(y2 + i, E::from_float2(__expf(f.x - mx) * inv, __expf(f.y - mx) * inv));
+    }
+  } else {
+    for (int i = tid; i < p.k; i += nt) y[i] = E::from_float(__expf(E::to_float(xs[i]) - mx) * inv);
+  }
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(256) softmax_strided_kernel(const SoftmaxParams p) {
   using E = Elem16<BF16>;
@@ -593,6 +771,23 @@ void softmax_launch(const SoftmaxParams& p, cudaStream_t stream) {
     if (epl <= 1) B200AIT_SMS(1); else if (epl <= 2) B200AIT_SMS(2); else if (epl <= 4) B200AIT_SMS(4);
     else if (epl <= 8) B200AIT_SMS(8); else if (epl <= 16) B200AIT_SMS(16); else B200AIT_SMS(32);
 #undef B200AIT_SMS
+  } else if (p.k <= kStagedMaxElems) {
+    B200AIT_REQUIRE(p.outer < (1ll << 31), "softmax: too many rows");
+    const bool w8 = p.k % 8 == 0 && al16(p.x) && al16(p.y), w2 = p.k % 2 == 0 && al4(p.x) && al4(p.y);
+    const int bytes = ((p.k * 2 + 15) / 16) * 16;
+    const unsigned grid = static_cast<unsigned>(p.outer);
+    const int threads = p.k >= 8192 ? 512 : p.k >= 2048 ? 256 : 128;  // short rows: more blocks per SM instead
+    static std::atomic<uint64_t> configured[3] = {{0}, {0}, {0}};
+    if (w8) {
+      opt_in_smem_once(configured[2], reinterpret_cast<const void*>(&softmax_block_staged_kernel<BF16, 8>), 2 * kStagedMaxElems);
+      ::b200ait::count_launch(), softmax_block_staged_kernel<BF16, 8><<<grid, threads, bytes, stream>>>(p);
+    } else if (w2) {
+      opt_in_smem_once(configured[0], reinterpret_cast<const void*>(&softmax_block_staged_kernel<BF16, 2>), 2 * kStagedMaxElems);
+      ::b200ait::count_launch(), softmax_block_staged_kernel<BF16, 2><<<grid, threads, bytes, stream>>>(p);
+    } else {
+      opt_in_smem_once(configured[1], reinterpret_cast<const void*>(&softmax_block_staged_kernel<BF16, 1>), 2 * kStagedMaxElems);
+      ::b200ait::count_launch(), softmax_block_staged_kernel<BF16, 1><<<grid, threads, bytes, stream>>>(p);
+    }
   } else {
     B200AIT_REQUIRE(p.outer < (1ll << 31), "softmax: too many rows");
     const int threads = p.k >= 2048 ? 512 : (p.k >= 256 ? 256 : (p.k >= 64 ? 64 : 32));

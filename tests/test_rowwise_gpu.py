@@ -147,3 +147,24 @@ def test_random_shapes():
             _close(kernels.softmax(x3.cuda(), 1), oracle.softmax(x3, 1), 1e-2)
         except AssertionError as e:
             raise AssertionError(f"m={m} n={n}: {e}") from None
+
+
+@pytest.mark.parametrize("n", [1030, 1031, 4100, 5001, 33000, 40000, 65537, 102400, 102401, 120000])
+def test_rows_staged_in_shared_memory(n):
+    """Row lengths the vector kernels do not take (not a multiple of 8 elements, or above 32768): up to 100 K elements
+    the row is staged in shared memory (even lengths two elements at a time), above that it is read three times."""
+    from aitemplate_b200 import kernels
+
+    m = 9
+    x = _rand((m, n), 31, scale=2.0)
+    g, b = (_rand((n,), 32, dist="uniform") + 0.5).half(), _rand((n,), 33, scale=0.1)
+    _close(kernels.layernorm(x.cuda(), g.cuda(), b.cuda(), eps=1e-5), oracle.layernorm(x, g, b, 1e-5), 4e-3)
+    _close(kernels.layernorm(x.cuda(), None, None, eps=1e-5), oracle.layernorm(x, None, None, 1e-5), 4e-3)
+    _close(kernels.softmax(x.cuda(), -1), oracle.softmax(x, -1), 1e-2)
+    xb = x.to(torch.bfloat16)
+    _close(kernels.softmax(xb.cuda(), -1), oracle.softmax(xb, -1), 2e-2)
+    # a view that starts at an odd element: 2-byte aligned rows only
+    flat = torch.zeros(m * n + 1, dtype=torch.float16)
+    flat[1:] = x.reshape(-1)
+    odd = flat.cuda()[1:].view(m, n)
+    _close(kernels.softmax(odd, -1), oracle.softmax(x, -1), 1e-2)
